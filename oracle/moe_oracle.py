@@ -1,0 +1,49 @@
+"""CPU oracle for the routed-MoE expert path (numpy). TEST INFRASTRUCTURE ONLY.
+
+Restates reference/python/moe.py:7-26 (the whole-layer forward with its BF16
+rounding points) and the activation of kernels/moe/swiglu.cu:12-26. Parity
+status: PINNED against an output of the reference Python frozen in
+tests/golden/moe_bf16.npz (floating point: compared within BF16 rounding).
+"""
+from __future__ import annotations
+
+import numpy as np
+
+from .nvfp4_oracle import bf16_to_f32, f32_to_bf16_bits
+
+
+def round_bf16(x: np.ndarray) -> np.ndarray:
+    """FP32 -> nearest-even BF16 -> FP32."""
+    return bf16_to_f32(f32_to_bf16_bits(np.asarray(x, dtype=np.float32)))
+
+
+def swiglu(gate_up: np.ndarray, route_weight: np.ndarray, clamp: float) -> np.ndarray:
+    """bf16(silu(min(g, c)) * clamp(u, -c, c) * w) with g = first half, u = second half.
+
+    reference/python/moe.py:21-23; kernels/moe/swiglu.cu:20-24.
+    """
+    inter = gate_up.shape[-1] // 2
+    g = np.minimum(gate_up[..., :inter], np.float32(clamp)).astype(np.float32)
+    u = np.clip(gate_up[..., inter:], np.float32(-clamp), np.float32(clamp)).astype(np.float32)
+    silu = (g / (np.float32(1.0) + np.exp(-g, dtype=np.float32))).astype(np.float32)
+    return round_bf16(silu * u * route_weight[..., None].astype(np.float32))
+
+
+def moe_forward(x, expert_ids, route_weights, w1, w2, clamp=10.0):
+    """x [T,H] f32 (bf16-representable), ids [T,k] global, weights [T,k] f32,
+    w1 [E,2I,H], w2 [E,H,I] f32 -> y [T,H] f32 (bf16-representable).
+
+    Per expert in ascending order: gate_up -> bf16, activation -> bf16, expert
+    output -> bf16, FP32 accumulation per token, final bf16 (moe.py:13-26).
+    """
+    tokens, hidden = x.shape
+    out = np.zeros((tokens, hidden), dtype=np.float32)
+    for e in range(w1.shape[0]):
+        tok, choice = np.nonzero(expert_ids == e)
+        if tok.size == 0:
+            continue
+        gate_up = round_bf16(x[tok] @ w1[e].T)
+        act = swiglu(gate_up, route_weights[tok, choice], clamp)
+        eo = round_bf16(act @ w2[e].T)
+        np.add.at(out, tok, eo)
+    return round_bf16(out)
