@@ -1,0 +1,338 @@
+#!/usr/bin/env python
+"""Benchmark of the NVFP4 GEMM hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One "step" is one pass of the hot path over one batch of synthetic input: one
+NVFP4 block-scaled GEMM of the named workload (default: M=N=K=8192, seeded bf16
+N(0,1) operands quantised to E2M1 + UE4M3 scales, FP32 accumulation, FP16
+output). With N > 1 (one rank per GPU under torchrun) B is sharded by rows over
+the ranks (N-column sharding of C) and the same total problem is timed: strong
+scaling. Rank 0 prints ONE JSON line.
+
+`--impl reference` times the reference's CPU path (dequantise both operands,
+FP32 matmul, FP16 rounding) restated in oracle/ on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOADS = {
+    # name: (M, N, K, sigma of B)
+    "gemm8192": (8192, 8192, 8192, 1.0),
+    "gemm16384": (16384, 16384, 16384, 1.0),
+    "skinny": (128, 28672, 8192, 0.02),
+    "gemm256": (256, 256, 256, 1.0),
+}
+METRIC = "nvfp4_gemm_tflops"
+UNIT = "TFLOP/s"
+NOMINAL_FP4_TFLOPS = 9000.0
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of nvfp4_gemm_kernel, from the
+# ncu captures summarised under profiles/ (None until a capture of that workload exists).
+NCU_DRAM_BYTES_PER_LAUNCH = {"gemm8192": None, "gemm16384": None, "skinny": None}
+
+
+def algorithmic_bytes(m, n, k):
+    """Packed A and B, both scale arrays, and C written once (FP16)."""
+    return m * k // 2 + n * k // 2 + m * k // 16 + n * k // 16 + 2 * m * n
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_burst": d["bf16_tflops"],
+                "bf16_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_burst": 1590.0, "bf16_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows, self.proc = [], None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50", "-i", str(index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.perf_counter(), [c.strip() for c in line.split(",")]))
+
+    def stop(self, t0, t1):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        self.thread.join(timeout=2)
+        inside = [r for t, r in self.rows if t0 <= t <= t1 and len(r) >= 7]
+        window = "timed region"
+        if len(inside) < 3:
+            inside = [r for _, r in self.rows if len(r) >= 7]
+            window = "warm-up + timed region + continuation"
+        if not inside:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        reasons = [n for i, n in enumerate(names) if any(r[3 + i].lower().startswith("active") for r in inside)]
+        nums = lambda j: [float(r[j]) for r in inside if r[j].replace(".", "", 1).isdigit()]
+        return {"sm_mhz": statistics.median(nums(0)) if nums(0) else None,
+                "sm_max_mhz": max(nums(1)) if nums(1) else None,
+                "power_w_max": max(nums(2)) if nums(2) else None,
+                "reasons": reasons, "samples": len(inside), "window": window}
+
+
+def cpu_reference_pass(m, n, k, sigma_b, budget_s=20.0):
+    """The reference's CPU path on a bounded sample: all of B, the first rows of A."""
+    import numpy as np
+    import torch
+    from oracle import nvfp4_oracle as O
+    cores = os.cpu_count() or 1
+    torch.manual_seed(0)
+    # measured here at ~0.45 TFLOP/s on 8 cores; size the A slab for about `budget_s` seconds in total
+    rows = m
+    est = (2.0 * m * n * k) / (0.05e12 * cores) + 3e-8 * (m + n) * k
+    if est > budget_s:
+        rows = max(128, int(m * budget_s / est) // 128 * 128)
+    # Quantising 2 x 64M values with the numpy oracle would take far longer than the timed pass itself,
+    # so a 1024-row seeded block of each operand is quantised and repeated down the rows (whole scale
+    # atoms, so the repeated arrays are valid operands with the same value distribution).
+    def operand(r, sigma):
+        base = min(r, 1024)
+        x = (torch.randn((base, k), dtype=torch.bfloat16).float() * sigma).numpy()
+        p, s = O.quantize(x)
+        reps = -(-r // base)
+        return np.tile(p, (reps, 1))[:r], np.tile(s, reps)[:r * k // 16]
+    pa, sa = operand(rows, 1.0)
+    pb, sb = operand(n, sigma_b)
+    t0 = time.perf_counter()
+    c = O.gemm(pa, sa, pb, sb)
+    dt = time.perf_counter() - t0
+    assert c.shape == (rows, n)
+    return 2.0 * rows * n * k / dt / 1e12, cores, f"rows 0..{rows - 1} of A against all of B ({rows}x{n}x{k}), dequantise + FP32 matmul + FP16, {dt:.1f} s"
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    m, n, k, sigma = WORKLOADS[args.workload]
+    for _ in range(min(args.warmup, 1)):
+        cpu_reference_pass(min(m, 256), min(n, 1024), min(k, 1024), sigma, 2.0)
+    values = []
+    steps = max(1, min(args.steps, 3))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        v, cores, sample = cpu_reference_pass(m, n, k, sigma, 20.0)
+        values.append(v)
+    dt = time.perf_counter() - t0
+    value = statistics.median(values)
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": steps, "warmup": min(args.warmup, 1), "ms_per_step": 1e3 * dt / steps, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "nvfp4 (e2m1 x ue4m3), f32 accumulate, f16 out",
+        "data": "synthetic", "config": {"workload": args.workload, "M": m, "N": n, "K": k, "layout": "TN"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+    import gpu_kernels_b200 as g
+    from gpu_kernels_b200 import _lib
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    m, n, k, sigma = WORKLOADS[args.workload]
+    lo, hi = g.slab_rows(n, world, rank)
+    n_local = hi - lo
+    lib = _lib.load()
+    l2 = lib.gpu_kernels_nvfp4_l2_bytes()
+
+    # Seeded synthetic operands (the full B on every rank, then this rank's slab).
+    gen = torch.Generator(device=dev).manual_seed(0)
+    a = torch.randn((m, k), generator=gen, device=dev, dtype=torch.float32).bfloat16()
+    pa, sa = g.quantize(a)
+    del a
+    b = (torch.randn((n, k), generator=gen, device=dev, dtype=torch.float32) * sigma).bfloat16()
+    pb_full, sb_full = g.quantize(b)
+    del b
+    pb, sb = (t.clone() for t in g.shard_b(pb_full, sb_full, world, rank))
+    del pb_full, sb_full
+    torch.cuda.empty_cache()
+
+    # Operand rotation: consecutive steps read different copies, together larger than twice the L2.
+    in_bytes = sum(t.numel() for t in (pa, sa, pb, sb))
+    rotations = max(2, -(-2 * l2 // in_bytes))
+    rotations = min(rotations, 64)
+    sets = [(pa, sa, pb, sb)] + [tuple(t.clone() for t in (pa, sa, pb, sb)) for _ in range(rotations - 1)]
+    plans = [g.Nvfp4Gemm(x[0], x[2], x[1], x[3]) for x in sets]
+    out = torch.empty((m, n_local), dtype=torch.float16, device=dev)
+    full = torch.empty((m, n), dtype=torch.float16, device=dev) if (world > 1 and args.gather) else None
+
+    def step(i):
+        plans[i % rotations].run(out)
+        if full is not None:
+            g.gather_columns(out, None, full)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    for i in range(max(3, args.warmup)):
+        step(i)
+    barrier()
+    launches0 = _lib.launch_count()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    start.record()
+    for i in range(args.steps):
+        step(i)
+    stop.record()
+    barrier()
+    t1 = time.perf_counter()
+    launches = _lib.launch_count() - launches0
+    ms = start.elapsed_time(stop)
+    if sampler is not None and (t1 - t0) < 0.5:
+        # the timed region is shorter than a few sampling periods: keep the same load running for the sampler only
+        until = time.perf_counter() + 0.7
+        i = 0
+        while time.perf_counter() < until:
+            step(i); i += 1
+            if i % 64 == 0:
+                torch.cuda.synchronize()
+        torch.cuda.synchronize()
+    clocks = sampler.stop(t0, t1) if sampler is not None else None
+    plans[0].validate()
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+
+    # End to end through the C ABI with HOST buffers: H2D of the operands, kernel, D2H of C, every step.
+    host = [t.cpu().pin_memory() for t in (pa, pb, sa, sb)]
+    host_c = torch.empty((m, n_local), dtype=torch.float16).pin_memory()
+    e2e_steps = max(2, min(args.steps, 10))
+    g.gemm_host(*host, host_c)
+    barrier()
+    te = time.perf_counter()
+    start.record()
+    for _ in range(e2e_steps):
+        g.gemm_host(*host, host_c)
+    stop.record()
+    barrier()
+    e2e_ms = start.elapsed_time(stop)
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    del te
+    h2d = sum(t.numel() * t.element_size() for t in host)
+    d2h = host_c.numel() * 2
+
+    if rank != 0:
+        return
+    flops = 2.0 * m * n * k
+    ms_per_step = ms / args.steps
+    value = flops / (ms_per_step * 1e-3) / 1e12
+    peaks = measured_peaks()
+    timed_s = ms * 1e-3
+    bf16 = peaks["bf16_sustained"] if timed_s > 1.0 else peaks["bf16_burst"]
+    tensor_peak = 4.0 * bf16
+    per_gpu_tflops = value / world
+    alg_bytes = algorithmic_bytes(m, n_local, k)
+    gbs = alg_bytes / (ms_per_step * 1e-3) / 1e9
+    # which roof bounds this workload: compare time at the tensor peak with time at the HBM peak
+    t_tensor = (flops / world) / (tensor_peak * 1e12)
+    t_hbm = alg_bytes / (peaks["hbm_gbs"] * 1e9)
+    if t_tensor >= t_hbm:
+        roofline = {"bound": "tensor", "achieved": per_gpu_tflops, "peak": tensor_peak, "unit": "TFLOP/s",
+                    "frac": per_gpu_tflops / tensor_peak,
+                    "peak_source": f"4 x {peaks['source']} cuBLAS bf16 ({'sustained' if timed_s > 1.0 else 'burst'}): "
+                                   "no FP4 peak is measured on this pool; FP4 dense is 4x bf16 on the same pipe",
+                    "frac_of_nominal_9pf": per_gpu_tflops / NOMINAL_FP4_TFLOPS}
+    else:
+        roofline = {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                    "frac": gbs / peaks["hbm_gbs"], "peak_source": f"{peaks['source']} copy bandwidth"}
+    roofline["kernel"] = "nvfp4_gemm_kernel"
+    roofline["algorithmic_bytes_per_launch"] = alg_bytes
+    roofline["traffic"] = NCU_DRAM_BYTES_PER_LAUNCH.get(args.workload) if world == 1 else None
+
+    cpu = None
+    if world == 1 and not args.no_cpu:
+        v, cores, sample = cpu_reference_pass(m, n, k, sigma, 15.0)
+        cpu = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
+
+    info = plans[0].info()
+    print(json.dumps({
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "nvfp4 (e2m1 x ue4m3), f32 accumulate, f16 out", "data": "synthetic",
+        "config": {"workload": args.workload, "M": m, "N": n, "K": k, "layout": "TN",
+                   "sharding": f"B rows over {world} rank(s), {n_local} columns of C per rank",
+                   "gather": bool(full is not None),
+                   "l2": f"operand rotation over {rotations} copies ({rotations * in_bytes >> 20} MiB > 2 x L2 {l2 >> 20} MiB)",
+                   "plan": info},
+        "clocks": clocks,
+        "e2e": {"value": flops / (e2e_ms / e2e_steps * 1e-3) / 1e12, "unit": UNIT,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+                "call": "gpu_kernels_nvfp4_gemm_host (pinned host buffers)"},
+        "gpu_launches": int(launches),
+        "roofline": roofline,
+        "cpu_baseline": cpu,
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="gemm8192", choices=sorted(WORKLOADS))
+    ap.add_argument("--gather", action="store_true", help="N>1: include the all-gather of C in every step")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        run_ours(args, rank, world, local_rank)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

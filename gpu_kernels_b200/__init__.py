@@ -1,0 +1,8 @@
+"""B200-native NVFP4 path: quantise/pack, block-scaled GEMM, N-sharded multi-GPU GEMM.
+
+Everything here drives hand-written sm_100a kernels through a C ABI
+(include/nvfp4_capi.h). There is no CPU or eager fallback.
+"""
+from .nvfp4 import dequantize, pack_scales, quantize, unpack_scales  # noqa: F401
+from .gemm import Nvfp4Gemm, gemm_host  # noqa: F401
+from .sharded import ShardedNvfp4Gemm, gather_columns, shard_b, slab_rows  # noqa: F401

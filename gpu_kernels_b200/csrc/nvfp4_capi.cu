@@ -1,0 +1,275 @@
+// extern "C" surface of libgpu_kernels_nvfp4_bench.so (declared in include/nvfp4_capi.h).
+// Every entry point catches all exceptions, stores the message per thread and
+// returns 1, the convention of the reference's bridge
+// (benchmarks/bindings/nvfp4_bridge.cu:11,88-91).
+#include "nvfp4.h"
+#include "nvfp4_capi.h"
+#include "nvfp4_internal.h"
+
+#include <cublasLt.h>
+
+#include <atomic>
+#include <cstring>
+#include <memory>
+#include <mutex>
+#include <string>
+
+namespace nvfp4_b200 {
+extern std::atomic<unsigned long long> g_launches;
+int gemm_stage_count(int cta_group, int tile_n);
+}
+
+namespace {
+
+thread_local std::string t_error;
+
+template <typename F>
+int guarded(F&& body) {
+    try {
+        body();
+        return 0;
+    } catch (const std::exception& e) {
+        t_error = e.what();
+    } catch (...) {
+        t_error = "unknown error";
+    }
+    return 1;
+}
+
+void lt_check(cublasStatus_t s, const char* what) {
+    if (s != CUBLAS_STATUS_SUCCESS)
+        throw std::runtime_error(std::string("cuBLASLt ") + what + " failed with status " + std::to_string(int(s)));
+}
+
+// cuBLASLt's own NVFP4 matmul on the plan's shape: the library bar this kernel is
+// compared with, never part of the product path. Built lazily on first use.
+class LtMatmul {
+public:
+    LtMatmul(int M, int N, int K, const void* sfa, const void* sfb, size_t workspace_limit) {
+        lt_check(cublasLtCreate(&handle_), "create");
+        lt_check(cublasLtMatmulDescCreate(&op_, CUBLAS_COMPUTE_32F, CUDA_R_32F), "desc");
+        // cuBLASLt is column-major: C^T[N,M] = B[N,K] * A[M,K]^T, i.e. its "A" operand is our B.
+        set(CUBLASLT_MATMUL_DESC_TRANSA, CUBLAS_OP_T);
+        set(CUBLASLT_MATMUL_DESC_TRANSB, CUBLAS_OP_N);
+        set(CUBLASLT_MATMUL_DESC_A_SCALE_MODE, CUBLASLT_MATMUL_MATRIX_SCALE_VEC16_UE4M3);
+        set(CUBLASLT_MATMUL_DESC_B_SCALE_MODE, CUBLASLT_MATMUL_MATRIX_SCALE_VEC16_UE4M3);
+        set(CUBLASLT_MATMUL_DESC_A_SCALE_POINTER, sfb);
+        set(CUBLASLT_MATMUL_DESC_B_SCALE_POINTER, sfa);
+        lt_check(cublasLtMatrixLayoutCreate(&lb_, CUDA_R_4F_E2M1, K, N, K), "layout B");
+        lt_check(cublasLtMatrixLayoutCreate(&la_, CUDA_R_4F_E2M1, K, M, K), "layout A");
+        lt_check(cublasLtMatrixLayoutCreate(&lc_, CUDA_R_16F, N, M, N), "layout C");
+        lt_check(cublasLtMatmulPreferenceCreate(&pref_), "preference");
+        lt_check(cublasLtMatmulPreferenceSetAttribute(pref_, CUBLASLT_MATMUL_PREF_MAX_WORKSPACE_BYTES,
+                                                      &workspace_limit, sizeof(workspace_limit)), "workspace");
+        cublasLtMatmulHeuristicResult_t found{};
+        int n = 0;
+        lt_check(cublasLtMatmulAlgoGetHeuristic(handle_, op_, lb_, la_, lc_, lc_, pref_, 1, &found, &n), "heuristic");
+        if (n == 0) throw std::runtime_error("cuBLASLt offers no NVFP4 algorithm for this shape on this device");
+        algo_ = found.algo;
+        workspace_bytes_ = found.workspaceSize;
+    }
+    ~LtMatmul() {
+        if (pref_) cublasLtMatmulPreferenceDestroy(pref_);
+        if (lc_) cublasLtMatrixLayoutDestroy(lc_);
+        if (la_) cublasLtMatrixLayoutDestroy(la_);
+        if (lb_) cublasLtMatrixLayoutDestroy(lb_);
+        if (op_) cublasLtMatmulDescDestroy(op_);
+        if (handle_) cublasLtDestroy(handle_);
+    }
+    void run(void* C, const void* A, const void* B, void* workspace, cudaStream_t stream) const {
+        const float one = 1.0f, zero = 0.0f;
+        lt_check(cublasLtMatmul(handle_, op_, &one, B, lb_, A, la_, &zero, C, lc_, C, lc_, &algo_,
+                                workspace, workspace_bytes_, stream), "matmul");
+    }
+
+private:
+    template <typename T>
+    void set(cublasLtMatmulDescAttributes_t attr, T value) {
+        lt_check(cublasLtMatmulDescSetAttribute(op_, attr, &value, sizeof(value)), "attribute");
+    }
+    cublasLtHandle_t handle_ = nullptr;
+    cublasLtMatmulDesc_t op_ = nullptr;
+    cublasLtMatrixLayout_t la_ = nullptr, lb_ = nullptr, lc_ = nullptr;
+    cublasLtMatmulPreference_t pref_ = nullptr;
+    cublasLtMatmulAlgo_t algo_{};
+    size_t workspace_bytes_ = 0;
+};
+
+struct Plan {
+    gpu_kernels::Nvfp4Params params{};
+    gpu_kernels::Nvfp4Implementation impl{};
+    const void* sfa = nullptr;
+    const void* sfb = nullptr;
+    void* workspace = nullptr;
+    size_t workspace_bytes = 0;
+    std::unique_ptr<LtMatmul> lt;
+};
+
+Plan& as_plan(void* p) {
+    if (!p) throw std::invalid_argument("null plan");
+    return *static_cast<Plan*>(p);
+}
+
+// Device staging for gpu_kernels_nvfp4_gemm_host, kept between calls of one shape.
+struct HostGemm {
+    int M = 0, N = 0, K = 0;
+    uint8_t *A = nullptr, *B = nullptr, *SFA = nullptr, *SFB = nullptr;
+    __half* C = nullptr;
+    Plan plan;
+    void release() {
+        for (void* p : {static_cast<void*>(A), static_cast<void*>(B), static_cast<void*>(SFA), static_cast<void*>(SFB),
+                        static_cast<void*>(C)})
+            if (p) cudaFree(p);
+        A = B = SFA = SFB = nullptr;
+        C = nullptr;
+        M = N = K = 0;
+    }
+};
+std::mutex g_host_lock;
+HostGemm g_host;
+
+}  // namespace
+
+extern "C" {
+
+const char* gpu_kernels_nvfp4_last_error(void) { return t_error.c_str(); }
+
+int gpu_kernels_nvfp4_plan_create(void** out, int M, int N, int K, const void* A, const void* B, const void* SFA,
+                                  const void* SFB, void* workspace, size_t workspace_bytes, void* stream) {
+    return guarded([&] {
+        if (!out) throw std::invalid_argument("plan_create: null result pointer");
+        auto plan = std::make_unique<Plan>();
+        plan->impl = gpu_kernels::nvfp4_sm100_implementation();
+        plan->impl.prepare(plan->params, static_cast<const uint8_t*>(A), static_cast<const uint8_t*>(B),
+                           static_cast<const uint8_t*>(SFA), static_cast<const uint8_t*>(SFB), M, N, K,
+                           static_cast<cudaStream_t>(stream));
+        plan->sfa = SFA;
+        plan->sfb = SFB;
+        plan->workspace = workspace;
+        plan->workspace_bytes = workspace_bytes;
+        *out = plan.release();
+    });
+}
+
+void gpu_kernels_nvfp4_plan_destroy(void* plan) { delete static_cast<Plan*>(plan); }
+
+int gpu_kernels_nvfp4_cublas(void* plan, void* C, const void* A, const void* B, void* stream) {
+    return guarded([&] {
+        Plan& p = as_plan(plan);
+        if (!p.lt)
+            p.lt = std::make_unique<LtMatmul>(p.params.M, p.params.N, p.params.K, p.sfa, p.sfb,
+                                              p.workspace ? p.workspace_bytes : 0);
+        p.lt->run(C, A, B, p.workspace, static_cast<cudaStream_t>(stream));
+    });
+}
+
+int gpu_kernels_nvfp4_custom(void* plan, void* C, void* stream) {
+    return guarded([&] {
+        Plan& p = as_plan(plan);
+        p.impl.launch(p.params, static_cast<__half*>(C), static_cast<cudaStream_t>(stream));
+    });
+}
+
+int gpu_kernels_nvfp4_validate(void* plan) {
+    return guarded([&] {
+        Plan& p = as_plan(plan);
+        p.impl.validate();
+    });
+}
+
+int gpu_kernels_nvfp4_l2_bytes(void) {
+    int device = 0, bytes = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) return 0;
+    if (cudaDeviceGetAttribute(&bytes, cudaDevAttrL2CacheSize, device) != cudaSuccess) return 0;
+    return bytes;
+}
+
+int gpu_kernels_nvfp4_quantize(const void* x, int dtype, void* packed, void* scales, int rows, int K, void* stream) {
+    return guarded([&] {
+        nvfp4_b200::require_sm100();
+        nvfp4_b200::quantise(x, dtype, static_cast<uint8_t*>(packed), static_cast<uint8_t*>(scales), rows, K,
+                             static_cast<cudaStream_t>(stream));
+        nvfp4_b200::g_launches.fetch_add(1, std::memory_order_relaxed);
+    });
+}
+
+int gpu_kernels_nvfp4_dequantize(const void* packed, const void* scales, void* out, int rows, int K, void* stream) {
+    return guarded([&] {
+        nvfp4_b200::require_sm100();
+        nvfp4_b200::dequantise(static_cast<const uint8_t*>(packed), static_cast<const uint8_t*>(scales),
+                               static_cast<float*>(out), rows, K, static_cast<cudaStream_t>(stream));
+        nvfp4_b200::g_launches.fetch_add(1, std::memory_order_relaxed);
+    });
+}
+
+int gpu_kernels_nvfp4_plan_set_alpha(void* plan, float alpha) {
+    return guarded([&] { gpu_kernels::nvfp4_set_alpha(as_plan(plan).params, alpha); });
+}
+
+int gpu_kernels_nvfp4_plan_set_option(void* plan, const char* key, int value) {
+    return guarded([&] {
+        Plan& p = as_plan(plan);
+        if (!key) throw std::invalid_argument("set_option: null key");
+        if (std::strcmp(key, "group_m") == 0) {
+            const int tiles_m = p.params.M / (128 * p.params.cta_group);
+            if (value < 1) throw std::invalid_argument("set_option: group_m must be >= 1");
+            p.params.group_m = value < tiles_m ? value : tiles_m;
+        } else {
+            throw std::invalid_argument(std::string("set_option: unknown key ") + key);
+        }
+    });
+}
+
+int gpu_kernels_nvfp4_plan_info(void* plan, int* info) {
+    return guarded([&] {
+        Plan& p = as_plan(plan);
+        if (!info) throw std::invalid_argument("plan_info: null output");
+        const auto& q = p.params;
+        const int values[8] = {q.M, q.N, q.K, q.clusters, q.cta_group, q.tile_n, q.group_m,
+                               nvfp4_b200::gemm_stage_count(q.cta_group, q.tile_n)};
+        std::memcpy(info, values, sizeof(values));
+    });
+}
+
+int gpu_kernels_nvfp4_gemm_host(int M, int N, int K, const void* A, const void* B, const void* SFA, const void* SFB,
+                                void* C, float alpha, void* stream_) {
+    return guarded([&] {
+        using nvfp4_b200::cuda_check;
+        if (!A || !B || !SFA || !SFB || !C) throw std::invalid_argument("gemm_host: null pointer");
+        nvfp4_b200::require_sm100();
+        auto stream = static_cast<cudaStream_t>(stream_);
+        std::lock_guard<std::mutex> hold(g_host_lock);
+        HostGemm& h = g_host;
+        const size_t a_bytes = size_t(M) * K / 2, b_bytes = size_t(N) * K / 2;
+        const size_t sfa_bytes = size_t(M) * K / 16, sfb_bytes = size_t(N) * K / 16, c_bytes = size_t(M) * N * 2;
+        if (h.M != M || h.N != N || h.K != K) {
+            h.release();
+            if (M <= 0 || N <= 0 || K <= 0 || M % 128 || N % 128 || K % 256)
+                throw std::invalid_argument("gemm_host: M, N multiples of 128 and K a multiple of 256 are required");
+            cuda_check(cudaMalloc(&h.A, a_bytes));
+            cuda_check(cudaMalloc(&h.B, b_bytes));
+            cuda_check(cudaMalloc(&h.SFA, sfa_bytes));
+            cuda_check(cudaMalloc(&h.SFB, sfb_bytes));
+            cuda_check(cudaMalloc(&h.C, c_bytes));
+            h.plan.impl = gpu_kernels::nvfp4_sm100_implementation();
+            h.plan.impl.prepare(h.plan.params, h.A, h.B, h.SFA, h.SFB, M, N, K, stream);
+            h.M = M; h.N = N; h.K = K;
+        }
+        h.plan.params.alpha = alpha;
+        cuda_check(cudaMemcpyAsync(h.A, A, a_bytes, cudaMemcpyHostToDevice, stream));
+        cuda_check(cudaMemcpyAsync(h.B, B, b_bytes, cudaMemcpyHostToDevice, stream));
+        cuda_check(cudaMemcpyAsync(h.SFA, SFA, sfa_bytes, cudaMemcpyHostToDevice, stream));
+        cuda_check(cudaMemcpyAsync(h.SFB, SFB, sfb_bytes, cudaMemcpyHostToDevice, stream));
+        h.plan.impl.launch(h.plan.params, h.C, stream);
+        cuda_check(cudaMemcpyAsync(C, h.C, c_bytes, cudaMemcpyDeviceToHost, stream));
+        cuda_check(cudaStreamSynchronize(stream));
+    });
+}
+
+const char* gpu_kernels_nvfp4_version(void) { return "nvfp4-b200 0.1 (sm_100a)"; }
+
+unsigned long long gpu_kernels_nvfp4_launch_count(void) {
+    return nvfp4_b200::g_launches.load(std::memory_order_relaxed);
+}
+
+}  // extern "C"

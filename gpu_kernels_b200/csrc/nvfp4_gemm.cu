@@ -1,0 +1,542 @@
+// NVFP4 block-scaled GEMM for B200 (sm_100a): C[M,N] fp16 = alpha * (A sfA)(B sfB)^T.
+//
+// One persistent kernel, three roles per CTA (192 threads):
+//   warps 0-3  epilogue: TMEM -> registers -> FP16 -> swizzled shared memory -> TMA store
+//   warp  4    MMA issuer (one lane): scale copies into TMEM + tcgen05 block-scaled MMAs
+//   warp  5    producer  (one lane): TMA tile loads of packed operands and scale atoms
+// A ring stage carries K = 256 of everything one MMA group needs (A rows, B rows,
+// SFA atoms, SFB atoms) behind a single "full" barrier, so the issuer waits once
+// per four MMAs. Accumulators are double-buffered in Tensor Memory; for 256-wide
+// tiles the two buffers overlap by the width of the scale columns and the
+// epilogue drains the shared columns first. Tiles are visited in bands of
+// `group_m` tile rows, serpentine along N, computed arithmetically per tile (no
+// table, no global state) so that the tiles in flight share A and B panels in L2.
+// With CTA pairs (cta_group::2) each CTA loads its own half of A and B and both
+// scale halves of B itself: no load in this file is multicast.
+//
+// Replaces the reference's kernels/gemm/matmul/sm100.cu (prepare/launch/validate
+// at :701-737, kernel at :393-529) behind the same C++ interface.
+#include "nvfp4.h"
+#include "nvfp4_internal.h"
+#include "ptx.cuh"
+
+#include <algorithm>
+#include <atomic>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+namespace nvfp4_b200 {
+
+std::atomic<unsigned long long> g_launches{0};
+
+namespace {
+
+using namespace ptx;
+
+constexpr int BLOCK_M = 128;        // rows of C per CTA (= TMEM lanes)
+constexpr int STAGE_K = 256;        // K values per ring stage: 128 bytes of packed FP4 per row
+constexpr int MMA_K = 64;           // K values per tcgen05.mma of this kind
+constexpr int ROW_BYTES = STAGE_K / 2;
+constexpr int SF_ATOM_BYTES = 512;  // 128 rows x 4 scale bytes (K = 64)
+constexpr int EPI_COLS = 64;        // FP16 columns per epilogue chunk: one 128-byte line per row
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int SMEM_LIMIT = 232448;  // 227 KiB opt-in maximum per CTA
+
+// Device-side status: [0] OR of StatusBits, [1] tag of the first wait that gave up.
+__device__ uint32_t g_status[4];
+
+template <int CG, int UN>
+struct Config {
+    static_assert(CG == 1 || CG == 2, "cta group");
+    static_assert(UN == 128 || UN == 256, "tile width");
+    static constexpr int TILE_M = BLOCK_M * CG;
+    static constexpr int B_ROWS = UN / CG;                       // B rows staged by each CTA
+    static constexpr int A_BYTES = BLOCK_M * ROW_BYTES;
+    static constexpr int B_BYTES = B_ROWS * ROW_BYTES;
+    static constexpr int SFA_BYTES = (STAGE_K / MMA_K) * SF_ATOM_BYTES;
+    static constexpr int SFB_BLOCKS = UN / 128;                  // 128-row scale blocks across the tile width
+    static constexpr int SFB_BLOCK_BYTES = (STAGE_K / MMA_K) * SF_ATOM_BYTES;
+    static constexpr int SFB_BYTES = SFB_BLOCKS * SFB_BLOCK_BYTES;
+    static constexpr int OFF_B = A_BYTES;
+    static constexpr int OFF_SFA = OFF_B + B_BYTES;
+    static constexpr int OFF_SFB = OFF_SFA + SFA_BYTES;
+    static constexpr int STAGE_BYTES = OFF_SFB + SFB_BYTES;
+    static constexpr int EPI_WARP_BYTES = 32 * EPI_COLS * 2;     // 32 rows x 128 B
+    static constexpr int EPI_BYTES = 4 * 2 * EPI_WARP_BYTES;     // 4 warps, double-buffered
+    static constexpr int CTRL_BYTES = 1024;
+    static constexpr int STAGES = (SMEM_LIMIT - 1024 - CTRL_BYTES - EPI_BYTES) / STAGE_BYTES;
+    static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + CTRL_BYTES;
+    // Tensor Memory columns: scale columns for the four MMAs of a stage at the top,
+    // two accumulators below them (overlapping when they cannot both fit).
+    static constexpr int SF_COLS_PER_MMA = 4 + UN / 32;
+    static constexpr int SF_COLS = (STAGE_K / MMA_K) * SF_COLS_PER_MMA;
+    static constexpr int SF_BASE = TMEM_COLS - SF_COLS;
+    static constexpr int ACC_STRIDE = (2 * UN <= SF_BASE) ? UN : SF_BASE - UN;
+    static constexpr int OVERLAP = UN - ACC_STRIDE;              // columns shared by the two accumulators
+    static_assert(OVERLAP <= EPI_COLS, "the first epilogue chunk must cover the overlap");
+    static_assert(STAGE_BYTES % 1024 == 0, "stages keep the 1024-byte swizzle alignment");
+    static_assert(STAGES >= 3, "ring too shallow");
+    // Instruction descriptor of kind::mxf4nvf4: A and B E2M1 (format 1) at bits 7 and 10,
+    // both K-major, N >> 3 at bit 17, UE4M3 scales (bit 23 = 0), M >> 4 at bit 24,
+    // scale-factor ids 0 (each MMA reads whole 32-bit scale columns).
+    static constexpr uint32_t IDESC = (1u << 7) | (1u << 10) | (uint32_t(UN >> 3) << 17) |
+                                      (uint32_t(TILE_M >> 4) << 24);
+};
+
+struct Control {
+    uint64_t full[8], empty[8];
+    uint64_t acc_full, acc_free;
+    uint32_t tmem_base;
+    WaitCtl wait;
+};
+static_assert(sizeof(Control) <= 1024, "control block");
+
+struct GemmArgs {
+    int M, N, K;
+    int tiles_m, tiles_n, group_m;
+    float alpha;
+    uint32_t* status;
+};
+
+// Shared-memory matrix descriptor, K-major operand rows of 128 bytes under the
+// 128-byte swizzle: start address >> 4, stride between 8-row groups 1024 B (>> 4)
+// at bit 32, descriptor version 1 at bit 46, swizzle mode 2 (128 B) at bit 61.
+__device__ __forceinline__ uint64_t operand_desc(uint32_t addr) {
+    return uint64_t((addr & 0x3FFFFu) >> 4) | (uint64_t(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Scale atom: 32 rows of 16 bytes, no swizzle: 8-row groups 128 B apart, 16 B leading offset.
+__device__ __forceinline__ uint64_t scale_desc(uint32_t addr) {
+    return uint64_t((addr & 0x3FFFFu) >> 4) | (uint64_t(16 >> 4) << 16) | (uint64_t(128 >> 4) << 32) | (1ull << 46);
+}
+
+// Tile t of the persistent sequence -> tile coordinates. Bands of `group_m` tile
+// rows, column-major inside a band, bands alternate direction along N.
+__device__ __forceinline__ void tile_coords(int t, const GemmArgs& g, int& tm, int& tn) {
+    const int per_band = g.group_m * g.tiles_n;
+    const int band = t / per_band;
+    const int first = band * g.group_m;
+    const int rows = min(g.group_m, g.tiles_m - first);
+    const int r = t - band * per_band;
+    const int c = r / rows;
+    tm = first + r - c * rows;
+    tn = (band & 1) ? g.tiles_n - 1 - c : c;
+}
+
+template <int CG, int UN>
+struct Roles {
+    using Cfg = Config<CG, UN>;
+
+    uint32_t smem;            // 1024-aligned shared-window address of stage 0
+    Control* ctrl;
+    uint32_t rank, unit, units, tiles, peer_abort;
+    const GemmArgs& g;
+
+    __device__ __forceinline__ uint32_t bar(const uint64_t* b) const { return smem_u32(b); }
+    __device__ __forceinline__ bool wait(const uint64_t* b, uint32_t parity, uint32_t who, uint32_t tag) const {
+        if (mbar_wait(bar(b), parity, &ctrl->wait, g.status, who, peer_abort)) return true;
+        if (who) atomicCAS(g.status + 1, 0u, tag);
+        return false;
+    }
+
+    // ---- warp 5, one lane: stream operand and scale tiles into the ring -------
+    __device__ void produce(const CUtensorMap* tmA, const CUtensorMap* tmB,
+                            const CUtensorMap* tmSFA, const CUtensorMap* tmSFB) const {
+        int stage = 0;
+        uint32_t phase = 0;
+        const int ksteps = g.K / STAGE_K;
+        const int sf_rows_per_block = (g.K / 64) * 4;          // 128-byte rows of the scale map per 128 tensor rows
+        for (uint32_t t = unit; t < tiles; t += units) {
+            int tm, tn;
+            tile_coords(int(t), g, tm, tn);
+            const int a_row = tm * Cfg::TILE_M + int(rank) * BLOCK_M;
+            const int b_row = tn * UN + int(rank) * Cfg::B_ROWS;
+            const int sfa_row0 = (a_row / 128) * sf_rows_per_block;
+            const int sfb_row0 = (tn * UN / 128) * sf_rows_per_block;
+            for (int ks = 0; ks < ksteps; ++ks) {
+                if (!wait(&ctrl->empty[stage], phase ^ 1u, STATUS_TIMEOUT_PRODUCER, 0x10000000u | (stage << 16) | ks))
+                    return;
+                const uint32_t base = smem + stage * Cfg::STAGE_BYTES;
+                if constexpr (CG == 1) {
+                    const uint32_t full = bar(&ctrl->full[stage]);
+                    mbar_arrive_expect_tx(full, Cfg::STAGE_BYTES);
+                    tma_load_2d(base, tmA, ks * ROW_BYTES, a_row, full);
+                    tma_load_2d(base + Cfg::OFF_B, tmB, ks * ROW_BYTES, b_row, full);
+                    tma_load_2d(base + Cfg::OFF_SFA, tmSFA, 0, sfa_row0 + ks * 16, full);
+                    #pragma unroll
+                    for (int b = 0; b < Cfg::SFB_BLOCKS; ++b)
+                        tma_load_2d(base + Cfg::OFF_SFB + b * Cfg::SFB_BLOCK_BYTES, tmSFB, 0,
+                                    sfb_row0 + b * sf_rows_per_block + ks * 16, full);
+                } else {
+                    // Both CTAs of the pair report their bytes to the leader's barrier.
+                    const uint32_t full = map_to_cta(bar(&ctrl->full[stage]), 0);
+                    if (rank == 0) mbar_arrive_expect_tx(bar(&ctrl->full[stage]), 2 * Cfg::STAGE_BYTES);
+                    tma_load_2d_pair(base, tmA, ks * ROW_BYTES, a_row, full);
+                    tma_load_2d_pair(base + Cfg::OFF_B, tmB, ks * ROW_BYTES, b_row, full);
+                    tma_load_2d_pair(base + Cfg::OFF_SFA, tmSFA, 0, sfa_row0 + ks * 16, full);
+                    #pragma unroll
+                    for (int b = 0; b < Cfg::SFB_BLOCKS; ++b)
+                        tma_load_2d_pair(base + Cfg::OFF_SFB + b * Cfg::SFB_BLOCK_BYTES, tmSFB, 0,
+                                         sfb_row0 + b * sf_rows_per_block + ks * 16, full);
+                }
+                if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
+            }
+        }
+    }
+
+    // ---- warp 4, one lane of the leader CTA: scale copies and MMAs --------------
+    __device__ void issue(uint32_t tmem) const {
+        int stage = 0;
+        uint32_t phase = 0, iter = 0;
+        const int ksteps = g.K / STAGE_K;
+        for (uint32_t t = unit; t < tiles; t += units, ++iter) {
+            const uint32_t acc = tmem + (iter & 1u) * Cfg::ACC_STRIDE;
+            if (iter > 0) {
+                // The epilogue has pulled the columns this tile shares with the previous one.
+                if (!wait(&ctrl->acc_free, (iter - 1u) & 1u, STATUS_TIMEOUT_MMA, 0x20000000u | iter)) return;
+                tc_fence_after_sync();
+            }
+            for (int ks = 0; ks < ksteps; ++ks) {
+                if (!wait(&ctrl->full[stage], phase, STATUS_TIMEOUT_MMA, 0x21000000u | (stage << 16) | ks)) return;
+                tc_fence_after_sync();
+                const uint32_t base = smem + stage * Cfg::STAGE_BYTES;
+                #pragma unroll
+                for (int j = 0; j < STAGE_K / MMA_K; ++j) {
+                    const uint32_t sf = tmem + Cfg::SF_BASE + j * Cfg::SF_COLS_PER_MMA;
+                    tmem_copy_scales<CG>(sf, scale_desc(base + Cfg::OFF_SFA + j * SF_ATOM_BYTES));
+                    #pragma unroll
+                    for (int b = 0; b < Cfg::SFB_BLOCKS; ++b)
+                        tmem_copy_scales<CG>(sf + 4 + 4 * b,
+                                             scale_desc(base + Cfg::OFF_SFB + b * Cfg::SFB_BLOCK_BYTES + j * SF_ATOM_BYTES));
+                    // K advances 32 bytes inside the 128-byte swizzled row per MMA.
+                    mma_nvfp4<CG>(acc, operand_desc(base + j * (MMA_K / 2)),
+                                  operand_desc(base + Cfg::OFF_B + j * (MMA_K / 2)),
+                                  Cfg::IDESC, sf, sf + 4, (ks | j) != 0 ? 1u : 0u);
+                }
+                mma_commit<CG>(bar(&ctrl->empty[stage]));       // stage reusable once these MMAs retire
+                if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
+            }
+            mma_commit<CG>(bar(&ctrl->acc_full));
+        }
+    }
+
+    // ---- warps 0-3: drain accumulators to C ---------------------------------------
+    __device__ void drain(uint32_t tmem, const CUtensorMap* tmC, int warp, int lane) const {
+        const uint32_t stage_base = smem + Cfg::STAGES * Cfg::STAGE_BYTES + warp * 2 * Cfg::EPI_WARP_BYTES;
+        const uint32_t acc_free_leader = CG == 2 ? map_to_cta(bar(&ctrl->acc_free), 0) : bar(&ctrl->acc_free);
+        uint32_t iter = 0, stores = 0;
+        const float alpha = g.alpha;
+        for (uint32_t t = unit; t < tiles; t += units, ++iter) {
+            int tm, tn;
+            tile_coords(int(t), g, tm, tn);
+            const int row0 = tm * Cfg::TILE_M + int(rank) * BLOCK_M + warp * 32;
+            const int col0 = tn * UN;
+            // The whole warp leaves together: the Tensor Memory loads below are warp-collective.
+            const bool ready = wait(&ctrl->acc_full, iter & 1u, lane == 0 ? STATUS_TIMEOUT_EPILOGUE : 0u, 0x30000000u | iter);
+            if (!__all_sync(0xFFFFFFFFu, ready)) break;
+            tc_fence_after_sync();
+            const uint32_t acc = tmem + (iter & 1u) * Cfg::ACC_STRIDE + (uint32_t(warp * 32) << 16);
+            #pragma unroll 1
+            for (int c = 0; c < UN / EPI_COLS; ++c) {
+                // Columns shared with the other accumulator go first: top of buffer 0, bottom of buffer 1.
+                const int chunk = (iter & 1u) ? c : UN / EPI_COLS - 1 - c;
+                uint32_t v[EPI_COLS];
+                tmem_ld_32x32(acc + chunk * EPI_COLS, v);
+                tmem_ld_32x32(acc + chunk * EPI_COLS + 32, v + 32);
+                tmem_ld_wait();
+                if (c == 0) {
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(acc_free_leader);
+                }
+                const uint32_t buf = stage_base + (stores & 1u) * Cfg::EPI_WARP_BYTES;
+                if (lane == 0) tma_store_wait_read<1>();        // the store that last read this buffer is done
+                __syncwarp();
+                #pragma unroll
+                for (int q = 0; q < EPI_COLS / 8; ++q) {
+                    uint32_t h[4];
+                    #pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const __half2 p = __floats2half2_rn(__uint_as_float(v[q * 8 + 2 * i]) * alpha,
+                                                            __uint_as_float(v[q * 8 + 2 * i + 1]) * alpha);
+                        h[i] = *reinterpret_cast<const uint32_t*>(&p);
+                    }
+                    // 128-byte swizzle: 16-byte chunk q of row `lane` lands in chunk q ^ (lane % 8).
+                    const uint32_t dst = buf + lane * 128 + ((q ^ (lane & 7)) << 4);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                                 :: "r"(dst), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]) : "memory");
+                }
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    tma_store_2d(tmC, buf, col0 + chunk * EPI_COLS, row0);
+                    tma_store_commit();
+                }
+                ++stores;
+            }
+        }
+        if (lane == 0) tma_store_wait_all();
+    }
+};
+
+template <int CG, int UN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                  const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB,
+                  const __grid_constant__ CUtensorMap tmC, const GemmArgs g) {
+    using Cfg = Config<CG, UN>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t smem = (raw + 1023u) & ~1023u;
+    Control* ctrl = reinterpret_cast<Control*>(smem_raw + (smem - raw) + Cfg::STAGES * Cfg::STAGE_BYTES + Cfg::EPI_BYTES);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = CG == 2 ? cluster_ctarank() : 0u;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < Cfg::STAGES; ++s) {
+            mbar_init(smem_u32(&ctrl->full[s]), 1);
+            mbar_init(smem_u32(&ctrl->empty[s]), 1);
+        }
+        mbar_init(smem_u32(&ctrl->acc_full), 1);
+        mbar_init(smem_u32(&ctrl->acc_free), 4 * CG);           // one arrival per epilogue warp of the pair
+        ctrl->wait.abort = 0;
+        mbar_init_fence();
+    }
+    if (warp == 4) {
+        tmem_alloc<CG>(smem_u32(&ctrl->tmem_base), TMEM_COLS);
+        tmem_relinquish<CG>();
+    }
+    if (warp == 5 && lane == 0) {
+        prefetch_tensormap(&tmA); prefetch_tensormap(&tmB);
+        prefetch_tensormap(&tmSFA); prefetch_tensormap(&tmSFB); prefetch_tensormap(&tmC);
+    }
+    tc_fence_before_sync();
+    if constexpr (CG == 2) { cluster_arrive(); cluster_wait(); } else { __syncthreads(); }
+    tc_fence_after_sync();
+    const uint32_t tmem = ctrl->tmem_base;
+
+    Roles<CG, UN> roles{smem, ctrl, rank,
+                        CG == 2 ? blockIdx.x / 2u : blockIdx.x, gridDim.x / CG,
+                        uint32_t(g.tiles_m) * uint32_t(g.tiles_n),
+                        CG == 2 ? map_to_cta(smem_u32(const_cast<uint32_t*>(&ctrl->wait.abort)), rank ^ 1u) : 0u, g};
+
+    if (warp == 5) {
+        if (lane == 0) roles.produce(&tmA, &tmB, &tmSFA, &tmSFB);
+    } else if (warp == 4) {
+        if (lane == 0 && rank == 0) roles.issue(tmem);
+    } else {
+        roles.drain(tmem, &tmC, warp, lane);
+    }
+    __syncwarp();
+
+    // Common teardown. After an abandoned wait, give copies still in flight time
+    // to land before the CTA's shared memory is released.
+    if (ctrl->wait.abort) {
+        for (int i = 0; i < 200; ++i) __nanosleep(1000);
+    }
+    tc_fence_before_sync();
+    if constexpr (CG == 2) { cluster_arrive(); cluster_wait(); } else { __syncthreads(); }
+    if (warp == 4) {
+        tc_fence_after_sync();
+        tmem_dealloc<CG>(tmem, TMEM_COLS);
+    }
+}
+
+// ---- host side ---------------------------------------------------------------
+
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver entry point is looked up through the runtime so that the library
+// loads (and exports its symbols) on a machine without a CUDA driver.
+EncodeTiled encode_tiled() {
+    static EncodeTiled fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q{};
+        cuda_check(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q));
+        if (!p || q != cudaDriverEntryPointSuccess) throw std::runtime_error("cuTensorMapEncodeTiled is unavailable");
+        return reinterpret_cast<EncodeTiled>(p);
+    }();
+    return fn;
+}
+
+CUtensorMap make_map_2d(CUtensorMapDataType type, const void* ptr, uint64_t inner, uint64_t outer,
+                        uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer,
+                        CUtensorMapSwizzle swizzle, CUtensorMapL2promotion promo) {
+    CUtensorMap map{};
+    const cuuint64_t shape[2] = {inner, outer};
+    const cuuint64_t strides[1] = {row_stride_bytes};
+    const cuuint32_t box[2] = {box_inner, box_outer};
+    const cuuint32_t steps[2] = {1, 1};
+    const CUresult r = encode_tiled()(&map, type, 2, const_cast<void*>(ptr), shape, strides, box, steps,
+                                      CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, promo,
+                                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled failed with code " + std::to_string(int(r)));
+    return map;
+}
+
+// Packed operand [rows, K/2] bytes, tiles of `box_rows` rows x 128 bytes, 128-byte swizzle.
+CUtensorMap operand_map(const uint8_t* p, int rows, int K, int box_rows) {
+    return make_map_2d(CU_TENSOR_MAP_DATA_TYPE_UINT8, p, uint64_t(K / 2), uint64_t(rows), uint64_t(K / 2),
+                       ROW_BYTES, uint32_t(box_rows), CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+}
+// The scale bytes seen as rows of 128 bytes: four rows per atom, the four atoms
+// of a K=256 step consecutive, so one 16-row box is one stage's 2 KiB.
+CUtensorMap scale_map(const uint8_t* p, int rows, int K) {
+    const uint64_t total = uint64_t(rows) * uint64_t(K / 16);
+    return make_map_2d(CU_TENSOR_MAP_DATA_TYPE_UINT8, p, 128, total / 128, 128, 128, 16,
+                       CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+}
+CUtensorMap output_map(const __half* C, int M, int N) {
+    return make_map_2d(CU_TENSOR_MAP_DATA_TYPE_FLOAT16, C, uint64_t(N), uint64_t(M), uint64_t(N) * 2,
+                       EPI_COLS, 32, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE);
+}
+
+template <int CG, int UN>
+int max_units(int device) {
+    using Cfg = Config<CG, UN>;
+    static int cached[64] = {};
+    if (device < 64 && cached[device]) return cached[device];
+    auto kernel = nvfp4_gemm_kernel<CG, UN>;
+    cuda_check(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+    int sms = 0;
+    cuda_check(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+    int units = sms;
+    if (CG == 2) {
+        cudaLaunchAttribute attr{};
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim = {2, 1, 1};
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(unsigned(sms / 2) * 2);
+        cfg.blockDim = dim3(NUM_THREADS);
+        cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int clusters = 0;
+        cuda_check(cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg));
+        units = clusters;
+    }
+    if (units < 1) throw std::runtime_error("nvfp4 gemm: the kernel does not fit on this device");
+    if (device < 64) cached[device] = units;
+    return units;
+}
+
+template <int CG, int UN>
+void launch_variant(const gpu_kernels::Nvfp4Params& p, const CUtensorMap& tmC, uint32_t* status, cudaStream_t stream) {
+    using Cfg = Config<CG, UN>;
+    GemmArgs g{p.M, p.N, p.K, p.M / Cfg::TILE_M, p.N / UN, std::max(1, p.group_m), p.alpha, status};
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim = {unsigned(CG), 1, 1};
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(unsigned(p.clusters) * CG);
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cfg.stream = stream;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    cuda_check(cudaLaunchKernelEx(&cfg, nvfp4_gemm_kernel<CG, UN>, p.A, p.B, p.SFA, p.SFB, tmC, g));
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+}
+
+uint32_t* status_word(int device) {
+    static std::mutex lock;
+    static uint32_t* cached[64] = {};
+    std::lock_guard<std::mutex> hold(lock);
+    if (device < 64 && cached[device]) return cached[device];
+    uint32_t* p = nullptr;
+    cuda_check(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_status));
+    if (device < 64) cached[device] = p;
+    return p;
+}
+
+int env_int(const char* name, int fallback) {
+    const char* v = std::getenv(name);
+    return v && *v ? std::atoi(v) : fallback;
+}
+
+void prepare(gpu_kernels::Nvfp4Params& p, const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB,
+             int M, int N, int K, cudaStream_t) {
+    require_sm100();
+    if (M <= 0 || N <= 0 || K <= 0) throw std::invalid_argument("nvfp4 gemm: M, N, K must be positive");
+    if (M % 128 || N % 128) throw std::invalid_argument("nvfp4 gemm: M and N must be multiples of 128");
+    if (K % STAGE_K) throw std::invalid_argument("nvfp4 gemm: K must be a multiple of 256");
+    if (!A || !B || !SFA || !SFB) throw std::invalid_argument("nvfp4 gemm: null operand pointer");
+    if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(SFA) |
+         reinterpret_cast<uintptr_t>(SFB)) & 15)
+        throw std::invalid_argument("nvfp4 gemm: operand pointers must be 16-byte aligned");
+    int device = 0;
+    cuda_check(cudaGetDevice(&device));
+    p.M = M; p.N = N; p.K = K;
+    p.alpha = 1.0f;
+    p.device = device;
+    const int force = env_int("NVFP4_B200_VARIANT", 0);        // 0 auto, 2256 / 1256 / 1128 for experiments
+    if ((force == 0 && M % 256 == 0 && N % 256 == 0) || force == 2256) { p.cta_group = 2; p.tile_n = 256; }
+    else if ((force == 0 && N % 256 == 0) || force == 1256) { p.cta_group = 1; p.tile_n = 256; }
+    else { p.cta_group = 1; p.tile_n = 128; }
+    if (M % (128 * p.cta_group) || N % p.tile_n) throw std::invalid_argument("nvfp4 gemm: forced variant does not divide the shape");
+    const int box_b = p.tile_n / p.cta_group;
+    p.A = operand_map(A, M, K, BLOCK_M);
+    p.B = operand_map(B, N, K, box_b);
+    p.SFA = scale_map(SFA, M, K);
+    p.SFB = scale_map(SFB, N, K);
+    const int tiles = (M / (128 * p.cta_group)) * (N / p.tile_n);
+    const int fit = p.cta_group == 2 ? max_units<2, 256>(device)
+                  : p.tile_n == 256 ? max_units<1, 256>(device) : max_units<1, 128>(device);
+    p.clusters = std::min(fit, tiles);
+    // About sqrt(units) tile rows per band keeps the A and B panels of the tiles in flight balanced.
+    int gm = 1;
+    while ((gm + 1) * (gm + 1) <= p.clusters) ++gm;
+    p.group_m = std::max(1, std::min(env_int("NVFP4_B200_GROUP_M", gm), M / (128 * p.cta_group)));
+    (void)status_word(device);
+}
+
+void launch(const gpu_kernels::Nvfp4Params& p, __half* C, cudaStream_t stream) {
+    if (!C || (reinterpret_cast<uintptr_t>(C) & 15)) throw std::invalid_argument("nvfp4 gemm: C must be 16-byte aligned");
+    const CUtensorMap tmC = output_map(C, p.M, p.N);
+    uint32_t* status = status_word(p.device);
+    if (p.cta_group == 2) launch_variant<2, 256>(p, tmC, status, stream);
+    else if (p.tile_n == 256) launch_variant<1, 256>(p, tmC, status, stream);
+    else launch_variant<1, 128>(p, tmC, status, stream);
+}
+
+void validate() {
+    cuda_check(cudaDeviceSynchronize());
+    uint32_t host[4] = {};
+    cuda_check(cudaMemcpyFromSymbol(host, g_status, sizeof(host)));
+    if (host[0]) {
+        const uint32_t zero[4] = {};
+        cuda_check(cudaMemcpyToSymbol(g_status, zero, sizeof(zero)));
+        char msg[160];
+        std::snprintf(msg, sizeof(msg), "nvfp4 gemm: a device wait gave up (status 0x%x, first tag 0x%08x); output is invalid",
+                      host[0], host[1]);
+        throw std::runtime_error(msg);
+    }
+}
+
+}  // namespace
+
+void require_sm100() {
+    int device = 0, major = 0;
+    cuda_check(cudaGetDevice(&device));
+    cuda_check(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
+    if (major != 10) throw std::runtime_error("this library only runs on compute capability 10.x (B200); there is no fallback");
+}
+
+int gemm_stage_count(int cta_group, int tile_n) {
+    return cta_group == 2 ? Config<2, 256>::STAGES : tile_n == 256 ? Config<1, 256>::STAGES : Config<1, 128>::STAGES;
+}
+
+}  // namespace nvfp4_b200
+
+namespace gpu_kernels {
+
+Nvfp4Implementation nvfp4_sm100_implementation() {
+    return {nvfp4_b200::prepare, nvfp4_b200::launch, nvfp4_b200::validate};
+}
+
+void nvfp4_set_alpha(Nvfp4Params& p, float alpha) { p.alpha = alpha; }
+
+}  // namespace gpu_kernels

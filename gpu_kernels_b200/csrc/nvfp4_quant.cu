@@ -1,0 +1,220 @@
+// NVFP4 quantise / pack and dequantise kernels for sm_100a.
+//
+// quantise: x[rows, K] (bf16 / fp16 / fp32) -> packed E2M1 [rows, K/2] plus one
+// UE4M3 scale per 16 values, written directly in the 128-row x 4-block scale
+// atoms that cuBLASLt's VEC16 mode and the tcgen05 block-scaled MMA read.
+// Arithmetic follows the reference's PyTorch quantiser step by step
+// (reference/python/nvfp4.py:30-37 and :6-14): amax -> IEEE divide by 6 ->
+// clamp [2^-9, 448] -> E4M3 nearest-even -> IEEE divide -> E2M1 nearest-even
+// with sign bit (q < 0). The kernel is HBM-bound: 2 B read (bf16) and 0.5625 B
+// written per value; a CTA owns a 128-row x 256-column tile so that each scale
+// atom (512 B) and each packed row segment (128 B) leaves in full lines.
+#include "nvfp4_internal.h"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+namespace nvfp4_b200 {
+namespace {
+
+constexpr int Q_ROWS = 128;      // rows per CTA tile = rows of one scale atom
+constexpr int Q_COLS = 256;      // K values per CTA tile = 16 scale blocks = 4 atoms
+constexpr int Q_THREADS = 256;
+
+// E4M3 byte of t, t already clamped to [2^-9, 448]; nearest-even in both the
+// normal range (3 mantissa bits) and the subnormal range (step 2^-9).
+__device__ __forceinline__ uint32_t ue4m3_from_float(float t) {
+    if (t < 0.015625f) return static_cast<uint32_t>(__float2int_rn(t * 512.0f));
+    const uint32_t b = __float_as_uint(t);
+    return ((b + 0x7FFFFu + ((b >> 20) & 1u)) >> 20) - (120u << 3);
+}
+
+__device__ __forceinline__ float ue4m3_to_float(uint32_t code) {
+    if (code < 8u) return static_cast<float>(code) * 0.001953125f;
+    return __uint_as_float((((code >> 3) + 120u) << 23) | ((code & 7u) << 20));
+}
+
+// Number of midpoints below |q|, a value on a midpoint going to the even code.
+__device__ __forceinline__ uint32_t e2m1_from_float(float q) {
+    const float m = fabsf(q);
+    const uint32_t code = (m > 0.25f) + (m >= 0.75f) + (m > 1.25f) + (m >= 1.75f) +
+                          (m > 2.5f) + (m >= 3.5f) + (m > 5.0f);
+    return code | (q < 0.0f ? 8u : 0u);
+}
+
+template <typename T> struct Loader;
+template <> struct Loader<__nv_bfloat16> {
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[16]) {
+        const uint4 a = __ldg(reinterpret_cast<const uint4*>(p));
+        const uint4 b = __ldg(reinterpret_cast<const uint4*>(p) + 1);
+        const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        #pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            v[2 * i] = __uint_as_float(w[i] << 16);
+            v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+        }
+    }
+};
+template <> struct Loader<__half> {
+    static __device__ __forceinline__ void load(const __half* p, float (&v)[16]) {
+        const uint4 a = __ldg(reinterpret_cast<const uint4*>(p));
+        const uint4 b = __ldg(reinterpret_cast<const uint4*>(p) + 1);
+        const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        #pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+            v[2 * i] = f.x;
+            v[2 * i + 1] = f.y;
+        }
+    }
+};
+template <> struct Loader<float> {
+    static __device__ __forceinline__ void load(const float* p, float (&v)[16]) {
+        #pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float4 f = __ldg(reinterpret_cast<const float4*>(p) + i);
+            v[4 * i] = f.x; v[4 * i + 1] = f.y; v[4 * i + 2] = f.z; v[4 * i + 3] = f.w;
+        }
+    }
+};
+
+// One 16-value block: returns the scale byte, writes the 8 packed bytes.
+__device__ __forceinline__ uint32_t quantise_block(const float (&v)[16], uint2& packed) {
+    float amax = 0.0f;
+    bool nan = false;
+    #pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        amax = fmaxf(amax, fabsf(v[i]));
+        nan |= (v[i] != v[i]);
+    }
+    if (nan) {
+        // A NaN poisons the block exactly as it does in the reference: NaN scale
+        // byte, and every element compares above all midpoints with sign 0.
+        packed = make_uint2(0x77777777u, 0x77777777u);
+        return 0x7Fu;
+    }
+    const float t = fminf(fmaxf(__fdiv_rn(amax, 6.0f), 0.001953125f), 448.0f);
+    const uint32_t sbyte = ue4m3_from_float(t);
+    const float s = ue4m3_to_float(sbyte);
+    uint32_t lo = 0, hi = 0;
+    #pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        lo |= e2m1_from_float(__fdiv_rn(v[i], s)) << (4 * i);
+        hi |= e2m1_from_float(__fdiv_rn(v[8 + i], s)) << (4 * i);
+    }
+    packed = make_uint2(lo, hi);
+    return sbyte;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(Q_THREADS)
+quantise_kernel(const T* __restrict__ x, uint8_t* __restrict__ packed, uint8_t* __restrict__ scales,
+                int rows, int K) {
+    __shared__ __align__(16) uint8_t sf_tile[4 * 512];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int kb = lane & 15;                                 // 16-value block inside the tile
+    const int col0 = blockIdx.x * Q_COLS;
+    const int row_base = blockIdx.y * Q_ROWS;
+    const int k = col0 + kb * 16;
+    const bool live = k < K;                                   // K is a multiple of 64, the tile of 256
+    #pragma unroll 2
+    for (int pass = 0; pass < 8; pass += 4) {
+        float v[4][16];
+        #pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int r = (pass + u) * 16 + warp * 2 + (lane >> 4);
+            if (live) Loader<T>::load(x + size_t(row_base + r) * K + k, v[u]);
+        }
+        #pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int r = (pass + u) * 16 + warp * 2 + (lane >> 4);
+            if (live) {
+                uint2 out;
+                const uint32_t sbyte = quantise_block(v[u], out);
+                *reinterpret_cast<uint2*>(packed + size_t(row_base + r) * (K / 2) + k / 2) = out;
+                sf_tile[(kb >> 2) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (kb & 3)] = static_cast<uint8_t>(sbyte);
+            }
+        }
+    }
+    __syncthreads();
+    // The tile's atoms are consecutive in the VEC16 layout: one 16-byte store per thread.
+    const int atoms = min(4, (K - col0) / 64);
+    if (threadIdx.x < atoms * 32) {
+        const size_t first_atom = size_t(blockIdx.y) * (K / 64) + size_t(blockIdx.x) * 4;
+        reinterpret_cast<uint4*>(scales + first_atom * 512)[threadIdx.x] =
+            reinterpret_cast<const uint4*>(sf_tile)[threadIdx.x];
+    }
+}
+
+// packed + scales -> FP32 [rows, K]; one thread per 16-value block
+// (reference/python/nvfp4.py:40-47).
+__global__ void __launch_bounds__(256)
+dequantise_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ scales,
+                  float* __restrict__ out, int rows, int K) {
+    const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    const int blocks_per_row = K / 16;
+    if (idx >= size_t(rows) * blocks_per_row) return;
+    const int r = static_cast<int>(idx / blocks_per_row), b = static_cast<int>(idx % blocks_per_row);
+    const size_t off = (size_t(r / 128) * (K / 64) + b / 4) * 512 + (r % 32) * 16 + ((r % 128) / 32) * 4 + b % 4;
+    const uint32_t sb = scales[off];
+    // 0x7F / 0xFF are NaN in E4M3 (finite-only format); the quantiser never sets the sign bit.
+    float s = (sb & 0x7Fu) == 0x7Fu ? __uint_as_float(0x7FC00000u) : ue4m3_to_float(sb & 0x7Fu);
+    if (sb & 0x80u) s = -s;
+    const uint2 p = __ldg(reinterpret_cast<const uint2*>(packed + size_t(r) * (K / 2) + b * 8));
+    const uint32_t w[2] = {p.x, p.y};
+    float4* dst = reinterpret_cast<float4*>(out + size_t(r) * K + b * 16);
+    #pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        float f[8];
+        #pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t c = (w[h] >> (4 * i)) & 15u;
+            const uint32_t m = c & 7u;
+            // levels 0, .5, 1, 1.5, 2, 3, 4, 6
+            const float level = m < 2u ? 0.5f * m : __uint_as_float(((126u + (m >> 1)) << 23) | ((m & 1u) << 22));
+            f[i] = level * (1.0f - 2.0f * static_cast<float>(c >> 3)) * s;
+        }
+        dst[2 * h] = make_float4(f[0], f[1], f[2], f[3]);
+        dst[2 * h + 1] = make_float4(f[4], f[5], f[6], f[7]);
+    }
+}
+
+}  // namespace
+
+void check_quant_shape(int rows, int K) {
+    if (rows <= 0 || K <= 0) throw std::invalid_argument("nvfp4 quantise: rows and K must be positive");
+    if (rows % 128 != 0) throw std::invalid_argument("nvfp4 quantise: rows must be a multiple of 128");
+    if (K % 64 != 0) throw std::invalid_argument("nvfp4 quantise: K must be a multiple of 64");
+}
+
+void quantise(const void* x, int dtype, uint8_t* packed, uint8_t* scales, int rows, int K, cudaStream_t stream) {
+    check_quant_shape(rows, K);
+    if (!x || !packed || !scales) throw std::invalid_argument("nvfp4 quantise: null pointer");
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(packed) | reinterpret_cast<uintptr_t>(scales)) & 15)
+        throw std::invalid_argument("nvfp4 quantise: pointers must be 16-byte aligned");
+    const dim3 grid((K + Q_COLS - 1) / Q_COLS, rows / Q_ROWS);
+    switch (dtype) {
+        case DTYPE_BF16:
+            quantise_kernel<<<grid, Q_THREADS, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), packed, scales, rows, K);
+            break;
+        case DTYPE_F16:
+            quantise_kernel<<<grid, Q_THREADS, 0, stream>>>(static_cast<const __half*>(x), packed, scales, rows, K);
+            break;
+        case DTYPE_F32:
+            quantise_kernel<<<grid, Q_THREADS, 0, stream>>>(static_cast<const float*>(x), packed, scales, rows, K);
+            break;
+        default:
+            throw std::invalid_argument("nvfp4 quantise: dtype must be 0 (bf16), 1 (fp16) or 2 (fp32)");
+    }
+    cuda_check(cudaGetLastError());
+}
+
+void dequantise(const uint8_t* packed, const uint8_t* scales, float* out, int rows, int K, cudaStream_t stream) {
+    check_quant_shape(rows, K);
+    if (!packed || !scales || !out) throw std::invalid_argument("nvfp4 dequantise: null pointer");
+    const size_t blocks = size_t(rows) * (K / 16);
+    dequantise_kernel<<<static_cast<unsigned>((blocks + 255) / 256), 256, 0, stream>>>(packed, scales, out, rows, K);
+    cuda_check(cudaGetLastError());
+}
+
+}  // namespace nvfp4_b200

@@ -1,0 +1,101 @@
+"""NVFP4 block-scaled GEMM plans (C[M,N] fp16 = alpha * A @ B.T on packed E2M1 operands).
+
+`Nvfp4Gemm` wraps the plan calls the reference's harness makes
+(benchmarks/nvfp4.py:52-66: plan_create / custom / cublas / validate / destroy)
+with the same argument meaning: operands are baked into the plan and must stay
+alive; `run(C)` is asynchronous on the current stream and capture-safe;
+`validate()` synchronises and raises if the kernel reported an error.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+class Nvfp4Gemm:
+    def __init__(self, a_packed, b_packed, sfa, sfb, alpha: float = 1.0, workspace: torch.Tensor | None = None):
+        for name, t in (("a_packed", a_packed), ("b_packed", b_packed), ("sfa", sfa), ("sfb", sfb)):
+            if not (t.is_cuda and t.dtype == torch.uint8 and t.is_contiguous()):
+                raise ValueError(f"{name} must be a contiguous CUDA uint8 tensor")
+        self.m, half_k = a_packed.shape
+        self.n, half_kb = b_packed.shape
+        if half_k != half_kb:
+            raise ValueError("A and B disagree on K")
+        self.k = 2 * half_k
+        if sfa.numel() != self.m * self.k // 16 or sfb.numel() != self.n * self.k // 16:
+            raise ValueError("scale tensors must hold rows*K/16 bytes")
+        self._keep = (a_packed, b_packed, sfa, sfb, workspace)
+        self.device = a_packed.device
+        self._plan = ctypes.c_void_p()
+        lib = _lib.load()
+        with torch.cuda.device(self.device):
+            _lib.check(lib.gpu_kernels_nvfp4_plan_create(
+                ctypes.byref(self._plan), self.m, self.n, self.k, a_packed.data_ptr(), b_packed.data_ptr(),
+                sfa.data_ptr(), sfb.data_ptr(),
+                workspace.data_ptr() if workspace is not None else None,
+                workspace.numel() if workspace is not None else 0, _stream()))
+        if alpha != 1.0:
+            self.set_alpha(alpha)
+
+    def set_alpha(self, alpha: float) -> None:
+        _lib.check(_lib.load().gpu_kernels_nvfp4_plan_set_alpha(self._plan, float(alpha)))
+
+    def set_option(self, key: str, value: int) -> None:
+        _lib.check(_lib.load().gpu_kernels_nvfp4_plan_set_option(self._plan, key.encode(), int(value)))
+
+    def info(self) -> dict:
+        buf = (ctypes.c_int * 8)()
+        _lib.check(_lib.load().gpu_kernels_nvfp4_plan_info(self._plan, buf))
+        keys = ("M", "N", "K", "units", "cta_group", "tile_n", "group_m", "stages")
+        return dict(zip(keys, list(buf)))
+
+    def run(self, out: torch.Tensor | None = None) -> torch.Tensor:
+        if out is None:
+            out = torch.empty((self.m, self.n), dtype=torch.float16, device=self.device)
+        if not (out.is_cuda and out.dtype == torch.float16 and out.is_contiguous() and out.shape == (self.m, self.n)):
+            raise ValueError("out must be a contiguous CUDA fp16 tensor [M, N]")
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.load().gpu_kernels_nvfp4_custom(self._plan, out.data_ptr(), _stream()))
+        return out
+
+    def run_cublaslt(self, out: torch.Tensor) -> torch.Tensor:
+        """cuBLASLt's NVFP4 matmul on the same operands (comparison only)."""
+        a, b = self._keep[0], self._keep[1]
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.load().gpu_kernels_nvfp4_cublas(self._plan, out.data_ptr(), a.data_ptr(), b.data_ptr(), _stream()))
+        return out
+
+    def validate(self) -> None:
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.load().gpu_kernels_nvfp4_validate(self._plan))
+
+    def close(self) -> None:
+        if self._plan:
+            _lib.load().gpu_kernels_nvfp4_plan_destroy(self._plan)
+            self._plan = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def gemm_host(a_packed, b_packed, sfa, sfb, out, alpha: float = 1.0) -> torch.Tensor:
+    """End-to-end GEMM on HOST tensors (pinned memory recommended): H2D, kernel, D2H, synchronised."""
+    for t in (a_packed, b_packed, sfa, sfb, out):
+        if t.is_cuda or not t.is_contiguous():
+            raise ValueError("gemm_host takes contiguous host tensors")
+    m, half_k = a_packed.shape
+    n = b_packed.shape[0]
+    _lib.check(_lib.load().gpu_kernels_nvfp4_gemm_host(
+        m, n, 2 * half_k, a_packed.data_ptr(), b_packed.data_ptr(), sfa.data_ptr(), sfb.data_ptr(),
+        out.data_ptr(), float(alpha), _stream()))
+    return out

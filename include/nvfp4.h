@@ -1,0 +1,61 @@
+// C++ boundary of the B200 NVFP4 block-scaled GEMM.
+//
+// Same names, argument order and ownership rules as the reference's
+// include/nvfp4.h:13-25 (struct Nvfp4Params, struct Nvfp4Implementation,
+// factory nvfp4_sm100_implementation()), so host code written against that
+// header — benchmarks/bindings/nvfp4_bridge.cu:19-21,83-85,115 in the reference
+// — compiles against this one unchanged. The implementation behind it is a
+// different kernel (gpu_kernels_b200/csrc/nvfp4_gemm.cu).
+//
+// Data contract (reference include/nvfp4.h:10-12):
+//   A [M, K/2], B [N, K/2]  packed E2M1, two values per byte, K contiguous,
+//                           even k in the low nibble ("TN": C = A * B^T);
+//   SFA, SFB                one UE4M3 byte per 16 K-values, stored in cuBLASLt's
+//                           VEC16 layout: 512-byte atoms of 128 rows x 4 blocks,
+//                           atoms ordered [row/128][k/64];
+//   C [M, N]                row-major FP16, leading dimension N, overwritten.
+// Extensions the reference does not have: an FP32 global scale `alpha`
+// (C = fp16(alpha * acc), default 1), M that is only a multiple of 128, and a
+// status word that reports a wait that gave up instead of hanging.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+
+namespace gpu_kernels {
+
+// The four tensor maps and the four integers lead the struct exactly as in the
+// reference (callers value-initialise it and never read the rest).
+struct Nvfp4Params {
+    CUtensorMap A, B, SFA, SFB;
+    int M, N, K, clusters;          // clusters = persistent scheduling units in the grid
+    // ---- extensions (filled by prepare) ----
+    float alpha;                    // FP32 global scale applied to the accumulator
+    int cta_group;                  // 2: CTA pairs on 256-row tiles; 1: single CTAs on 128-row tiles
+    int tile_n;                     // columns of C per tile (256 or 128)
+    int group_m;                    // tile rows per rasterisation band
+    int device;                     // device the plan was prepared on
+};
+
+struct Nvfp4Implementation {
+    // Builds descriptors for the given device buffers, which must outlive the
+    // plan. May query the device; never call it during stream capture.
+    // Throws std::invalid_argument on a shape or pointer it cannot serve:
+    // M, N multiples of 128, K a multiple of 256, pointers 16-byte aligned.
+    void (*prepare)(Nvfp4Params&, const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB,
+                    int M, int N, int K, cudaStream_t);
+    // One asynchronous kernel launch on `stream`; safe inside stream capture.
+    void (*launch)(const Nvfp4Params&, __half* C, cudaStream_t);
+    // Synchronises the device and throws std::runtime_error if any launch since
+    // the last call reported a wait that timed out.
+    void (*validate)();
+};
+
+Nvfp4Implementation nvfp4_sm100_implementation();
+
+// Extension: set the FP32 global scale of a prepared plan (takes effect at the next launch).
+void nvfp4_set_alpha(Nvfp4Params&, float alpha);
+
+}  // namespace gpu_kernels

@@ -1,0 +1,228 @@
+"""CUDA NVFP4 GEMM through the C ABI against the CPU oracle (small) and the FP32
+dequantise-then-matmul path on the GPU (full size).
+
+Acceptance (floating point): relative Frobenius error <= 1e-3 and max abs error
+<= 2e-2 x output RMS against the FP32 reference of the same quantised operands.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import nvfp4_oracle as O
+from helpers import assert_gemm_close, random_operand, to_np
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def g():
+    import gpu_kernels_b200
+    torch.backends.cuda.matmul.allow_tf32 = False
+    return gpu_kernels_b200
+
+
+def nan_output(m, n):
+    return torch.full((m, n), float("nan"), device="cuda", dtype=torch.float16)
+
+
+def run_plan(g, pa, sa, pb, sb, alpha=1.0, variant=None, group_m=None):
+    if variant is not None:
+        os.environ["NVFP4_B200_VARIANT"] = str(variant)
+    try:
+        plan = g.Nvfp4Gemm(pa, pb, sa, sb, alpha=alpha)
+    finally:
+        os.environ.pop("NVFP4_B200_VARIANT", None)
+    if group_m is not None:
+        plan.set_option("group_m", group_m)
+    out = plan.run(nan_output(pa.shape[0], pb.shape[0]))
+    plan.validate()
+    info = plan.info()
+    plan.close()
+    return out, info
+
+
+def test_golden_cfg0(g, golden):
+    f = golden("cfg0_256.npz")
+    pa, sa, pb, sb = (torch.from_numpy(f[k]).cuda() for k in ("a_packed", "a_scales", "b_packed", "b_scales"))
+    out, info = run_plan(g, pa, sa, pb, sb)
+    assert info["cta_group"] == 2 and info["tile_n"] == 256
+    assert_gemm_close(out, f["c_f32"], "cfg0 vs frozen reference output")
+    ref16 = torch.from_numpy(f["c_f16"].view(np.float16).copy())
+    # FP16 rounding of nearly equal FP32 sums: the two outputs may differ by one FP16 step on a few elements
+    same = (out.cpu() == ref16).float().mean()
+    assert same > 0.99, f"only {same:.4f} of FP16 outputs identical to the reference's"
+    for variant in (1256, 1128):
+        out_v, info_v = run_plan(g, pa, sa, pb, sb, variant=variant)
+        assert info_v["cta_group"] == 1
+        assert_gemm_close(out_v, f["c_f32"], f"cfg0 variant {variant}")
+
+
+SHAPES = [
+    # (M, N, K, forced variant or None)
+    (256, 256, 256, None),          # one stage, one tile
+    (256, 256, 512, None),
+    (2048, 4096, 2048, None),       # ring wraps, accumulator ping-pong, several tiles per unit
+    (128, 512, 1024, None),         # M = 128: single-CTA tiles of 128 x 256
+    (128, 384, 512, None),          # N only a multiple of 128: 128 x 128 tiles
+    (384, 640, 768, None),
+    (512, 256, 4096, None),
+    (1024, 1024, 1536, 1256),
+    (1024, 1024, 1536, 1128),
+    (4096, 2048, 256, None),        # many tiles, single K step: epilogue-bound
+]
+
+
+@pytest.mark.parametrize("m,n,k,variant", SHAPES)
+def test_shapes_against_oracle(g, m, n, k, variant):
+    a = random_operand(m, k, seed=1 + m + n + k)
+    b = random_operand(n, k, seed=2 + m + n + k, scale=0.02)
+    pa, sa = g.quantize(a)
+    pb, sb = g.quantize(b)
+    out, _ = run_plan(g, pa, sa, pb, sb, variant=variant)
+    ref = O.gemm_f32(to_np(pa), to_np(sa), to_np(pb), to_np(sb))
+    assert_gemm_close(out, ref, f"{m}x{n}x{k}")
+
+
+def test_distinct_scale_everywhere(g):
+    # every (row, K block) has its own scale byte and codes are random nibbles: a wrong
+    # scale column, swizzle or K-slice order cannot cancel out
+    m, n, k = 512, 768, 1024
+    rng = np.random.default_rng(5)
+    pa = rng.integers(0, 256, size=(m, k // 2), dtype=np.uint8)
+    pb = rng.integers(0, 256, size=(n, k // 2), dtype=np.uint8)
+    sa_raw = (40 + (np.arange(m)[:, None] * 7 + np.arange(k // 16)[None, :] * 3) % 24).astype(np.uint8)
+    sb_raw = (36 + (np.arange(n)[:, None] * 5 + np.arange(k // 16)[None, :] * 11) % 28).astype(np.uint8)
+    sa, sb = O.pack_scales(sa_raw), O.pack_scales(sb_raw)
+    ref = O.gemm_f32(pa, sa, pb, sb)
+    for variant in (None, 1256, 1128):
+        out, _ = run_plan(g, *(torch.from_numpy(x).cuda() for x in (pa, sa, pb, sb)), variant=variant)
+        assert_gemm_close(out, ref, f"distinct scales, variant {variant}")
+
+
+def test_alpha_and_group_m(g):
+    m, n, k = 1024, 1536, 512
+    pa, sa = g.quantize(random_operand(m, k, seed=11))
+    pb, sb = g.quantize(random_operand(n, k, seed=12))
+    ref = O.gemm_f32(to_np(pa), to_np(sa), to_np(pb), to_np(sb))
+    base, _ = run_plan(g, pa, sa, pb, sb)
+    assert_gemm_close(base, ref, "alpha 1")
+    scaled, _ = run_plan(g, pa, sa, pb, sb, alpha=0.125)
+    assert torch.equal(scaled, (base.float() * 0.125).half())       # power of two: exact
+    odd, _ = run_plan(g, pa, sa, pb, sb, alpha=0.3)
+    assert_gemm_close(odd, ref * np.float32(0.3), "alpha 0.3")
+    for gm in (1, 2, 3, 100):
+        again, info = run_plan(g, pa, sa, pb, sb, group_m=gm)
+        assert torch.equal(again, base), f"tile order group_m={gm} changed the result"
+
+
+def test_matches_cublaslt(g):
+    m = n = k = 1024
+    pa, sa = g.quantize(random_operand(m, k, seed=21))
+    pb, sb = g.quantize(random_operand(n, k, seed=22))
+    ws = torch.empty(32 << 20, dtype=torch.uint8, device="cuda")
+    plan = g.Nvfp4Gemm(pa, pb, sa, sb, workspace=ws)
+    ours = plan.run(nan_output(m, n))
+    theirs = plan.run_cublaslt(nan_output(m, n))
+    plan.validate()
+    ref = O.gemm_f32(to_np(pa), to_np(sa), to_np(pb), to_np(sb))
+    assert_gemm_close(theirs, ref, "cuBLASLt")
+    assert_gemm_close(ours, ref, "ours")
+    plan.close()
+
+
+def test_plans_of_different_shapes_interleave(g):
+    # per-plan state only: two live plans of different shapes alternate on one stream
+    specs = [(256, 512, 512), (1024, 256, 1024)]
+    plans, refs = [], []
+    for i, (m, n, k) in enumerate(specs):
+        pa, sa = g.quantize(random_operand(m, k, seed=31 + i))
+        pb, sb = g.quantize(random_operand(n, k, seed=41 + i))
+        plans.append(g.Nvfp4Gemm(pa, pb, sa, sb))
+        refs.append(O.gemm_f32(to_np(pa), to_np(sa), to_np(pb), to_np(sb)))
+    outs = [nan_output(m, n) for m, n, _ in specs]
+    for _ in range(3):
+        for plan, out in zip(plans, outs):
+            plan.run(out)
+    for plan, out, ref in zip(plans, outs, refs):
+        plan.validate()
+        assert_gemm_close(out, ref, "interleaved plans")
+        plan.close()
+
+
+def test_graph_capture_replay(g):
+    m = n = k = 512
+    pa, sa = g.quantize(random_operand(m, k, seed=51))
+    pb, sb = g.quantize(random_operand(n, k, seed=52))
+    plan = g.Nvfp4Gemm(pa, pb, sa, sb)
+    out = nan_output(m, n)
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        plan.run(out)
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for _ in range(4):
+                plan.run(out)
+        out.fill_(float("nan"))
+        graph.replay()
+        stream.synchronize()
+    plan.validate()
+    assert_gemm_close(out, O.gemm_f32(to_np(pa), to_np(sa), to_np(pb), to_np(sb)), "graph replay")
+    plan.close()
+
+
+def test_host_entry_point(g):
+    m, n, k = 256, 384, 512
+    pa, sa = g.quantize(random_operand(m, k, seed=61))
+    pb, sb = g.quantize(random_operand(n, k, seed=62))
+    host = [t.cpu().pin_memory() for t in (pa, pb, sa, sb)]
+    out = torch.empty((m, n), dtype=torch.float16).pin_memory()
+    g.gemm_host(*host, out)
+    assert_gemm_close(out, O.gemm_f32(to_np(pa), to_np(sa), to_np(pb), to_np(sb)), "host entry point")
+
+
+def test_argument_errors(g):
+    from gpu_kernels_b200._lib import Nvfp4Error
+    z = lambda *s: torch.zeros(*s, dtype=torch.uint8, device="cuda")
+    with pytest.raises(Nvfp4Error):          # K not a multiple of 256
+        g.Nvfp4Gemm(z(128, 64), z(128, 64), z(128 * 8), z(128 * 8))
+    with pytest.raises(Nvfp4Error):          # M not a multiple of 128
+        g.Nvfp4Gemm(z(64, 128), z(128, 128), z(64 * 16), z(128 * 16))
+    with pytest.raises(ValueError):
+        g.Nvfp4Gemm(z(128, 128), z(128, 256), z(128 * 16), z(128 * 32))
+
+
+def fp32_reference_on_gpu(g, pa, sa, pb, sb):
+    """The reference's check (dequantise both operands, FP32 matmul) at full size on the GPU.
+    The dequantise kernel is itself pinned bit-exactly to the oracle in test_quantize_gpu.py."""
+    return g.dequantize(pa, sa) @ g.dequantize(pb, sb).T
+
+
+@pytest.mark.parametrize("size", [8192, 16384])
+def test_full_size_square(g, size):
+    a = random_operand(size, size, seed=0)
+    b = random_operand(size, size, seed=1)
+    pa, sa = g.quantize(a)
+    pb, sb = g.quantize(b)
+    del a, b
+    out, info = run_plan(g, pa, sa, pb, sb)
+    assert info["cta_group"] == 2
+    ref = fp32_reference_on_gpu(g, pa, sa, pb, sb)
+    assert_gemm_close(out, ref, f"{size}^3 vs FP32 dequantise-then-matmul")
+    if size == 8192:
+        # 64 sampled rows against the CPU oracle too
+        rows = torch.arange(0, size, 128)[:64] + torch.arange(64) % 128
+        a_rows = O.dequantize(to_np(pa), to_np(sa))[rows.numpy()]
+        b_all = O.dequantize(to_np(pb), to_np(sb))
+        assert_gemm_close(out[rows.cuda()], a_rows @ b_all.T, "8192^3 sampled rows vs CPU oracle")
+
+
+def test_full_size_skinny(g):
+    m, n, k = 128, 28672, 8192
+    pa, sa = g.quantize(random_operand(m, k, seed=0))
+    pb, sb = g.quantize(random_operand(n, k, seed=1, scale=0.02))
+    out, info = run_plan(g, pa, sa, pb, sb)
+    assert info["cta_group"] == 1
+    assert_gemm_close(out, fp32_reference_on_gpu(g, pa, sa, pb, sb), "skinny vs FP32 dequantise-then-matmul")

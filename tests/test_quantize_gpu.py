@@ -1,0 +1,122 @@
+"""CUDA quantiser / dequantiser against the oracle and the frozen reference outputs: bit-exact."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import nvfp4_oracle as O
+from helpers import bf16_from_bits, random_operand, to_np
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def g():
+    import gpu_kernels_b200
+    return gpu_kernels_b200
+
+
+def check_exact(g, x: torch.Tensor, expect_packed, expect_scales):
+    packed, scales = g.quantize(x)
+    torch.cuda.synchronize()
+    assert np.array_equal(to_np(scales), expect_scales), "scale bytes differ"
+    assert np.array_equal(to_np(packed), expect_packed), "packed codes differ"
+    return packed, scales
+
+
+def test_golden_cfg0(g, golden):
+    f = golden("cfg0_256.npz")
+    for name in ("a", "b"):
+        p, s = check_exact(g, bf16_from_bits(f[f"{name}_bf16"]), f[f"{name}_packed"], f[f"{name}_scales"])
+    d = g.dequantize(p, s)
+    assert np.array_equal(to_np(d), O.dequantize(f["b_packed"], f["b_scales"]))
+    pa = torch.from_numpy(f["a_packed"]).cuda()
+    sa = torch.from_numpy(f["a_scales"]).cuda()
+    assert np.array_equal(to_np(g.dequantize(pa, sa)), f["a_dequant"])
+
+
+def test_golden_distributions(g, golden):
+    f = golden("dists.npz")
+    check_exact(g, bf16_from_bits(f["w_bf16"]), f["w_packed"], f["w_scales"])
+    check_exact(g, torch.from_numpy(f["f_f32"]).cuda(), f["f_packed"], f["f_scales"])
+
+
+def test_golden_adversarial(g, golden):
+    f = golden("adversarial.npz")
+    p, s = check_exact(g, torch.from_numpy(f["x_f32"]).cuda(), f["packed"], f["scales"])
+    d = to_np(g.dequantize(p, s))
+    assert np.array_equal(np.isnan(d), np.isnan(f["dequant"]))
+    assert np.array_equal(np.nan_to_num(d), np.nan_to_num(f["dequant"]))
+
+
+def test_reference_known_answers(g):
+    # tests/test_nvfp4.py:30-35 of the reference, through the CUDA path
+    values = torch.tensor([0, .5, 1, 1.5, 2, 3, 4, 6, 0, -.5, -1, -1.5, -2, -3, -4, -6]).repeat(128, 4).cuda()
+    packed, scales = g.quantize(values)
+    assert packed[0, :8].tolist() == [0x10, 0x32, 0x54, 0x76, 0x90, 0xBA, 0xDC, 0xFE]
+    assert torch.equal(g.dequantize(packed, scales), values)
+    # tests/test_nvfp4.py:12-15: every code and every tie, one value per block so the scale is known
+    x = torch.zeros(128, 64 * 18)
+    probes = [0, .5, 1, 1.5, 2, 3, 4, 6, -.5, -6, .25, .75, 1.25, 1.75, 2.5, 3.5, 5, 100]
+    for i, v in enumerate(probes):
+        x[:, i * 64 + 1] = v
+        x[:, i * 64] = 6.0 if abs(v) <= 6 else 0.0          # pins the scale to 1.0 (except the saturating probe)
+    p, s = O.quantize(x.numpy())
+    check_exact(g, x.cuda(), p, s)
+    codes = p[0, 0::32] >> 4
+    assert codes[:17].tolist() == [0, 1, 2, 3, 4, 5, 6, 7, 9, 15, 0, 2, 2, 4, 4, 6, 6]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("rows,k,scale", [(128, 64, 1.0), (256, 192, 0.02), (384, 320, 30.0), (1024, 2048, 1.0),
+                                          (128, 8192, 1e-3)])
+def test_random_against_oracle(g, dtype, rows, k, scale):
+    x = random_operand(rows, k, seed=rows + k, scale=scale, dtype=dtype)
+    p, s = O.quantize(to_np(x.float()))
+    packed, scales = check_exact(g, x, p, s)
+    assert np.array_equal(to_np(g.dequantize(packed, scales)), O.dequantize(p, s))
+
+
+def test_every_bf16_value(g):
+    # all 65536 bf16 bit patterns (NaNs and infinities included), one per block position in turn
+    bits = np.arange(65536, dtype=np.uint16)
+    x = np.zeros((128, 65536 // 128 * 16), dtype=np.uint16)         # 512 blocks per row
+    x.reshape(128, -1, 16)[:, :, 3] = bits.reshape(128, 512)
+    x.reshape(128, -1, 16)[:, :, 7] = 0x3F80                        # a 1.0 beside it
+    xt = bf16_from_bits(x)
+    p, s = O.quantize(O.bf16_to_f32(x))
+    check_exact(g, xt, p, s)
+
+
+def test_full_size_slabs_match_oracle(g):
+    # 8192 x 8192 (the benchmark operand): 128-row slabs are independent, so random slabs pin the whole
+    x = random_operand(8192, 8192, seed=0)
+    packed, scales = g.quantize(x)
+    torch.cuda.synchronize()
+    rng = np.random.default_rng(0)
+    for blk in rng.choice(64, size=5, replace=False):
+        rows = slice(blk * 128, (blk + 1) * 128)
+        p, s = O.quantize(to_np(x[rows].float()))
+        assert np.array_equal(to_np(packed[rows]), p)
+        assert np.array_equal(to_np(scales[blk * 128 * 512:(blk + 1) * 128 * 512]), s)
+    # size-independent properties over every element: the scale is the E4M3 rounding of
+    # clamp(amax/6), and each code is a nearest E2M1 level of x / scale.
+    xf = x.float()
+    amax = xf.reshape(8192, -1, 16).abs().amax(-1)
+    want_scale = (amax / 6).clamp(min=2 ** -9, max=448).to(torch.float8_e4m3fn)
+    got_scale = g.unpack_scales(scales, 8192, 8192)
+    assert torch.equal(got_scale, want_scale.view(torch.uint8))
+    levels = torch.tensor([0, .5, 1, 1.5, 2, 3, 4, 6], device="cuda")
+    q = (xf.reshape(8192, -1, 16) / want_scale.float()[..., None]).reshape(8192, 8192)
+    codes = torch.stack((packed & 15, packed >> 4), dim=-1).reshape(8192, 8192)
+    chosen = levels[(codes & 7).long()]
+    best = (q.abs()[..., None] - levels).abs().amin(-1)
+    assert torch.equal((q.abs() - chosen).abs(), best)
+    assert torch.equal((codes >> 3).bool(), q < 0)
+
+
+def test_shape_errors(g):
+    from gpu_kernels_b200._lib import Nvfp4Error
+    with pytest.raises(Nvfp4Error):
+        g.quantize(torch.zeros(100, 64, device="cuda"))
+    with pytest.raises(Nvfp4Error):
+        g.quantize(torch.zeros(128, 48, device="cuda"))
