@@ -28,6 +28,8 @@ SIGNATURES = {
     "gpu_kernels_nvfp4_plan_set_alpha": ([P, F], I),
     "gpu_kernels_nvfp4_plan_set_option": ([P, ctypes.c_char_p, I], I),
     "gpu_kernels_nvfp4_plan_info": ([P, ctypes.POINTER(I)], I),
+    "gpu_kernels_nvfp4_plan_profile": ([P, P, P, ctypes.POINTER(ctypes.c_ulonglong), I, ctypes.POINTER(I)], I),
+    "gpu_kernels_nvfp4_last_kernel_cycles": ([], ctypes.c_uint),
     "gpu_kernels_nvfp4_gemm_host": ([I, I, I, P, P, P, P, P, F, P], I),
     "gpu_kernels_nvfp4_version": ([], ctypes.c_char_p),
     "gpu_kernels_nvfp4_launch_count": ([], ctypes.c_ulonglong),

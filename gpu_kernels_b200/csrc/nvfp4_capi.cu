@@ -17,6 +17,8 @@
 namespace nvfp4_b200 {
 extern std::atomic<unsigned long long> g_launches;
 int gemm_stage_count(int cta_group, int tile_n);
+unsigned last_kernel_cycles();
+int gemm_profile(const gpu_kernels::Nvfp4Params& p, __half* C, cudaStream_t stream, unsigned long long* host, int max_words);
 }
 
 namespace {
@@ -214,6 +216,11 @@ int gpu_kernels_nvfp4_plan_set_option(void* plan, const char* key, int value) {
             const int tiles_m = p.params.M / (128 * p.params.cta_group);
             if (value < 1) throw std::invalid_argument("set_option: group_m must be >= 1");
             p.params.group_m = value < tiles_m ? value : tiles_m;
+        } else if (std::strcmp(key, "prefetch") == 0) {
+            if (value < 0 || value > 64) throw std::invalid_argument("set_option: prefetch must be in 0..64");
+            p.params.prefetch = value;
+        } else if (std::strcmp(key, "c_evict_first") == 0) {
+            p.params.c_evict_first = value ? 1 : 0;
         } else {
             throw std::invalid_argument(std::string("set_option: unknown key ") + key);
         }
@@ -264,6 +271,22 @@ int gpu_kernels_nvfp4_gemm_host(int M, int N, int K, const void* A, const void* 
         cuda_check(cudaMemcpyAsync(C, h.C, c_bytes, cudaMemcpyDeviceToHost, stream));
         cuda_check(cudaStreamSynchronize(stream));
     });
+}
+
+int gpu_kernels_nvfp4_plan_profile(void* plan, void* C, void* stream, unsigned long long* counters, int max_words,
+                                   int* words_written) {
+    return guarded([&] {
+        Plan& p = as_plan(plan);
+        if (!counters || !words_written) throw std::invalid_argument("plan_profile: null output");
+        *words_written = nvfp4_b200::gemm_profile(p.params, static_cast<__half*>(C), static_cast<cudaStream_t>(stream),
+                                                  counters, max_words);
+    });
+}
+
+unsigned gpu_kernels_nvfp4_last_kernel_cycles(void) {
+    unsigned cycles = 0;
+    guarded([&] { cycles = nvfp4_b200::last_kernel_cycles(); });
+    return cycles;
 }
 
 const char* gpu_kernels_nvfp4_version(void) { return "nvfp4-b200 0.1 (sm_100a)"; }

@@ -2,8 +2,8 @@
 //
 // One persistent kernel, three roles per CTA (192 threads):
 //   warps 0-3  epilogue: TMEM -> registers -> FP16 -> swizzled shared memory -> TMA store
-//   warp  4    MMA issuer (one lane): scale copies into TMEM + tcgen05 block-scaled MMAs
-//   warp  5    producer  (one lane): TMA tile loads of packed operands and scale atoms
+//   warp  4    MMA issuer (one elected lane): scale copies into TMEM + tcgen05 block-scaled MMAs
+//   warp  5    producer  (one elected lane): TMA tile loads of packed operands and scale atoms
 // A ring stage carries K = 256 of everything one MMA group needs (A rows, B rows,
 // SFA atoms, SFB atoms) behind a single "full" barrier, so the issuer waits once
 // per four MMAs. Accumulators are double-buffered in Tensor Memory; for 256-wide
@@ -44,7 +44,8 @@ constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 512;
 constexpr int SMEM_LIMIT = 232448;  // 227 KiB opt-in maximum per CTA
 
-// Device-side status: [0] OR of StatusBits, [1] tag of the first wait that gave up.
+// Device-side status: [0] OR of StatusBits, [1] tag of the first wait that gave up,
+// [2] SM cycles the first CTA of the most recent GEMM launch was resident (diagnostic).
 __device__ uint32_t g_status[4];
 
 template <int CG, int UN>
@@ -98,18 +99,22 @@ struct GemmArgs {
     int tiles_m, tiles_n, group_m;
     float alpha;
     uint32_t* status;
+    unsigned long long* prof;       // optional: per-unit wait/role cycle counters (16 words per CTA)
+    uint32_t debug;                 // diagnostics only (results invalid): 1 skip C stores, 2 skip scale copies, 4 skip MMAs
+    int prefetch;                   // ring steps by which L2 prefetches run ahead of the loads (0 = off)
+    int c_evict_first;              // store C with the evict-first L2 policy
 };
 
-// Shared-memory matrix descriptor, K-major operand rows of 128 bytes under the
-// 128-byte swizzle: start address >> 4, stride between 8-row groups 1024 B (>> 4)
-// at bit 32, descriptor version 1 at bit 46, swizzle mode 2 (128 B) at bit 61.
-__device__ __forceinline__ uint64_t operand_desc(uint32_t addr) {
-    return uint64_t((addr & 0x3FFFFu) >> 4) | (uint64_t(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
-}
-// Scale atom: 32 rows of 16 bytes, no swizzle: 8-row groups 128 B apart, 16 B leading offset.
-__device__ __forceinline__ uint64_t scale_desc(uint32_t addr) {
-    return uint64_t((addr & 0x3FFFFu) >> 4) | (uint64_t(16 >> 4) << 16) | (uint64_t(128 >> 4) << 32) | (1ull << 46);
-}
+enum ProfSlot { PROF_PROD_WAIT = 0, PROF_PROD_TOTAL, PROF_MMA_WAIT_FULL, PROF_MMA_WAIT_ACC, PROF_MMA_TOTAL,
+                PROF_EPI_WAIT_ACC, PROF_EPI_WAIT_STORE, PROF_EPI_TOTAL, PROF_SMID, PROF_WORDS = 16 };
+
+
+// Shared-memory matrix descriptors (built in Roles::issue from two 32-bit halves):
+//   operands: K-major rows of 128 bytes under the 128-byte swizzle: start address >> 4, stride
+//             between 8-row groups 1024 B (>> 4) at bit 32, version 1 at bit 46, swizzle mode 2
+//             (128 B) at bit 61; K advances by adding 32 B to the start address inside the row;
+//   scale atoms: 32 rows of 16 bytes, no swizzle: 8-row groups 128 B apart (bit 32), 16 B leading
+//             offset (bit 16), version 1.
 
 // Tile t of the persistent sequence -> tile coordinates. Bands of `group_m` tile
 // rows, column-major inside a band, bands alternate direction along N.
@@ -140,13 +145,49 @@ struct Roles {
         return false;
     }
 
-    // ---- warp 5, one lane: stream operand and scale tiles into the ring -------
+    // Both single-issuer roles below run their loops with the WHOLE warp in uniform control
+    // flow and let one elected lane execute the asynchronous instructions. Addresses,
+    // descriptors and coordinates are then warp-uniform values the compiler can keep in
+    // uniform registers, which is what TMA and tcgen05 instructions take; computing them
+    // inside a one-lane branch costs a register-to-uniform move chain per instruction.
+
+    // ---- warp 5: stream operand and scale tiles into the ring ----------------------
     __device__ void produce(const CUtensorMap* tmA, const CUtensorMap* tmB,
-                            const CUtensorMap* tmSFA, const CUtensorMap* tmSFB) const {
+                            const CUtensorMap* tmSFA, const CUtensorMap* tmSFB, int lane) const {
         int stage = 0;
         uint32_t phase = 0;
         const int ksteps = g.K / STAGE_K;
         const int sf_rows_per_block = (g.K / 64) * 4;          // 128-byte rows of the scale map per 128 tensor rows
+        long long waited = 0;
+        const long long born = clock64();
+        // A second cursor runs `g.prefetch` ring steps ahead and asks L2 for the tiles the ring will
+        // load later, so that a DRAM miss is paid long before the data is needed in shared memory.
+        uint32_t pt = unit;
+        int pks = 0, pa_row = 0, pb_row = 0, psfa = 0, psfb = 0;
+        auto aim = [&]() {
+            if (pt < tiles) {
+                int tm, tn;
+                tile_coords(int(pt), g, tm, tn);
+                pa_row = tm * Cfg::TILE_M + int(rank) * BLOCK_M;
+                pb_row = tn * UN + int(rank) * Cfg::B_ROWS;
+                psfa = (pa_row / 128) * sf_rows_per_block;
+                psfb = (tn * UN / 128) * sf_rows_per_block;
+            }
+        };
+        auto prefetch_step = [&]() {
+            if (pt >= tiles) return;
+            if (elect_one()) {
+                tma_prefetch_l2_2d(tmA, pks * ROW_BYTES, pa_row);
+                tma_prefetch_l2_2d(tmB, pks * ROW_BYTES, pb_row);
+                tma_prefetch_l2_2d(tmSFA, 0, psfa + pks * 16);
+                #pragma unroll
+                for (int b = 0; b < Cfg::SFB_BLOCKS; ++b)
+                    tma_prefetch_l2_2d(tmSFB, 0, psfb + b * sf_rows_per_block + pks * 16);
+            }
+            if (++pks == ksteps) { pks = 0; pt += units; aim(); }
+        };
+        aim();
+        for (int i = 0; i < g.prefetch; ++i) prefetch_step();
         for (uint32_t t = unit; t < tiles; t += units) {
             int tm, tn;
             tile_coords(int(t), g, tm, tn);
@@ -155,69 +196,126 @@ struct Roles {
             const int sfa_row0 = (a_row / 128) * sf_rows_per_block;
             const int sfb_row0 = (tn * UN / 128) * sf_rows_per_block;
             for (int ks = 0; ks < ksteps; ++ks) {
-                if (!wait(&ctrl->empty[stage], phase ^ 1u, STATUS_TIMEOUT_PRODUCER, 0x10000000u | (stage << 16) | ks))
-                    return;
+                const long long w0 = g.prof ? clock64() : 0;
+                const bool ok = wait(&ctrl->empty[stage], phase ^ 1u, lane == 0 ? STATUS_TIMEOUT_PRODUCER : 0u,
+                                     0x10000000u | (stage << 16) | ks);
+                if (!__all_sync(0xFFFFFFFFu, ok)) return;
+                if (g.prof) waited += clock64() - w0;
+                if (g.prefetch) prefetch_step();
                 const uint32_t base = smem + stage * Cfg::STAGE_BYTES;
+                const uint32_t own_full = bar(&ctrl->full[stage]);
                 if constexpr (CG == 1) {
-                    const uint32_t full = bar(&ctrl->full[stage]);
-                    mbar_arrive_expect_tx(full, Cfg::STAGE_BYTES);
-                    tma_load_2d(base, tmA, ks * ROW_BYTES, a_row, full);
-                    tma_load_2d(base + Cfg::OFF_B, tmB, ks * ROW_BYTES, b_row, full);
-                    tma_load_2d(base + Cfg::OFF_SFA, tmSFA, 0, sfa_row0 + ks * 16, full);
-                    #pragma unroll
-                    for (int b = 0; b < Cfg::SFB_BLOCKS; ++b)
-                        tma_load_2d(base + Cfg::OFF_SFB + b * Cfg::SFB_BLOCK_BYTES, tmSFB, 0,
-                                    sfb_row0 + b * sf_rows_per_block + ks * 16, full);
+                    if (elect_one()) {
+                        mbar_arrive_expect_tx(own_full, Cfg::STAGE_BYTES);
+                        tma_load_2d(base, tmA, ks * ROW_BYTES, a_row, own_full);
+                        tma_load_2d(base + Cfg::OFF_B, tmB, ks * ROW_BYTES, b_row, own_full);
+                        tma_load_2d(base + Cfg::OFF_SFA, tmSFA, 0, sfa_row0 + ks * 16, own_full);
+                        #pragma unroll
+                        for (int b = 0; b < Cfg::SFB_BLOCKS; ++b)
+                            tma_load_2d(base + Cfg::OFF_SFB + b * Cfg::SFB_BLOCK_BYTES, tmSFB, 0,
+                                        sfb_row0 + b * sf_rows_per_block + ks * 16, own_full);
+                    }
                 } else {
                     // Both CTAs of the pair report their bytes to the leader's barrier.
-                    const uint32_t full = map_to_cta(bar(&ctrl->full[stage]), 0);
-                    if (rank == 0) mbar_arrive_expect_tx(bar(&ctrl->full[stage]), 2 * Cfg::STAGE_BYTES);
-                    tma_load_2d_pair(base, tmA, ks * ROW_BYTES, a_row, full);
-                    tma_load_2d_pair(base + Cfg::OFF_B, tmB, ks * ROW_BYTES, b_row, full);
-                    tma_load_2d_pair(base + Cfg::OFF_SFA, tmSFA, 0, sfa_row0 + ks * 16, full);
-                    #pragma unroll
-                    for (int b = 0; b < Cfg::SFB_BLOCKS; ++b)
-                        tma_load_2d_pair(base + Cfg::OFF_SFB + b * Cfg::SFB_BLOCK_BYTES, tmSFB, 0,
-                                         sfb_row0 + b * sf_rows_per_block + ks * 16, full);
+                    const uint32_t full = map_to_cta(own_full, 0);
+                    if (elect_one()) {
+                        if (rank == 0) mbar_arrive_expect_tx(own_full, 2 * Cfg::STAGE_BYTES);
+                        tma_load_2d_pair(base, tmA, ks * ROW_BYTES, a_row, full);
+                        tma_load_2d_pair(base + Cfg::OFF_B, tmB, ks * ROW_BYTES, b_row, full);
+                        tma_load_2d_pair(base + Cfg::OFF_SFA, tmSFA, 0, sfa_row0 + ks * 16, full);
+                        #pragma unroll
+                        for (int b = 0; b < Cfg::SFB_BLOCKS; ++b)
+                            tma_load_2d_pair(base + Cfg::OFF_SFB + b * Cfg::SFB_BLOCK_BYTES, tmSFB, 0,
+                                             sfb_row0 + b * sf_rows_per_block + ks * 16, full);
+                    }
                 }
                 if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
             }
         }
+        if (g.prof && lane == 0) {
+            unsigned long long* out = g.prof + (size_t(unit) * CG + rank) * PROF_WORDS;
+            out[PROF_PROD_WAIT] = waited;
+            out[PROF_PROD_TOTAL] = clock64() - born;
+        }
     }
 
-    // ---- warp 4, one lane of the leader CTA: scale copies and MMAs --------------
-    __device__ void issue(uint32_t tmem) const {
+    // ---- warp 4 of the leader CTA: scale copies and MMAs ------------------------------
+    // Per ring step the warp spends its time on: noticing that the stage has landed, the 12
+    // scale copies + 4 MMAs + commit, and loop control. The tensor pipe needs 4 x 128 cycles per
+    // step, so the thread side has to stay clearly below that or the pipe runs dry at every
+    // step. Two things keep it there: the barrier of the NEXT stage is probed (non-blocking)
+    // before this stage's instructions are issued, so its latency hides behind them and the
+    // blocking wait is skipped when the probe succeeded; and every descriptor is a uniform
+    // 32-bit add on values computed outside the one-lane block.
+    __device__ void issue(uint32_t tmem, int lane) const {
         int stage = 0;
         uint32_t phase = 0, iter = 0;
         const int ksteps = g.K / STAGE_K;
+        long long wait_full = 0, wait_acc = 0;
+        const long long born = clock64();
+        const bool copy_scales = !(g.debug & 2u), do_mma = !(g.debug & 4u);
+        // Descriptor words. Low word: start address >> 4 (bits 0-13), leading offset >> 4 (bits 16-29).
+        // High word: stride >> 4 (bits 0-13), version 1 (bit 14), swizzle mode (bits 29-31).
+        constexpr uint32_t OPERAND_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
+        constexpr uint32_t SCALE_HI = (128u >> 4) | (1u << 14);
+        constexpr uint32_t SCALE_LBO = (16u >> 4) << 16;
+        const uint32_t ring_lo = (smem & 0x3FFFFu) >> 4;
+        const uint32_t sf_tmem = tmem + Cfg::SF_BASE;
+        bool landed = false;                                    // the probe of this step's barrier succeeded
         for (uint32_t t = unit; t < tiles; t += units, ++iter) {
             const uint32_t acc = tmem + (iter & 1u) * Cfg::ACC_STRIDE;
             if (iter > 0) {
                 // The epilogue has pulled the columns this tile shares with the previous one.
-                if (!wait(&ctrl->acc_free, (iter - 1u) & 1u, STATUS_TIMEOUT_MMA, 0x20000000u | iter)) return;
-                tc_fence_after_sync();
+                const long long w0 = g.prof ? clock64() : 0;
+                const bool ok = wait(&ctrl->acc_free, (iter - 1u) & 1u, lane == 0 ? STATUS_TIMEOUT_MMA : 0u, 0x20000000u | iter);
+                if (!__all_sync(0xFFFFFFFFu, ok)) return;
+                if (g.prof) wait_acc += clock64() - w0;
             }
             for (int ks = 0; ks < ksteps; ++ks) {
-                if (!wait(&ctrl->full[stage], phase, STATUS_TIMEOUT_MMA, 0x21000000u | (stage << 16) | ks)) return;
-                tc_fence_after_sync();
-                const uint32_t base = smem + stage * Cfg::STAGE_BYTES;
-                #pragma unroll
-                for (int j = 0; j < STAGE_K / MMA_K; ++j) {
-                    const uint32_t sf = tmem + Cfg::SF_BASE + j * Cfg::SF_COLS_PER_MMA;
-                    tmem_copy_scales<CG>(sf, scale_desc(base + Cfg::OFF_SFA + j * SF_ATOM_BYTES));
-                    #pragma unroll
-                    for (int b = 0; b < Cfg::SFB_BLOCKS; ++b)
-                        tmem_copy_scales<CG>(sf + 4 + 4 * b,
-                                             scale_desc(base + Cfg::OFF_SFB + b * Cfg::SFB_BLOCK_BYTES + j * SF_ATOM_BYTES));
-                    // K advances 32 bytes inside the 128-byte swizzled row per MMA.
-                    mma_nvfp4<CG>(acc, operand_desc(base + j * (MMA_K / 2)),
-                                  operand_desc(base + Cfg::OFF_B + j * (MMA_K / 2)),
-                                  Cfg::IDESC, sf, sf + 4, (ks | j) != 0 ? 1u : 0u);
+                if (!landed) {
+                    const long long w0 = g.prof ? clock64() : 0;
+                    const bool ok = wait(&ctrl->full[stage], phase, lane == 0 ? STATUS_TIMEOUT_MMA : 0u,
+                                         0x21000000u | (stage << 16) | ks);
+                    if (!__all_sync(0xFFFFFFFFu, ok)) return;
+                    if (g.prof) wait_full += clock64() - w0;
                 }
-                mma_commit<CG>(bar(&ctrl->empty[stage]));       // stage reusable once these MMAs retire
-                if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
+                tc_fence_after_sync();
+                const int next_stage = stage + 1 == Cfg::STAGES ? 0 : stage + 1;
+                const uint32_t next_phase = stage + 1 == Cfg::STAGES ? phase ^ 1u : phase;
+                const bool probe = mbar_test_wait(bar(&ctrl->full[next_stage]), next_phase);
+                const uint32_t lo = ring_lo + uint32_t(stage) * (Cfg::STAGE_BYTES >> 4);
+                const uint32_t empty = bar(&ctrl->empty[stage]);
+                const uint32_t first = ks != 0 ? 1u : 0u;
+                if (elect_one()) {
+                    #pragma unroll
+                    for (int j = 0; j < STAGE_K / MMA_K; ++j) {
+                        const uint32_t sf = sf_tmem + j * Cfg::SF_COLS_PER_MMA;
+                        if (copy_scales) {
+                            tmem_copy_scales<CG>(sf, (lo + ((Cfg::OFF_SFA + j * SF_ATOM_BYTES) >> 4)) | SCALE_LBO, SCALE_HI);
+                            #pragma unroll
+                            for (int b = 0; b < Cfg::SFB_BLOCKS; ++b)
+                                tmem_copy_scales<CG>(sf + 4 + 4 * b,
+                                                     (lo + ((Cfg::OFF_SFB + b * Cfg::SFB_BLOCK_BYTES + j * SF_ATOM_BYTES) >> 4)) | SCALE_LBO,
+                                                     SCALE_HI);
+                        }
+                        // K advances 32 bytes inside the 128-byte swizzled row per MMA.
+                        if (do_mma)
+                            mma_nvfp4<CG>(acc, lo + ((j * (MMA_K / 2)) >> 4), lo + ((Cfg::OFF_B + j * (MMA_K / 2)) >> 4),
+                                          OPERAND_HI, Cfg::IDESC, sf, sf + 4, j != 0 ? 1u : first);
+                    }
+                    mma_commit<CG>(empty);                      // stage reusable once these MMAs retire
+                    if (ks == ksteps - 1) mma_commit<CG>(bar(&ctrl->acc_full));
+                }
+                landed = __all_sync(0xFFFFFFFFu, probe);
+                stage = next_stage;
+                phase = next_phase;
             }
-            mma_commit<CG>(bar(&ctrl->acc_full));
+        }
+        if (g.prof && lane == 0) {
+            unsigned long long* out = g.prof + size_t(unit) * CG * PROF_WORDS;
+            out[PROF_MMA_WAIT_FULL] = wait_full;
+            out[PROF_MMA_WAIT_ACC] = wait_acc;
+            out[PROF_MMA_TOTAL] = clock64() - born;
         }
     }
 
@@ -227,14 +325,19 @@ struct Roles {
         const uint32_t acc_free_leader = CG == 2 ? map_to_cta(bar(&ctrl->acc_free), 0) : bar(&ctrl->acc_free);
         uint32_t iter = 0, stores = 0;
         const float alpha = g.alpha;
+        const uint64_t c_policy = policy_evict_first();
+        long long wait_acc = 0, wait_store = 0;
+        const long long born = clock64();
         for (uint32_t t = unit; t < tiles; t += units, ++iter) {
             int tm, tn;
             tile_coords(int(t), g, tm, tn);
             const int row0 = tm * Cfg::TILE_M + int(rank) * BLOCK_M + warp * 32;
             const int col0 = tn * UN;
             // The whole warp leaves together: the Tensor Memory loads below are warp-collective.
+            const long long w0 = g.prof ? clock64() : 0;
             const bool ready = wait(&ctrl->acc_full, iter & 1u, lane == 0 ? STATUS_TIMEOUT_EPILOGUE : 0u, 0x30000000u | iter);
             if (!__all_sync(0xFFFFFFFFu, ready)) break;
+            if (g.prof) wait_acc += clock64() - w0;
             tc_fence_after_sync();
             const uint32_t acc = tmem + (iter & 1u) * Cfg::ACC_STRIDE + (uint32_t(warp * 32) << 16);
             #pragma unroll 1
@@ -251,8 +354,10 @@ struct Roles {
                     if (lane == 0) mbar_arrive_cluster(acc_free_leader);
                 }
                 const uint32_t buf = stage_base + (stores & 1u) * Cfg::EPI_WARP_BYTES;
+                const long long s0 = g.prof ? clock64() : 0;
                 if (lane == 0) tma_store_wait_read<1>();        // the store that last read this buffer is done
                 __syncwarp();
+                if (g.prof) wait_store += clock64() - s0;
                 #pragma unroll
                 for (int q = 0; q < EPI_COLS / 8; ++q) {
                     uint32_t h[4];
@@ -269,14 +374,24 @@ struct Roles {
                 }
                 fence_async_smem();
                 __syncwarp();
-                if (lane == 0) {
-                    tma_store_2d(tmC, buf, col0 + chunk * EPI_COLS, row0);
+                if (lane == 0 && !(g.debug & 1u)) {
+                    if (g.c_evict_first) tma_store_2d_hint(tmC, buf, col0 + chunk * EPI_COLS, row0, c_policy);
+                    else tma_store_2d(tmC, buf, col0 + chunk * EPI_COLS, row0);
                     tma_store_commit();
                 }
                 ++stores;
             }
         }
         if (lane == 0) tma_store_wait_all();
+        if (g.prof && warp == 0 && lane == 0) {
+            unsigned long long* out = g.prof + (size_t(unit) * CG + rank) * PROF_WORDS;
+            out[PROF_EPI_WAIT_ACC] = wait_acc;
+            out[PROF_EPI_WAIT_STORE] = wait_store;
+            out[PROF_EPI_TOTAL] = clock64() - born;
+            uint32_t smid;
+            asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+            out[PROF_SMID] = smid;
+        }
     }
 };
 
@@ -292,6 +407,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     Control* ctrl = reinterpret_cast<Control*>(smem_raw + (smem - raw) + Cfg::STAGES * Cfg::STAGE_BYTES + Cfg::EPI_BYTES);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = CG == 2 ? cluster_ctarank() : 0u;
+    const long long entered = clock64();
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < Cfg::STAGES; ++s) {
@@ -322,9 +438,9 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                         CG == 2 ? map_to_cta(smem_u32(const_cast<uint32_t*>(&ctrl->wait.abort)), rank ^ 1u) : 0u, g};
 
     if (warp == 5) {
-        if (lane == 0) roles.produce(&tmA, &tmB, &tmSFA, &tmSFB);
+        roles.produce(&tmA, &tmB, &tmSFA, &tmSFB, lane);
     } else if (warp == 4) {
-        if (lane == 0 && rank == 0) roles.issue(tmem);
+        if (rank == 0) roles.issue(tmem, lane);
     } else {
         roles.drain(tmem, &tmC, warp, lane);
     }
@@ -341,6 +457,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         tc_fence_after_sync();
         tmem_dealloc<CG>(tmem, TMEM_COLS);
     }
+    if (blockIdx.x == 0 && threadIdx.x == 0) g.status[2] = uint32_t(clock64() - entered);
 }
 
 // ---- host side ---------------------------------------------------------------
@@ -394,6 +511,11 @@ CUtensorMap output_map(const __half* C, int M, int N) {
                        EPI_COLS, 32, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE);
 }
 
+int env_int(const char* name, int fallback) {
+    const char* v = std::getenv(name);
+    return v && *v ? std::atoi(v) : fallback;
+}
+
 template <int CG, int UN>
 int max_units(int device) {
     using Cfg = Config<CG, UN>;
@@ -424,9 +546,11 @@ int max_units(int device) {
 }
 
 template <int CG, int UN>
-void launch_variant(const gpu_kernels::Nvfp4Params& p, const CUtensorMap& tmC, uint32_t* status, cudaStream_t stream) {
+void launch_variant(const gpu_kernels::Nvfp4Params& p, const CUtensorMap& tmC, uint32_t* status, cudaStream_t stream,
+                    unsigned long long* prof) {
     using Cfg = Config<CG, UN>;
-    GemmArgs g{p.M, p.N, p.K, p.M / Cfg::TILE_M, p.N / UN, std::max(1, p.group_m), p.alpha, status};
+    GemmArgs g{p.M, p.N, p.K, p.M / Cfg::TILE_M, p.N / UN, std::max(1, p.group_m), p.alpha, status, prof,
+               uint32_t(env_int("NVFP4_B200_DEBUG", 0)), std::max(0, p.prefetch), p.c_evict_first};
     cudaLaunchAttribute attr{};
     attr.id = cudaLaunchAttributeClusterDimension;
     attr.val.clusterDim = {unsigned(CG), 1, 1};
@@ -452,11 +576,6 @@ uint32_t* status_word(int device) {
     return p;
 }
 
-int env_int(const char* name, int fallback) {
-    const char* v = std::getenv(name);
-    return v && *v ? std::atoi(v) : fallback;
-}
-
 void prepare(gpu_kernels::Nvfp4Params& p, const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB,
              int M, int N, int K, cudaStream_t) {
     require_sm100();
@@ -472,6 +591,8 @@ void prepare(gpu_kernels::Nvfp4Params& p, const uint8_t* A, const uint8_t* B, co
     p.M = M; p.N = N; p.K = K;
     p.alpha = 1.0f;
     p.device = device;
+    p.prefetch = env_int("NVFP4_B200_PREFETCH", 8);
+    p.c_evict_first = env_int("NVFP4_B200_C_EVICT_FIRST", 1);
     const int force = env_int("NVFP4_B200_VARIANT", 0);        // 0 auto, 2256 / 1256 / 1128 for experiments
     if ((force == 0 && M % 256 == 0 && N % 256 == 0) || force == 2256) { p.cta_group = 2; p.tile_n = 256; }
     else if ((force == 0 && N % 256 == 0) || force == 1256) { p.cta_group = 1; p.tile_n = 256; }
@@ -493,14 +614,16 @@ void prepare(gpu_kernels::Nvfp4Params& p, const uint8_t* A, const uint8_t* B, co
     (void)status_word(device);
 }
 
-void launch(const gpu_kernels::Nvfp4Params& p, __half* C, cudaStream_t stream) {
+void launch_with(const gpu_kernels::Nvfp4Params& p, __half* C, cudaStream_t stream, unsigned long long* prof) {
     if (!C || (reinterpret_cast<uintptr_t>(C) & 15)) throw std::invalid_argument("nvfp4 gemm: C must be 16-byte aligned");
     const CUtensorMap tmC = output_map(C, p.M, p.N);
     uint32_t* status = status_word(p.device);
-    if (p.cta_group == 2) launch_variant<2, 256>(p, tmC, status, stream);
-    else if (p.tile_n == 256) launch_variant<1, 256>(p, tmC, status, stream);
-    else launch_variant<1, 128>(p, tmC, status, stream);
+    if (p.cta_group == 2) launch_variant<2, 256>(p, tmC, status, stream, prof);
+    else if (p.tile_n == 256) launch_variant<1, 256>(p, tmC, status, stream, prof);
+    else launch_variant<1, 128>(p, tmC, status, stream, prof);
 }
+
+void launch(const gpu_kernels::Nvfp4Params& p, __half* C, cudaStream_t stream) { launch_with(p, C, stream, nullptr); }
 
 void validate() {
     cuda_check(cudaDeviceSynchronize());
@@ -523,6 +646,29 @@ void require_sm100() {
     cuda_check(cudaGetDevice(&device));
     cuda_check(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
     if (major != 10) throw std::runtime_error("this library only runs on compute capability 10.x (B200); there is no fallback");
+}
+
+// One launch with the per-role cycle counters switched on; copies 16 words per CTA to `host`
+// (synchronises). Diagnostic: the counters cost a few clock reads per wait.
+int gemm_profile(const gpu_kernels::Nvfp4Params& p, __half* C, cudaStream_t stream, unsigned long long* host, int max_words) {
+    const int words = p.clusters * p.cta_group * PROF_WORDS;
+    if (words > max_words) throw std::invalid_argument("nvfp4 gemm profile: output buffer too small");
+    unsigned long long* dev = nullptr;
+    cuda_check(cudaMalloc(&dev, size_t(words) * 8));
+    cuda_check(cudaMemsetAsync(dev, 0, size_t(words) * 8, stream));
+    launch_with(p, C, stream, dev);
+    cudaError_t e = cudaMemcpyAsync(host, dev, size_t(words) * 8, cudaMemcpyDeviceToHost, stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    cudaFree(dev);
+    cuda_check(e);
+    return words;
+}
+
+// SM cycles the first CTA of the last finished GEMM launch on the current device spent in the kernel.
+unsigned last_kernel_cycles() {
+    uint32_t host[4] = {};
+    cuda_check(cudaMemcpyFromSymbol(host, g_status, sizeof(host)));
+    return host[2];
 }
 
 int gemm_stage_count(int cta_group, int tile_n) {

@@ -29,6 +29,17 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t ran
     return out;
 }
 
+// True in exactly one lane of a fully active warp (the same lane on every call).
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xFFFFFFFF;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
+
 __device__ __forceinline__ uint64_t globaltimer_ns() {
     uint64_t t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -64,6 +75,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+
+// Non-blocking probe of the same condition (never suspends the warp).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
@@ -130,6 +152,22 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
         "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
         " [%0], [%1, {%3, %4}], [%2];"
         :: "r"(dst), "l"(map), "r"(cluster_bar), "r"(x), "r"(y) : "memory");
+}
+// Pull one tile of the tensor map into L2 only (no shared memory, no barrier).
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* map, int x, int y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
+                 :: "l"(map), "r"(x), "r"(y) : "memory");
+}
+// L2 policy for data that is written once and not read again by this kernel.
+__device__ __forceinline__ uint64_t policy_evict_first() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ void tma_store_2d_hint(const CUtensorMap* map, uint32_t src, int x, int y, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;"
+        :: "l"(map), "r"(src), "r"(x), "r"(y), "l"(policy) : "memory");
 }
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
     asm volatile(
@@ -206,6 +244,39 @@ __device__ __forceinline__ void tmem_copy_scales(uint32_t taddr, uint64_t smem_d
         asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" :: "r"(taddr), "l"(smem_desc) : "memory");
     else
         asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" :: "r"(taddr), "l"(smem_desc) : "memory");
+}
+
+// The same two instructions with each 64-bit shared-memory descriptor passed as its two 32-bit
+// halves: the halves are warp-uniform values computed outside the one-lane issue block, and
+// only the cheap pack into a 64-bit register happens beside the instruction.
+template <int CG>
+__device__ __forceinline__ void tmem_copy_scales(uint32_t taddr, uint32_t desc_lo, uint32_t desc_hi) {
+    if constexpr (CG == 1)
+        asm volatile("{\n\t.reg .b64 d;\n\tmov.b64 d, {%1, %2};\n\t"
+                     "tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], d;\n\t}"
+                     :: "r"(taddr), "r"(desc_lo), "r"(desc_hi) : "memory");
+    else
+        asm volatile("{\n\t.reg .b64 d;\n\tmov.b64 d, {%1, %2};\n\t"
+                     "tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], d;\n\t}"
+                     :: "r"(taddr), "r"(desc_lo), "r"(desc_hi) : "memory");
+}
+template <int CG>
+__device__ __forceinline__ void mma_nvfp4(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi,
+                                          uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+    if constexpr (CG == 1)
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+            "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\tsetp.ne.b32 p, %7, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], da, db, %4, [%5], [%6], p;\n\t}"
+            :: "r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+            : "memory");
+    else
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+            "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\tsetp.ne.b32 p, %7, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], da, db, %4, [%5], [%6], p;\n\t}"
+            :: "r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+            : "memory");
 }
 
 // D[tmem] (+)= (A * sfA) x (B * sfB)^T, E2M1 operands from shared memory, one

@@ -65,6 +65,18 @@ class Nvfp4Gemm:
             _lib.check(_lib.load().gpu_kernels_nvfp4_custom(self._plan, out.data_ptr(), _stream()))
         return out
 
+    def profile(self, out: torch.Tensor):
+        """One launch with the kernel's per-role wait counters on. Returns a list of dicts, one per CTA."""
+        n = 4096 * 16
+        buf = (ctypes.c_ulonglong * n)()
+        written = ctypes.c_int()
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.load().gpu_kernels_nvfp4_plan_profile(self._plan, out.data_ptr(), _stream(), buf, n,
+                                                                  ctypes.byref(written)))
+        keys = ("producer_wait", "producer_total", "mma_wait_data", "mma_wait_acc", "mma_total",
+                "epi_wait_acc", "epi_wait_store", "epi_total", "smid")
+        return [dict(zip(keys, buf[i:i + len(keys)])) for i in range(0, written.value, 16)]
+
     def run_cublaslt(self, out: torch.Tensor) -> torch.Tensor:
         """cuBLASLt's NVFP4 matmul on the same operands (comparison only)."""
         a, b = self._keep[0], self._keep[1]

@@ -53,10 +53,22 @@ int gpu_kernels_nvfp4_dequantize(const void* packed, const void* scales, void* o
 
 /* FP32 global scale: C = fp16(alpha * accumulator). The reference fixes alpha = 1 (nvfp4_bridge.cu:101). */
 int gpu_kernels_nvfp4_plan_set_alpha(void* plan, float alpha);
-/* Tuning knobs. key: "group_m" (tile rows per rasterisation band, >= 1). */
+/* Tuning knobs. key: "group_m" (tile rows per rasterisation band, >= 1); "prefetch" (ring steps by which
+ * L2 prefetches run ahead of the shared-memory loads, 0..64); "c_evict_first" (0/1: L2 policy of the C stores). */
 int gpu_kernels_nvfp4_plan_set_option(void* plan, const char* key, int value);
 /* Fills info[0..7] = {M, N, K, units, cta_group, tile_n, group_m, stages}. */
 int gpu_kernels_nvfp4_plan_info(void* plan, int* info);
+
+/* Diagnostic: one launch with per-role wait counters on; writes 16 words per CTA
+ * {producer wait, producer total, MMA wait-for-data, MMA wait-for-accumulator, MMA total, epilogue
+ * wait-for-accumulator, epilogue wait-for-store, epilogue total, SM id, ...} in SM clock cycles.
+ * Allocates and frees a small device buffer and synchronises the stream. */
+int gpu_kernels_nvfp4_plan_profile(void* plan, void* C, void* stream, unsigned long long* counters, int max_words,
+                                   int* words_written);
+
+/* Diagnostic: SM clock cycles that the first CTA of the most recent finished GEMM launch on the current
+ * device spent inside the kernel (synchronising copy of one word); 0 on error. */
+unsigned gpu_kernels_nvfp4_last_kernel_cycles(void);
 
 /* Whole GEMM from HOST buffers: copies the four operands to the device, runs the kernel and copies
  * C back, all on `stream`, then synchronises it. Device staging is cached per (M,N,K) inside the
