@@ -107,6 +107,11 @@ struct GemmArgs {
 
 enum ProfSlot { PROF_PROD_WAIT = 0, PROF_PROD_TOTAL, PROF_MMA_WAIT_FULL, PROF_MMA_WAIT_ACC, PROF_MMA_TOTAL,
                 PROF_EPI_WAIT_ACC, PROF_EPI_WAIT_STORE, PROF_EPI_TOTAL, PROF_SMID, PROF_WORDS = 16 };
+// After the per-CTA counters: for the first TR_TILES tiles of unit 0, eight clock64 stamps around the
+// tile hand-over {0 issuer: last step issued, 1 issuer: acc_free seen, 2 issuer: first step of the
+// next tile issued, 3 leader epilogue warp 0: acc_full seen, 4 same: first chunk loaded,
+// 5 same: acc_free arrival sent, 6 peer CTA epilogue warp 0: acc_full seen, 7 peer: arrival sent}.
+constexpr int TR_TILES = 16;
 
 
 // Shared-memory matrix descriptors (built in Roles::issue from two 32-bit halves):
@@ -264,12 +269,17 @@ struct Roles {
         bool landed = false;                                    // the probe of this step's barrier succeeded
         for (uint32_t t = unit; t < tiles; t += units, ++iter) {
             const uint32_t acc = tmem + (iter & 1u) * Cfg::ACC_STRIDE;
+            unsigned long long* tr = nullptr;
+            if (g.prof && unit == 0 && lane == 0 && iter > 0 && iter <= TR_TILES)
+                tr = g.prof + size_t(units) * CG * PROF_WORDS + size_t(iter - 1) * 8;
             if (iter > 0) {
                 // The epilogue has pulled the columns this tile shares with the previous one.
                 const long long w0 = g.prof ? clock64() : 0;
+                if (tr) tr[0] = w0;
                 const bool ok = wait(&ctrl->acc_free, (iter - 1u) & 1u, lane == 0 ? STATUS_TIMEOUT_MMA : 0u, 0x20000000u | iter);
                 if (!__all_sync(0xFFFFFFFFu, ok)) return;
                 if (g.prof) wait_acc += clock64() - w0;
+                if (tr) tr[1] = clock64();
             }
             for (int ks = 0; ks < ksteps; ++ks) {
                 if (!landed) {
@@ -306,6 +316,7 @@ struct Roles {
                     mma_commit<CG>(empty);                      // stage reusable once these MMAs retire
                     if (ks == ksteps - 1) mma_commit<CG>(bar(&ctrl->acc_full));
                 }
+                if (tr && ks == 0) tr[2] = clock64();
                 landed = __all_sync(0xFFFFFFFFu, probe);
                 stage = next_stage;
                 phase = next_phase;
@@ -338,6 +349,10 @@ struct Roles {
             const bool ready = wait(&ctrl->acc_full, iter & 1u, lane == 0 ? STATUS_TIMEOUT_EPILOGUE : 0u, 0x30000000u | iter);
             if (!__all_sync(0xFFFFFFFFu, ready)) break;
             if (g.prof) wait_acc += clock64() - w0;
+            unsigned long long* tr = nullptr;
+            if (g.prof && unit == 0 && warp == 0 && lane == 0 && iter < TR_TILES)
+                tr = g.prof + size_t(units) * CG * PROF_WORDS + size_t(iter) * 8 + (rank ? 6 : 3);
+            if (tr) tr[0] = clock64();
             tc_fence_after_sync();
             const uint32_t acc = tmem + (iter & 1u) * Cfg::ACC_STRIDE + (uint32_t(warp * 32) << 16);
             #pragma unroll 1
@@ -349,9 +364,11 @@ struct Roles {
                 tmem_ld_32x32(acc + chunk * EPI_COLS + 32, v + 32);
                 tmem_ld_wait();
                 if (c == 0) {
+                    if (tr && rank == 0) tr[1] = clock64();
                     tc_fence_before_sync();
                     __syncwarp();
                     if (lane == 0) mbar_arrive_cluster(acc_free_leader);
+                    if (tr) tr[rank ? 1 : 2] = clock64();
                 }
                 const uint32_t buf = stage_base + (stores & 1u) * Cfg::EPI_WARP_BYTES;
                 const long long s0 = g.prof ? clock64() : 0;
@@ -651,7 +668,7 @@ void require_sm100() {
 // One launch with the per-role cycle counters switched on; copies 16 words per CTA to `host`
 // (synchronises). Diagnostic: the counters cost a few clock reads per wait.
 int gemm_profile(const gpu_kernels::Nvfp4Params& p, __half* C, cudaStream_t stream, unsigned long long* host, int max_words) {
-    const int words = p.clusters * p.cta_group * PROF_WORDS;
+    const int words = p.clusters * p.cta_group * PROF_WORDS + TR_TILES * 8;
     if (words > max_words) throw std::invalid_argument("nvfp4 gemm profile: output buffer too small");
     unsigned long long* dev = nullptr;
     cuda_check(cudaMalloc(&dev, size_t(words) * 8));

@@ -67,8 +67,10 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(bar) : "memory");
 }
 // Arrive on a barrier that may live in another CTA of the cluster (address from map_to_cta).
+// Release at CTA scope only: the waiter needs the arrival itself, not this thread's earlier
+// memory writes (a cluster-scope release costs on the order of a thousand cycles here).
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" :: "r"(cluster_bar) : "memory");
+    asm volatile("mbarrier.arrive.release.cta.shared::cluster.b64 _, [%0];" :: "r"(cluster_bar) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;

@@ -75,7 +75,9 @@ class Nvfp4Gemm:
                                                                   ctypes.byref(written)))
         keys = ("producer_wait", "producer_total", "mma_wait_data", "mma_wait_acc", "mma_total",
                 "epi_wait_acc", "epi_wait_store", "epi_total", "smid")
-        return [dict(zip(keys, buf[i:i + len(keys)])) for i in range(0, written.value, 16)]
+        ctas = (written.value - 128) // 16
+        self.handover = [tuple(buf[ctas * 16 + 8 * i: ctas * 16 + 8 * i + 8]) for i in range(16)]
+        return [dict(zip(keys, buf[i:i + len(keys)])) for i in range(0, ctas * 16, 16)]
 
     def run_cublaslt(self, out: torch.Tensor) -> torch.Tensor:
         """cuBLASLt's NVFP4 matmul on the same operands (comparison only)."""
