@@ -216,9 +216,6 @@ int gpu_kernels_nvfp4_plan_set_option(void* plan, const char* key, int value) {
             const int tiles_m = p.params.M / (128 * p.params.cta_group);
             if (value < 1) throw std::invalid_argument("set_option: group_m must be >= 1");
             p.params.group_m = value < tiles_m ? value : tiles_m;
-        } else if (std::strcmp(key, "prefetch") == 0) {
-            if (value < 0 || value > 64) throw std::invalid_argument("set_option: prefetch must be in 0..64");
-            p.params.prefetch = value;
         } else if (std::strcmp(key, "c_evict_first") == 0) {
             p.params.c_evict_first = value ? 1 : 0;
         } else {

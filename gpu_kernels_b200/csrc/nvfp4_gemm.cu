@@ -101,7 +101,6 @@ struct GemmArgs {
     uint32_t* status;
     unsigned long long* prof;       // optional: per-unit wait/role cycle counters (16 words per CTA)
     uint32_t debug;                 // diagnostics only (results invalid): 1 skip C stores, 2 skip scale copies, 4 skip MMAs
-    int prefetch;                   // ring steps by which L2 prefetches run ahead of the loads (0 = off)
     int c_evict_first;              // store C with the evict-first L2 policy
 };
 
@@ -165,34 +164,6 @@ struct Roles {
         const int sf_rows_per_block = (g.K / 64) * 4;          // 128-byte rows of the scale map per 128 tensor rows
         long long waited = 0;
         const long long born = clock64();
-        // A second cursor runs `g.prefetch` ring steps ahead and asks L2 for the tiles the ring will
-        // load later, so that a DRAM miss is paid long before the data is needed in shared memory.
-        uint32_t pt = unit;
-        int pks = 0, pa_row = 0, pb_row = 0, psfa = 0, psfb = 0;
-        auto aim = [&]() {
-            if (pt < tiles) {
-                int tm, tn;
-                tile_coords(int(pt), g, tm, tn);
-                pa_row = tm * Cfg::TILE_M + int(rank) * BLOCK_M;
-                pb_row = tn * UN + int(rank) * Cfg::B_ROWS;
-                psfa = (pa_row / 128) * sf_rows_per_block;
-                psfb = (tn * UN / 128) * sf_rows_per_block;
-            }
-        };
-        auto prefetch_step = [&]() {
-            if (pt >= tiles) return;
-            if (elect_one()) {
-                tma_prefetch_l2_2d(tmA, pks * ROW_BYTES, pa_row);
-                tma_prefetch_l2_2d(tmB, pks * ROW_BYTES, pb_row);
-                tma_prefetch_l2_2d(tmSFA, 0, psfa + pks * 16);
-                #pragma unroll
-                for (int b = 0; b < Cfg::SFB_BLOCKS; ++b)
-                    tma_prefetch_l2_2d(tmSFB, 0, psfb + b * sf_rows_per_block + pks * 16);
-            }
-            if (++pks == ksteps) { pks = 0; pt += units; aim(); }
-        };
-        aim();
-        for (int i = 0; i < g.prefetch; ++i) prefetch_step();
         for (uint32_t t = unit; t < tiles; t += units) {
             int tm, tn;
             tile_coords(int(t), g, tm, tn);
@@ -206,7 +177,6 @@ struct Roles {
                                      0x10000000u | (stage << 16) | ks);
                 if (!__all_sync(0xFFFFFFFFu, ok)) return;
                 if (g.prof) waited += clock64() - w0;
-                if (g.prefetch) prefetch_step();
                 const uint32_t base = smem + stage * Cfg::STAGE_BYTES;
                 const uint32_t own_full = bar(&ctrl->full[stage]);
                 if constexpr (CG == 1) {
@@ -567,7 +537,7 @@ void launch_variant(const gpu_kernels::Nvfp4Params& p, const CUtensorMap& tmC, u
                     unsigned long long* prof) {
     using Cfg = Config<CG, UN>;
     GemmArgs g{p.M, p.N, p.K, p.M / Cfg::TILE_M, p.N / UN, std::max(1, p.group_m), p.alpha, status, prof,
-               uint32_t(env_int("NVFP4_B200_DEBUG", 0)), std::max(0, p.prefetch), p.c_evict_first};
+               uint32_t(env_int("NVFP4_B200_DEBUG", 0)), p.c_evict_first};
     cudaLaunchAttribute attr{};
     attr.id = cudaLaunchAttributeClusterDimension;
     attr.val.clusterDim = {unsigned(CG), 1, 1};
@@ -608,7 +578,6 @@ void prepare(gpu_kernels::Nvfp4Params& p, const uint8_t* A, const uint8_t* B, co
     p.M = M; p.N = N; p.K = K;
     p.alpha = 1.0f;
     p.device = device;
-    p.prefetch = env_int("NVFP4_B200_PREFETCH", 8);
     p.c_evict_first = env_int("NVFP4_B200_C_EVICT_FIRST", 1);
     const int force = env_int("NVFP4_B200_VARIANT", 0);        // 0 auto, 2256 / 1256 / 1128 for experiments
     if ((force == 0 && M % 256 == 0 && N % 256 == 0) || force == 2256) { p.cta_group = 2; p.tile_n = 256; }

@@ -109,20 +109,31 @@ enum StatusBits : uint32_t {
     STATUS_BAD_ARGUMENT = 1u << 4,
 };
 
+// Same test, but the hardware may park the warp for up to `hint_ns` nanoseconds while the phase
+// is incomplete (it is woken at once when the phase completes), so a waiting warp issues no
+// instructions and draws no issue power.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity), "r"(hint_ns) : "memory");
+    return ok != 0;
+}
+
 // Wait for the phase with the given parity. Returns false if the wait was
 // abandoned (time limit, or another role already aborted); the caller must then
 // leave its loop and go to the common teardown.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, WaitCtl* ctl,
                                           uint32_t* status, uint32_t who, uint32_t peer_abort_addr) {
-    #pragma unroll 1
-    for (int i = 0; i < 64; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait(bar, parity)) return true;
     const uint64_t start = globaltimer_ns();
     #pragma unroll 1
     while (true) {
-        #pragma unroll 1
-        for (int i = 0; i < 128; ++i)
-            if (mbar_try_wait(bar, parity)) return true;
+        // parked in hardware for up to 20 us at a time; the abort flag and the clock are only
+        // looked at between parks
+        if (mbar_try_wait_parked(bar, parity, 20000u)) return true;
         if (ctl->abort) return false;
         if (globaltimer_ns() - start > WAIT_LIMIT_NS) {
             ctl->abort = 1;
@@ -154,11 +165,6 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
         "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
         " [%0], [%1, {%3, %4}], [%2];"
         :: "r"(dst), "l"(map), "r"(cluster_bar), "r"(x), "r"(y) : "memory");
-}
-// Pull one tile of the tensor map into L2 only (no shared memory, no barrier).
-__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* map, int x, int y) {
-    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
-                 :: "l"(map), "r"(x), "r"(y) : "memory");
 }
 // L2 policy for data that is written once and not read again by this kernel.
 __device__ __forceinline__ uint64_t policy_evict_first() {

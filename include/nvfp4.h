@@ -37,7 +37,6 @@ struct Nvfp4Params {
     int tile_n;                     // columns of C per tile (256 or 128)
     int group_m;                    // tile rows per rasterisation band
     int device;                     // device the plan was prepared on
-    int prefetch;                   // ring steps by which L2 prefetches run ahead of the loads (0 = off)
     int c_evict_first;              // 1: C is stored with the evict-first L2 policy
 };
 
