@@ -41,7 +41,7 @@ NOMINAL_FP4_TFLOPS = 9000.0
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of nvfp4_gemm_kernel, from the
 # ncu captures summarised under profiles/ (None until a capture of that workload exists).
-NCU_DRAM_BYTES_PER_LAUNCH = {"gemm8192": None, "gemm16384": None, "skinny": None}
+NCU_DRAM_BYTES_PER_LAUNCH = {"gemm8192": 226_928_896, "gemm16384": None, "skinny": None}
 
 
 def algorithmic_bytes(m, n, k):
