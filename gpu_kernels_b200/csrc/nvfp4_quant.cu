@@ -6,7 +6,7 @@
 // Arithmetic follows the reference's PyTorch quantiser step by step
 // (reference/python/nvfp4.py:30-37 and :6-14): amax -> IEEE divide by 6 ->
 // clamp [2^-9, 448] -> E4M3 nearest-even -> IEEE divide -> E2M1 nearest-even
-// with sign bit (q < 0). The kernel is HBM-bound: 2 B read (bf16) and 0.5625 B
+// with sign bit (q < 0), bit for bit. The kernel is HBM-bound: 2 B read (bf16) and 0.5625 B
 // written per value; a CTA owns a 128-row x 256-column tile so that each scale
 // atom (512 B) and each packed row segment (128 B) leaves in full lines.
 #include "nvfp4_internal.h"
@@ -34,12 +34,24 @@ __device__ __forceinline__ float ue4m3_to_float(uint32_t code) {
     return __uint_as_float((((code >> 3) + 120u) << 23) | ((code & 7u) << 20));
 }
 
-// Number of midpoints below |q|, a value on a midpoint going to the even code.
-__device__ __forceinline__ uint32_t e2m1_from_float(float q) {
-    const float m = fabsf(q);
-    const uint32_t code = (m > 0.25f) + (m >= 0.75f) + (m > 1.25f) + (m >= 1.75f) +
-                          (m > 2.5f) + (m >= 3.5f) + (m > 5.0f);
-    return code | (q < 0.0f ? 8u : 0u);
+// Four bytes of packed E2M1 from eight non-negative quotients (element 0 in the low nibble of
+// byte 0). The hardware conversion rounds to nearest with ties to the even code and saturates at
+// 6, which is the reference's midpoint rule (reference/python/nvfp4.py:8-13); signs are added by
+// the caller because the reference's sign bit is (q < 0), not the sign of the input.
+// Measured alternatives on 8192 x 8192 bf16: sixteen IEEE divisions plus a compare ladder 110 us;
+// this conversion 74 us (its pipe is then the busiest unit); rounding with an FP-adder magic
+// constant plus shifts 88 us (instruction issue bound).
+__device__ __forceinline__ uint32_t e2m1x8_from_quotients(const float (&q)[8]) {
+    uint32_t w;
+    asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n\t"
+        "mov.b32 %0, {b0, b1, b2, b3};\n\t}"
+        : "=r"(w)
+        : "f"(q[0]), "f"(q[1]), "f"(q[2]), "f"(q[3]), "f"(q[4]), "f"(q[5]), "f"(q[6]), "f"(q[7]));
+    return w;
 }
 
 template <typename T> struct Loader;
@@ -79,30 +91,56 @@ template <> struct Loader<float> {
 };
 
 // One 16-value block: returns the scale byte, writes the 8 packed bytes.
+//
+// The reference divides every value by the block scale with an IEEE division. Sixteen
+// `__fdiv_rn` per block made this kernel compute-bound at a quarter of HBM speed, so the
+// division is done as one correctly rounded reciprocal per block and, per value, a product plus
+// one residual correction: q0 = x*r, e = fma(-q0, s, x), q = fma(e, r, q0). With r = RN(1/s) this
+// is the correctly rounded quotient RN(x/s) for every value whose quotient is a normal number
+// (Markstein's division theorem; s has a 4-bit significand, far from the one excluded divisor),
+// i.e. the same bits as the division. Quotients so small that they
+// leave the normal range encode as 0 whatever their last bit is; the only thing that depends on
+// them is the sign bit of a negative value whose quotient rounds to zero, which needs |x| below
+// 2^-141 and is sent through the real division (FP32 input only: no bf16 or fp16 value is that
+// small).
+template <bool TINY_POSSIBLE>
 __device__ __forceinline__ uint32_t quantise_block(const float (&v)[16], uint2& packed) {
-    float amax = 0.0f;
-    bool nan = false;
+    uint32_t mx = 0;
     #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        amax = fmaxf(amax, fabsf(v[i]));
-        nan |= (v[i] != v[i]);
-    }
-    if (nan) {
+    for (int i = 0; i < 16; ++i) mx = max(mx, __float_as_uint(v[i]) & 0x7FFFFFFFu);
+    if (mx > 0x7F800000u) {
         // A NaN poisons the block exactly as it does in the reference: NaN scale
         // byte, and every element compares above all midpoints with sign 0.
         packed = make_uint2(0x77777777u, 0x77777777u);
         return 0x7Fu;
     }
+    const float amax = __uint_as_float(mx);
     const float t = fminf(fmaxf(__fdiv_rn(amax, 6.0f), 0.001953125f), 448.0f);
     const uint32_t sbyte = ue4m3_from_float(t);
     const float s = ue4m3_to_float(sbyte);
-    uint32_t lo = 0, hi = 0;
+    const float r = __frcp_rn(s);
+    // Magnitudes are clamped to 8 * s: everything above 5 * s encodes as 6 anyway, and the clamp
+    // keeps the product finite when the scale saturated at 448 or sits in the E4M3 subnormals.
+    const float limit = 8.0f * s;
+    uint32_t words[2];
     #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        lo |= e2m1_from_float(__fdiv_rn(v[i], s)) << (4 * i);
-        hi |= e2m1_from_float(__fdiv_rn(v[8 + i], s)) << (4 * i);
+    for (int h = 0; h < 2; ++h) {
+        float q[8];
+        uint32_t signs = 0;
+        #pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float x = v[8 * h + i];
+            const float ax = fminf(fabsf(x), limit);
+            const float q0 = __fmul_rn(ax, r);
+            const float e = __fmaf_rn(-q0, s, ax);
+            q[i] = __fmaf_rn(e, r, q0);
+            bool negative = x < 0.0f;
+            if (TINY_POSSIBLE && ax < 1e-42f) negative = negative && __fdiv_rn(ax, s) != 0.0f;
+            signs |= negative ? (8u << (4 * i)) : 0u;
+        }
+        words[h] = e2m1x8_from_quotients(q) | signs;
     }
-    packed = make_uint2(lo, hi);
+    packed = make_uint2(words[0], words[1]);
     return sbyte;
 }
 
@@ -130,7 +168,7 @@ quantise_kernel(const T* __restrict__ x, uint8_t* __restrict__ packed, uint8_t* 
             const int r = (pass + u) * 16 + warp * 2 + (lane >> 4);
             if (live) {
                 uint2 out;
-                const uint32_t sbyte = quantise_block(v[u], out);
+                const uint32_t sbyte = quantise_block<sizeof(T) == 4>(v[u], out);
                 *reinterpret_cast<uint2*>(packed + size_t(row_base + r) * (K / 2) + k / 2) = out;
                 sf_tile[(kb >> 2) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (kb & 3)] = static_cast<uint8_t>(sbyte);
             }

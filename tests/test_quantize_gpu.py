@@ -76,6 +76,57 @@ def test_random_against_oracle(g, dtype, rows, k, scale):
     assert np.array_equal(to_np(g.dequantize(packed, scales)), O.dequantize(p, s))
 
 
+def _all_scales():
+    return O.ue4m3_to_f32(np.arange(1, 0x7F, dtype=np.uint8))          # every finite positive E4M3 value
+
+
+def test_division_free_path_fp32_neighbourhood_of_every_midpoint(g):
+    # The kernel replaces the 16 IEEE divisions by a reciprocal and a residual correction; this is
+    # where that could differ from the reference: FP32 values within a few ulps of every midpoint
+    # times every possible scale, both signs, with an element 6*s pinning the block scale to s.
+    s = _all_scales()                                                # 126 scales
+    mids = np.array([.25, .75, 1.25, 1.75, 2.5, 3.5, 5.0], dtype=np.float32)
+    t = (mids[None, :] * s[:, None]).astype(np.float32)             # exact products
+    ulps = np.arange(-3, 4)
+    probes = (t.view(np.int32)[:, :, None] + ulps[None, None, :].astype(np.int32)).view(np.float32)
+    probes = probes.reshape(126, 49)                                  # per scale: 7 midpoints x 7 offsets
+    x = np.zeros((128, 126 * 8 * 16), dtype=np.float32)             # per row and scale: 8 blocks of 16
+    blocks = x.reshape(128, 126, 8, 16)
+    lane = np.arange(14)
+    for r in range(128):
+        for b in range(8):
+            pick = (15 * b + 3 * r + lane) % 49
+            sign = np.where((lane + r + b) % 2, -1.0, 1.0).astype(np.float32)
+            blocks[r, :, b, 0] = 6.0 * s
+            blocks[r, :, b, 1:15] = probes[:, pick] * sign[None, :]
+            blocks[r, :, b, 15] = (-1.0 if r % 2 else 1.0) * s * np.float32(2.0 ** -140)   # quotient below the normal range
+    p, sc = O.quantize(x)
+    assert set(np.unique(O.unpack_scales_u8(sc, 128, x.shape[1]))) == set(range(1, 0x7F))
+    check_exact(g, torch.from_numpy(x).cuda(), p, sc)
+
+
+def test_division_free_path_every_bf16_against_every_scale(g):
+    # every non-negative bf16 value up to 8*s (and its negative) beside a 6*s pin, for all 126 scales
+    s = _all_scales()
+    rows = []
+    for sv in s:
+        top = np.float32(8.0) * sv
+        top_bits = int(np.float32(top).view(np.uint32)) >> 16
+        vals = O.bf16_to_f32(np.arange(0, top_bits + 1, dtype=np.uint16))
+        vals = np.concatenate((vals, -vals))
+        n = -(-len(vals) // 15) * 15
+        vals = np.concatenate((vals, np.zeros(n - len(vals), dtype=np.float32))).reshape(-1, 15)
+        blk = np.concatenate((np.full((len(vals), 1), 6.0 * sv, dtype=np.float32), vals), axis=1)
+        rows.append(blk.reshape(-1))
+    flat = np.concatenate(rows)
+    k = 4096
+    total = -(-len(flat) // (128 * k)) * 128 * k
+    x = np.concatenate((flat, np.zeros(total - len(flat), dtype=np.float32))).reshape(-1, k)
+    p, sc = O.quantize(x)
+    check_exact(g, torch.from_numpy(x).cuda().bfloat16(), p, sc)
+    check_exact(g, torch.from_numpy(x).cuda(), p, sc)
+
+
 def test_every_bf16_value(g):
     # all 65536 bf16 bit patterns (NaNs and infinities included), one per block position in turn
     bits = np.arange(65536, dtype=np.uint16)
