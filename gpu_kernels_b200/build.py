@@ -19,7 +19,7 @@ ROOT = Path(__file__).resolve().parents[1]
 CSRC = ROOT / "gpu_kernels_b200" / "csrc"
 OUT_DIR = ROOT / "build"
 LIB_NAME = "libgpu_kernels_nvfp4_bench.so"
-SOURCES = ("nvfp4_quant.cu", "nvfp4_gemm.cu", "nvfp4_capi.cu")
+SOURCES = ("nvfp4_quant.cu", "nvfp4_gemm.cu", "nvfp4_moe.cu", "nvfp4_capi.cu")
 ARCH = ("-gencode", "arch=compute_100a,code=sm_100a")
 
 

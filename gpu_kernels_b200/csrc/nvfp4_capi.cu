@@ -286,6 +286,111 @@ unsigned gpu_kernels_nvfp4_last_kernel_cycles(void) {
     return cycles;
 }
 
+/* ---- routed-MoE expert path ---- */
+
+int gpu_kernels_nvfp4_grouped_plan_create(void** out, int pool_rows, int n, int k, int experts, const void* A,
+                                          const void* B, const void* SFA, const void* SFB, const void* block_expert,
+                                          const void* num_blocks) {
+    return guarded([&] {
+        if (!out) throw std::invalid_argument("grouped_plan_create: null result pointer");
+        auto plan = std::make_unique<nvfp4_b200::GroupedGemm>();
+        nvfp4_b200::grouped_prepare(*plan, static_cast<const uint8_t*>(A), static_cast<const uint8_t*>(B),
+                                    static_cast<const uint8_t*>(SFA), static_cast<const uint8_t*>(SFB), pool_rows, n, k,
+                                    experts, static_cast<const int*>(block_expert), static_cast<const int*>(num_blocks));
+        *out = plan.release();
+    });
+}
+
+void gpu_kernels_nvfp4_grouped_plan_destroy(void* plan) { delete static_cast<nvfp4_b200::GroupedGemm*>(plan); }
+
+int gpu_kernels_nvfp4_grouped_run(void* plan, void* C, int out_bf16, void* stream) {
+    return guarded([&] {
+        if (!plan) throw std::invalid_argument("null plan");
+        nvfp4_b200::grouped_launch(*static_cast<nvfp4_b200::GroupedGemm*>(plan), C, out_bf16,
+                                   static_cast<cudaStream_t>(stream));
+    });
+}
+
+int gpu_kernels_nvfp4_moe_payload_bytes(int hidden) { return nvfp4_b200::moe_payload_bytes(hidden); }
+
+int gpu_kernels_nvfp4_moe_route_count(const void* ids, int routes, int experts, void* counts, void* stream) {
+    return guarded([&] {
+        nvfp4_b200::require_sm100();
+        nvfp4_b200::moe_route_count(static_cast<const long long*>(ids), routes, experts, static_cast<int*>(counts),
+                                    static_cast<cudaStream_t>(stream));
+        nvfp4_b200::g_launches.fetch_add(1, std::memory_order_relaxed);
+    });
+}
+
+int gpu_kernels_nvfp4_moe_plan(const void* counts_matrix, int world, int rank, int experts, int capacity_rows,
+                               void* send_offset, void* seg_src_offset, void* seg_pool_offset, void* block_expert,
+                               void* num_blocks, void* totals, void* stream) {
+    return guarded([&] {
+        nvfp4_b200::require_sm100();
+        nvfp4_b200::moe_plan(static_cast<const int*>(counts_matrix), world, rank, experts, capacity_rows,
+                             static_cast<int*>(send_offset), static_cast<int*>(seg_src_offset),
+                             static_cast<int*>(seg_pool_offset), static_cast<int*>(block_expert),
+                             static_cast<int*>(num_blocks), static_cast<int*>(totals), static_cast<cudaStream_t>(stream));
+        nvfp4_b200::g_launches.fetch_add(1, std::memory_order_relaxed);
+    });
+}
+
+int gpu_kernels_nvfp4_moe_pack(const void* xq, const void* xs, const void* ids, const void* weights, int tokens,
+                               int topk, int hidden, const void* send_offset, void* cursor, void* send_rows,
+                               void* send_pos, void* stream) {
+    return guarded([&] {
+        nvfp4_b200::moe_pack(static_cast<const uint8_t*>(xq), static_cast<const uint8_t*>(xs),
+                             static_cast<const long long*>(ids), static_cast<const float*>(weights), tokens, topk, hidden,
+                             static_cast<const int*>(send_offset), static_cast<int*>(cursor),
+                             static_cast<uint8_t*>(send_rows), static_cast<int*>(send_pos),
+                             static_cast<cudaStream_t>(stream));
+        nvfp4_b200::g_launches.fetch_add(1, std::memory_order_relaxed);
+    });
+}
+
+int gpu_kernels_nvfp4_moe_unpack(const void* recv_rows, int recv_capacity, const void* totals, int world,
+                                 int local_experts, int hidden, const void* seg_src_offset, const void* seg_pool_offset,
+                                 void* pool_packed, void* pool_scales, void* pool_weight, void* pool_of_recv,
+                                 void* stream) {
+    return guarded([&] {
+        nvfp4_b200::moe_unpack(static_cast<const uint8_t*>(recv_rows), recv_capacity, static_cast<const int*>(totals),
+                               world, local_experts, hidden, static_cast<const int*>(seg_src_offset),
+                               static_cast<const int*>(seg_pool_offset), static_cast<uint8_t*>(pool_packed),
+                               static_cast<uint8_t*>(pool_scales), static_cast<float*>(pool_weight),
+                               static_cast<int*>(pool_of_recv), static_cast<cudaStream_t>(stream));
+        nvfp4_b200::g_launches.fetch_add(1, std::memory_order_relaxed);
+    });
+}
+
+int gpu_kernels_nvfp4_moe_swiglu_quant(const void* gate_up, const void* pool_weight, const void* num_blocks,
+                                       int pool_rows, int intermediate, float clamp, void* act_packed,
+                                       void* act_scales, void* stream) {
+    return guarded([&] {
+        nvfp4_b200::moe_swiglu_quant(gate_up, static_cast<const float*>(pool_weight), static_cast<const int*>(num_blocks),
+                                     pool_rows, intermediate, clamp, static_cast<uint8_t*>(act_packed),
+                                     static_cast<uint8_t*>(act_scales), static_cast<cudaStream_t>(stream));
+        nvfp4_b200::g_launches.fetch_add(1, std::memory_order_relaxed);
+    });
+}
+
+int gpu_kernels_nvfp4_moe_return_rows(const void* out_pool, const void* pool_of_recv, const void* totals, int capacity,
+                                      int hidden, void* return_rows, void* stream) {
+    return guarded([&] {
+        nvfp4_b200::moe_return_rows(out_pool, static_cast<const int*>(pool_of_recv), static_cast<const int*>(totals),
+                                    capacity, hidden, return_rows, static_cast<cudaStream_t>(stream));
+        nvfp4_b200::g_launches.fetch_add(1, std::memory_order_relaxed);
+    });
+}
+
+int gpu_kernels_nvfp4_moe_reduce(const void* returned, const void* send_pos, int tokens, int topk, int hidden, void* y,
+                                 void* stream) {
+    return guarded([&] {
+        nvfp4_b200::moe_reduce(returned, static_cast<const int*>(send_pos), tokens, topk, hidden, y,
+                               static_cast<cudaStream_t>(stream));
+        nvfp4_b200::g_launches.fetch_add(1, std::memory_order_relaxed);
+    });
+}
+
 const char* gpu_kernels_nvfp4_version(void) { return "nvfp4-b200 0.1 (sm_100a)"; }
 
 unsigned long long gpu_kernels_nvfp4_launch_count(void) {

@@ -20,6 +20,8 @@
 #include "nvfp4_internal.h"
 #include "ptx.cuh"
 
+#include <cuda_bf16.h>
+
 #include <algorithm>
 #include <atomic>
 #include <cstdlib>
@@ -102,6 +104,13 @@ struct GemmArgs {
     unsigned long long* prof;       // optional: per-unit wait/role cycle counters (16 words per CTA)
     uint32_t debug;                 // diagnostics only (results invalid): 1 skip C stores, 2 skip scale copies, 4 skip MMAs
     int c_evict_first;              // store C with the evict-first L2 policy
+    int out_bf16;                   // 1: C is bfloat16 instead of float16
+    // Grouped mode (routed-MoE experts): A is a pool of 128-row blocks, block i belongs to expert
+    // block_expert[i] and multiplies rows [expert * b_rows_per_expert, +N) of the stacked B. The
+    // number of live blocks is only known on the device. Null block_expert = one dense GEMM.
+    const int* block_expert;
+    const int* num_blocks;
+    int b_rows_per_expert;
 };
 
 enum ProfSlot { PROF_PROD_WAIT = 0, PROF_PROD_TOTAL, PROF_MMA_WAIT_FULL, PROF_MMA_WAIT_ACC, PROF_MMA_TOTAL,
@@ -122,7 +131,15 @@ constexpr int TR_TILES = 16;
 
 // Tile t of the persistent sequence -> tile coordinates. Bands of `group_m` tile
 // rows, column-major inside a band, bands alternate direction along N.
-__device__ __forceinline__ void tile_coords(int t, const GemmArgs& g, int& tm, int& tn) {
+__device__ __forceinline__ void tile_coords(int t, const GemmArgs& g, int& tm, int& tn, int& b_base) {
+    if (g.block_expert) {
+        // grouped: all N tiles of one row block are consecutive, so an expert's weights are streamed once
+        tm = t / g.tiles_n;
+        tn = t - tm * g.tiles_n;
+        b_base = __ldg(g.block_expert + tm) * g.b_rows_per_expert;
+        return;
+    }
+    b_base = 0;
     const int per_band = g.group_m * g.tiles_n;
     const int band = t / per_band;
     const int first = band * g.group_m;
@@ -165,12 +182,12 @@ struct Roles {
         long long waited = 0;
         const long long born = clock64();
         for (uint32_t t = unit; t < tiles; t += units) {
-            int tm, tn;
-            tile_coords(int(t), g, tm, tn);
+            int tm, tn, b_base;
+            tile_coords(int(t), g, tm, tn, b_base);
             const int a_row = tm * Cfg::TILE_M + int(rank) * BLOCK_M;
-            const int b_row = tn * UN + int(rank) * Cfg::B_ROWS;
+            const int b_row = b_base + tn * UN + int(rank) * Cfg::B_ROWS;
             const int sfa_row0 = (a_row / 128) * sf_rows_per_block;
-            const int sfb_row0 = (tn * UN / 128) * sf_rows_per_block;
+            const int sfb_row0 = ((b_base + tn * UN) / 128) * sf_rows_per_block;
             for (int ks = 0; ks < ksteps; ++ks) {
                 const long long w0 = g.prof ? clock64() : 0;
                 const bool ok = wait(&ctrl->empty[stage], phase ^ 1u, lane == 0 ? STATUS_TIMEOUT_PRODUCER : 0u,
@@ -310,8 +327,8 @@ struct Roles {
         long long wait_acc = 0, wait_store = 0;
         const long long born = clock64();
         for (uint32_t t = unit; t < tiles; t += units, ++iter) {
-            int tm, tn;
-            tile_coords(int(t), g, tm, tn);
+            int tm, tn, b_base;
+            tile_coords(int(t), g, tm, tn, b_base);
             const int row0 = tm * Cfg::TILE_M + int(rank) * BLOCK_M + warp * 32;
             const int col0 = tn * UN;
             // The whole warp leaves together: the Tensor Memory loads below are warp-collective.
@@ -350,9 +367,15 @@ struct Roles {
                     uint32_t h[4];
                     #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        const __half2 p = __floats2half2_rn(__uint_as_float(v[q * 8 + 2 * i]) * alpha,
-                                                            __uint_as_float(v[q * 8 + 2 * i + 1]) * alpha);
-                        h[i] = *reinterpret_cast<const uint32_t*>(&p);
+                        const float lo = __uint_as_float(v[q * 8 + 2 * i]) * alpha;
+                        const float hi = __uint_as_float(v[q * 8 + 2 * i + 1]) * alpha;
+                        if (g.out_bf16) {
+                            const __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+                            h[i] = *reinterpret_cast<const uint32_t*>(&p);
+                        } else {
+                            const __half2 p = __floats2half2_rn(lo, hi);
+                            h[i] = *reinterpret_cast<const uint32_t*>(&p);
+                        }
                     }
                     // 128-byte swizzle: 16-byte chunk q of row `lane` lands in chunk q ^ (lane % 8).
                     const uint32_t dst = buf + lane * 128 + ((q ^ (lane & 7)) << 4);
@@ -421,7 +444,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 
     Roles<CG, UN> roles{smem, ctrl, rank,
                         CG == 2 ? blockIdx.x / 2u : blockIdx.x, gridDim.x / CG,
-                        uint32_t(g.tiles_m) * uint32_t(g.tiles_n),
+                        uint32_t(g.block_expert ? __ldg(g.num_blocks) : g.tiles_m) * uint32_t(g.tiles_n),
                         CG == 2 ? map_to_cta(smem_u32(const_cast<uint32_t*>(&ctrl->wait.abort)), rank ^ 1u) : 0u, g};
 
     if (warp == 5) {
@@ -537,7 +560,7 @@ void launch_variant(const gpu_kernels::Nvfp4Params& p, const CUtensorMap& tmC, u
                     unsigned long long* prof) {
     using Cfg = Config<CG, UN>;
     GemmArgs g{p.M, p.N, p.K, p.M / Cfg::TILE_M, p.N / UN, std::max(1, p.group_m), p.alpha, status, prof,
-               uint32_t(env_int("NVFP4_B200_DEBUG", 0)), p.c_evict_first};
+               uint32_t(env_int("NVFP4_B200_DEBUG", 0)), p.c_evict_first, 0, nullptr, nullptr, 0};
     cudaLaunchAttribute attr{};
     attr.id = cudaLaunchAttributeClusterDimension;
     attr.val.clusterDim = {unsigned(CG), 1, 1};
@@ -655,6 +678,42 @@ unsigned last_kernel_cycles() {
     uint32_t host[4] = {};
     cuda_check(cudaMemcpyFromSymbol(host, g_status, sizeof(host)));
     return host[2];
+}
+
+void grouped_prepare(GroupedGemm& p, const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB,
+                     int pool_rows, int n, int k, int experts, const int* block_expert, const int* num_blocks) {
+    require_sm100();
+    if (pool_rows <= 0 || pool_rows % 128) throw std::invalid_argument("grouped gemm: pool rows must be a positive multiple of 128");
+    if (n <= 0 || n % 256) throw std::invalid_argument("grouped gemm: N per expert must be a multiple of 256");
+    if (k <= 0 || k % STAGE_K) throw std::invalid_argument("grouped gemm: K must be a multiple of 256");
+    if (experts <= 0 || !A || !B || !SFA || !SFB || !block_expert || !num_blocks)
+        throw std::invalid_argument("grouped gemm: null pointer or no experts");
+    cuda_check(cudaGetDevice(&p.device));
+    p.pool_rows = pool_rows; p.n = n; p.k = k; p.experts = experts; p.tile_n = 256;
+    p.block_expert = block_expert; p.num_blocks = num_blocks;
+    p.A = operand_map(A, pool_rows, k, BLOCK_M);
+    p.B = operand_map(B, experts * n, k, 256);
+    p.SFA = scale_map(SFA, pool_rows, k);
+    p.SFB = scale_map(SFB, experts * n, k);
+    p.units = std::min(max_units<1, 256>(p.device), (pool_rows / 128) * (n / 256));
+    (void)status_word(p.device);
+}
+
+void grouped_launch(const GroupedGemm& p, void* C, int out_bf16, cudaStream_t stream) {
+    if (!C || (reinterpret_cast<uintptr_t>(C) & 15)) throw std::invalid_argument("grouped gemm: C must be 16-byte aligned");
+    using Cfg = Config<1, 256>;
+    const CUtensorMap tmC = make_map_2d(out_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, C,
+                                        uint64_t(p.n), uint64_t(p.pool_rows), uint64_t(p.n) * 2, EPI_COLS, 32,
+                                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE);
+    GemmArgs g{p.pool_rows, p.n, p.k, p.pool_rows / 128, p.n / 256, 1, 1.0f, status_word(p.device), nullptr,
+               0u, 1, out_bf16, p.block_expert, p.num_blocks, p.n};
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(unsigned(p.units));
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cfg.stream = stream;
+    cuda_check(cudaLaunchKernelEx(&cfg, nvfp4_gemm_kernel<1, 256>, p.A, p.B, p.SFA, p.SFB, tmC, g));
+    g_launches.fetch_add(1, std::memory_order_relaxed);
 }
 
 int gemm_stage_count(int cta_group, int tile_n) {

@@ -24,4 +24,40 @@ void check_quant_shape(int rows, int K);
 void quantise(const void* x, int dtype, uint8_t* packed, uint8_t* scales, int rows, int K, cudaStream_t stream);
 void dequantise(const uint8_t* packed, const uint8_t* scales, float* out, int rows, int K, cudaStream_t stream);
 
+// nvfp4_gemm.cu: grouped GEMM for routed-MoE experts. A is a pool of 128-row blocks
+// [pool_rows, K/2]; B stacks the experts' weights [experts * n, K/2]; block i of the pool uses
+// expert block_expert[i]; only the first *num_blocks blocks are computed (both device arrays are
+// read by the kernel, so no host synchronisation is needed between routing and the GEMM).
+struct GroupedGemm {
+    CUtensorMap A, B, SFA, SFB;
+    int pool_rows, n, k, experts, units, tile_n, device;
+    const int* block_expert;
+    const int* num_blocks;
+};
+void grouped_prepare(GroupedGemm& p, const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB,
+                     int pool_rows, int n, int k, int experts, const int* block_expert, const int* num_blocks);
+void grouped_launch(const GroupedGemm& p, void* C, int out_bf16, cudaStream_t stream);
+
+// nvfp4_moe.cu: routing metadata, dispatch packing, SwiGLU + re-quantise, top-k reduce.
+struct MoeShape {
+    int tokens, hidden, intermediate, experts, topk, rank, world;
+    float clamp;
+};
+void moe_route_count(const long long* ids, int routes, int experts, int* counts, cudaStream_t stream);
+void moe_plan(const int* counts_matrix, int world, int rank, int experts, int pool_capacity_rows,
+              int* send_offset, int* seg_src_offset, int* seg_pool_offset, int* block_expert, int* num_blocks,
+              int* totals, cudaStream_t stream);
+void moe_pack(const uint8_t* xq, const uint8_t* xs, const long long* ids, const float* weights, int tokens, int topk,
+              int hidden, const int* send_offset, int* cursor, uint8_t* send_rows, int* send_pos, cudaStream_t stream);
+void moe_unpack(const uint8_t* recv_rows, int recv_count_capacity, const int* totals, int world, int local_experts,
+                int hidden, const int* seg_src_offset, const int* seg_pool_offset, uint8_t* pool_packed,
+                uint8_t* pool_scales, float* pool_weight, int* pool_of_recv, cudaStream_t stream);
+void moe_swiglu_quant(const void* gate_up_bf16, const float* pool_weight, const int* num_blocks, int pool_rows,
+                      int intermediate, float clamp, uint8_t* act_packed, uint8_t* act_scales, cudaStream_t stream);
+void moe_return_rows(const void* out_pool_bf16, const int* pool_of_recv, const int* totals, int capacity, int hidden,
+                     void* return_rows_bf16, cudaStream_t stream);
+int moe_payload_bytes(int hidden);
+void moe_reduce(const void* returned_bf16, const int* send_pos, int tokens, int topk, int hidden, void* y_bf16,
+                cudaStream_t stream);
+
 }  // namespace nvfp4_b200

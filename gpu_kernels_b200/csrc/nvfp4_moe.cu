@@ -1,0 +1,311 @@
+// Routed-MoE expert path in NVFP4: the small kernels around the two grouped GEMMs.
+//
+//   route_count   histogram of this rank's routes per global expert
+//   plan          (one CTA) from the all-gathered count matrix: where each route goes in the send
+//                 buffer, where each (source rank, local expert) segment lands in the expert-major
+//                 pool, which expert owns each 128-row pool block
+//   pack          token rows (already quantised: packed E2M1 + scale bytes) + route weight ->
+//                 send buffer ordered by destination expert
+//   unpack        received rows -> pool (packed rows, scale bytes in the 128-row atom layout)
+//   swiglu_quant  gate_up (bf16) -> bf16(silu(min(g,c)) * clamp(u,+-c) * w) -> NVFP4 for the second GEMM
+//   return_rows   expert outputs back into the order the rows were received in
+//   reduce        y[t] = bf16(sum_j fp32(row of route (t,j))), fixed j order
+//
+// The reference's expert path is BF16 on sm_90a with device-side peer pulls
+// (kernels/moe/fused/sm90.cu:32-139 metadata/offsets/reduce kernels, :209-550 the fused kernel;
+// activation maths kernels/moe/swiglu.cu:12-26; whole-layer semantics reference/python/moe.py:7-26).
+// This file keeps those semantics (rounding points, clamp order, fixed-order top-k sum) and the
+// phase structure (metadata / FC1 / FC2 / reduce), with NVFP4 operands and an all-to-all exchange.
+#include "nvfp4_internal.h"
+#include "quant_device.cuh"
+
+#include <cuda_bf16.h>
+
+#include <algorithm>
+#include <string>
+
+namespace nvfp4_b200 {
+namespace {
+
+constexpr int PAYLOAD_TAIL = 16;          // route weight (float) + padding, keeps rows 16-byte aligned
+
+__host__ __device__ inline int payload_bytes(int hidden) { return hidden / 2 + hidden / 16 + PAYLOAD_TAIL; }
+
+__global__ void route_count_kernel(const long long* __restrict__ ids, int routes, int experts, int* __restrict__ counts) {
+    extern __shared__ int local[];
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) local[e] = 0;
+    __syncthreads();
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < routes; i += gridDim.x * blockDim.x) {
+        const long long e = ids[i];
+        if (e >= 0 && e < experts) atomicAdd(&local[int(e)], 1);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < experts; e += blockDim.x)
+        if (local[e]) atomicAdd(&counts[e], local[e]);
+}
+
+// counts[r * experts + ge]: routes rank r sends to global expert ge. One CTA; experts <= 4096.
+__global__ void plan_kernel(const int* __restrict__ counts, int world, int rank, int experts, int capacity_rows,
+                            int* __restrict__ send_offset, int* __restrict__ seg_src_offset,
+                            int* __restrict__ seg_pool_offset, int* __restrict__ block_expert,
+                            int* __restrict__ num_blocks, int* __restrict__ totals) {
+    extern __shared__ int sh[];
+    const int local_experts = experts / world;
+    int* expert_rows = sh;                           // [local_experts] rows routed to each local expert
+    int* pool_off = sh + local_experts;              // [local_experts + 1] padded prefix
+    for (int e = threadIdx.x; e < local_experts; e += blockDim.x) {
+        int sum = 0;
+        for (int r = 0; r < world; ++r) sum += counts[r * experts + rank * local_experts + e];
+        expert_rows[e] = sum;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        // where this rank's routes go in its send buffer (ordered by global expert = by destination rank)
+        int acc = 0;
+        for (int ge = 0; ge < experts; ++ge) { send_offset[ge] = acc; acc += counts[rank * experts + ge]; }
+        send_offset[experts] = acc;
+        // expert-major pool, every expert padded to whole 128-row blocks
+        int rows = 0, blocks = 0;
+        for (int e = 0; e < local_experts; ++e) {
+            pool_off[e] = rows;
+            const int padded = (expert_rows[e] + 127) / 128 * 128;
+            for (int b = 0; b < padded / 128 && (blocks + b) * 128 < capacity_rows; ++b) block_expert[blocks + b] = e;
+            rows += padded;
+            blocks += padded / 128;
+        }
+        pool_off[local_experts] = rows;
+        const bool overflow = rows > capacity_rows;
+        *num_blocks = overflow ? 0 : blocks;          // an overflowing plan computes nothing; the host reports it
+        totals[1] = rows;
+        totals[2] = overflow ? 1 : 0;
+    }
+    __syncthreads();
+    // segments (source rank r, local expert e): position in the receive buffer (source-major, expert
+    // order inside a source, which is the order pack() wrote them) and destination row in the pool
+    if (threadIdx.x == 0) {
+        int acc = 0;
+        for (int r = 0; r < world; ++r)
+            for (int e = 0; e < local_experts; ++e) {
+                seg_src_offset[r * local_experts + e] = acc;
+                acc += counts[r * experts + rank * local_experts + e];
+            }
+        seg_src_offset[world * local_experts] = acc;
+        totals[0] = acc;
+    }
+    for (int e = threadIdx.x; e < local_experts; e += blockDim.x) {
+        int acc = pool_off[e];
+        for (int r = 0; r < world; ++r) {
+            seg_pool_offset[r * local_experts + e] = acc;
+            acc += counts[r * experts + rank * local_experts + e];
+        }
+    }
+}
+
+// One warp per route: copies the token's quantised row and gathers its scale bytes out of the atom layout.
+__global__ void pack_kernel(const uint8_t* __restrict__ xq, const uint8_t* __restrict__ xs,
+                            const long long* __restrict__ ids, const float* __restrict__ weights, int routes,
+                            int topk, int hidden, const int* __restrict__ send_offset, int* __restrict__ cursor,
+                            uint8_t* __restrict__ send_rows, int* __restrict__ send_pos) {
+    const int lane = threadIdx.x & 31;
+    const int route = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (route >= routes) return;
+    const int token = route / topk;
+    const int expert = int(ids[route]);
+    int dst = 0;
+    if (lane == 0) {
+        dst = send_offset[expert] + atomicAdd(&cursor[expert], 1);
+        send_pos[route] = dst;
+    }
+    dst = __shfl_sync(0xFFFFFFFFu, dst, 0);
+    uint8_t* out = send_rows + size_t(dst) * payload_bytes(hidden);
+    const uint4* src = reinterpret_cast<const uint4*>(xq + size_t(token) * (hidden / 2));
+    for (int i = lane; i < hidden / 32; i += 32) reinterpret_cast<uint4*>(out)[i] = __ldg(src + i);
+    for (int b = lane; b < hidden / 16; b += 32) out[hidden / 2 + b] = xs[scale_byte_offset(token, b, hidden)];
+    if (lane == 0) *reinterpret_cast<float*>(out + hidden / 2 + hidden / 16) = weights[route];
+}
+
+__global__ void unpack_kernel(const uint8_t* __restrict__ recv_rows, const int* __restrict__ totals, int segments,
+                              int hidden, const int* __restrict__ seg_src_offset, const int* __restrict__ seg_pool_offset,
+                              uint8_t* __restrict__ pool_packed, uint8_t* __restrict__ pool_scales,
+                              float* __restrict__ pool_weight, int* __restrict__ pool_of_recv) {
+    const int lane = threadIdx.x & 31;
+    const int p = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (p >= totals[0] || totals[2]) return;
+    // last segment whose start is <= p (segments may be empty, so starts repeat)
+    int lo = 0, hi = segments;
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (seg_src_offset[mid] <= p) lo = mid; else hi = mid;
+    }
+    const int row = seg_pool_offset[lo] + (p - seg_src_offset[lo]);
+    const uint8_t* in = recv_rows + size_t(p) * payload_bytes(hidden);
+    uint4* dst = reinterpret_cast<uint4*>(pool_packed + size_t(row) * (hidden / 2));
+    for (int i = lane; i < hidden / 32; i += 32) dst[i] = reinterpret_cast<const uint4*>(in)[i];
+    for (int b = lane; b < hidden / 16; b += 32) pool_scales[scale_byte_offset(row, b, hidden)] = in[hidden / 2 + b];
+    if (lane == 0) {
+        pool_weight[row] = *reinterpret_cast<const float*>(in + hidden / 2 + hidden / 16);
+        pool_of_recv[p] = row;
+    }
+}
+
+// gate_up [rows, 2I] bf16 (gate columns first) -> act = bf16(silu(min(g,c)) * clamp(u,-c,c) * w_row)
+// -> NVFP4 along I. Same tiling as the stand-alone quantiser: a CTA owns 128 rows x 256 columns of
+// the activation so that every scale atom and packed row segment leaves in full lines.
+__global__ void __launch_bounds__(256)
+swiglu_quant_kernel(const __nv_bfloat16* __restrict__ gate_up, const float* __restrict__ pool_weight,
+                    const int* __restrict__ num_blocks, int inter, float clamp,
+                    uint8_t* __restrict__ act_packed, uint8_t* __restrict__ act_scales) {
+    __shared__ __align__(16) uint8_t sf_tile[4 * 512];
+    if (int(blockIdx.y) >= *num_blocks) return;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int kb = lane & 15;
+    const int col0 = blockIdx.x * 256;
+    const int row_base = blockIdx.y * 128;
+    const int k = col0 + kb * 16;
+    #pragma unroll 1
+    for (int pass = 0; pass < 8; ++pass) {
+        const int r = pass * 16 + warp * 2 + (lane >> 4);
+        const size_t row = size_t(row_base + r);
+        const uint4* gp = reinterpret_cast<const uint4*>(gate_up + row * (2 * inter) + k);
+        const uint4* up = reinterpret_cast<const uint4*>(gate_up + row * (2 * inter) + inter + k);
+        const uint4 g4[2] = {__ldg(gp), __ldg(gp + 1)}, u4[2] = {__ldg(up), __ldg(up + 1)};
+        const float w = pool_weight[row];
+        const uint32_t* gw = reinterpret_cast<const uint32_t*>(g4);
+        const uint32_t* uw = reinterpret_cast<const uint32_t*>(u4);
+        float v[16];
+        #pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const uint32_t gbits = (i & 1) ? (gw[i >> 1] & 0xFFFF0000u) : (gw[i >> 1] << 16);
+            const uint32_t ubits = (i & 1) ? (uw[i >> 1] & 0xFFFF0000u) : (uw[i >> 1] << 16);
+            const float gate = fminf(__uint_as_float(gbits), clamp);
+            const float upv = fminf(fmaxf(__uint_as_float(ubits), -clamp), clamp);
+            const float silu = gate / (1.0f + expf(-gate));
+            v[i] = __bfloat162float(__float2bfloat16_rn(silu * upv * w));
+        }
+        uint2 out;
+        const uint32_t sbyte = quantise_block<false>(v, out);
+        *reinterpret_cast<uint2*>(act_packed + row * (inter / 2) + k / 2) = out;
+        sf_tile[(kb >> 2) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (kb & 3)] = static_cast<uint8_t>(sbyte);
+    }
+    __syncthreads();
+    if (threadIdx.x < 128) {
+        const size_t first_atom = size_t(blockIdx.y) * (inter / 64) + size_t(blockIdx.x) * 4;
+        reinterpret_cast<uint4*>(act_scales + first_atom * 512)[threadIdx.x] =
+            reinterpret_cast<const uint4*>(sf_tile)[threadIdx.x];
+    }
+}
+
+__global__ void return_rows_kernel(const uint4* __restrict__ out_pool, const int* __restrict__ pool_of_recv,
+                                   const int* __restrict__ totals, int row_vec, uint4* __restrict__ ret) {
+    const int p = blockIdx.x;
+    if (p >= totals[0] || totals[2]) return;
+    const uint4* src = out_pool + size_t(pool_of_recv[p]) * row_vec;
+    uint4* dst = ret + size_t(p) * row_vec;
+    for (int i = threadIdx.x; i < row_vec; i += blockDim.x) dst[i] = __ldg(src + i);
+}
+
+// y[t] = bf16(sum over j of fp32(row of route (t, j))), j ascending: the order of the reference's
+// reduce kernel (kernels/moe/fused/sm90.cu:125-133).
+__global__ void reduce_kernel(const uint4* __restrict__ returned, const int* __restrict__ send_pos, int topk,
+                              int row_vec, uint4* __restrict__ y) {
+    const int t = blockIdx.x;
+    for (int i = threadIdx.x; i < row_vec; i += blockDim.x) {
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int j = 0; j < topk; ++j) {
+            const uint4 v = __ldg(returned + size_t(send_pos[t * topk + j]) * row_vec + i);
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+            #pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                acc[2 * q] += __uint_as_float(w[q] << 16);
+                acc[2 * q + 1] += __uint_as_float(w[q] & 0xFFFF0000u);
+            }
+        }
+        uint32_t o[4];
+        #pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const __nv_bfloat162 p = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
+            o[q] = *reinterpret_cast<const uint32_t*>(&p);
+        }
+        y[size_t(t) * row_vec + i] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
+void check_hidden(int hidden, const char* what) {
+    if (hidden <= 0 || hidden % 256) throw std::invalid_argument(std::string(what) + ": width must be a positive multiple of 256");
+}
+
+}  // namespace
+
+void moe_route_count(const long long* ids, int routes, int experts, int* counts, cudaStream_t stream) {
+    if (!ids || !counts || routes < 0 || experts <= 0 || experts > 4096) throw std::invalid_argument("moe route_count: bad argument");
+    if (routes == 0) return;
+    const int blocks = std::min(64, (routes + 255) / 256);
+    route_count_kernel<<<blocks, 256, experts * sizeof(int), stream>>>(ids, routes, experts, counts);
+    cuda_check(cudaGetLastError());
+}
+
+void moe_plan(const int* counts_matrix, int world, int rank, int experts, int pool_capacity_rows,
+              int* send_offset, int* seg_src_offset, int* seg_pool_offset, int* block_expert, int* num_blocks,
+              int* totals, cudaStream_t stream) {
+    if (world <= 0 || rank < 0 || rank >= world || experts <= 0 || experts % world || experts > 4096)
+        throw std::invalid_argument("moe plan: experts must divide over the ranks (and be <= 4096)");
+    if (pool_capacity_rows <= 0 || pool_capacity_rows % 128) throw std::invalid_argument("moe plan: pool capacity must be a multiple of 128 rows");
+    const int local = experts / world;
+    plan_kernel<<<1, 256, (2 * local + 1) * sizeof(int), stream>>>(counts_matrix, world, rank, experts, pool_capacity_rows,
+                                                                   send_offset, seg_src_offset, seg_pool_offset,
+                                                                   block_expert, num_blocks, totals);
+    cuda_check(cudaGetLastError());
+}
+
+void moe_pack(const uint8_t* xq, const uint8_t* xs, const long long* ids, const float* weights, int tokens, int topk,
+              int hidden, const int* send_offset, int* cursor, uint8_t* send_rows, int* send_pos, cudaStream_t stream) {
+    check_hidden(hidden, "moe pack");
+    const int routes = tokens * topk;
+    if (routes == 0) return;
+    pack_kernel<<<(routes * 32 + 255) / 256, 256, 0, stream>>>(xq, xs, ids, weights, routes, topk, hidden, send_offset,
+                                                               cursor, send_rows, send_pos);
+    cuda_check(cudaGetLastError());
+}
+
+void moe_unpack(const uint8_t* recv_rows, int recv_count_capacity, const int* totals, int world, int local_experts,
+                int hidden, const int* seg_src_offset, const int* seg_pool_offset, uint8_t* pool_packed,
+                uint8_t* pool_scales, float* pool_weight, int* pool_of_recv, cudaStream_t stream) {
+    check_hidden(hidden, "moe unpack");
+    if (recv_count_capacity <= 0) return;
+    unpack_kernel<<<(recv_count_capacity * 32 + 255) / 256, 256, 0, stream>>>(
+        recv_rows, totals, world * local_experts, hidden, seg_src_offset, seg_pool_offset, pool_packed, pool_scales,
+        pool_weight, pool_of_recv);
+    cuda_check(cudaGetLastError());
+}
+
+void moe_swiglu_quant(const void* gate_up_bf16, const float* pool_weight, const int* num_blocks, int pool_rows,
+                      int intermediate, float clamp, uint8_t* act_packed, uint8_t* act_scales, cudaStream_t stream) {
+    check_hidden(intermediate, "moe swiglu_quant");
+    if (pool_rows <= 0 || pool_rows % 128) throw std::invalid_argument("moe swiglu_quant: pool rows must be a multiple of 128");
+    const dim3 grid(intermediate / 256, pool_rows / 128);
+    swiglu_quant_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(gate_up_bf16), pool_weight, num_blocks,
+                                                  intermediate, clamp, act_packed, act_scales);
+    cuda_check(cudaGetLastError());
+}
+
+void moe_return_rows(const void* out_pool_bf16, const int* pool_of_recv, const int* totals, int capacity, int hidden,
+                     void* return_rows_bf16, cudaStream_t stream) {
+    check_hidden(hidden, "moe return_rows");
+    if (capacity <= 0) return;
+    return_rows_kernel<<<capacity, 128, 0, stream>>>(static_cast<const uint4*>(out_pool_bf16), pool_of_recv, totals,
+                                                     hidden / 8, static_cast<uint4*>(return_rows_bf16));
+    cuda_check(cudaGetLastError());
+}
+
+void moe_reduce(const void* returned_bf16, const int* send_pos, int tokens, int topk, int hidden, void* y_bf16,
+                cudaStream_t stream) {
+    check_hidden(hidden, "moe reduce");
+    if (tokens <= 0) return;
+    reduce_kernel<<<tokens, 128, 0, stream>>>(static_cast<const uint4*>(returned_bf16), send_pos, topk, hidden / 8,
+                                              static_cast<uint4*>(y_bf16));
+    cuda_check(cudaGetLastError());
+}
+
+int moe_payload_bytes(int hidden) { return payload_bytes(hidden); }
+
+}  // namespace nvfp4_b200

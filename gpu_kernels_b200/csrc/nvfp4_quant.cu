@@ -10,6 +10,7 @@
 // written per value; a CTA owns a 128-row x 256-column tile so that each scale
 // atom (512 B) and each packed row segment (128 B) leaves in full lines.
 #include "nvfp4_internal.h"
+#include "quant_device.cuh"
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -20,39 +21,6 @@ namespace {
 constexpr int Q_ROWS = 128;      // rows per CTA tile = rows of one scale atom
 constexpr int Q_COLS = 256;      // K values per CTA tile = 16 scale blocks = 4 atoms
 constexpr int Q_THREADS = 256;
-
-// E4M3 byte of t, t already clamped to [2^-9, 448]; nearest-even in both the
-// normal range (3 mantissa bits) and the subnormal range (step 2^-9).
-__device__ __forceinline__ uint32_t ue4m3_from_float(float t) {
-    if (t < 0.015625f) return static_cast<uint32_t>(__float2int_rn(t * 512.0f));
-    const uint32_t b = __float_as_uint(t);
-    return ((b + 0x7FFFFu + ((b >> 20) & 1u)) >> 20) - (120u << 3);
-}
-
-__device__ __forceinline__ float ue4m3_to_float(uint32_t code) {
-    if (code < 8u) return static_cast<float>(code) * 0.001953125f;
-    return __uint_as_float((((code >> 3) + 120u) << 23) | ((code & 7u) << 20));
-}
-
-// Four bytes of packed E2M1 from eight non-negative quotients (element 0 in the low nibble of
-// byte 0). The hardware conversion rounds to nearest with ties to the even code and saturates at
-// 6, which is the reference's midpoint rule (reference/python/nvfp4.py:8-13); signs are added by
-// the caller because the reference's sign bit is (q < 0), not the sign of the input.
-// Measured alternatives on 8192 x 8192 bf16: sixteen IEEE divisions plus a compare ladder 110 us;
-// this conversion 74 us (its pipe is then the busiest unit); rounding with an FP-adder magic
-// constant plus shifts 88 us (instruction issue bound).
-__device__ __forceinline__ uint32_t e2m1x8_from_quotients(const float (&q)[8]) {
-    uint32_t w;
-    asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
-        "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n\t"
-        "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n\t"
-        "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n\t"
-        "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n\t"
-        "mov.b32 %0, {b0, b1, b2, b3};\n\t}"
-        : "=r"(w)
-        : "f"(q[0]), "f"(q[1]), "f"(q[2]), "f"(q[3]), "f"(q[4]), "f"(q[5]), "f"(q[6]), "f"(q[7]));
-    return w;
-}
 
 template <typename T> struct Loader;
 template <> struct Loader<__nv_bfloat16> {
@@ -89,60 +57,6 @@ template <> struct Loader<float> {
         }
     }
 };
-
-// One 16-value block: returns the scale byte, writes the 8 packed bytes.
-//
-// The reference divides every value by the block scale with an IEEE division. Sixteen
-// `__fdiv_rn` per block made this kernel compute-bound at a quarter of HBM speed, so the
-// division is done as one correctly rounded reciprocal per block and, per value, a product plus
-// one residual correction: q0 = x*r, e = fma(-q0, s, x), q = fma(e, r, q0). With r = RN(1/s) this
-// is the correctly rounded quotient RN(x/s) for every value whose quotient is a normal number
-// (Markstein's division theorem; s has a 4-bit significand, far from the one excluded divisor),
-// i.e. the same bits as the division. Quotients so small that they
-// leave the normal range encode as 0 whatever their last bit is; the only thing that depends on
-// them is the sign bit of a negative value whose quotient rounds to zero, which needs |x| below
-// 2^-141 and is sent through the real division (FP32 input only: no bf16 or fp16 value is that
-// small).
-template <bool TINY_POSSIBLE>
-__device__ __forceinline__ uint32_t quantise_block(const float (&v)[16], uint2& packed) {
-    uint32_t mx = 0;
-    #pragma unroll
-    for (int i = 0; i < 16; ++i) mx = max(mx, __float_as_uint(v[i]) & 0x7FFFFFFFu);
-    if (mx > 0x7F800000u) {
-        // A NaN poisons the block exactly as it does in the reference: NaN scale
-        // byte, and every element compares above all midpoints with sign 0.
-        packed = make_uint2(0x77777777u, 0x77777777u);
-        return 0x7Fu;
-    }
-    const float amax = __uint_as_float(mx);
-    const float t = fminf(fmaxf(__fdiv_rn(amax, 6.0f), 0.001953125f), 448.0f);
-    const uint32_t sbyte = ue4m3_from_float(t);
-    const float s = ue4m3_to_float(sbyte);
-    const float r = __frcp_rn(s);
-    // Magnitudes are clamped to 8 * s: everything above 5 * s encodes as 6 anyway, and the clamp
-    // keeps the product finite when the scale saturated at 448 or sits in the E4M3 subnormals.
-    const float limit = 8.0f * s;
-    uint32_t words[2];
-    #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        float q[8];
-        uint32_t signs = 0;
-        #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const float x = v[8 * h + i];
-            const float ax = fminf(fabsf(x), limit);
-            const float q0 = __fmul_rn(ax, r);
-            const float e = __fmaf_rn(-q0, s, ax);
-            q[i] = __fmaf_rn(e, r, q0);
-            bool negative = x < 0.0f;
-            if (TINY_POSSIBLE && ax < 1e-42f) negative = negative && __fdiv_rn(ax, s) != 0.0f;
-            signs |= negative ? (8u << (4 * i)) : 0u;
-        }
-        words[h] = e2m1x8_from_quotients(q) | signs;
-    }
-    packed = make_uint2(words[0], words[1]);
-    return sbyte;
-}
 
 template <typename T>
 __global__ void __launch_bounds__(Q_THREADS)

@@ -1,0 +1,186 @@
+"""Routed-MoE expert layer in NVFP4 with expert parallelism over the GPUs of one box.
+
+Semantics follow the reference's whole-layer oracle (reference/python/moe.py:7-26): per expert
+gate_up = bf16(x W1^T), act = bf16(silu(min(g, c)) * clamp(u, -c, c) * route_weight),
+out = bf16(act W2^T), per token an FP32 sum over its routes, bf16 result. Here both GEMMs run on
+NVFP4 operands (weights quantised once at construction, tokens and activations quantised on the
+fly, one UE4M3 scale per 16 values along K), experts are split over the ranks, and token rows
+travel as quantised rows (2304 B instead of 8 KiB at H=4096) through one all-to-all each way.
+
+The call structure mirrors the reference's `CustomMoE` (benchmarks/fused_moe.py:22-191): allocate
+once, call collectively on one stream per rank, inputs may change between calls, the output tensor
+is overwritten by the next call. Phases as there: metadata, FC1 (+SwiGLU), FC2, reduce.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+from .nvfp4 import quantize
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+class Nvfp4MoE:
+    def __init__(self, w1: torch.Tensor, w2: torch.Tensor, num_experts: int, topk: int, clamp: float = 10.0,
+                 max_tokens: int = 4096, group=None, pool_rows: int | None = None):
+        """w1 [E_local, 2I, H], w2 [E_local, H, I]: this rank's experts (bf16/fp16/fp32 CUDA tensors)."""
+        if not (w1.is_cuda and w2.is_cuda):
+            raise ValueError("expert weights must be CUDA tensors: this package has no CPU path")
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.local_experts, two_i, self.hidden = w1.shape
+        self.inter = two_i // 2
+        if w2.shape != (self.local_experts, self.hidden, self.inter):
+            raise ValueError("w2 must be [E_local, H, I] for w1 [E_local, 2I, H]")
+        if num_experts != self.local_experts * self.world:
+            raise ValueError("num_experts must equal E_local * world")
+        if self.hidden % 256 or self.inter % 256:
+            raise ValueError("H and I must be multiples of 256")
+        self.experts, self.topk, self.clamp, self.max_tokens = num_experts, topk, float(clamp), max_tokens
+        self.device = w1.device
+        lib = _lib.load()
+        self.payload = lib.gpu_kernels_nvfp4_moe_payload_bytes(self.hidden)
+        # weights, quantised once along K (H for W1, I for W2); the experts are stacked along the rows
+        self.w1q, self.w1s = quantize(w1.reshape(self.local_experts * two_i, self.hidden))
+        self.w2q, self.w2s = quantize(w2.reshape(self.local_experts * self.hidden, self.inter))
+        # pool: worst case every route of every rank lands here, each expert padded to 128 rows
+        worst = self.world * max_tokens * topk + self.local_experts * 127
+        self.pool_rows = pool_rows if pool_rows is not None else -(-worst // 128) * 128
+        d, u8, i32 = self.device, torch.uint8, torch.int32
+        routes = max_tokens * topk
+        self.t_pad = -(-max_tokens // 128) * 128
+        self.x_pad = torch.zeros((self.t_pad, self.hidden), dtype=torch.bfloat16, device=d)
+        self.counts = torch.zeros(num_experts, dtype=i32, device=d)
+        self.counts_matrix = torch.zeros((self.world, num_experts), dtype=i32, device=d)
+        self.send_offset = torch.zeros(num_experts + 1, dtype=i32, device=d)
+        self.seg_src = torch.zeros(self.world * self.local_experts + 1, dtype=i32, device=d)
+        self.seg_pool = torch.zeros(self.world * self.local_experts, dtype=i32, device=d)
+        self.block_expert = torch.zeros(self.pool_rows // 128, dtype=i32, device=d)
+        self.num_blocks = torch.zeros(1, dtype=i32, device=d)
+        self.totals = torch.zeros(4, dtype=i32, device=d)
+        self.cursor = torch.zeros(num_experts, dtype=i32, device=d)
+        self.send_rows = torch.empty((routes, self.payload), dtype=u8, device=d)
+        self.send_pos = torch.zeros(routes, dtype=i32, device=d)
+        recv_cap = self.world * routes
+        self.recv_cap = recv_cap
+        self.recv_rows = self.send_rows if self.world == 1 else torch.empty((recv_cap, self.payload), dtype=u8, device=d)
+        self.pool_packed = torch.zeros((self.pool_rows, self.hidden // 2), dtype=u8, device=d)
+        self.pool_scales = torch.zeros(self.pool_rows * self.hidden // 16, dtype=u8, device=d)
+        self.pool_weight = torch.zeros(self.pool_rows, dtype=torch.float32, device=d)
+        self.pool_of_recv = torch.zeros(recv_cap, dtype=i32, device=d)
+        self.gate_up = torch.empty((self.pool_rows, two_i), dtype=torch.bfloat16, device=d)
+        self.act_packed = torch.empty((self.pool_rows, self.inter // 2), dtype=u8, device=d)
+        self.act_scales = torch.empty(self.pool_rows * self.inter // 16, dtype=u8, device=d)
+        self.out_pool = torch.empty((self.pool_rows, self.hidden), dtype=torch.bfloat16, device=d)
+        self.ret_send = torch.empty((recv_cap, self.hidden), dtype=torch.bfloat16, device=d)
+        self.ret_recv = self.ret_send if self.world == 1 else torch.empty((routes, self.hidden), dtype=torch.bfloat16, device=d)
+        self.y = torch.empty((max_tokens, self.hidden), dtype=torch.bfloat16, device=d)
+        self._fc1, self._fc2 = ctypes.c_void_p(), ctypes.c_void_p()
+        with torch.cuda.device(d):
+            _lib.check(lib.gpu_kernels_nvfp4_grouped_plan_create(
+                ctypes.byref(self._fc1), self.pool_rows, two_i, self.hidden, self.local_experts,
+                self.pool_packed.data_ptr(), self.w1q.data_ptr(), self.pool_scales.data_ptr(), self.w1s.data_ptr(),
+                self.block_expert.data_ptr(), self.num_blocks.data_ptr()))
+            _lib.check(lib.gpu_kernels_nvfp4_grouped_plan_create(
+                ctypes.byref(self._fc2), self.pool_rows, self.hidden, self.inter, self.local_experts,
+                self.act_packed.data_ptr(), self.w2q.data_ptr(), self.act_scales.data_ptr(), self.w2s.data_ptr(),
+                self.block_expert.data_ptr(), self.num_blocks.data_ptr()))
+
+    # ---- phases ----------------------------------------------------------------------------------
+    def _metadata(self, ids, tokens):
+        lib, s = _lib.load(), _stream()
+        routes = tokens * self.topk
+        self.counts.zero_()
+        _lib.check(lib.gpu_kernels_nvfp4_moe_route_count(ids.data_ptr(), routes, self.experts, self.counts.data_ptr(), s))
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.counts_matrix.view(-1), self.counts, group=self.group)
+        else:
+            self.counts_matrix.copy_(self.counts.view(1, -1))
+        _lib.check(lib.gpu_kernels_nvfp4_moe_plan(
+            self.counts_matrix.data_ptr(), self.world, self.rank, self.experts, self.pool_rows,
+            self.send_offset.data_ptr(), self.seg_src.data_ptr(), self.seg_pool.data_ptr(),
+            self.block_expert.data_ptr(), self.num_blocks.data_ptr(), self.totals.data_ptr(), s))
+        # the split sizes of the all-to-all have to be host integers: one small D2H copy per call
+        host = self.counts_matrix.cpu().view(self.world, self.world, self.local_experts).sum(-1)   # [src, dst]
+        send_splits = host[self.rank].tolist()
+        recv_splits = host[:, self.rank].tolist()
+        expert_rows = self.counts_matrix.cpu().view(self.world, self.world, self.local_experts)[:, self.rank].sum(0)
+        need = int(((expert_rows + 127) // 128 * 128).sum())
+        if need > self.pool_rows:
+            raise RuntimeError(f"expert pool overflow: {need} rows needed, {self.pool_rows} allocated")
+        return send_splits, recv_splits
+
+    def forward(self, x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+        """x [T, H] bf16, ids [T, topk] int64 global expert ids, weights [T, topk] f32 -> y [T, H] bf16."""
+        tokens = x.shape[0]
+        if tokens > self.max_tokens or x.shape[1] != self.hidden or ids.shape != (tokens, self.topk):
+            raise ValueError("shape mismatch with the layer this object was built for")
+        lib = _lib.load()
+        ids = ids.contiguous().to(torch.int64)
+        weights = weights.contiguous().to(torch.float32)
+        with torch.cuda.device(self.device):
+            s = _stream()
+            # quantise the tokens once; rows are padded to whole 128-row scale atoms
+            self.x_pad[:tokens].copy_(x)
+            xq, xs = quantize(self.x_pad)
+            send_splits, recv_splits = self._metadata(ids, tokens)
+            self.cursor.zero_()
+            _lib.check(lib.gpu_kernels_nvfp4_moe_pack(
+                xq.data_ptr(), xs.data_ptr(), ids.data_ptr(), weights.data_ptr(), tokens, self.topk, self.hidden,
+                self.send_offset.data_ptr(), self.cursor.data_ptr(), self.send_rows.data_ptr(),
+                self.send_pos.data_ptr(), s))
+            total_recv = sum(recv_splits)
+            if self.world > 1:
+                dist.all_to_all_single(self.recv_rows[:total_recv], self.send_rows[:tokens * self.topk],
+                                       recv_splits, send_splits, group=self.group)
+            self.pool_scales.zero_()
+            self.pool_weight.zero_()
+            _lib.check(lib.gpu_kernels_nvfp4_moe_unpack(
+                self.recv_rows.data_ptr(), self.recv_cap, self.totals.data_ptr(), self.world, self.local_experts,
+                self.hidden, self.seg_src.data_ptr(), self.seg_pool.data_ptr(), self.pool_packed.data_ptr(),
+                self.pool_scales.data_ptr(), self.pool_weight.data_ptr(), self.pool_of_recv.data_ptr(), s))
+            _lib.check(lib.gpu_kernels_nvfp4_grouped_run(self._fc1, self.gate_up.data_ptr(), 1, s))
+            _lib.check(lib.gpu_kernels_nvfp4_moe_swiglu_quant(
+                self.gate_up.data_ptr(), self.pool_weight.data_ptr(), self.num_blocks.data_ptr(), self.pool_rows,
+                self.inter, self.clamp, self.act_packed.data_ptr(), self.act_scales.data_ptr(), s))
+            _lib.check(lib.gpu_kernels_nvfp4_grouped_run(self._fc2, self.out_pool.data_ptr(), 1, s))
+            _lib.check(lib.gpu_kernels_nvfp4_moe_return_rows(
+                self.out_pool.data_ptr(), self.pool_of_recv.data_ptr(), self.totals.data_ptr(), self.recv_cap,
+                self.hidden, self.ret_send.data_ptr(), s))
+            if self.world > 1:
+                dist.all_to_all_single(self.ret_recv[:tokens * self.topk].view(torch.uint8),
+                                       self.ret_send[:total_recv].view(torch.uint8),
+                                       send_splits, recv_splits, group=self.group)
+            _lib.check(lib.gpu_kernels_nvfp4_moe_reduce(
+                self.ret_recv.data_ptr(), self.send_pos.data_ptr(), tokens, self.topk, self.hidden,
+                self.y.data_ptr(), s))
+        return self.y[:tokens]
+
+    __call__ = forward
+
+    def close(self) -> None:
+        lib = _lib.load()
+        for plan in (self._fc1, self._fc2):
+            if plan:
+                lib.gpu_kernels_nvfp4_grouped_plan_destroy(plan)
+        self._fc1, self._fc2 = ctypes.c_void_p(), ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def route(logits: torch.Tensor, topk: int):
+    """softmax over router logits, top-k, weights renormalised to sum 1 (the benchmark's routing)."""
+    prob = torch.softmax(logits.float(), dim=-1)
+    weights, ids = prob.topk(topk, dim=-1)
+    return ids, weights / weights.sum(-1, keepdim=True)

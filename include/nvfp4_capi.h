@@ -77,6 +77,55 @@ unsigned gpu_kernels_nvfp4_last_kernel_cycles(void);
 int gpu_kernels_nvfp4_gemm_host(int M, int N, int K, const void* A, const void* B, const void* SFA, const void* SFB,
                                 void* C, float alpha, void* stream);
 
+/* ---- routed-MoE expert path in NVFP4 (phase structure of the reference's gpu_kernels_moe_phase,
+ *      benchmarks/bindings/fused_moe_bridge.cu:11-26: metadata / FC1 / FC2 / reduce; the reference's
+ *      kernels are BF16 for sm_90a and move tokens through peer pointers, these move quantised rows
+ *      through an all-to-all the caller runs between pack and unpack). All pointers are device pointers. ---- */
+
+/* Grouped GEMM: pool A [pool_rows, K/2] of 128-row blocks, stacked weights B [experts*n, K/2] (+ scales);
+ * block i multiplies expert block_expert[i]; *num_blocks blocks are live (device values, read by the kernel).
+ * C [pool_rows, n], fp16 or bf16. Replaces the two WGMMA phases of kernels/moe/fused/sm90.cu:209-550. */
+int gpu_kernels_nvfp4_grouped_plan_create(void** plan, int pool_rows, int n, int k, int experts, const void* A,
+                                          const void* B, const void* SFA, const void* SFB, const void* block_expert,
+                                          const void* num_blocks);
+void gpu_kernels_nvfp4_grouped_plan_destroy(void* plan);
+int gpu_kernels_nvfp4_grouped_run(void* plan, void* C, int out_bf16, void* stream);
+
+/* Bytes of one dispatched token row: hidden/2 packed + hidden/16 scale bytes + 16 (route weight). */
+int gpu_kernels_nvfp4_moe_payload_bytes(int hidden);
+/* replaces metadata_kernel's histogram (kernels/moe/fused/sm90.cu:43-101): counts[e] += routes to global expert e
+ * (ids int64 [routes]); counts must be zeroed by the caller. */
+int gpu_kernels_nvfp4_moe_route_count(const void* ids, int routes, int experts, void* counts, void* stream);
+/* replaces offsets_kernel (sm90.cu:103-119): counts_matrix int32 [world, experts] (all ranks' counts) ->
+ * send_offset [experts+1], seg_src_offset [world*local+1], seg_pool_offset [world*local],
+ * block_expert [capacity_rows/128], num_blocks [1], totals [3] = {rows received, pool rows used, overflow}. */
+int gpu_kernels_nvfp4_moe_plan(const void* counts_matrix, int world, int rank, int experts, int capacity_rows,
+                               void* send_offset, void* seg_src_offset, void* seg_pool_offset, void* block_expert,
+                               void* num_blocks, void* totals, void* stream);
+/* quantised tokens (xq [T_pad, hidden/2], xs VEC16 scales), ids int64 [T, topk], weights f32 [T, topk] ->
+ * send_rows [T*topk, payload] ordered by destination expert; send_pos [T*topk] = row of each route;
+ * cursor int32 [experts] zeroed by the caller. */
+int gpu_kernels_nvfp4_moe_pack(const void* xq, const void* xs, const void* ids, const void* weights, int tokens,
+                               int topk, int hidden, const void* send_offset, void* cursor, void* send_rows,
+                               void* send_pos, void* stream);
+/* received rows (source-major) -> expert-major pool: packed rows, scale atoms (zeroed by the caller first),
+ * per-row route weight, and pool_of_recv [recv_capacity] for the way back. */
+int gpu_kernels_nvfp4_moe_unpack(const void* recv_rows, int recv_capacity, const void* totals, int world,
+                                 int local_experts, int hidden, const void* seg_src_offset, const void* seg_pool_offset,
+                                 void* pool_packed, void* pool_scales, void* pool_weight, void* pool_of_recv,
+                                 void* stream);
+/* replaces kernels/moe/swiglu.cu:12-26 fused with the re-quantisation for the second GEMM:
+ * gate_up bf16 [pool_rows, 2*intermediate] -> NVFP4 activation [pool_rows, intermediate/2] + scales. */
+int gpu_kernels_nvfp4_moe_swiglu_quant(const void* gate_up, const void* pool_weight, const void* num_blocks,
+                                       int pool_rows, int intermediate, float clamp, void* act_packed,
+                                       void* act_scales, void* stream);
+/* expert outputs bf16 [pool_rows, hidden] -> rows in the order they were received (for the all-to-all back). */
+int gpu_kernels_nvfp4_moe_return_rows(const void* out_pool, const void* pool_of_recv, const void* totals, int capacity,
+                                      int hidden, void* return_rows, void* stream);
+/* replaces reduce_kernel (sm90.cu:121-139): y[t] = bf16(sum_j fp32(returned[send_pos[t*topk+j]])), j ascending. */
+int gpu_kernels_nvfp4_moe_reduce(const void* returned, const void* send_pos, int tokens, int topk, int hidden, void* y,
+                                 void* stream);
+
 /* Library version string and the number of kernels this library has launched so far in this process. */
 const char* gpu_kernels_nvfp4_version(void);
 unsigned long long gpu_kernels_nvfp4_launch_count(void);

@@ -47,3 +47,40 @@ def moe_forward(x, expert_ids, route_weights, w1, w2, clamp=10.0):
         eo = round_bf16(act @ w2[e].T)
         np.add.at(out, tok, eo)
     return round_bf16(out)
+
+
+def _quant_dequant_rows(v: np.ndarray) -> np.ndarray:
+    """NVFP4 round trip of every row (one scale per 16 values along the row); rows are independent,
+    so they are padded to whole 128-row scale atoms and cut back."""
+    from .nvfp4_oracle import dequantize, quantize
+    rows = v.shape[0]
+    pad = -(-rows // 128) * 128
+    buf = np.zeros((pad, v.shape[1]), dtype=np.float32)
+    buf[:rows] = v
+    return dequantize(*quantize(buf))[:rows]
+
+
+def moe_forward_nvfp4(x, expert_ids, route_weights, w1, w2, clamp=10.0):
+    """The same layer with both GEMMs on NVFP4 operands: the FP32 dequantise-then-matmul statement of
+    what the CUDA expert path computes. Tokens are quantised along H, each expert's W1 along H and W2
+    along I, the activation (after its bf16 rounding) along I; every other rounding point is the
+    reference's (moe.py:18-26). The per-token sum runs over the routes in slot order, as the
+    reference's reduce kernel does (kernels/moe/fused/sm90.cu:125-133).
+    """
+    tokens, hidden = x.shape
+    topk = expert_ids.shape[1]
+    xq = _quant_dequant_rows(x)
+    slots = np.zeros((tokens, topk, hidden), dtype=np.float32)
+    for e in range(w1.shape[0]):
+        tok, choice = np.nonzero(expert_ids == e)
+        if tok.size == 0:
+            continue
+        w1q = _quant_dequant_rows(w1[e])
+        w2q = _quant_dequant_rows(w2[e])
+        gate_up = round_bf16(xq[tok] @ w1q.T)
+        act = swiglu(gate_up, route_weights[tok, choice], clamp)
+        slots[tok, choice] = round_bf16(_quant_dequant_rows(act) @ w2q.T)
+    out = np.zeros((tokens, hidden), dtype=np.float32)
+    for j in range(topk):
+        out = (out + slots[:, j]).astype(np.float32)
+    return round_bf16(out)

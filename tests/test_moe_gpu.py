@@ -1,0 +1,138 @@
+"""NVFP4 routed-MoE expert path on one GPU (expert parallelism 1) against the CPU oracle.
+
+Integer/byte stages (routing plan, pack, unpack, reduce order) are checked exactly; the two grouped
+GEMMs and the activation are floating point with bf16 rounding points, compared within the stated
+tolerances against `oracle.moe_oracle.moe_forward_nvfp4` (FP32 dequantise-then-matmul).
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import moe_oracle as MO
+from oracle import nvfp4_oracle as O
+from helpers import to_np
+
+pytestmark = pytest.mark.gpu
+
+# Floating-point acceptance for the whole layer (bf16 output, two quantised GEMMs in sequence):
+# relative Frobenius error and max abs error over output RMS. A 1-ulp bf16 difference in gate_up
+# (FP32 summation order) can flip an E2M1 code of the re-quantised activation, which moves single
+# outputs by a quantisation step times a weight, hence looser than the single-GEMM bound.
+LAYER_REL_FROBENIUS = 2e-2
+LAYER_MAX_ABS_OVER_RMS = 0.25
+
+
+@pytest.fixture(scope="module")
+def g():
+    import gpu_kernels_b200
+    return gpu_kernels_b200
+
+
+def make_layer(seed, tokens, hidden, inter, experts, topk, skew=False):
+    gen = torch.Generator(device="cuda").manual_seed(seed)
+    x = torch.randn((tokens, hidden), generator=gen, device="cuda").bfloat16()
+    logits = torch.randn((tokens, experts), generator=gen, device="cuda")
+    if skew:
+        logits[:, 0] += 4.0                                  # most tokens pick expert 0; some experts stay empty
+        logits[:, experts // 2:] -= 8.0
+    w1 = (torch.randn((experts, 2 * inter, hidden), generator=gen, device="cuda") * 0.02).bfloat16()
+    w2 = (torch.randn((experts, hidden, inter), generator=gen, device="cuda") * 0.02).bfloat16()
+    return x, logits, w1, w2
+
+
+def oracle_layer(x, ids, wts, w1, w2, clamp):
+    return MO.moe_forward_nvfp4(to_np(x.float()), to_np(ids), to_np(wts), to_np(w1.float()), to_np(w2.float()), clamp)
+
+
+def assert_layer_close(y, ref, what):
+    y = to_np(y.float()).astype(np.float64)
+    ref = ref.astype(np.float64)
+    assert not np.isnan(y).any(), f"{what}: NaN in the output"
+    rel = np.linalg.norm(y - ref) / max(np.linalg.norm(ref), 1e-30)
+    worst = np.abs(y - ref).max() / max(np.sqrt((ref ** 2).mean()), 1e-30)
+    assert rel <= LAYER_REL_FROBENIUS, f"{what}: relative Frobenius error {rel:.3e}"
+    assert worst <= LAYER_MAX_ABS_OVER_RMS, f"{what}: max abs error / rms {worst:.3e}"
+    return rel, worst
+
+
+@pytest.mark.parametrize("tokens,hidden,inter,experts,topk,skew", [
+    (37, 512, 256, 8, 2, False),
+    (1, 512, 256, 8, 2, False),          # a single token
+    (200, 256, 512, 16, 6, False),       # top-6 as in the benchmark layer
+    (300, 512, 256, 8, 2, True),         # skewed routing: one expert spans several 128-row blocks, others empty
+])
+def test_layer_against_oracle(g, tokens, hidden, inter, experts, topk, skew):
+    x, logits, w1, w2 = make_layer(tokens + hidden, tokens, hidden, inter, experts, topk, skew)
+    ids, wts = g.route(logits, topk)
+    layer = g.Nvfp4MoE(w1, w2, experts, topk, clamp=10.0, max_tokens=max(tokens, 64))
+    y = layer(x, ids, wts).clone()
+    torch.cuda.synchronize()
+    assert_layer_close(y, oracle_layer(x, ids, wts, w1, w2, 10.0), f"T={tokens} H={hidden} I={inter} E={experts} k={topk}")
+    # changed inputs through the same object: nothing stale may survive (routes, counts, pool contents)
+    x2 = torch.roll(x, 1, dims=0) * 0.5
+    ids2, wts2 = g.route(torch.roll(logits, 3, dims=1), topk)
+    y2 = layer(x2, ids2, wts2).clone()
+    assert_layer_close(y2, oracle_layer(x2, ids2, wts2, w1, w2, 10.0), "second call with changed inputs")
+    layer.close()
+
+
+def test_routing_plan_pack_unpack_exact(g):
+    tokens, hidden, inter, experts, topk = 150, 512, 256, 8, 3
+    x, logits, w1, w2 = make_layer(5, tokens, hidden, inter, experts, topk, skew=True)
+    ids, wts = g.route(logits, topk)
+    layer = g.Nvfp4MoE(w1, w2, experts, topk, max_tokens=256)
+    layer(x, ids, wts)
+    torch.cuda.synchronize()
+    ids_np, w_np = to_np(ids), to_np(wts)
+    counts = np.bincount(ids_np.reshape(-1), minlength=experts)
+    assert np.array_equal(to_np(layer.counts), counts)
+    # plan: expert-major pool, each expert padded to 128 rows
+    padded = (counts + 127) // 128 * 128
+    assert int(layer.num_blocks.item()) == padded.sum() // 128
+    expect_blocks = np.repeat(np.arange(experts), padded // 128)
+    assert np.array_equal(to_np(layer.block_expert)[:len(expect_blocks)], expect_blocks)
+    totals = to_np(layer.totals)
+    assert totals[0] == tokens * topk and totals[1] == padded.sum() and totals[2] == 0
+    # the pool holds, per expert, exactly the quantised rows (and weights) of the tokens routed to it
+    xp = np.zeros((256, hidden), dtype=np.float32)
+    xp[:tokens] = to_np(x.float())
+    xq, xs = O.quantize(xp)
+    xs_rows = O.unpack_scales_u8(xs, 256, hidden)
+    pool_q = to_np(layer.pool_packed)
+    pool_s = O.unpack_scales_u8(to_np(layer.pool_scales), layer.pool_rows, hidden)
+    pool_w = to_np(layer.pool_weight)
+    start = np.concatenate(([0], np.cumsum(padded)))
+    for e in range(experts):
+        tok, choice = np.nonzero(ids_np == e)
+        got = slice(start[e], start[e] + counts[e])
+        key = lambda q, s, w: sorted(zip(map(bytes, q), map(bytes, s), w.tolist()))
+        assert key(pool_q[got], pool_s[got], pool_w[got]) == key(xq[tok], xs_rows[tok], w_np[tok, choice])
+        pad = slice(start[e] + counts[e], start[e + 1])
+        assert not pool_s[pad].any() and not pool_w[pad].any()          # padding rows carry zero scales
+    layer.close()
+
+
+def test_reduce_order_exact(g):
+    # y[t] = bf16(((r0 + r1) + r2) ...) in FP32: bit-exact against the same sequential sum
+    from gpu_kernels_b200 import _lib
+    tokens, topk, hidden = 9, 6, 512
+    gen = torch.Generator(device="cuda").manual_seed(1)
+    rows = torch.randn((tokens * topk, hidden), generator=gen, device="cuda").bfloat16()
+    pos = torch.randperm(tokens * topk, generator=gen, device="cuda").to(torch.int32)
+    y = torch.empty((tokens, hidden), dtype=torch.bfloat16, device="cuda")
+    _lib.check(_lib.load().gpu_kernels_nvfp4_moe_reduce(rows.data_ptr(), pos.data_ptr(), tokens, topk, hidden,
+                                                        y.data_ptr(), torch.cuda.current_stream().cuda_stream))
+    r = to_np(rows.float())[to_np(pos).astype(np.int64)].reshape(tokens, topk, hidden)
+    acc = np.zeros((tokens, hidden), dtype=np.float32)
+    for j in range(topk):
+        acc = (acc + r[:, j]).astype(np.float32)
+    assert np.array_equal(to_np(y.float()), MO.round_bf16(acc))
+
+
+def test_pool_overflow_is_reported(g):
+    x, logits, w1, w2 = make_layer(3, 64, 256, 256, 4, 2)
+    ids, wts = g.route(logits, 2)
+    layer = g.Nvfp4MoE(w1, w2, 4, 2, max_tokens=64, pool_rows=128)
+    with pytest.raises(RuntimeError, match="overflow"):
+        layer(x, ids, wts)
+    layer.close()
