@@ -42,6 +42,7 @@ SIGNATURES = {
     "gpu_kernels_nvfp4_moe_swiglu_quant": ([P, P, P, I, I, F, P, P, P], I),
     "gpu_kernels_nvfp4_moe_return_rows": ([P, P, P, I, I, P, P], I),
     "gpu_kernels_nvfp4_moe_reduce": ([P, P, I, I, I, P, P], I),
+    "gpu_kernels_nvfp4_gemm_host_static": ([I, I, I, P, P, P, P, P, F, P], I),
     "gpu_kernels_nvfp4_version": ([], ctypes.c_char_p),
     "gpu_kernels_nvfp4_launch_count": ([], ctypes.c_ulonglong),
 }

@@ -130,6 +130,43 @@ struct HostGemm {
 std::mutex g_host_lock;
 HostGemm g_host;
 
+// ---- staging for gpu_kernels_nvfp4_gemm_host_static ---------------------------------------
+// Some hosts of this library may not allocate device memory while they run: a service that sized
+// its memory pool up front and forbids later cudaMalloc calls (they synchronise the device and can
+// fail when the pool owns the whole GPU), or code that runs between the capture-time and run-time
+// phases of a larger program. For them the device copies of the operands live in this one
+// file-scope array. It costs every process that loads the library 2.7 MiB per GPU until exit.
+constexpr int STATIC_MAX_M = 512, STATIC_MAX_N = 1024, STATIC_MAX_K = 2048;
+constexpr size_t STATIC_OFF_A = 0;
+constexpr size_t STATIC_OFF_B = STATIC_OFF_A + size_t(STATIC_MAX_M) * STATIC_MAX_K / 2;
+constexpr size_t STATIC_OFF_SFA = STATIC_OFF_B + size_t(STATIC_MAX_N) * STATIC_MAX_K / 2;
+constexpr size_t STATIC_OFF_SFB = STATIC_OFF_SFA + size_t(STATIC_MAX_M) * STATIC_MAX_K / 16;
+constexpr size_t STATIC_OFF_C = STATIC_OFF_SFB + size_t(STATIC_MAX_N) * STATIC_MAX_K / 16;
+constexpr size_t STATIC_BYTES = STATIC_OFF_C + size_t(STATIC_MAX_M) * STATIC_MAX_N * 2;
+static_assert(STATIC_OFF_B % 256 == 0 && STATIC_OFF_SFA % 256 == 0 && STATIC_OFF_SFB % 256 == 0 && STATIC_OFF_C % 256 == 0,
+              "sub-buffers keep the 256-byte alignment of the array");
+static __device__ __align__(256) unsigned char g_static_stage[STATIC_BYTES];
+
+// In host code `g_static_stage` is only a handle for the runtime, not a device address; the
+// address a kernel or a tensor map can use comes from cudaGetSymbolAddress, once per device, with
+// that device current.
+std::mutex g_static_lock;
+unsigned char* g_static_base[64] = {};
+
+unsigned char* static_stage_base() {
+    int device = 0;
+    nvfp4_b200::cuda_check(cudaGetDevice(&device));
+    if (device < 0 || device >= 64) throw std::runtime_error("gemm_host_static: device index out of range");
+    std::lock_guard<std::mutex> hold(g_static_lock);
+    if (!g_static_base[device]) {
+        void* p = nullptr;
+        nvfp4_b200::cuda_check(cudaGetSymbolAddress(&p, g_static_stage));
+        if (!p) throw std::runtime_error("gemm_host_static: the staging array has no address on this device");
+        g_static_base[device] = static_cast<unsigned char*>(p);
+    }
+    return g_static_base[device];
+}
+
 }  // namespace
 
 extern "C" {
@@ -388,6 +425,46 @@ int gpu_kernels_nvfp4_moe_reduce(const void* returned, const void* send_pos, int
         nvfp4_b200::moe_reduce(returned, static_cast<const int*>(send_pos), tokens, topk, hidden, y,
                                static_cast<cudaStream_t>(stream));
         nvfp4_b200::g_launches.fetch_add(1, std::memory_order_relaxed);
+    });
+}
+
+int gpu_kernels_nvfp4_gemm_host_static(int M, int N, int K, const void* A, const void* B, const void* SFA,
+                                       const void* SFB, void* C, float alpha, void* stream_) {
+    return guarded([&] {
+        using nvfp4_b200::cuda_check;
+        if (!A || !B || !SFA || !SFB || !C) throw std::invalid_argument("gemm_host_static: null pointer");
+        if (M <= 0 || N <= 0 || K <= 0 || M % 128 || N % 128 || K % 256)
+            throw std::invalid_argument("gemm_host_static: M, N multiples of 128 and K a multiple of 256 are required");
+        if (M > STATIC_MAX_M || N > STATIC_MAX_N || K > STATIC_MAX_K)
+            throw std::invalid_argument("gemm_host_static: shape " + std::to_string(M) + "x" + std::to_string(N) + "x" +
+                                        std::to_string(K) + " exceeds the built-in staging (M <= " +
+                                        std::to_string(STATIC_MAX_M) + ", N <= " + std::to_string(STATIC_MAX_N) +
+                                        ", K <= " + std::to_string(STATIC_MAX_K) + "); use gpu_kernels_nvfp4_gemm_host");
+        nvfp4_b200::require_sm100();
+        auto stream = static_cast<cudaStream_t>(stream_);
+        unsigned char* base = static_stage_base();
+        uint8_t* dA = base + STATIC_OFF_A;
+        uint8_t* dB = base + STATIC_OFF_B;
+        uint8_t* dSFA = base + STATIC_OFF_SFA;
+        uint8_t* dSFB = base + STATIC_OFF_SFB;
+        __half* dC = reinterpret_cast<__half*>(base + STATIC_OFF_C);
+        const size_t a_bytes = size_t(M) * K / 2, b_bytes = size_t(N) * K / 2;
+        const size_t sfa_bytes = size_t(M) * K / 16, sfb_bytes = size_t(N) * K / 16, c_bytes = size_t(M) * N * 2;
+        // One caller at a time: every call uses the same array, so two calls in flight would overwrite
+        // each other's operands. Nothing in the array has to start at zero (operands and C are fully
+        // overwritten), so nothing is cleared.
+        std::lock_guard<std::mutex> hold(g_host_lock);
+        gpu_kernels::Nvfp4Params params{};
+        const gpu_kernels::Nvfp4Implementation impl = gpu_kernels::nvfp4_sm100_implementation();
+        impl.prepare(params, dA, dB, dSFA, dSFB, M, N, K, stream);
+        params.alpha = alpha;
+        cuda_check(cudaMemcpyAsync(dA, A, a_bytes, cudaMemcpyHostToDevice, stream));
+        cuda_check(cudaMemcpyAsync(dB, B, b_bytes, cudaMemcpyHostToDevice, stream));
+        cuda_check(cudaMemcpyAsync(dSFA, SFA, sfa_bytes, cudaMemcpyHostToDevice, stream));
+        cuda_check(cudaMemcpyAsync(dSFB, SFB, sfb_bytes, cudaMemcpyHostToDevice, stream));
+        impl.launch(params, dC, stream);
+        cuda_check(cudaMemcpyAsync(C, dC, c_bytes, cudaMemcpyDeviceToHost, stream));
+        cuda_check(cudaStreamSynchronize(stream));
     });
 }
 

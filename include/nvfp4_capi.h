@@ -126,6 +126,20 @@ int gpu_kernels_nvfp4_moe_return_rows(const void* out_pool, const void* pool_of_
 int gpu_kernels_nvfp4_moe_reduce(const void* returned, const void* send_pos, int tokens, int topk, int hidden, void* y,
                                  void* stream);
 
+/* No counterpart in the reference. The same whole GEMM from HOST buffers as gpu_kernels_nvfp4_gemm_host,
+ * for callers that must not allocate device memory while they run (a process whose memory pool owns
+ * the GPU and forbids later cudaMalloc, or a phase of a program in which allocation is not allowed):
+ * the device copies of A, B, the scales and C live in one array built into the library instead of
+ * cudaMalloc'ed buffers, and the call itself allocates nothing. Limits: M <= 512, N <= 1024, K <= 2048
+ * (plus the usual multiples of 128 / 128 / 256); larger shapes are refused with a message. The array
+ * (2.7 MiB) is held on every GPU that loads the library until the process exits. The first call on
+ * each device looks up the array's device address (make that call before any stream capture begins);
+ * every call shares the array, which keeps the previous call's data; calls that overlap on the GPU,
+ * from several threads or streams, would race on it, so the library serialises them and each call
+ * synchronises `stream` before it returns. */
+int gpu_kernels_nvfp4_gemm_host_static(int M, int N, int K, const void* A, const void* B, const void* SFA,
+                                       const void* SFB, void* C, float alpha, void* stream);
+
 /* Library version string and the number of kernels this library has launched so far in this process. */
 const char* gpu_kernels_nvfp4_version(void);
 unsigned long long gpu_kernels_nvfp4_launch_count(void);
