@@ -35,6 +35,9 @@ WORKLOADS = {
     "skinny": (128, 28672, 8192, 0.02),
     "gemm256": (256, 256, 256, 1.0),
 }
+# Routed-MoE expert layer (H=4096, I=2048, 256 experts, top-6), tokens PER GPU; experts are split over the ranks.
+MOE_WORKLOADS = {"moe_t1": 1, "moe_t64": 64, "moe_t1024": 1024, "moe_t4096": 4096}
+MOE_SHAPE = {"hidden": 4096, "inter": 2048, "experts": 256, "topk": 6, "clamp": 10.0}
 METRIC = "nvfp4_gemm_tflops"
 UNIT = "TFLOP/s"
 NOMINAL_FP4_TFLOPS = 9000.0
@@ -305,13 +308,117 @@ def run_ours(args, rank, world, local_rank):
     }))
 
 
+def run_moe(args, rank, world, local_rank):
+    """One step = one forward of the NVFP4 expert layer on `tokens` tokens per GPU (weak scaling in tokens)."""
+    import torch
+    import torch.distributed as dist
+    import gpu_kernels_b200 as g
+    from gpu_kernels_b200 import _lib
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    tokens = MOE_WORKLOADS[args.workload]
+    H, I, E, topk, clamp = (MOE_SHAPE[k] for k in ("hidden", "inter", "experts", "topk", "clamp"))
+    local = E // world
+    gen = torch.Generator(device=dev).manual_seed(rank)
+    w1 = torch.empty((local, 2 * I, H), dtype=torch.bfloat16, device=dev)
+    w2 = torch.empty((local, H, I), dtype=torch.bfloat16, device=dev)
+    for e in range(local):                                      # expert by expert: keeps the FP32 temporaries small
+        w1[e] = (torch.randn((2 * I, H), generator=gen, device=dev) * 0.02).bfloat16()
+        w2[e] = (torch.randn((H, I), generator=gen, device=dev) * 0.02).bfloat16()
+    layer = g.Nvfp4MoE(w1, w2, E, topk, clamp=clamp, max_tokens=tokens)
+    del w1, w2
+    torch.cuda.empty_cache()
+    sets = []
+    for i in range(4):                                          # rotating inputs: routing changes every step
+        x = torch.randn((tokens, H), generator=gen, device=dev).bfloat16()
+        ids, wts = g.route(torch.randn((tokens, E), generator=gen, device=dev), topk)
+        sets.append((x, ids, wts))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    for i in range(max(3, args.warmup)):
+        layer(*sets[i % 4])
+    barrier()
+    launches0 = _lib.launch_count()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    start.record()
+    for i in range(args.steps):
+        layer(*sets[i % 4])
+    stop.record()
+    barrier()
+    t1 = time.perf_counter()
+    launches = _lib.launch_count() - launches0
+    ms = start.elapsed_time(stop)
+    clocks = sampler.stop(t0, t1) if sampler is not None else None
+    # end to end: inputs from pinned host memory, result back to the host, every step
+    host = [tuple(t.cpu().pin_memory() for t in s_) for s_ in sets]
+    y_host = torch.empty((tokens, H), dtype=torch.bfloat16).pin_memory()
+    e2e_steps = max(2, min(args.steps, 10))
+    barrier()
+    start.record()
+    for i in range(e2e_steps):
+        xs = [t.to(dev, non_blocking=True) for t in host[i % 4]]
+        y_host.copy_(layer(*xs), non_blocking=True)
+    stop.record()
+    barrier()
+    e2e_ms = start.elapsed_time(stop)
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = (float(v) for v in t.tolist())
+    touched = int((layer.counts_matrix.sum(0)[rank * local:(rank + 1) * local] > 0).sum().item())
+    if rank != 0:
+        return
+    routes = world * tokens * topk
+    flops = routes * 2.0 * (2 * I * H + H * I)
+    ms_per_step = ms / args.steps
+    value = flops / (ms_per_step * 1e-3) / 1e12
+    peaks = measured_peaks()
+    weight_bytes = touched * (2 * I * H + H * I) * 9 // 16      # packed values + scale bytes of the experts this rank touched
+    act_bytes = tokens * topk * (H // 2 + H // 16 + 2 * (2 * I) * 2 + I // 2 + I // 16 + 2 * H * 2)
+    alg_bytes = weight_bytes + act_bytes
+    t_hbm = alg_bytes / (peaks["hbm_gbs"] * 1e9)
+    tensor_peak = 4.0 * peaks["bf16_burst"]
+    t_tensor = (flops / world) / (tensor_peak * 1e12)
+    if t_hbm >= t_tensor:
+        gbs = alg_bytes / (ms_per_step * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
+                    "peak_source": f"{peaks['source']} copy bandwidth", "traffic": None,
+                    "algorithmic_bytes_per_step": alg_bytes, "kernel": "nvfp4_gemm_kernel<1,256> grouped (FC1 + FC2)",
+                    "note": "whole-step time (8 kernels + 2 all-to-alls + one host sync) against the bytes of the two grouped GEMMs"}
+    else:
+        roofline = {"bound": "tensor", "achieved": value / world, "peak": tensor_peak, "unit": "TFLOP/s",
+                    "frac": value / world / tensor_peak, "peak_source": f"4 x {peaks['source']} cuBLAS bf16 (burst)",
+                    "traffic": None, "kernel": "nvfp4_gemm_kernel<1,256> grouped (FC1 + FC2)",
+                    "note": "whole-step time against the FLOPs of the two grouped GEMMs"}
+    print(json.dumps({
+        "metric": "nvfp4_moe_tflops", "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "nvfp4 operands, f32 accumulate, bf16 activations and output", "data": "synthetic",
+        "config": {"workload": args.workload, "tokens_per_gpu": tokens, **MOE_SHAPE, "expert_parallel": world,
+                   "experts_touched_rank0": touched, "l2": "expert weights (3.6 GB per 256 experts) far exceed L2; inputs rotate over 4 sets"},
+        "clocks": clocks,
+        "e2e": {"value": flops / (e2e_ms / e2e_steps * 1e-3) / 1e12, "unit": UNIT,
+                "h2d_bytes_per_step": tokens * (H * 2 + topk * 12), "d2h_bytes_per_step": tokens * H * 2, "steps": e2e_steps,
+                "call": "Nvfp4MoE.forward on tensors copied from pinned host memory, result copied back"},
+        "gpu_launches": int(launches), "roofline": roofline, "cpu_baseline": None,
+    }))
+    layer.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="gemm8192", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="gemm8192", choices=sorted(WORKLOADS) + sorted(MOE_WORKLOADS))
     ap.add_argument("--gather", action="store_true", help="N>1: include the all-gather of C in every step")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
@@ -319,6 +426,10 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
+        if args.workload in MOE_WORKLOADS:
+            if rank == 0:
+                print(json.dumps({"impl": "reference", "unavailable": "the CPU reference arm times the GEMM workloads only"}))
+            return
         run_reference(args, rank, world)
         return
     if world > 1:
@@ -328,7 +439,10 @@ def main():
         from datetime import timedelta
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), timeout=timedelta(seconds=90))
     try:
-        run_ours(args, rank, world, local_rank)
+        if args.workload in MOE_WORKLOADS:
+            run_moe(args, rank, world, local_rank)
+        else:
+            run_ours(args, rank, world, local_rank)
     finally:
         if world > 1:
             import torch.distributed as dist

@@ -26,6 +26,24 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+def exchange_splits(counts_matrix: torch.Tensor, rank: int, local_experts: int):
+    """Row counts of the two all-to-alls from the all-gathered route counts.
+
+    counts_matrix [world, experts] (host): routes rank r sends to global expert e. A rank's send buffer
+    is ordered by global expert id, i.e. by destination rank and, inside one destination, by its local
+    expert; so the dispatch sends `send[d]` consecutive rows to rank d and receives `recv[r]` rows from
+    rank r, source-major. The combine runs the same exchange backwards. Also returns the pool rows this
+    rank needs (each local expert padded to whole 128-row blocks).
+    """
+    world = counts_matrix.shape[0]
+    per_pair = counts_matrix.view(world, world, local_experts)           # [src, dst, local expert]
+    send = per_pair[rank].sum(-1).tolist()
+    recv = per_pair[:, rank].sum(-1).tolist()
+    expert_rows = per_pair[:, rank].sum(0)
+    need = int(((expert_rows + 127) // 128 * 128).sum())
+    return send, recv, need
+
+
 class Nvfp4MoE:
     def __init__(self, w1: torch.Tensor, w2: torch.Tensor, num_experts: int, topk: int, clamp: float = 10.0,
                  max_tokens: int = 4096, group=None, pool_rows: int | None = None):
@@ -108,11 +126,7 @@ class Nvfp4MoE:
             self.send_offset.data_ptr(), self.seg_src.data_ptr(), self.seg_pool.data_ptr(),
             self.block_expert.data_ptr(), self.num_blocks.data_ptr(), self.totals.data_ptr(), s))
         # the split sizes of the all-to-all have to be host integers: one small D2H copy per call
-        host = self.counts_matrix.cpu().view(self.world, self.world, self.local_experts).sum(-1)   # [src, dst]
-        send_splits = host[self.rank].tolist()
-        recv_splits = host[:, self.rank].tolist()
-        expert_rows = self.counts_matrix.cpu().view(self.world, self.world, self.local_experts)[:, self.rank].sum(0)
-        need = int(((expert_rows + 127) // 128 * 128).sum())
+        send_splits, recv_splits, need = exchange_splits(self.counts_matrix.cpu(), self.rank, self.local_experts)
         if need > self.pool_rows:
             raise RuntimeError(f"expert pool overflow: {need} rows needed, {self.pool_rows} allocated")
         return send_splits, recv_splits

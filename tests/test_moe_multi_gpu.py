@@ -1,0 +1,59 @@
+"""Expert parallelism over two GPUs (NCCL all-to-all each way) against the CPU oracle.
+Skipped on a single-GPU box; run with two or more GPUs visible."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    from datetime import timedelta
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank),
+                            timeout=timedelta(seconds=60))
+    try:
+        import gpu_kernels_b200 as g
+        from oracle import moe_oracle as MO
+        hidden, inter, experts, topk = 512, 256, 8, 2
+        local = experts // world
+        gen = torch.Generator(device="cuda").manual_seed(100)                # same weights on every rank
+        w1 = (torch.randn((experts, 2 * inter, hidden), generator=gen, device="cuda") * 0.02).bfloat16()
+        w2 = (torch.randn((experts, hidden, inter), generator=gen, device="cuda") * 0.02).bfloat16()
+        layer = g.Nvfp4MoE(w1[rank * local:(rank + 1) * local], w2[rank * local:(rank + 1) * local], experts, topk,
+                           max_tokens=128)
+        for call, tokens in enumerate((50 + 30 * rank, 7)):                   # ragged token counts, two calls
+            gen_r = torch.Generator(device="cuda").manual_seed(1000 * call + rank)
+            x = torch.randn((tokens, hidden), generator=gen_r, device="cuda").bfloat16()
+            ids, wts = g.route(torch.randn((tokens, experts), generator=gen_r, device="cuda"), topk)
+            y = layer(x, ids, wts)
+            torch.cuda.synchronize()
+            ref = MO.moe_forward_nvfp4(x.float().cpu().numpy(), ids.cpu().numpy(), wts.cpu().numpy(),
+                                       w1.float().cpu().numpy(), w2.float().cpu().numpy(), 10.0)
+            got = y.float().cpu().numpy()
+            rel = np.linalg.norm(got - ref) / np.linalg.norm(ref)
+            assert not np.isnan(got).any() and rel <= 2e-2, f"rank {rank} call {call}: rel {rel:.3e}"
+        layer.close()
+        open(os.path.join(out_dir, f"ok{rank}"), "w").close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_expert_parallel_two_gpus(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world, port = 2, _free_port()
+    mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    assert all((tmp_path / f"ok{r}").exists() for r in range(world))
