@@ -259,15 +259,6 @@ struct Roles {
             unsigned long long* tr = nullptr;
             if (g.prof && unit == 0 && lane == 0 && iter > 0 && iter <= TR_TILES)
                 tr = g.prof + size_t(units) * CG * PROF_WORDS + size_t(iter - 1) * 8;
-            if (iter > 0) {
-                // The epilogue has pulled the columns this tile shares with the previous one.
-                const long long w0 = g.prof ? clock64() : 0;
-                if (tr) tr[0] = w0;
-                const bool ok = wait(&ctrl->acc_free, (iter - 1u) & 1u, lane == 0 ? STATUS_TIMEOUT_MMA : 0u, 0x20000000u | iter);
-                if (!__all_sync(0xFFFFFFFFu, ok)) return;
-                if (g.prof) wait_acc += clock64() - w0;
-                if (tr) tr[1] = clock64();
-            }
             for (int ks = 0; ks < ksteps; ++ks) {
                 if (!landed) {
                     const long long w0 = g.prof ? clock64() : 0;
@@ -283,22 +274,42 @@ struct Roles {
                 const uint32_t lo = ring_lo + uint32_t(stage) * (Cfg::STAGE_BYTES >> 4);
                 const uint32_t empty = bar(&ctrl->empty[stage]);
                 const uint32_t first = ks != 0 ? 1u : 0u;
+                auto copies = [&](int j) {
+                    const uint32_t sf = sf_tmem + j * Cfg::SF_COLS_PER_MMA;
+                    tmem_copy_scales<CG>(sf, (lo + ((Cfg::OFF_SFA + j * SF_ATOM_BYTES) >> 4)) | SCALE_LBO, SCALE_HI);
+                    #pragma unroll
+                    for (int b = 0; b < Cfg::SFB_BLOCKS; ++b)
+                        tmem_copy_scales<CG>(sf + 4 + 4 * b,
+                                             (lo + ((Cfg::OFF_SFB + b * Cfg::SFB_BLOCK_BYTES + j * SF_ATOM_BYTES) >> 4)) | SCALE_LBO,
+                                             SCALE_HI);
+                };
+                auto mma = [&](int j) {
+                    // K advances 32 bytes inside the 128-byte swizzled row per MMA.
+                    const uint32_t sf = sf_tmem + j * Cfg::SF_COLS_PER_MMA;
+                    mma_nvfp4<CG>(acc, lo + ((j * (MMA_K / 2)) >> 4), lo + ((Cfg::OFF_B + j * (MMA_K / 2)) >> 4),
+                                  OPERAND_HI, Cfg::IDESC, sf, sf + 4, j != 0 ? 1u : first);
+                };
+                const bool handover = ks == 0 && iter > 0;
+                if (handover) {
+                    // First step of a tile: the scale copies do not touch the accumulators, so they go out
+                    // before the wait for the epilogue to pull the columns this tile shares with the last one.
+                    if (copy_scales && elect_one()) {
+                        #pragma unroll
+                        for (int j = 0; j < STAGE_K / MMA_K; ++j) copies(j);
+                    }
+                    const long long w0 = g.prof ? clock64() : 0;
+                    if (tr) tr[0] = w0;
+                    const bool ok = wait(&ctrl->acc_free, (iter - 1u) & 1u, lane == 0 ? STATUS_TIMEOUT_MMA : 0u, 0x20000000u | iter);
+                    if (!__all_sync(0xFFFFFFFFu, ok)) return;
+                    if (g.prof) wait_acc += clock64() - w0;
+                    if (tr) tr[1] = clock64();
+                    tc_fence_after_sync();
+                }
                 if (elect_one()) {
                     #pragma unroll
                     for (int j = 0; j < STAGE_K / MMA_K; ++j) {
-                        const uint32_t sf = sf_tmem + j * Cfg::SF_COLS_PER_MMA;
-                        if (copy_scales) {
-                            tmem_copy_scales<CG>(sf, (lo + ((Cfg::OFF_SFA + j * SF_ATOM_BYTES) >> 4)) | SCALE_LBO, SCALE_HI);
-                            #pragma unroll
-                            for (int b = 0; b < Cfg::SFB_BLOCKS; ++b)
-                                tmem_copy_scales<CG>(sf + 4 + 4 * b,
-                                                     (lo + ((Cfg::OFF_SFB + b * Cfg::SFB_BLOCK_BYTES + j * SF_ATOM_BYTES) >> 4)) | SCALE_LBO,
-                                                     SCALE_HI);
-                        }
-                        // K advances 32 bytes inside the 128-byte swizzled row per MMA.
-                        if (do_mma)
-                            mma_nvfp4<CG>(acc, lo + ((j * (MMA_K / 2)) >> 4), lo + ((Cfg::OFF_B + j * (MMA_K / 2)) >> 4),
-                                          OPERAND_HI, Cfg::IDESC, sf, sf + 4, j != 0 ? 1u : first);
+                        if (copy_scales && !handover) copies(j);
+                        if (do_mma) mma(j);
                     }
                     mma_commit<CG>(empty);                      // stage reusable once these MMAs retire
                     if (ks == ksteps - 1) mma_commit<CG>(bar(&ctrl->acc_full));

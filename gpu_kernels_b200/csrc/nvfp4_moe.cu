@@ -44,60 +44,79 @@ __global__ void route_count_kernel(const long long* __restrict__ ids, int routes
         if (local[e]) atomicAdd(&counts[e], local[e]);
 }
 
-// counts[r * experts + ge]: routes rank r sends to global expert ge. One CTA; experts <= 4096.
+// Exclusive prefix sum over n <= 4096 ints held in shared memory, by one CTA of 256 threads: each thread
+// scans a contiguous chunk serially, the chunk totals are scanned by one thread (<= 256 values).
+__device__ void block_exclusive_scan(int* data, int n, int* chunk_sums) {
+    const int per = (n + int(blockDim.x) - 1) / int(blockDim.x);
+    const int lo = min(int(threadIdx.x) * per, n), hi = min(lo + per, n);
+    int acc = 0;
+    for (int i = lo; i < hi; ++i) { const int v = data[i]; data[i] = acc; acc += v; }
+    chunk_sums[threadIdx.x] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (unsigned i = 0; i < blockDim.x; ++i) { const int v = chunk_sums[i]; chunk_sums[i] = run; run += v; }
+        chunk_sums[blockDim.x] = run;
+    }
+    __syncthreads();
+    for (int i = lo; i < hi; ++i) data[i] += chunk_sums[threadIdx.x];
+    __syncthreads();
+}
+
+// counts[r * experts + ge]: routes rank r sends to global expert ge. One CTA of 256 threads; experts <= 4096.
 __global__ void plan_kernel(const int* __restrict__ counts, int world, int rank, int experts, int capacity_rows,
                             int* __restrict__ send_offset, int* __restrict__ seg_src_offset,
                             int* __restrict__ seg_pool_offset, int* __restrict__ block_expert,
                             int* __restrict__ num_blocks, int* __restrict__ totals) {
     extern __shared__ int sh[];
     const int local_experts = experts / world;
-    int* expert_rows = sh;                           // [local_experts] rows routed to each local expert
-    int* pool_off = sh + local_experts;              // [local_experts + 1] padded prefix
+    const int segments = world * local_experts;          // == experts
+    int* scan = sh;                                       // [experts] scratch for the three scans
+    int* pool_off = sh + experts;                         // [local_experts] padded start of each expert
+    int* chunk = pool_off + local_experts;                // [blockDim.x + 1]
+    // 1. where this rank's routes go in its send buffer (ordered by global expert = by destination rank)
+    for (int ge = threadIdx.x; ge < experts; ge += blockDim.x) scan[ge] = counts[rank * experts + ge];
+    __syncthreads();
+    block_exclusive_scan(scan, experts, chunk);
+    for (int ge = threadIdx.x; ge < experts; ge += blockDim.x) send_offset[ge] = scan[ge];
+    if (threadIdx.x == 0) send_offset[experts] = chunk[blockDim.x];
+    __syncthreads();
+    // 2. segments (source rank r, local expert e) in the receive buffer: source-major, expert order inside
+    //    a source, which is the order pack() wrote them
+    for (int i = threadIdx.x; i < segments; i += blockDim.x) {
+        const int r = i / local_experts, e = i - r * local_experts;
+        scan[i] = counts[r * experts + rank * local_experts + e];
+    }
+    __syncthreads();
+    block_exclusive_scan(scan, segments, chunk);
+    for (int i = threadIdx.x; i < segments; i += blockDim.x) seg_src_offset[i] = scan[i];
+    if (threadIdx.x == 0) { seg_src_offset[segments] = chunk[blockDim.x]; totals[0] = chunk[blockDim.x]; }
+    __syncthreads();
+    // 3. expert-major pool, every expert padded to whole 128-row blocks
     for (int e = threadIdx.x; e < local_experts; e += blockDim.x) {
         int sum = 0;
         for (int r = 0; r < world; ++r) sum += counts[r * experts + rank * local_experts + e];
-        expert_rows[e] = sum;
+        scan[e] = (sum + 127) / 128 * 128;
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        // where this rank's routes go in its send buffer (ordered by global expert = by destination rank)
-        int acc = 0;
-        for (int ge = 0; ge < experts; ++ge) { send_offset[ge] = acc; acc += counts[rank * experts + ge]; }
-        send_offset[experts] = acc;
-        // expert-major pool, every expert padded to whole 128-row blocks
-        int rows = 0, blocks = 0;
-        for (int e = 0; e < local_experts; ++e) {
-            pool_off[e] = rows;
-            const int padded = (expert_rows[e] + 127) / 128 * 128;
-            for (int b = 0; b < padded / 128 && (blocks + b) * 128 < capacity_rows; ++b) block_expert[blocks + b] = e;
-            rows += padded;
-            blocks += padded / 128;
-        }
-        pool_off[local_experts] = rows;
-        const bool overflow = rows > capacity_rows;
-        *num_blocks = overflow ? 0 : blocks;          // an overflowing plan computes nothing; the host reports it
-        totals[1] = rows;
-        totals[2] = overflow ? 1 : 0;
-    }
-    __syncthreads();
-    // segments (source rank r, local expert e): position in the receive buffer (source-major, expert
-    // order inside a source, which is the order pack() wrote them) and destination row in the pool
-    if (threadIdx.x == 0) {
-        int acc = 0;
-        for (int r = 0; r < world; ++r)
-            for (int e = 0; e < local_experts; ++e) {
-                seg_src_offset[r * local_experts + e] = acc;
-                acc += counts[r * experts + rank * local_experts + e];
-            }
-        seg_src_offset[world * local_experts] = acc;
-        totals[0] = acc;
-    }
+    block_exclusive_scan(scan, local_experts, chunk);
+    const int pool_rows = chunk[blockDim.x];
+    const bool overflow = pool_rows > capacity_rows;
     for (int e = threadIdx.x; e < local_experts; e += blockDim.x) {
-        int acc = pool_off[e];
+        pool_off[e] = scan[e];
+        const int end = e + 1 < local_experts ? scan[e + 1] : pool_rows;
+        if (!overflow)
+            for (int blk = scan[e] / 128; blk < end / 128; ++blk) block_expert[blk] = e;
+        int acc = scan[e];
         for (int r = 0; r < world; ++r) {
             seg_pool_offset[r * local_experts + e] = acc;
             acc += counts[r * experts + rank * local_experts + e];
         }
+    }
+    if (threadIdx.x == 0) {
+        *num_blocks = overflow ? 0 : pool_rows / 128;     // an overflowing plan computes nothing; the host reports it
+        totals[1] = pool_rows;
+        totals[2] = overflow ? 1 : 0;
     }
 }
 
@@ -168,8 +187,15 @@ swiglu_quant_kernel(const __nv_bfloat16* __restrict__ gate_up, const float* __re
         const size_t row = size_t(row_base + r);
         const uint4* gp = reinterpret_cast<const uint4*>(gate_up + row * (2 * inter) + k);
         const uint4* up = reinterpret_cast<const uint4*>(gate_up + row * (2 * inter) + inter + k);
-        const uint4 g4[2] = {__ldg(gp), __ldg(gp + 1)}, u4[2] = {__ldg(up), __ldg(up + 1)};
         const float w = pool_weight[row];
+        if (w == 0.0f) {
+            // Padding row of the pool (or a route that contributes nothing): act is all zeros, whose NVFP4
+            // encoding is the smallest scale and zero codes. No reason to read gate_up or evaluate anything.
+            *reinterpret_cast<uint2*>(act_packed + row * (inter / 2) + k / 2) = make_uint2(0u, 0u);
+            sf_tile[(kb >> 2) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (kb & 3)] = 0x01;
+            continue;
+        }
+        const uint4 g4[2] = {__ldg(gp), __ldg(gp + 1)}, u4[2] = {__ldg(up), __ldg(up + 1)};
         const uint32_t* gw = reinterpret_cast<const uint32_t*>(g4);
         const uint32_t* uw = reinterpret_cast<const uint32_t*>(u4);
         float v[16];
@@ -251,7 +277,7 @@ void moe_plan(const int* counts_matrix, int world, int rank, int experts, int po
         throw std::invalid_argument("moe plan: experts must divide over the ranks (and be <= 4096)");
     if (pool_capacity_rows <= 0 || pool_capacity_rows % 128) throw std::invalid_argument("moe plan: pool capacity must be a multiple of 128 rows");
     const int local = experts / world;
-    plan_kernel<<<1, 256, (2 * local + 1) * sizeof(int), stream>>>(counts_matrix, world, rank, experts, pool_capacity_rows,
+    plan_kernel<<<1, 256, (experts + local + 257) * sizeof(int), stream>>>(counts_matrix, world, rank, experts, pool_capacity_rows,
                                                                    send_offset, seg_src_offset, seg_pool_offset,
                                                                    block_expert, num_blocks, totals);
     cuda_check(cudaGetLastError());
