@@ -198,18 +198,24 @@ swiglu_quant_kernel(const __nv_bfloat16* __restrict__ gate_up, const float* __re
         const uint4 g4[2] = {__ldg(gp), __ldg(gp + 1)}, u4[2] = {__ldg(up), __ldg(up + 1)};
         const uint32_t* gw = reinterpret_cast<const uint32_t*>(g4);
         const uint32_t* uw = reinterpret_cast<const uint32_t*>(u4);
-        float v[16];
+        uint32_t act[8];                                       // bf16 pairs of the rounded activation
         #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            const uint32_t gbits = (i & 1) ? (gw[i >> 1] & 0xFFFF0000u) : (gw[i >> 1] << 16);
-            const uint32_t ubits = (i & 1) ? (uw[i >> 1] & 0xFFFF0000u) : (uw[i >> 1] << 16);
-            const float gate = fminf(__uint_as_float(gbits), clamp);
-            const float upv = fminf(fmaxf(__uint_as_float(ubits), -clamp), clamp);
-            const float silu = gate / (1.0f + expf(-gate));
-            v[i] = __bfloat162float(__float2bfloat16_rn(silu * upv * w));
+        for (int i = 0; i < 8; ++i) {
+            float a2[2];
+            #pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint32_t gbits = h ? (gw[i] & 0xFFFF0000u) : (gw[i] << 16);
+                const uint32_t ubits = h ? (uw[i] & 0xFFFF0000u) : (uw[i] << 16);
+                const float gate = fminf(__uint_as_float(gbits), clamp);
+                const float upv = fminf(fmaxf(__uint_as_float(ubits), -clamp), clamp);
+                const float silu = gate / (1.0f + expf(-gate));
+                a2[h] = silu * upv * w;
+            }
+            const __nv_bfloat162 p = __floats2bfloat162_rn(a2[0], a2[1]);
+            act[i] = *reinterpret_cast<const uint32_t*>(&p);
         }
         uint2 out;
-        const uint32_t sbyte = quantise_block<false>(v, out);
+        const uint32_t sbyte = quantise_block_pairs<Bf16Pairs>(act, out);
         *reinterpret_cast<uint2*>(act_packed + row * (inter / 2) + k / 2) = out;
         sf_tile[(kb >> 2) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (kb & 3)] = static_cast<uint8_t>(sbyte);
     }

@@ -23,31 +23,6 @@ constexpr int Q_COLS = 256;      // K values per CTA tile = 16 scale blocks = 4 
 constexpr int Q_THREADS = 256;
 
 template <typename T> struct Loader;
-template <> struct Loader<__nv_bfloat16> {
-    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[16]) {
-        const uint4 a = __ldg(reinterpret_cast<const uint4*>(p));
-        const uint4 b = __ldg(reinterpret_cast<const uint4*>(p) + 1);
-        const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-        #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            v[2 * i] = __uint_as_float(w[i] << 16);
-            v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
-        }
-    }
-};
-template <> struct Loader<__half> {
-    static __device__ __forceinline__ void load(const __half* p, float (&v)[16]) {
-        const uint4 a = __ldg(reinterpret_cast<const uint4*>(p));
-        const uint4 b = __ldg(reinterpret_cast<const uint4*>(p) + 1);
-        const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-        #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
-            v[2 * i] = f.x;
-            v[2 * i + 1] = f.y;
-        }
-    }
-};
 template <> struct Loader<float> {
     static __device__ __forceinline__ void load(const float* p, float (&v)[16]) {
         #pragma unroll
@@ -57,6 +32,25 @@ template <> struct Loader<float> {
         }
     }
 };
+
+template <typename T> struct PairFormat { using type = void; };
+template <> struct PairFormat<__nv_bfloat16> { using type = Bf16Pairs; };
+template <> struct PairFormat<__half> { using type = Fp16Pairs; };
+
+// One block of 16 values straight from global memory to its scale byte and packed codes.
+template <typename T>
+__device__ __forceinline__ uint32_t quantise_from(const T* p, uint2& out) {
+    if constexpr (sizeof(T) == 2) {
+        const uint4 a = __ldg(reinterpret_cast<const uint4*>(p));
+        const uint4 b = __ldg(reinterpret_cast<const uint4*>(p) + 1);
+        const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        return quantise_block_pairs<typename PairFormat<T>::type>(w, out);
+    } else {
+        float v[16];
+        Loader<T>::load(p, v);
+        return quantise_block<true>(v, out);
+    }
+}
 
 template <typename T>
 __global__ void __launch_bounds__(Q_THREADS)
@@ -69,23 +63,14 @@ quantise_kernel(const T* __restrict__ x, uint8_t* __restrict__ packed, uint8_t* 
     const int row_base = blockIdx.y * Q_ROWS;
     const int k = col0 + kb * 16;
     const bool live = k < K;                                   // K is a multiple of 64, the tile of 256
-    #pragma unroll 2
-    for (int pass = 0; pass < 8; pass += 4) {
-        float v[4][16];
-        #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int r = (pass + u) * 16 + warp * 2 + (lane >> 4);
-            if (live) Loader<T>::load(x + size_t(row_base + r) * K + k, v[u]);
-        }
-        #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int r = (pass + u) * 16 + warp * 2 + (lane >> 4);
-            if (live) {
-                uint2 out;
-                const uint32_t sbyte = quantise_block<sizeof(T) == 4>(v[u], out);
-                *reinterpret_cast<uint2*>(packed + size_t(row_base + r) * (K / 2) + k / 2) = out;
-                sf_tile[(kb >> 2) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (kb & 3)] = static_cast<uint8_t>(sbyte);
-            }
+    #pragma unroll 4
+    for (int pass = 0; pass < 8; ++pass) {
+        const int r = pass * 16 + warp * 2 + (lane >> 4);
+        if (live) {
+            uint2 out;
+            const uint32_t sbyte = quantise_from(x + size_t(row_base + r) * K + k, out);
+            *reinterpret_cast<uint2*>(packed + size_t(row_base + r) * (K / 2) + k / 2) = out;
+            sf_tile[(kb >> 2) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (kb & 3)] = static_cast<uint8_t>(sbyte);
         }
     }
     __syncthreads();

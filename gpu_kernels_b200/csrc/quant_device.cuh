@@ -3,6 +3,8 @@
 // (amax -> scale -> sixteen exact quotients -> E2M1 codes) and the scale-atom addressing.
 #pragma once
 
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <cstdint>
 
@@ -31,9 +33,8 @@ __device__ __forceinline__ float ue4m3_to_float(uint32_t code) {
 // byte 0). The hardware conversion rounds to nearest with ties to the even code and saturates at
 // 6, which is the reference's midpoint rule (reference/python/nvfp4.py:8-13); signs are added by
 // the caller because the reference's sign bit is (q < 0), not the sign of the input.
-// Measured alternatives on 8192 x 8192 bf16: sixteen IEEE divisions plus a compare ladder 110 us;
-// this conversion 74 us (its pipe is then the busiest unit); rounding with an FP-adder magic
-// constant plus shifts 88 us (instruction issue bound).
+// The conversion is slow (its pipe was the busiest unit when 16-bit inputs still came this way);
+// it remains for FP32 inputs, which have twice the bytes per value to hide it behind.
 __device__ __forceinline__ uint32_t e2m1x8_from_quotients(const float (&q)[8]) {
     uint32_t w;
     asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
@@ -98,6 +99,81 @@ __device__ __forceinline__ uint32_t quantise_block(const float (&v)[16], uint2& 
         words[h] = e2m1x8_from_quotients(q) | signs;
     }
     packed = make_uint2(words[0], words[1]);
+    return sbyte;
+}
+
+// ---- 16-bit inputs: two values per instruction, no division -----------------------------------
+//
+// For a bf16 or fp16 input the E2M1 code of x/s can be read off x itself: RN(x/s) lies above,
+// on or below a midpoint m exactly when |x| lies above, on or below m*s, and m*s is an exact
+// number with at most 7 significant bits (m has 3, an E4M3 scale 4), i.e. representable in the
+// input's own 16-bit format. So the block routine compares packed pairs of |x| against the seven
+// products m_j*s (strictly for the midpoints whose tie goes down, >= for those whose tie goes
+// up: reference/python/nvfp4.py:8-13) and counts. The count is accumulated on top of a constant
+// whose ulp is 1 (128 in bf16, 1024 in fp16), so the low bits of the sum are the code; the sign
+// bit (x < 0, false for -0.0 as in the reference, where q = -0.0 is not < 0) is added as 8.
+// No value of these formats is small enough for a non-zero quotient to round to zero.
+struct Bf16Pairs {
+    using pair = __nv_bfloat162;
+    static constexpr uint32_t INF_BITS = 0x7F80u;
+    static __device__ __forceinline__ pair from_bits(uint32_t w) { return *reinterpret_cast<const pair*>(&w); }
+    static __device__ __forceinline__ uint32_t bits(pair p) { return *reinterpret_cast<const uint32_t*>(&p); }
+    static __device__ __forceinline__ pair both(float v) { return __float2bfloat162_rn(v); }
+    static __device__ __forceinline__ float widen(uint32_t bits16) { return __uint_as_float(bits16 << 16); }
+    static __device__ __forceinline__ float count_base() { return 128.0f; }
+};
+struct Fp16Pairs {
+    using pair = __half2;
+    static constexpr uint32_t INF_BITS = 0x7C00u;
+    static __device__ __forceinline__ pair from_bits(uint32_t w) { return *reinterpret_cast<const pair*>(&w); }
+    static __device__ __forceinline__ uint32_t bits(pair p) { return *reinterpret_cast<const uint32_t*>(&p); }
+    static __device__ __forceinline__ pair both(float v) { return __float2half2_rn(v); }
+    static __device__ __forceinline__ float widen(uint32_t bits16) { return __half2float(__ushort_as_half(static_cast<unsigned short>(bits16))); }
+    static __device__ __forceinline__ float count_base() { return 1024.0f; }
+};
+
+// w[k] holds values 2k (low half) and 2k+1 (high half) of the block as raw 16-bit patterns.
+template <typename F>
+__device__ __forceinline__ uint32_t quantise_block_pairs(const uint32_t (&w)[8], uint2& packed) {
+    using pair = typename F::pair;
+    uint32_t a[8];
+    #pragma unroll
+    for (int k = 0; k < 8; ++k) a[k] = w[k] & 0x7FFF7FFFu;
+    // magnitudes of these formats order like their bit patterns
+    uint32_t m = __vimax3_u16x2(__vimax3_u16x2(a[0], a[1], a[2]), __vimax3_u16x2(a[3], a[4], a[5]), __vimax3_u16x2(a[6], a[7], a[7]));
+    const uint32_t top = max(m & 0xFFFFu, m >> 16);
+    if (top > F::INF_BITS) {
+        packed = make_uint2(0x77777777u, 0x77777777u);       // NaN block, as quantise_block
+        return 0x7Fu;
+    }
+    const float amax = F::widen(top);
+    // amax / 6, correctly rounded, without the division: reciprocal constant plus one residual step
+    const float sixth = 0.16666667163372039794921875f;       // RN(1/6)
+    const float d0 = __fmul_rn(amax, sixth);
+    const float de = __fmaf_rn(-d0, 6.0f, amax);
+    const float t = fminf(fmaxf(__fmaf_rn(de, sixth, d0), 0.001953125f), 448.0f);
+    const uint32_t sbyte = ue4m3_from_float(amax <= 3.0e38f ? t : 448.0f);
+    const float s = ue4m3_to_float(sbyte);
+    const pair t0 = F::both(0.25f * s), t1 = F::both(0.75f * s), t2 = F::both(1.25f * s), t3 = F::both(1.75f * s),
+               t4 = F::both(2.5f * s), t5 = F::both(3.5f * s), t6 = F::both(5.0f * s);
+    const pair base = F::both(F::count_base()), eight = F::both(8.0f), zero = F::both(0.0f);
+    uint32_t bytes[8];
+    #pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const pair mag = F::from_bits(a[k]);
+        pair n = __hadd2(base, __hgt2(mag, t0));
+        n = __hadd2(n, __hge2(mag, t1));
+        n = __hadd2(n, __hgt2(mag, t2));
+        n = __hadd2(n, __hge2(mag, t3));
+        n = __hadd2(n, __hgt2(mag, t4));
+        n = __hadd2(n, __hge2(mag, t5));
+        n = __hadd2(n, __hgt2(mag, t6));
+        n = __hfma2(__hlt2(F::from_bits(w[k]), zero), eight, n);
+        const uint32_t nib = F::bits(n) & 0x000F000Fu;
+        bytes[k] = (nib | (nib >> 12)) & 0xFFu;
+    }
+    packed = make_uint2(bytes[0] | (bytes[1] << 8) | (bytes[2] << 16) | (bytes[3] << 24),
+                        bytes[4] | (bytes[5] << 8) | (bytes[6] << 16) | (bytes[7] << 24));
     return sbyte;
 }
 

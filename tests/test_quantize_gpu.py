@@ -127,6 +127,23 @@ def test_division_free_path_every_bf16_against_every_scale(g):
     check_exact(g, torch.from_numpy(x).cuda(), p, sc)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_every_16bit_value_as_block_maximum(g, dtype):
+    # amax / 6 is computed without a division for 16-bit inputs: every positive pattern (NaNs and
+    # infinity included) alone in its block, and again beside smaller neighbours
+    bits = np.arange(0x8000, dtype=np.uint16)
+    vals = (O.bf16_to_f32(bits) if dtype == torch.bfloat16 else bits.view(np.float16).astype(np.float32))
+    x = np.zeros((256, 128 * 16), dtype=np.float32)
+    blocks = x.reshape(256, 128, 16)
+    blocks[:, :, 5] = vals.reshape(256, 128)
+    with np.errstate(invalid="ignore", over="ignore"):
+        blocks[:, :, 9] = np.where(np.isfinite(vals), -vals * np.float32(0.4140625), 0).reshape(256, 128)
+        blocks[:, :, 12] = np.where(np.isfinite(vals), vals * np.float32(0.2080078125), 0).reshape(256, 128)
+    xt = torch.from_numpy(x).cuda().to(dtype)
+    p, sc = O.quantize(xt.float().cpu().numpy())
+    check_exact(g, xt, p, sc)
+
+
 def test_every_bf16_value(g):
     # all 65536 bf16 bit patterns (NaNs and infinities included), one per block position in turn
     bits = np.arange(65536, dtype=np.uint16)
