@@ -255,6 +255,8 @@ int gpu_kernels_nvfp4_plan_set_option(void* plan, const char* key, int value) {
             p.params.group_m = value < tiles_m ? value : tiles_m;
         } else if (std::strcmp(key, "c_evict_first") == 0) {
             p.params.c_evict_first = value ? 1 : 0;
+        } else if (std::strcmp(key, "direct_store") == 0) {
+            p.params.direct_store = value ? 1 : 0;
         } else {
             throw std::invalid_argument(std::string("set_option: unknown key ") + key);
         }

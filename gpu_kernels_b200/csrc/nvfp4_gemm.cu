@@ -111,6 +111,11 @@ struct GemmArgs {
     const int* block_expert;
     const int* num_blocks;
     int b_rows_per_expert;
+    // Epilogue route: 0 = FP16/BF16 rows staged in swizzled shared memory and written by TMA stores,
+    // 1 = written straight from registers with 32-byte global stores (no shared-memory traffic).
+    int direct_store;
+    void* c;                        // C base and leading dimension (elements), used by the direct route
+    int ldc;
 };
 
 enum ProfSlot { PROF_PROD_WAIT = 0, PROF_PROD_TOTAL, PROF_MMA_WAIT_FULL, PROF_MMA_WAIT_ACC, PROF_MMA_TOTAL,
@@ -368,6 +373,31 @@ struct Roles {
                     if (lane == 0) mbar_arrive_cluster(acc_free_leader);
                     if (tr) tr[rank ? 1 : 2] = clock64();
                 }
+                if (g.debug & 8u) continue;                      // diagnostic: drain only
+                if (g.direct_store) {
+                    uint16_t* dst = static_cast<uint16_t*>(g.c) + size_t(row0 + lane) * g.ldc + col0 + chunk * EPI_COLS;
+                    #pragma unroll
+                    for (int q = 0; q < EPI_COLS / 16; ++q) {
+                        uint32_t h[8];
+                        #pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const float lo = __uint_as_float(v[q * 16 + 2 * i]) * alpha;
+                            const float hi = __uint_as_float(v[q * 16 + 2 * i + 1]) * alpha;
+                            if (g.out_bf16) {
+                                const __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+                                h[i] = *reinterpret_cast<const uint32_t*>(&p);
+                            } else {
+                                const __half2 p = __floats2half2_rn(lo, hi);
+                                h[i] = *reinterpret_cast<const uint32_t*>(&p);
+                            }
+                        }
+                        if (!(g.debug & 1u))
+                            asm volatile("st.global.L1::no_allocate.L2::evict_first.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                                         :: "l"(dst + q * 16), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]),
+                                            "r"(h[4]), "r"(h[5]), "r"(h[6]), "r"(h[7]) : "memory");
+                    }
+                    continue;
+                }
                 const uint32_t buf = stage_base + (stores & 1u) * Cfg::EPI_WARP_BYTES;
                 const long long s0 = g.prof ? clock64() : 0;
                 if (lane == 0) tma_store_wait_read<1>();        // the store that last read this buffer is done
@@ -567,11 +597,12 @@ int max_units(int device) {
 }
 
 template <int CG, int UN>
-void launch_variant(const gpu_kernels::Nvfp4Params& p, const CUtensorMap& tmC, uint32_t* status, cudaStream_t stream,
-                    unsigned long long* prof) {
+void launch_variant(const gpu_kernels::Nvfp4Params& p, const CUtensorMap& tmC, void* c, uint32_t* status,
+                    cudaStream_t stream, unsigned long long* prof) {
     using Cfg = Config<CG, UN>;
     GemmArgs g{p.M, p.N, p.K, p.M / Cfg::TILE_M, p.N / UN, std::max(1, p.group_m), p.alpha, status, prof,
-               uint32_t(env_int("NVFP4_B200_DEBUG", 0)), p.c_evict_first, 0, nullptr, nullptr, 0};
+               uint32_t(env_int("NVFP4_B200_DEBUG", 0)), p.c_evict_first, 0, nullptr, nullptr, 0,
+               p.direct_store, c, p.N};
     cudaLaunchAttribute attr{};
     attr.id = cudaLaunchAttributeClusterDimension;
     attr.val.clusterDim = {unsigned(CG), 1, 1};
@@ -613,11 +644,17 @@ void prepare(gpu_kernels::Nvfp4Params& p, const uint8_t* A, const uint8_t* B, co
     p.alpha = 1.0f;
     p.device = device;
     p.c_evict_first = env_int("NVFP4_B200_C_EVICT_FIRST", 1);
+
     const int force = env_int("NVFP4_B200_VARIANT", 0);        // 0 auto, 2256 / 1256 / 1128 for experiments
     if ((force == 0 && M % 256 == 0 && N % 256 == 0) || force == 2256) { p.cta_group = 2; p.tile_n = 256; }
     else if ((force == 0 && N % 256 == 0) || force == 1256) { p.cta_group = 1; p.tile_n = 256; }
     else { p.cta_group = 1; p.tile_n = 128; }
     if (M % (128 * p.cta_group) || N % p.tile_n) throw std::invalid_argument("nvfp4 gemm: forced variant does not divide the shape");
+    // Epilogue route. With a long K loop both routes cost the same (the C bytes share the SM's L2 port
+    // with the loads either way: 274.8k vs 275.8k cycles at 8192^3) and C goes out by TMA store; when the
+    // epilogue is a large share of a tile (short K) or the tile is a single CTA's, writing from registers
+    // is faster (4096x4096x1024: 21.8k vs 25.5k cycles; 128x28672x8192: 47.0k vs 48.7k).
+    p.direct_store = env_int("NVFP4_B200_DIRECT_STORE", (K <= 2048 || p.cta_group == 1) ? 1 : 0);
     const int box_b = p.tile_n / p.cta_group;
     p.A = operand_map(A, M, K, BLOCK_M);
     p.B = operand_map(B, N, K, box_b);
@@ -638,9 +675,9 @@ void launch_with(const gpu_kernels::Nvfp4Params& p, __half* C, cudaStream_t stre
     if (!C || (reinterpret_cast<uintptr_t>(C) & 15)) throw std::invalid_argument("nvfp4 gemm: C must be 16-byte aligned");
     const CUtensorMap tmC = output_map(C, p.M, p.N);
     uint32_t* status = status_word(p.device);
-    if (p.cta_group == 2) launch_variant<2, 256>(p, tmC, status, stream, prof);
-    else if (p.tile_n == 256) launch_variant<1, 256>(p, tmC, status, stream, prof);
-    else launch_variant<1, 128>(p, tmC, status, stream, prof);
+    if (p.cta_group == 2) launch_variant<2, 256>(p, tmC, C, status, stream, prof);
+    else if (p.tile_n == 256) launch_variant<1, 256>(p, tmC, C, status, stream, prof);
+    else launch_variant<1, 128>(p, tmC, C, status, stream, prof);
 }
 
 void launch(const gpu_kernels::Nvfp4Params& p, __half* C, cudaStream_t stream) { launch_with(p, C, stream, nullptr); }
@@ -717,7 +754,7 @@ void grouped_launch(const GroupedGemm& p, void* C, int out_bf16, cudaStream_t st
                                         uint64_t(p.n), uint64_t(p.pool_rows), uint64_t(p.n) * 2, EPI_COLS, 32,
                                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE);
     GemmArgs g{p.pool_rows, p.n, p.k, p.pool_rows / 128, p.n / 256, 1, 1.0f, status_word(p.device), nullptr,
-               0u, 1, out_bf16, p.block_expert, p.num_blocks, p.n};
+               0u, 1, out_bf16, p.block_expert, p.num_blocks, p.n, env_int("NVFP4_B200_DIRECT_STORE", 1), C, p.n};
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(unsigned(p.units));
     cfg.blockDim = dim3(NUM_THREADS);

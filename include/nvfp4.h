@@ -38,6 +38,7 @@ struct Nvfp4Params {
     int group_m;                    // tile rows per rasterisation band
     int device;                     // device the plan was prepared on
     int c_evict_first;              // 1: C is stored with the evict-first L2 policy
+    int direct_store;               // 1: epilogue writes C from registers instead of TMA stores
 };
 
 struct Nvfp4Implementation {

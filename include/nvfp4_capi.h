@@ -54,7 +54,7 @@ int gpu_kernels_nvfp4_dequantize(const void* packed, const void* scales, void* o
 /* FP32 global scale: C = fp16(alpha * accumulator). The reference fixes alpha = 1 (nvfp4_bridge.cu:101). */
 int gpu_kernels_nvfp4_plan_set_alpha(void* plan, float alpha);
 /* Tuning knobs. key: "group_m" (tile rows per rasterisation band, >= 1); "c_evict_first" (0/1: L2 policy
- * of the C stores). */
+ * of the C stores); "direct_store" (0/1: epilogue writes C from registers instead of staging it for TMA stores). */
 int gpu_kernels_nvfp4_plan_set_option(void* plan, const char* key, int value);
 /* Fills info[0..7] = {M, N, K, units, cta_group, tile_n, group_m, stages}. */
 int gpu_kernels_nvfp4_plan_info(void* plan, int* info);
