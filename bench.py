@@ -38,6 +38,8 @@ WORKLOADS = {
 # Routed-MoE expert layer (H=4096, I=2048, 256 experts, top-6), tokens PER GPU; experts are split over the ranks.
 MOE_WORKLOADS = {"moe_t1": 1, "moe_t64": 64, "moe_t1024": 1024, "moe_t4096": 4096}
 MOE_SHAPE = {"hidden": 4096, "inter": 2048, "experts": 256, "topk": 6, "clamp": 10.0}
+# Stand-alone quantise/pack kernel: (rows, K) of a bf16 operand.
+QUANT_WORKLOADS = {"quantise8192": (8192, 8192), "quantise16384": (16384, 16384), "quantise_skinny_b": (28672, 8192)}
 METRIC = "nvfp4_gemm_tflops"
 UNIT = "TFLOP/s"
 NOMINAL_FP4_TFLOPS = 9000.0
@@ -308,6 +310,49 @@ def run_ours(args, rank, world, local_rank):
     }))
 
 
+def run_quantise(args, rank, world, local_rank):
+    """One step = quantise one bf16 [rows, K] operand (different copies in turn, together larger than L2)."""
+    import torch
+    import gpu_kernels_b200 as g
+    from gpu_kernels_b200 import _lib
+    if rank != 0:
+        return
+    torch.cuda.set_device(local_rank)
+    rows, k = QUANT_WORKLOADS[args.workload]
+    copies = max(2, (512 << 20) // (rows * k * 2))
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    xs = [torch.randn((rows, k), generator=gen, device="cuda").bfloat16() for _ in range(copies)]
+    packed = torch.empty((rows, k // 2), dtype=torch.uint8, device="cuda")
+    scales = torch.empty(rows * k // 16, dtype=torch.uint8, device="cuda")
+    lib, stream = _lib.load(), torch.cuda.current_stream().cuda_stream
+    def step(i):
+        _lib.check(lib.gpu_kernels_nvfp4_quantize(xs[i % copies].data_ptr(), 0, packed.data_ptr(), scales.data_ptr(), rows, k, stream))
+    for i in range(max(3, args.warmup)):
+        step(i)
+    torch.cuda.synchronize()
+    n0 = _lib.launch_count()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(args.steps):
+        step(i)
+    stop.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(stop) / args.steps
+    alg = rows * k * 2 + rows * k // 2 + rows * k // 16
+    gbs = alg / (ms * 1e-3) / 1e9
+    peaks = measured_peaks()
+    print(json.dumps({
+        "metric": "nvfp4_quantise_gbs", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16 in, e2m1 + ue4m3 out", "data": "synthetic",
+        "config": {"workload": args.workload, "rows": rows, "K": k, "l2": f"{copies} input copies in turn ({copies * rows * k * 2 >> 20} MiB)"},
+        "gpu_launches": int(_lib.launch_count() - n0),
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
+                     "peak_source": f"{peaks['source']} copy bandwidth", "kernel": "quantise_kernel<bf16>",
+                     "algorithmic_bytes_per_launch": alg, "traffic": None},
+        "cpu_baseline": None, "e2e": None}))
+
+
 def run_moe(args, rank, world, local_rank):
     """One step = one forward of the NVFP4 expert layer on `tokens` tokens per GPU (weak scaling in tokens)."""
     import torch
@@ -418,7 +463,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="gemm8192", choices=sorted(WORKLOADS) + sorted(MOE_WORKLOADS))
+    ap.add_argument("--workload", default="gemm8192", choices=sorted(WORKLOADS) + sorted(MOE_WORKLOADS) + sorted(QUANT_WORKLOADS))
     ap.add_argument("--gather", action="store_true", help="N>1: include the all-gather of C in every step")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
@@ -426,7 +471,7 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
-        if args.workload in MOE_WORKLOADS:
+        if args.workload in MOE_WORKLOADS or args.workload in QUANT_WORKLOADS:
             if rank == 0:
                 print(json.dumps({"impl": "reference", "unavailable": "the CPU reference arm times the GEMM workloads only"}))
             return
@@ -441,6 +486,8 @@ def main():
     try:
         if args.workload in MOE_WORKLOADS:
             run_moe(args, rank, world, local_rank)
+        elif args.workload in QUANT_WORKLOADS:
+            run_quantise(args, rank, world, local_rank)
         else:
             run_ours(args, rank, world, local_rank)
     finally:

@@ -125,6 +125,10 @@ class Nvfp4MoE:
             self.counts_matrix.data_ptr(), self.world, self.rank, self.experts, self.pool_rows,
             self.send_offset.data_ptr(), self.seg_src.data_ptr(), self.seg_pool.data_ptr(),
             self.block_expert.data_ptr(), self.num_blocks.data_ptr(), self.totals.data_ptr(), s))
+        if self.world == 1 and self.pool_rows >= routes + self.local_experts * 127:
+            # one rank, pool sized for the worst case: nothing to exchange and nothing can overflow, so the
+            # host never has to look at the counts and the whole forward stays asynchronous
+            return [routes], [routes]
         # the split sizes of the all-to-all have to be host integers: one small D2H copy per call
         send_splits, recv_splits, need = exchange_splits(self.counts_matrix.cpu(), self.rank, self.local_experts)
         if need > self.pool_rows:
