@@ -67,7 +67,10 @@ struct Config {
     static constexpr int OFF_SFB = OFF_SFA + SFA_BYTES;
     static constexpr int STAGE_BYTES = OFF_SFB + SFB_BYTES;
     static constexpr int EPI_WARP_BYTES = 32 * EPI_COLS * 2;     // 32 rows x 128 B
-    static constexpr int EPI_BYTES = 4 * 2 * EPI_WARP_BYTES;     // 4 warps, double-buffered
+    // Single-CTA tiles write C straight from registers, so they keep no staging and get a deeper
+    // ring instead (their workloads stream weights from HBM and live on bytes in flight).
+    static constexpr bool STAGED_EPILOGUE = CG == 2;
+    static constexpr int EPI_BYTES = STAGED_EPILOGUE ? 4 * 2 * EPI_WARP_BYTES : 0;   // 4 warps, double-buffered
     static constexpr int CTRL_BYTES = 1024;
     static constexpr int STAGES = (SMEM_LIMIT - 1024 - CTRL_BYTES - EPI_BYTES) / STAGE_BYTES;
     static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + CTRL_BYTES;
@@ -374,7 +377,7 @@ struct Roles {
                     if (tr) tr[rank ? 1 : 2] = clock64();
                 }
                 if (g.debug & 8u) continue;                      // diagnostic: drain only
-                if (g.direct_store) {
+                if (!Cfg::STAGED_EPILOGUE || g.direct_store) {
                     uint16_t* dst = static_cast<uint16_t*>(g.c) + size_t(row0 + lane) * g.ldc + col0 + chunk * EPI_COLS;
                     #pragma unroll
                     for (int q = 0; q < EPI_COLS / 16; ++q) {

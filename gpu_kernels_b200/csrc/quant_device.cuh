@@ -154,8 +154,11 @@ __device__ __forceinline__ uint32_t quantise_block_pairs(const uint32_t (&w)[8],
     const float t = fminf(fmaxf(__fmaf_rn(de, sixth, d0), 0.001953125f), 448.0f);
     const uint32_t sbyte = ue4m3_from_float(amax <= 3.0e38f ? t : 448.0f);
     const float s = ue4m3_to_float(sbyte);
-    const pair t0 = F::both(0.25f * s), t1 = F::both(0.75f * s), t2 = F::both(1.25f * s), t3 = F::both(1.75f * s),
-               t4 = F::both(2.5f * s), t5 = F::both(3.5f * s), t6 = F::both(5.0f * s);
+    // one conversion of the scale, then exact 16-bit products (<= 7 significant bits each)
+    const pair s2 = F::both(s);
+    const pair t0 = __hmul2(s2, F::both(0.25f)), t1 = __hmul2(s2, F::both(0.75f)), t2 = __hmul2(s2, F::both(1.25f)),
+               t3 = __hmul2(s2, F::both(1.75f)), t4 = __hmul2(s2, F::both(2.5f)), t5 = __hmul2(s2, F::both(3.5f)),
+               t6 = __hmul2(s2, F::both(5.0f));
     const pair base = F::both(F::count_base()), eight = F::both(8.0f), zero = F::both(0.0f);
     uint32_t bytes[8];
     #pragma unroll
