@@ -236,6 +236,28 @@ def run_ours(args, rank, world, local_rank):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
 
+    # The library bar on the same box in the same run: cuBLASLt's own NVFP4 matmul on the same operands.
+    library_bar = None
+    if world == 1:
+        try:
+            ws = torch.empty(64 << 20, dtype=torch.uint8, device=dev)
+            lt_plans = [g.Nvfp4Gemm(x[0], x[2], x[1], x[3], workspace=ws) for x in sets]
+            for i in range(3):
+                lt_plans[i % rotations].run_cublaslt(out)
+            torch.cuda.synchronize()
+            start.record()
+            for i in range(args.steps):
+                lt_plans[i % rotations].run_cublaslt(out)
+            stop.record()
+            torch.cuda.synchronize()
+            lt_ms = start.elapsed_time(stop) / args.steps
+            library_bar = {"name": "cuBLASLt NVFP4 matmul (VEC16_UE4M3), same operands, same run",
+                           "ms_per_step": lt_ms, "value": 2.0 * m * n * k / (lt_ms * 1e-3) / 1e12, "unit": UNIT}
+            for p_ in lt_plans:
+                p_.close()
+        except Exception as exc:                                  # the bar is informative only
+            library_bar = {"name": "cuBLASLt NVFP4 matmul", "unavailable": str(exc)[:200]}
+
     # End to end through the C ABI with HOST buffers: H2D of the operands, kernel, D2H of C, every step.
     host = [t.cpu().pin_memory() for t in (pa, pb, sa, sb)]
     host_c = torch.empty((m, n_local), dtype=torch.float16).pin_memory()
@@ -307,6 +329,7 @@ def run_ours(args, rank, world, local_rank):
         "gpu_launches": int(launches),
         "roofline": roofline,
         "cpu_baseline": cpu,
+        "library_bar": library_bar,
     }))
 
 
