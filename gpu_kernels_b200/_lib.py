@@ -34,6 +34,7 @@ SIGNATURES = {
     "gpu_kernels_nvfp4_grouped_plan_create": ([ctypes.POINTER(P), I, I, I, I, P, P, P, P, P, P], I),
     "gpu_kernels_nvfp4_grouped_plan_destroy": ([P], None),
     "gpu_kernels_nvfp4_grouped_run": ([P, P, I, P], I),
+    "gpu_kernels_nvfp4_grouped_run_swiglu": ([P, P, F, P, P, P], I),
     "gpu_kernels_nvfp4_moe_payload_bytes": ([I], I),
     "gpu_kernels_nvfp4_moe_route_count": ([P, I, I, P, P], I),
     "gpu_kernels_nvfp4_moe_plan": ([P, I, I, I, I, P, P, P, P, P, P, P], I),

@@ -350,6 +350,16 @@ int gpu_kernels_nvfp4_grouped_run(void* plan, void* C, int out_bf16, void* strea
     });
 }
 
+int gpu_kernels_nvfp4_grouped_run_swiglu(void* plan, const void* row_weight, float clamp, void* act_packed,
+                                         void* act_scales, void* stream) {
+    return guarded([&] {
+        if (!plan) throw std::invalid_argument("null plan");
+        nvfp4_b200::grouped_launch_fused(*static_cast<nvfp4_b200::GroupedGemm*>(plan), nullptr, 1,
+                                         static_cast<uint8_t*>(act_packed), static_cast<uint8_t*>(act_scales),
+                                         static_cast<const float*>(row_weight), clamp, static_cast<cudaStream_t>(stream));
+    });
+}
+
 int gpu_kernels_nvfp4_moe_payload_bytes(int hidden) { return nvfp4_b200::moe_payload_bytes(hidden); }
 
 int gpu_kernels_nvfp4_moe_route_count(const void* ids, int routes, int experts, void* counts, void* stream) {

@@ -19,6 +19,7 @@
 #include "nvfp4.h"
 #include "nvfp4_internal.h"
 #include "ptx.cuh"
+#include "quant_device.cuh"
 
 #include <cuda_bf16.h>
 
@@ -119,6 +120,14 @@ struct GemmArgs {
     int direct_store;
     void* c;                        // C base and leading dimension (elements), used by the direct route
     int ldc;
+    // Fused first expert GEMM (grouped mode only): the weight rows arrive interleaved as 16 gate rows, 16 up
+    // rows, ..., so a lane's 64 accumulator columns are two (gate, up) block pairs; the epilogue rounds them to
+    // bf16, applies the clamped SwiGLU and the row's route weight, rounds to bf16, quantises each 16-value
+    // block to NVFP4 and writes packed codes and scale bytes for the second GEMM. Null act_packed = off.
+    uint8_t* act_packed;            // [pool_rows, N/4] (N/2 activation columns, two per byte)
+    uint8_t* act_scales;            // VEC16 layout of [pool_rows, N/2]
+    const float* row_weight;        // [pool_rows]
+    float swiglu_clamp;
 };
 
 enum ProfSlot { PROF_PROD_WAIT = 0, PROF_PROD_TOTAL, PROF_MMA_WAIT_FULL, PROF_MMA_WAIT_ACC, PROF_MMA_TOTAL,
@@ -377,6 +386,45 @@ struct Roles {
                     if (tr) tr[rank ? 1 : 2] = clock64();
                 }
                 if (g.debug & 8u) continue;                      // diagnostic: drain only
+                if (g.act_packed) {
+                    const int inter = g.N / 2;
+                    const int row = row0 + lane;
+                    const float w = __ldg(g.row_weight + row);
+                    const int act_col = tn * (UN / 2) + chunk * (EPI_COLS / 2);        // first activation column of this chunk
+                    uint2 codes[2];
+                    uint32_t sb[2];
+                    if (w == 0.0f) {
+                        // padding row of the pool: the activation is zero (smallest scale, zero codes)
+                        codes[0] = codes[1] = make_uint2(0u, 0u);
+                        sb[0] = sb[1] = 0x01u;
+                    } else {
+                        const float c = g.swiglu_clamp;
+                        #pragma unroll
+                        for (int b = 0; b < 2; ++b) {
+                            uint32_t act[8];
+                            #pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                float a2[2];
+                                #pragma unroll
+                                for (int h = 0; h < 2; ++h) {
+                                    // gate_up is rounded to bf16 first, as the unfused pipeline stores it
+                                    const uint32_t gb = v[b * 32 + 2 * i + h], ub = v[b * 32 + 16 + 2 * i + h];
+                                    const float gate = fminf(__uint_as_float((gb + 0x7FFFu + ((gb >> 16) & 1u)) & 0xFFFF0000u), c);
+                                    const float up = fminf(fmaxf(__uint_as_float((ub + 0x7FFFu + ((ub >> 16) & 1u)) & 0xFFFF0000u), -c), c);
+                                    a2[h] = gate / (1.0f + expf(-gate)) * up * w;
+                                }
+                                const __nv_bfloat162 p = __floats2bfloat162_rn(a2[0], a2[1]);
+                                act[i] = *reinterpret_cast<const uint32_t*>(&p);
+                            }
+                            sb[b] = quantise_block_pairs<Bf16Pairs>(act, codes[b]);
+                        }
+                    }
+                    *reinterpret_cast<uint4*>(g.act_packed + size_t(row) * (inter / 2) + act_col / 2) =
+                        make_uint4(codes[0].x, codes[0].y, codes[1].x, codes[1].y);
+                    *reinterpret_cast<uint16_t*>(g.act_scales + scale_byte_offset(row, act_col / 16, inter)) =
+                        static_cast<uint16_t>(sb[0] | (sb[1] << 8));
+                    continue;
+                }
                 if (!Cfg::STAGED_EPILOGUE || g.direct_store) {
                     uint16_t* dst = static_cast<uint16_t*>(g.c) + size_t(row0 + lane) * g.ldc + col0 + chunk * EPI_COLS;
                     #pragma unroll
@@ -605,7 +653,7 @@ void launch_variant(const gpu_kernels::Nvfp4Params& p, const CUtensorMap& tmC, v
     using Cfg = Config<CG, UN>;
     GemmArgs g{p.M, p.N, p.K, p.M / Cfg::TILE_M, p.N / UN, std::max(1, p.group_m), p.alpha, status, prof,
                uint32_t(env_int("NVFP4_B200_DEBUG", 0)), p.c_evict_first, 0, nullptr, nullptr, 0,
-               p.direct_store, c, p.N};
+               p.direct_store, c, p.N, nullptr, nullptr, nullptr, 0.0f};
     cudaLaunchAttribute attr{};
     attr.id = cudaLaunchAttributeClusterDimension;
     attr.val.clusterDim = {unsigned(CG), 1, 1};
@@ -754,13 +802,21 @@ void grouped_prepare(GroupedGemm& p, const uint8_t* A, const uint8_t* B, const u
 }
 
 void grouped_launch(const GroupedGemm& p, void* C, int out_bf16, cudaStream_t stream) {
-    if (!C || (reinterpret_cast<uintptr_t>(C) & 15)) throw std::invalid_argument("grouped gemm: C must be 16-byte aligned");
+    grouped_launch_fused(p, C, out_bf16, nullptr, nullptr, nullptr, 0.0f, stream);
+}
+
+void grouped_launch_fused(const GroupedGemm& p, void* C, int out_bf16, uint8_t* act_packed, uint8_t* act_scales,
+                          const float* row_weight, float clamp, cudaStream_t stream) {
+    const bool fused = act_packed != nullptr;
+    if (fused && (!act_scales || !row_weight)) throw std::invalid_argument("grouped gemm: fused SwiGLU needs scales and row weights");
+    if (!fused && (!C || (reinterpret_cast<uintptr_t>(C) & 15))) throw std::invalid_argument("grouped gemm: C must be 16-byte aligned");
+    if (fused) C = act_packed;       // only the tensor map needs a valid address; the fused route never stores C
     using Cfg = Config<1, 256>;
     const CUtensorMap tmC = make_map_2d(out_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, C,
                                         uint64_t(p.n), uint64_t(p.pool_rows), uint64_t(p.n) * 2, EPI_COLS, 32,
                                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE);
     GemmArgs g{p.pool_rows, p.n, p.k, p.pool_rows / 128, p.n / 256, 1, 1.0f, status_word(p.device), nullptr,
-               0u, 1, out_bf16, p.block_expert, p.num_blocks, p.n, env_int("NVFP4_B200_DIRECT_STORE", 1), C, p.n};
+               0u, 1, out_bf16, p.block_expert, p.num_blocks, p.n, 1, C, p.n, act_packed, act_scales, row_weight, clamp};
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(unsigned(p.units));
     cfg.blockDim = dim3(NUM_THREADS);

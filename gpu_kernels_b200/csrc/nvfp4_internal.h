@@ -37,6 +37,10 @@ struct GroupedGemm {
 void grouped_prepare(GroupedGemm& p, const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB,
                      int pool_rows, int n, int k, int experts, const int* block_expert, const int* num_blocks);
 void grouped_launch(const GroupedGemm& p, void* C, int out_bf16, cudaStream_t stream);
+// First expert GEMM with the SwiGLU + re-quantise epilogue: B's rows must be interleaved 16 gate / 16 up;
+// writes the NVFP4 activation [pool_rows, n/2] instead of C.
+void grouped_launch_fused(const GroupedGemm& p, void* C, int out_bf16, uint8_t* act_packed, uint8_t* act_scales,
+                          const float* row_weight, float clamp, cudaStream_t stream);
 
 // nvfp4_moe.cu: routing metadata, dispatch packing, SwiGLU + re-quantise, top-k reduce.
 struct MoeShape {

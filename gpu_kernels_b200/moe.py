@@ -46,7 +46,7 @@ def exchange_splits(counts_matrix: torch.Tensor, rank: int, local_experts: int):
 
 class Nvfp4MoE:
     def __init__(self, w1: torch.Tensor, w2: torch.Tensor, num_experts: int, topk: int, clamp: float = 10.0,
-                 max_tokens: int = 4096, group=None, pool_rows: int | None = None):
+                 max_tokens: int = 4096, group=None, pool_rows: int | None = None, fused: bool = True):
         """w1 [E_local, 2I, H], w2 [E_local, H, I]: this rank's experts (bf16/fp16/fp32 CUDA tensors)."""
         if not (w1.is_cuda and w2.is_cuda):
             raise ValueError("expert weights must be CUDA tensors: this package has no CPU path")
@@ -65,7 +65,13 @@ class Nvfp4MoE:
         self.device = w1.device
         lib = _lib.load()
         self.payload = lib.gpu_kernels_nvfp4_moe_payload_bytes(self.hidden)
-        # weights, quantised once along K (H for W1, I for W2); the experts are stacked along the rows
+        # weights, quantised once along K (H for W1, I for W2); the experts are stacked along the rows.
+        # For the fused FC1 epilogue W1's rows are interleaved 16 gate rows / 16 up rows, so that one lane's
+        # accumulator chunk holds whole (gate, up) block pairs.
+        self.fused = fused
+        if fused:
+            w1 = (w1.reshape(self.local_experts, 2, self.inter // 16, 16, self.hidden)
+                  .permute(0, 2, 1, 3, 4).reshape(self.local_experts, two_i, self.hidden))
         self.w1q, self.w1s = quantize(w1.reshape(self.local_experts * two_i, self.hidden))
         self.w2q, self.w2s = quantize(w2.reshape(self.local_experts * self.hidden, self.inter))
         # pool: worst case every route of every rank lands here, each expert padded to 128 rows
@@ -93,7 +99,7 @@ class Nvfp4MoE:
         self.pool_scales = torch.zeros(self.pool_rows * self.hidden // 16, dtype=u8, device=d)
         self.pool_weight = torch.zeros(self.pool_rows, dtype=torch.float32, device=d)
         self.pool_of_recv = torch.zeros(recv_cap, dtype=i32, device=d)
-        self.gate_up = torch.empty((self.pool_rows, two_i), dtype=torch.bfloat16, device=d)
+        self.gate_up = None if fused else torch.empty((self.pool_rows, two_i), dtype=torch.bfloat16, device=d)
         self.act_packed = torch.empty((self.pool_rows, self.inter // 2), dtype=u8, device=d)
         self.act_scales = torch.empty(self.pool_rows * self.inter // 16, dtype=u8, device=d)
         self.out_pool = torch.empty((self.pool_rows, self.hidden), dtype=torch.bfloat16, device=d)
@@ -164,10 +170,15 @@ class Nvfp4MoE:
                 self.recv_rows.data_ptr(), self.recv_cap, self.totals.data_ptr(), self.world, self.local_experts,
                 self.hidden, self.seg_src.data_ptr(), self.seg_pool.data_ptr(), self.pool_packed.data_ptr(),
                 self.pool_scales.data_ptr(), self.pool_weight.data_ptr(), self.pool_of_recv.data_ptr(), s))
-            _lib.check(lib.gpu_kernels_nvfp4_grouped_run(self._fc1, self.gate_up.data_ptr(), 1, s))
-            _lib.check(lib.gpu_kernels_nvfp4_moe_swiglu_quant(
-                self.gate_up.data_ptr(), self.pool_weight.data_ptr(), self.num_blocks.data_ptr(), self.pool_rows,
-                self.inter, self.clamp, self.act_packed.data_ptr(), self.act_scales.data_ptr(), s))
+            if self.fused:
+                _lib.check(lib.gpu_kernels_nvfp4_grouped_run_swiglu(
+                    self._fc1, self.pool_weight.data_ptr(), self.clamp, self.act_packed.data_ptr(),
+                    self.act_scales.data_ptr(), s))
+            else:
+                _lib.check(lib.gpu_kernels_nvfp4_grouped_run(self._fc1, self.gate_up.data_ptr(), 1, s))
+                _lib.check(lib.gpu_kernels_nvfp4_moe_swiglu_quant(
+                    self.gate_up.data_ptr(), self.pool_weight.data_ptr(), self.num_blocks.data_ptr(), self.pool_rows,
+                    self.inter, self.clamp, self.act_packed.data_ptr(), self.act_scales.data_ptr(), s))
             _lib.check(lib.gpu_kernels_nvfp4_grouped_run(self._fc2, self.out_pool.data_ptr(), 1, s))
             _lib.check(lib.gpu_kernels_nvfp4_moe_return_rows(
                 self.out_pool.data_ptr(), self.pool_of_recv.data_ptr(), self.totals.data_ptr(), self.recv_cap,

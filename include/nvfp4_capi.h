@@ -91,6 +91,13 @@ int gpu_kernels_nvfp4_grouped_plan_create(void** plan, int pool_rows, int n, int
 void gpu_kernels_nvfp4_grouped_plan_destroy(void* plan);
 int gpu_kernels_nvfp4_grouped_run(void* plan, void* C, int out_bf16, void* stream);
 
+/* The first expert GEMM with the activation fused into its epilogue (FC1 + kernels/moe/swiglu.cu:12-26 + the
+ * re-quantisation for FC2 in one kernel): the plan's B must hold each expert's W1 with rows interleaved as
+ * 16 gate rows, 16 up rows, 16 gate rows, ...; writes act_packed [pool_rows, n/4] and act_scales (VEC16 layout
+ * of [pool_rows, n/2]) instead of C. row_weight f32 [pool_rows], 0 marks a padding row. */
+int gpu_kernels_nvfp4_grouped_run_swiglu(void* plan, const void* row_weight, float clamp, void* act_packed,
+                                         void* act_scales, void* stream);
+
 /* Bytes of one dispatched token row: hidden/2 packed + hidden/16 scale bytes + 16 (route weight). */
 int gpu_kernels_nvfp4_moe_payload_bytes(int hidden);
 /* replaces metadata_kernel's histogram (kernels/moe/fused/sm90.cu:43-101): counts[e] += routes to global expert e

@@ -61,10 +61,11 @@ def assert_layer_close(y, ref, what):
     (200, 256, 512, 16, 6, False),       # top-6 as in the benchmark layer
     (300, 512, 256, 8, 2, True),         # skewed routing: one expert spans several 128-row blocks, others empty
 ])
-def test_layer_against_oracle(g, tokens, hidden, inter, experts, topk, skew):
+@pytest.mark.parametrize("fused", [True, False])
+def test_layer_against_oracle(g, tokens, hidden, inter, experts, topk, skew, fused):
     x, logits, w1, w2 = make_layer(tokens + hidden, tokens, hidden, inter, experts, topk, skew)
     ids, wts = g.route(logits, topk)
-    layer = g.Nvfp4MoE(w1, w2, experts, topk, clamp=10.0, max_tokens=max(tokens, 64))
+    layer = g.Nvfp4MoE(w1, w2, experts, topk, clamp=10.0, max_tokens=max(tokens, 64), fused=fused)
     y = layer(x, ids, wts).clone()
     torch.cuda.synchronize()
     assert_layer_close(y, oracle_layer(x, ids, wts, w1, w2, 10.0), f"T={tokens} H={hidden} I={inter} E={experts} k={topk}")
@@ -74,6 +75,31 @@ def test_layer_against_oracle(g, tokens, hidden, inter, experts, topk, skew):
     y2 = layer(x2, ids2, wts2).clone()
     assert_layer_close(y2, oracle_layer(x2, ids2, wts2, w1, w2, 10.0), "second call with changed inputs")
     layer.close()
+
+
+def test_fused_and_unfused_first_gemm_agree(g):
+    # the fused epilogue (SwiGLU + re-quantise inside FC1) must produce the activation bytes of the
+    # separate kernel, up to code flips from FP32 summation-order differences in single elements
+    tokens, hidden, inter, experts, topk = 200, 512, 512, 4, 2
+    x, logits, w1, w2 = make_layer(77, tokens, hidden, inter, experts, topk)
+    ids, wts = g.route(logits, topk)
+    acts = []
+    for fused in (True, False):
+        layer = g.Nvfp4MoE(w1, w2, experts, topk, max_tokens=256, fused=fused)
+        layer(x, ids, wts)
+        torch.cuda.synchronize()
+        rows = int(layer.totals[1].item())
+        acts.append((to_np(layer.act_packed[:rows]).copy(),
+                     O.unpack_scales_u8(to_np(layer.act_scales), layer.pool_rows, inter)[:rows].copy(),
+                     to_np(layer.pool_weight[:rows]).copy()))
+        layer.close()
+    (pf, sf, wf), (pu, su, wu) = acts
+    # rows land in an arbitrary order inside an expert's group: match them through the route weight
+    order_f, order_u = np.argsort(wf, kind="stable"), np.argsort(wu, kind="stable")
+    assert np.array_equal(wf[order_f], wu[order_u])
+    same_scale = (sf[order_f] == su[order_u]).mean()
+    same_code = (pf[order_f] == pu[order_u]).mean()
+    assert same_scale > 0.999 and same_code > 0.999, (same_scale, same_code)
 
 
 def test_routing_plan_pack_unpack_exact(g):
