@@ -397,6 +397,21 @@ int gpu_kernels_nvfp4_moe_pack(const void* xq, const void* xs, const void* ids, 
     });
 }
 
+int gpu_kernels_nvfp4_moe_pack_to_pool(const void* xq, const void* xs, const void* ids, const void* weights, int tokens,
+                                       int topk, int hidden, const void* seg_pool_offset, void* cursor,
+                                       void* pool_packed, void* pool_scales, void* pool_weight, void* route_row,
+                                       void* stream) {
+    return guarded([&] {
+        nvfp4_b200::moe_pack_to_pool(static_cast<const uint8_t*>(xq), static_cast<const uint8_t*>(xs),
+                                     static_cast<const long long*>(ids), static_cast<const float*>(weights), tokens, topk,
+                                     hidden, static_cast<const int*>(seg_pool_offset), static_cast<int*>(cursor),
+                                     static_cast<uint8_t*>(pool_packed), static_cast<uint8_t*>(pool_scales),
+                                     static_cast<float*>(pool_weight), static_cast<int*>(route_row),
+                                     static_cast<cudaStream_t>(stream));
+        nvfp4_b200::g_launches.fetch_add(1, std::memory_order_relaxed);
+    });
+}
+
 int gpu_kernels_nvfp4_moe_unpack(const void* recv_rows, int recv_capacity, const void* totals, int world,
                                  int local_experts, int hidden, const void* seg_src_offset, const void* seg_pool_offset,
                                  void* pool_packed, void* pool_scales, void* pool_weight, void* pool_of_recv,

@@ -53,6 +53,11 @@ void moe_plan(const int* counts_matrix, int world, int rank, int experts, int po
               int* totals, cudaStream_t stream);
 void moe_pack(const uint8_t* xq, const uint8_t* xs, const long long* ids, const float* weights, int tokens, int topk,
               int hidden, const int* send_offset, int* cursor, uint8_t* send_rows, int* send_pos, cudaStream_t stream);
+// Single-rank shortcut: rows go straight into the expert-major pool (no send buffer, no unpack);
+// route_row[route] is then the pool row, which moe_reduce can read the second GEMM's output by.
+void moe_pack_to_pool(const uint8_t* xq, const uint8_t* xs, const long long* ids, const float* weights, int tokens,
+                      int topk, int hidden, const int* seg_pool_offset, int* cursor, uint8_t* pool_packed,
+                      uint8_t* pool_scales, float* pool_weight, int* route_row, cudaStream_t stream);
 void moe_unpack(const uint8_t* recv_rows, int recv_count_capacity, const int* totals, int world, int local_experts,
                 int hidden, const int* seg_src_offset, const int* seg_pool_offset, uint8_t* pool_packed,
                 uint8_t* pool_scales, float* pool_weight, int* pool_of_recv, cudaStream_t stream);

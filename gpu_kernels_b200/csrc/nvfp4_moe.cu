@@ -124,7 +124,9 @@ __global__ void plan_kernel(const int* __restrict__ counts, int world, int rank,
 __global__ void pack_kernel(const uint8_t* __restrict__ xq, const uint8_t* __restrict__ xs,
                             const long long* __restrict__ ids, const float* __restrict__ weights, int routes,
                             int topk, int hidden, const int* __restrict__ send_offset, int* __restrict__ cursor,
-                            uint8_t* __restrict__ send_rows, int* __restrict__ send_pos) {
+                            uint8_t* __restrict__ send_rows, int* __restrict__ send_pos,
+                            const int* __restrict__ seg_pool_offset, uint8_t* __restrict__ pool_packed,
+                            uint8_t* __restrict__ pool_scales, float* __restrict__ pool_weight) {
     const int lane = threadIdx.x & 31;
     const int route = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (route >= routes) return;
@@ -132,12 +134,22 @@ __global__ void pack_kernel(const uint8_t* __restrict__ xq, const uint8_t* __res
     const int expert = int(ids[route]);
     int dst = 0;
     if (lane == 0) {
-        dst = send_offset[expert] + atomicAdd(&cursor[expert], 1);
+        const int slot = atomicAdd(&cursor[expert], 1);
+        // one rank: the row goes straight into its expert's group of the pool, no send buffer in between
+        dst = (pool_packed ? seg_pool_offset[expert] : send_offset[expert]) + slot;
         send_pos[route] = dst;
     }
     dst = __shfl_sync(0xFFFFFFFFu, dst, 0);
-    uint8_t* out = send_rows + size_t(dst) * payload_bytes(hidden);
     const uint4* src = reinterpret_cast<const uint4*>(xq + size_t(token) * (hidden / 2));
+    if (pool_packed) {
+        uint4* row = reinterpret_cast<uint4*>(pool_packed + size_t(dst) * (hidden / 2));
+        for (int i = lane; i < hidden / 32; i += 32) row[i] = __ldg(src + i);
+        for (int b = lane; b < hidden / 16; b += 32)
+            pool_scales[scale_byte_offset(dst, b, hidden)] = xs[scale_byte_offset(token, b, hidden)];
+        if (lane == 0) pool_weight[dst] = weights[route];
+        return;
+    }
+    uint8_t* out = send_rows + size_t(dst) * payload_bytes(hidden);
     for (int i = lane; i < hidden / 32; i += 32) reinterpret_cast<uint4*>(out)[i] = __ldg(src + i);
     for (int b = lane; b < hidden / 16; b += 32) out[hidden / 2 + b] = xs[scale_byte_offset(token, b, hidden)];
     if (lane == 0) *reinterpret_cast<float*>(out + hidden / 2 + hidden / 16) = weights[route];
@@ -295,7 +307,20 @@ void moe_pack(const uint8_t* xq, const uint8_t* xs, const long long* ids, const 
     const int routes = tokens * topk;
     if (routes == 0) return;
     pack_kernel<<<(routes * 32 + 255) / 256, 256, 0, stream>>>(xq, xs, ids, weights, routes, topk, hidden, send_offset,
-                                                               cursor, send_rows, send_pos);
+                                                               cursor, send_rows, send_pos, nullptr, nullptr, nullptr, nullptr);
+    cuda_check(cudaGetLastError());
+}
+
+void moe_pack_to_pool(const uint8_t* xq, const uint8_t* xs, const long long* ids, const float* weights, int tokens,
+                      int topk, int hidden, const int* seg_pool_offset, int* cursor, uint8_t* pool_packed,
+                      uint8_t* pool_scales, float* pool_weight, int* route_row, cudaStream_t stream) {
+    check_hidden(hidden, "moe pack_to_pool");
+    const int routes = tokens * topk;
+    if (routes == 0) return;
+    if (!pool_packed || !pool_scales || !pool_weight) throw std::invalid_argument("moe pack_to_pool: null pool");
+    pack_kernel<<<(routes * 32 + 255) / 256, 256, 0, stream>>>(xq, xs, ids, weights, routes, topk, hidden, nullptr, cursor,
+                                                               nullptr, route_row, seg_pool_offset, pool_packed,
+                                                               pool_scales, pool_weight);
     cuda_check(cudaGetLastError());
 }
 

@@ -156,20 +156,26 @@ class Nvfp4MoE:
             xq, xs = quantize(self.x_pad)
             send_splits, recv_splits = self._metadata(ids, tokens)
             self.cursor.zero_()
-            _lib.check(lib.gpu_kernels_nvfp4_moe_pack(
-                xq.data_ptr(), xs.data_ptr(), ids.data_ptr(), weights.data_ptr(), tokens, self.topk, self.hidden,
-                self.send_offset.data_ptr(), self.cursor.data_ptr(), self.send_rows.data_ptr(),
-                self.send_pos.data_ptr(), s))
-            total_recv = sum(recv_splits)
-            if self.world > 1:
-                dist.all_to_all_single(self.recv_rows[:total_recv], self.send_rows[:tokens * self.topk],
-                                       recv_splits, send_splits, group=self.group)
             self.pool_scales.zero_()
             self.pool_weight.zero_()
-            _lib.check(lib.gpu_kernels_nvfp4_moe_unpack(
-                self.recv_rows.data_ptr(), self.recv_cap, self.totals.data_ptr(), self.world, self.local_experts,
-                self.hidden, self.seg_src.data_ptr(), self.seg_pool.data_ptr(), self.pool_packed.data_ptr(),
-                self.pool_scales.data_ptr(), self.pool_weight.data_ptr(), self.pool_of_recv.data_ptr(), s))
+            total_recv = sum(recv_splits)
+            if self.world == 1:
+                # nothing to exchange: rows go straight into the expert-major pool
+                _lib.check(lib.gpu_kernels_nvfp4_moe_pack_to_pool(
+                    xq.data_ptr(), xs.data_ptr(), ids.data_ptr(), weights.data_ptr(), tokens, self.topk, self.hidden,
+                    self.seg_pool.data_ptr(), self.cursor.data_ptr(), self.pool_packed.data_ptr(),
+                    self.pool_scales.data_ptr(), self.pool_weight.data_ptr(), self.send_pos.data_ptr(), s))
+            else:
+                _lib.check(lib.gpu_kernels_nvfp4_moe_pack(
+                    xq.data_ptr(), xs.data_ptr(), ids.data_ptr(), weights.data_ptr(), tokens, self.topk, self.hidden,
+                    self.send_offset.data_ptr(), self.cursor.data_ptr(), self.send_rows.data_ptr(),
+                    self.send_pos.data_ptr(), s))
+                dist.all_to_all_single(self.recv_rows[:total_recv], self.send_rows[:tokens * self.topk],
+                                       recv_splits, send_splits, group=self.group)
+                _lib.check(lib.gpu_kernels_nvfp4_moe_unpack(
+                    self.recv_rows.data_ptr(), self.recv_cap, self.totals.data_ptr(), self.world, self.local_experts,
+                    self.hidden, self.seg_src.data_ptr(), self.seg_pool.data_ptr(), self.pool_packed.data_ptr(),
+                    self.pool_scales.data_ptr(), self.pool_weight.data_ptr(), self.pool_of_recv.data_ptr(), s))
             if self.fused:
                 _lib.check(lib.gpu_kernels_nvfp4_grouped_run_swiglu(
                     self._fc1, self.pool_weight.data_ptr(), self.clamp, self.act_packed.data_ptr(),
@@ -180,16 +186,21 @@ class Nvfp4MoE:
                     self.gate_up.data_ptr(), self.pool_weight.data_ptr(), self.num_blocks.data_ptr(), self.pool_rows,
                     self.inter, self.clamp, self.act_packed.data_ptr(), self.act_scales.data_ptr(), s))
             _lib.check(lib.gpu_kernels_nvfp4_grouped_run(self._fc2, self.out_pool.data_ptr(), 1, s))
-            _lib.check(lib.gpu_kernels_nvfp4_moe_return_rows(
-                self.out_pool.data_ptr(), self.pool_of_recv.data_ptr(), self.totals.data_ptr(), self.recv_cap,
-                self.hidden, self.ret_send.data_ptr(), s))
-            if self.world > 1:
+            if self.world == 1:
+                # send_pos holds pool rows: the reduce reads the second GEMM's output in place
+                _lib.check(lib.gpu_kernels_nvfp4_moe_reduce(
+                    self.out_pool.data_ptr(), self.send_pos.data_ptr(), tokens, self.topk, self.hidden,
+                    self.y.data_ptr(), s))
+            else:
+                _lib.check(lib.gpu_kernels_nvfp4_moe_return_rows(
+                    self.out_pool.data_ptr(), self.pool_of_recv.data_ptr(), self.totals.data_ptr(), self.recv_cap,
+                    self.hidden, self.ret_send.data_ptr(), s))
                 dist.all_to_all_single(self.ret_recv[:tokens * self.topk].view(torch.uint8),
                                        self.ret_send[:total_recv].view(torch.uint8),
                                        send_splits, recv_splits, group=self.group)
-            _lib.check(lib.gpu_kernels_nvfp4_moe_reduce(
-                self.ret_recv.data_ptr(), self.send_pos.data_ptr(), tokens, self.topk, self.hidden,
-                self.y.data_ptr(), s))
+                _lib.check(lib.gpu_kernels_nvfp4_moe_reduce(
+                    self.ret_recv.data_ptr(), self.send_pos.data_ptr(), tokens, self.topk, self.hidden,
+                    self.y.data_ptr(), s))
         return self.y[:tokens]
 
     __call__ = forward

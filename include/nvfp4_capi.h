@@ -115,6 +115,13 @@ int gpu_kernels_nvfp4_moe_plan(const void* counts_matrix, int world, int rank, i
 int gpu_kernels_nvfp4_moe_pack(const void* xq, const void* xs, const void* ids, const void* weights, int tokens,
                                int topk, int hidden, const void* send_offset, void* cursor, void* send_rows,
                                void* send_pos, void* stream);
+/* Single-rank shortcut (world = 1): the same as pack + unpack in one kernel, rows written straight into the pool;
+ * route_row [T*topk] receives each route's pool row, so reduce can read the second GEMM's output directly
+ * (pass the output pool as `returned` and route_row as `send_pos`). seg_pool_offset from moe_plan. */
+int gpu_kernels_nvfp4_moe_pack_to_pool(const void* xq, const void* xs, const void* ids, const void* weights, int tokens,
+                                       int topk, int hidden, const void* seg_pool_offset, void* cursor,
+                                       void* pool_packed, void* pool_scales, void* pool_weight, void* route_row,
+                                       void* stream);
 /* received rows (source-major) -> expert-major pool: packed rows, scale atoms (zeroed by the caller first),
  * per-row route weight, and pool_of_recv [recv_capacity] for the way back. */
 int gpu_kernels_nvfp4_moe_unpack(const void* recv_rows, int recv_capacity, const void* totals, int world,
