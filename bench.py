@@ -440,6 +440,10 @@ def run_moe(args, rank, world, local_rank):
         t = torch.tensor([ms, e2e_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, e2e_ms = (float(v) for v in t.tolist())
+    layer.phase_events = []
+    layer(*sets[0])
+    phases = {k_: round(v_, 1) for k_, v_ in layer.phase_times_us().items()}
+    layer.phase_events = None
     touched = int((layer.counts_matrix.sum(0)[rank * local:(rank + 1) * local] > 0).sum().item())
     if rank != 0:
         return
@@ -470,7 +474,7 @@ def run_moe(args, rank, world, local_rank):
         "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "nvfp4 operands, f32 accumulate, bf16 activations and output", "data": "synthetic",
         "config": {"workload": args.workload, "tokens_per_gpu": tokens, **MOE_SHAPE, "expert_parallel": world,
-                   "experts_touched_rank0": touched, "l2": "expert weights (3.6 GB per 256 experts) far exceed L2; inputs rotate over 4 sets"},
+                   "experts_touched_rank0": touched, "phases_us_rank0": phases, "l2": "expert weights (3.6 GB per 256 experts) far exceed L2; inputs rotate over 4 sets"},
         "clocks": clocks,
         "e2e": {"value": flops / (e2e_ms / e2e_steps * 1e-3) / 1e12, "unit": UNIT,
                 "h2d_bytes_per_step": tokens * (H * 2 + topk * 12), "d2h_bytes_per_step": tokens * H * 2, "steps": e2e_steps,

@@ -327,15 +327,16 @@ unsigned gpu_kernels_nvfp4_last_kernel_cycles(void) {
 
 /* ---- routed-MoE expert path ---- */
 
-int gpu_kernels_nvfp4_grouped_plan_create(void** out, int pool_rows, int n, int k, int experts, const void* A,
-                                          const void* B, const void* SFA, const void* SFB, const void* block_expert,
-                                          const void* num_blocks) {
+int gpu_kernels_nvfp4_grouped_plan_create(void** out, int pool_rows, int n, int k, int experts, int block_rows,
+                                          const void* A, const void* B, const void* SFA, const void* SFB,
+                                          const void* block_expert, const void* num_blocks) {
     return guarded([&] {
         if (!out) throw std::invalid_argument("grouped_plan_create: null result pointer");
         auto plan = std::make_unique<nvfp4_b200::GroupedGemm>();
         nvfp4_b200::grouped_prepare(*plan, static_cast<const uint8_t*>(A), static_cast<const uint8_t*>(B),
                                     static_cast<const uint8_t*>(SFA), static_cast<const uint8_t*>(SFB), pool_rows, n, k,
-                                    experts, static_cast<const int*>(block_expert), static_cast<const int*>(num_blocks));
+                                    experts, block_rows, static_cast<const int*>(block_expert),
+                                    static_cast<const int*>(num_blocks));
         *out = plan.release();
     });
 }
@@ -372,11 +373,11 @@ int gpu_kernels_nvfp4_moe_route_count(const void* ids, int routes, int experts, 
 }
 
 int gpu_kernels_nvfp4_moe_plan(const void* counts_matrix, int world, int rank, int experts, int capacity_rows,
-                               void* send_offset, void* seg_src_offset, void* seg_pool_offset, void* block_expert,
+                               int block_rows, void* send_offset, void* seg_src_offset, void* seg_pool_offset, void* block_expert,
                                void* num_blocks, void* totals, void* stream) {
     return guarded([&] {
         nvfp4_b200::require_sm100();
-        nvfp4_b200::moe_plan(static_cast<const int*>(counts_matrix), world, rank, experts, capacity_rows,
+        nvfp4_b200::moe_plan(static_cast<const int*>(counts_matrix), world, rank, experts, capacity_rows, block_rows,
                              static_cast<int*>(send_offset), static_cast<int*>(seg_src_offset),
                              static_cast<int*>(seg_pool_offset), static_cast<int*>(block_expert),
                              static_cast<int*>(num_blocks), static_cast<int*>(totals), static_cast<cudaStream_t>(stream));
@@ -427,11 +428,11 @@ int gpu_kernels_nvfp4_moe_unpack(const void* recv_rows, int recv_capacity, const
 }
 
 int gpu_kernels_nvfp4_moe_swiglu_quant(const void* gate_up, const void* pool_weight, const void* num_blocks,
-                                       int pool_rows, int intermediate, float clamp, void* act_packed,
+                                       int block_rows, int pool_rows, int intermediate, float clamp, void* act_packed,
                                        void* act_scales, void* stream) {
     return guarded([&] {
         nvfp4_b200::moe_swiglu_quant(gate_up, static_cast<const float*>(pool_weight), static_cast<const int*>(num_blocks),
-                                     pool_rows, intermediate, clamp, static_cast<uint8_t*>(act_packed),
+                                     block_rows, pool_rows, intermediate, clamp, static_cast<uint8_t*>(act_packed),
                                      static_cast<uint8_t*>(act_scales), static_cast<cudaStream_t>(stream));
         nvfp4_b200::g_launches.fetch_add(1, std::memory_order_relaxed);
     });

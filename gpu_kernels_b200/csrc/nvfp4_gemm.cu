@@ -783,21 +783,26 @@ unsigned last_kernel_cycles() {
 }
 
 void grouped_prepare(GroupedGemm& p, const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB,
-                     int pool_rows, int n, int k, int experts, const int* block_expert, const int* num_blocks) {
+                     int pool_rows, int n, int k, int experts, int block_rows, const int* block_expert,
+                     const int* num_blocks) {
     require_sm100();
-    if (pool_rows <= 0 || pool_rows % 128) throw std::invalid_argument("grouped gemm: pool rows must be a positive multiple of 128");
+    if (block_rows != 128 && block_rows != 256) throw std::invalid_argument("grouped gemm: block rows must be 128 or 256");
+    if (pool_rows <= 0 || pool_rows % block_rows) throw std::invalid_argument("grouped gemm: pool rows must be a positive multiple of the block rows");
     if (n <= 0 || n % 256) throw std::invalid_argument("grouped gemm: N per expert must be a multiple of 256");
     if (k <= 0 || k % STAGE_K) throw std::invalid_argument("grouped gemm: K must be a multiple of 256");
     if (experts <= 0 || !A || !B || !SFA || !SFB || !block_expert || !num_blocks)
         throw std::invalid_argument("grouped gemm: null pointer or no experts");
     cuda_check(cudaGetDevice(&p.device));
-    p.pool_rows = pool_rows; p.n = n; p.k = k; p.experts = experts; p.tile_n = 256;
+    p.pool_rows = pool_rows; p.n = n; p.k = k; p.experts = experts; p.tile_n = 256; p.block_rows = block_rows;
     p.block_expert = block_expert; p.num_blocks = num_blocks;
+    // 256-row blocks run on CTA pairs (each CTA stages half of the expert's weight tile: half the L2 traffic
+    // per FLOP, which is what bounds the single-CTA tiles once an expert has many rows)
     p.A = operand_map(A, pool_rows, k, BLOCK_M);
-    p.B = operand_map(B, experts * n, k, 256);
+    p.B = operand_map(B, experts * n, k, block_rows == 256 ? 128 : 256);
     p.SFA = scale_map(SFA, pool_rows, k);
     p.SFB = scale_map(SFB, experts * n, k);
-    p.units = std::min(max_units<1, 256>(p.device), (pool_rows / 128) * (n / 256));
+    const int fit = block_rows == 256 ? max_units<2, 256>(p.device) : max_units<1, 256>(p.device);
+    p.units = std::min(fit, (pool_rows / block_rows) * (n / 256));
     (void)status_word(p.device);
 }
 
@@ -811,18 +816,24 @@ void grouped_launch_fused(const GroupedGemm& p, void* C, int out_bf16, uint8_t* 
     if (fused && (!act_scales || !row_weight)) throw std::invalid_argument("grouped gemm: fused SwiGLU needs scales and row weights");
     if (!fused && (!C || (reinterpret_cast<uintptr_t>(C) & 15))) throw std::invalid_argument("grouped gemm: C must be 16-byte aligned");
     if (fused) C = act_packed;       // only the tensor map needs a valid address; the fused route never stores C
-    using Cfg = Config<1, 256>;
     const CUtensorMap tmC = make_map_2d(out_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, C,
                                         uint64_t(p.n), uint64_t(p.pool_rows), uint64_t(p.n) * 2, EPI_COLS, 32,
                                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE);
-    GemmArgs g{p.pool_rows, p.n, p.k, p.pool_rows / 128, p.n / 256, 1, 1.0f, status_word(p.device), nullptr,
+    const int cg = p.block_rows == 256 ? 2 : 1;
+    GemmArgs g{p.pool_rows, p.n, p.k, p.pool_rows / p.block_rows, p.n / 256, 1, 1.0f, status_word(p.device), nullptr,
                0u, 1, out_bf16, p.block_expert, p.num_blocks, p.n, 1, C, p.n, act_packed, act_scales, row_weight, clamp};
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim = {unsigned(cg), 1, 1};
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(unsigned(p.units));
+    cfg.gridDim = dim3(unsigned(p.units) * cg);
     cfg.blockDim = dim3(NUM_THREADS);
-    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cfg.dynamicSmemBytes = cg == 2 ? Config<2, 256>::SMEM_BYTES : Config<1, 256>::SMEM_BYTES;
     cfg.stream = stream;
-    cuda_check(cudaLaunchKernelEx(&cfg, nvfp4_gemm_kernel<1, 256>, p.A, p.B, p.SFA, p.SFB, tmC, g));
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    if (cg == 2) cuda_check(cudaLaunchKernelEx(&cfg, nvfp4_gemm_kernel<2, 256>, p.A, p.B, p.SFA, p.SFB, tmC, g));
+    else cuda_check(cudaLaunchKernelEx(&cfg, nvfp4_gemm_kernel<1, 256>, p.A, p.B, p.SFA, p.SFB, tmC, g));
     g_launches.fetch_add(1, std::memory_order_relaxed);
 }
 

@@ -30,12 +30,13 @@ void dequantise(const uint8_t* packed, const uint8_t* scales, float* out, int ro
 // read by the kernel, so no host synchronisation is needed between routing and the GEMM).
 struct GroupedGemm {
     CUtensorMap A, B, SFA, SFB;
-    int pool_rows, n, k, experts, units, tile_n, device;
+    int pool_rows, n, k, experts, units, tile_n, device, block_rows;
     const int* block_expert;
     const int* num_blocks;
 };
 void grouped_prepare(GroupedGemm& p, const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB,
-                     int pool_rows, int n, int k, int experts, const int* block_expert, const int* num_blocks);
+                     int pool_rows, int n, int k, int experts, int block_rows, const int* block_expert,
+                     const int* num_blocks);
 void grouped_launch(const GroupedGemm& p, void* C, int out_bf16, cudaStream_t stream);
 // First expert GEMM with the SwiGLU + re-quantise epilogue: B's rows must be interleaved 16 gate / 16 up;
 // writes the NVFP4 activation [pool_rows, n/2] instead of C.
@@ -48,7 +49,7 @@ struct MoeShape {
     float clamp;
 };
 void moe_route_count(const long long* ids, int routes, int experts, int* counts, cudaStream_t stream);
-void moe_plan(const int* counts_matrix, int world, int rank, int experts, int pool_capacity_rows,
+void moe_plan(const int* counts_matrix, int world, int rank, int experts, int pool_capacity_rows, int block_rows,
               int* send_offset, int* seg_src_offset, int* seg_pool_offset, int* block_expert, int* num_blocks,
               int* totals, cudaStream_t stream);
 void moe_pack(const uint8_t* xq, const uint8_t* xs, const long long* ids, const float* weights, int tokens, int topk,
@@ -61,7 +62,7 @@ void moe_pack_to_pool(const uint8_t* xq, const uint8_t* xs, const long long* ids
 void moe_unpack(const uint8_t* recv_rows, int recv_count_capacity, const int* totals, int world, int local_experts,
                 int hidden, const int* seg_src_offset, const int* seg_pool_offset, uint8_t* pool_packed,
                 uint8_t* pool_scales, float* pool_weight, int* pool_of_recv, cudaStream_t stream);
-void moe_swiglu_quant(const void* gate_up_bf16, const float* pool_weight, const int* num_blocks, int pool_rows,
+void moe_swiglu_quant(const void* gate_up_bf16, const float* pool_weight, const int* num_blocks, int block_rows, int pool_rows,
                       int intermediate, float clamp, uint8_t* act_packed, uint8_t* act_scales, cudaStream_t stream);
 void moe_return_rows(const void* out_pool_bf16, const int* pool_of_recv, const int* totals, int capacity, int hidden,
                      void* return_rows_bf16, cudaStream_t stream);

@@ -65,6 +65,7 @@ __device__ void block_exclusive_scan(int* data, int n, int* chunk_sums) {
 
 // counts[r * experts + ge]: routes rank r sends to global expert ge. One CTA of 256 threads; experts <= 4096.
 __global__ void plan_kernel(const int* __restrict__ counts, int world, int rank, int experts, int capacity_rows,
+                            int block_rows,
                             int* __restrict__ send_offset, int* __restrict__ seg_src_offset,
                             int* __restrict__ seg_pool_offset, int* __restrict__ block_expert,
                             int* __restrict__ num_blocks, int* __restrict__ totals) {
@@ -92,11 +93,11 @@ __global__ void plan_kernel(const int* __restrict__ counts, int world, int rank,
     for (int i = threadIdx.x; i < segments; i += blockDim.x) seg_src_offset[i] = scan[i];
     if (threadIdx.x == 0) { seg_src_offset[segments] = chunk[blockDim.x]; totals[0] = chunk[blockDim.x]; }
     __syncthreads();
-    // 3. expert-major pool, every expert padded to whole 128-row blocks
+    // 3. expert-major pool, every expert padded to whole blocks of block_rows (128 or 256) rows
     for (int e = threadIdx.x; e < local_experts; e += blockDim.x) {
         int sum = 0;
         for (int r = 0; r < world; ++r) sum += counts[r * experts + rank * local_experts + e];
-        scan[e] = (sum + 127) / 128 * 128;
+        scan[e] = (sum + block_rows - 1) / block_rows * block_rows;
     }
     __syncthreads();
     block_exclusive_scan(scan, local_experts, chunk);
@@ -106,7 +107,7 @@ __global__ void plan_kernel(const int* __restrict__ counts, int world, int rank,
         pool_off[e] = scan[e];
         const int end = e + 1 < local_experts ? scan[e + 1] : pool_rows;
         if (!overflow)
-            for (int blk = scan[e] / 128; blk < end / 128; ++blk) block_expert[blk] = e;
+            for (int blk = scan[e] / block_rows; blk < end / block_rows; ++blk) block_expert[blk] = e;
         int acc = scan[e];
         for (int r = 0; r < world; ++r) {
             seg_pool_offset[r * local_experts + e] = acc;
@@ -114,7 +115,7 @@ __global__ void plan_kernel(const int* __restrict__ counts, int world, int rank,
         }
     }
     if (threadIdx.x == 0) {
-        *num_blocks = overflow ? 0 : pool_rows / 128;     // an overflowing plan computes nothing; the host reports it
+        *num_blocks = overflow ? 0 : pool_rows / block_rows;     // an overflowing plan computes nothing; the host reports it
         totals[1] = pool_rows;
         totals[2] = overflow ? 1 : 0;
     }
@@ -184,10 +185,10 @@ __global__ void unpack_kernel(const uint8_t* __restrict__ recv_rows, const int* 
 // the activation so that every scale atom and packed row segment leaves in full lines.
 __global__ void __launch_bounds__(256)
 swiglu_quant_kernel(const __nv_bfloat16* __restrict__ gate_up, const float* __restrict__ pool_weight,
-                    const int* __restrict__ num_blocks, int inter, float clamp,
+                    const int* __restrict__ num_blocks, int block_rows, int inter, float clamp,
                     uint8_t* __restrict__ act_packed, uint8_t* __restrict__ act_scales) {
     __shared__ __align__(16) uint8_t sf_tile[4 * 512];
-    if (int(blockIdx.y) >= *num_blocks) return;
+    if (int(blockIdx.y) * 128 >= *num_blocks * block_rows) return;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int kb = lane & 15;
     const int col0 = blockIdx.x * 256;
@@ -288,14 +289,15 @@ void moe_route_count(const long long* ids, int routes, int experts, int* counts,
     cuda_check(cudaGetLastError());
 }
 
-void moe_plan(const int* counts_matrix, int world, int rank, int experts, int pool_capacity_rows,
+void moe_plan(const int* counts_matrix, int world, int rank, int experts, int pool_capacity_rows, int block_rows,
               int* send_offset, int* seg_src_offset, int* seg_pool_offset, int* block_expert, int* num_blocks,
               int* totals, cudaStream_t stream) {
     if (world <= 0 || rank < 0 || rank >= world || experts <= 0 || experts % world || experts > 4096)
         throw std::invalid_argument("moe plan: experts must divide over the ranks (and be <= 4096)");
-    if (pool_capacity_rows <= 0 || pool_capacity_rows % 128) throw std::invalid_argument("moe plan: pool capacity must be a multiple of 128 rows");
+    if (block_rows != 128 && block_rows != 256) throw std::invalid_argument("moe plan: block rows must be 128 or 256");
+    if (pool_capacity_rows <= 0 || pool_capacity_rows % block_rows) throw std::invalid_argument("moe plan: pool capacity must be a multiple of the block rows");
     const int local = experts / world;
-    plan_kernel<<<1, 256, (experts + local + 257) * sizeof(int), stream>>>(counts_matrix, world, rank, experts, pool_capacity_rows,
+    plan_kernel<<<1, 256, (experts + local + 257) * sizeof(int), stream>>>(counts_matrix, world, rank, experts, pool_capacity_rows, block_rows,
                                                                    send_offset, seg_src_offset, seg_pool_offset,
                                                                    block_expert, num_blocks, totals);
     cuda_check(cudaGetLastError());
@@ -335,12 +337,12 @@ void moe_unpack(const uint8_t* recv_rows, int recv_count_capacity, const int* to
     cuda_check(cudaGetLastError());
 }
 
-void moe_swiglu_quant(const void* gate_up_bf16, const float* pool_weight, const int* num_blocks, int pool_rows,
+void moe_swiglu_quant(const void* gate_up_bf16, const float* pool_weight, const int* num_blocks, int block_rows, int pool_rows,
                       int intermediate, float clamp, uint8_t* act_packed, uint8_t* act_scales, cudaStream_t stream) {
     check_hidden(intermediate, "moe swiglu_quant");
     if (pool_rows <= 0 || pool_rows % 128) throw std::invalid_argument("moe swiglu_quant: pool rows must be a multiple of 128");
     const dim3 grid(intermediate / 256, pool_rows / 128);
-    swiglu_quant_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(gate_up_bf16), pool_weight, num_blocks,
+    swiglu_quant_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(gate_up_bf16), pool_weight, num_blocks, block_rows,
                                                   intermediate, clamp, act_packed, act_scales);
     cuda_check(cudaGetLastError());
 }

@@ -26,27 +26,28 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
-def exchange_splits(counts_matrix: torch.Tensor, rank: int, local_experts: int):
+def exchange_splits(counts_matrix: torch.Tensor, rank: int, local_experts: int, block_rows: int = 128):
     """Row counts of the two all-to-alls from the all-gathered route counts.
 
     counts_matrix [world, experts] (host): routes rank r sends to global expert e. A rank's send buffer
     is ordered by global expert id, i.e. by destination rank and, inside one destination, by its local
     expert; so the dispatch sends `send[d]` consecutive rows to rank d and receives `recv[r]` rows from
     rank r, source-major. The combine runs the same exchange backwards. Also returns the pool rows this
-    rank needs (each local expert padded to whole 128-row blocks).
+    rank needs (each local expert padded to whole blocks of `block_rows` rows).
     """
     world = counts_matrix.shape[0]
     per_pair = counts_matrix.view(world, world, local_experts)           # [src, dst, local expert]
     send = per_pair[rank].sum(-1).tolist()
     recv = per_pair[:, rank].sum(-1).tolist()
     expert_rows = per_pair[:, rank].sum(0)
-    need = int(((expert_rows + 127) // 128 * 128).sum())
+    need = int(((expert_rows + block_rows - 1) // block_rows * block_rows).sum())
     return send, recv, need
 
 
 class Nvfp4MoE:
     def __init__(self, w1: torch.Tensor, w2: torch.Tensor, num_experts: int, topk: int, clamp: float = 10.0,
-                 max_tokens: int = 4096, group=None, pool_rows: int | None = None, fused: bool = True):
+                 max_tokens: int = 4096, group=None, pool_rows: int | None = None, fused: bool = True,
+                 block_rows: int | None = None):
         """w1 [E_local, 2I, H], w2 [E_local, H, I]: this rank's experts (bf16/fp16/fp32 CUDA tensors)."""
         if not (w1.is_cuda and w2.is_cuda):
             raise ValueError("expert weights must be CUDA tensors: this package has no CPU path")
@@ -69,14 +70,20 @@ class Nvfp4MoE:
         # For the fused FC1 epilogue W1's rows are interleaved 16 gate rows / 16 up rows, so that one lane's
         # accumulator chunk holds whole (gate, up) block pairs.
         self.fused = fused
+        self.phase_events = None        # set to [] to record (name, cuda event) pairs during forward()
         if fused:
             w1 = (w1.reshape(self.local_experts, 2, self.inter // 16, 16, self.hidden)
                   .permute(0, 2, 1, 3, 4).reshape(self.local_experts, two_i, self.hidden))
         self.w1q, self.w1s = quantize(w1.reshape(self.local_experts * two_i, self.hidden))
         self.w2q, self.w2s = quantize(w2.reshape(self.local_experts * self.hidden, self.inter))
         # pool: worst case every route of every rank lands here, each expert padded to 128 rows
-        worst = self.world * max_tokens * topk + self.local_experts * 127
-        self.pool_rows = pool_rows if pool_rows is not None else -(-worst // 128) * 128
+        # block_rows: rows per pool block, 128 (single-CTA tiles) or 256 (CTA pairs); None = per call, 256 once
+        # an expert sees about 160 rows or more
+        self.block_rows = block_rows
+        worst = self.world * max_tokens * topk + self.local_experts * 255
+        self.pool_rows = pool_rows if pool_rows is not None else -(-worst // 256) * 256
+        if self.pool_rows % 256:
+            raise ValueError("pool_rows must be a multiple of 256")
         d, u8, i32 = self.device, torch.uint8, torch.int32
         routes = max_tokens * topk
         self.t_pad = -(-max_tokens // 128) * 128
@@ -86,7 +93,7 @@ class Nvfp4MoE:
         self.send_offset = torch.zeros(num_experts + 1, dtype=i32, device=d)
         self.seg_src = torch.zeros(self.world * self.local_experts + 1, dtype=i32, device=d)
         self.seg_pool = torch.zeros(self.world * self.local_experts, dtype=i32, device=d)
-        self.block_expert = torch.zeros(self.pool_rows // 128, dtype=i32, device=d)
+        self.block_expert = torch.zeros(self.pool_rows // 128, dtype=i32, device=d)        # sized for the smaller block
         self.num_blocks = torch.zeros(1, dtype=i32, device=d)
         self.totals = torch.zeros(4, dtype=i32, device=d)
         self.cursor = torch.zeros(num_experts, dtype=i32, device=d)
@@ -106,19 +113,34 @@ class Nvfp4MoE:
         self.ret_send = torch.empty((recv_cap, self.hidden), dtype=torch.bfloat16, device=d)
         self.ret_recv = self.ret_send if self.world == 1 else torch.empty((routes, self.hidden), dtype=torch.bfloat16, device=d)
         self.y = torch.empty((max_tokens, self.hidden), dtype=torch.bfloat16, device=d)
-        self._fc1, self._fc2 = ctypes.c_void_p(), ctypes.c_void_p()
+        self._plans = {}
         with torch.cuda.device(d):
-            _lib.check(lib.gpu_kernels_nvfp4_grouped_plan_create(
-                ctypes.byref(self._fc1), self.pool_rows, two_i, self.hidden, self.local_experts,
-                self.pool_packed.data_ptr(), self.w1q.data_ptr(), self.pool_scales.data_ptr(), self.w1s.data_ptr(),
-                self.block_expert.data_ptr(), self.num_blocks.data_ptr()))
-            _lib.check(lib.gpu_kernels_nvfp4_grouped_plan_create(
-                ctypes.byref(self._fc2), self.pool_rows, self.hidden, self.inter, self.local_experts,
-                self.act_packed.data_ptr(), self.w2q.data_ptr(), self.act_scales.data_ptr(), self.w2s.data_ptr(),
-                self.block_expert.data_ptr(), self.num_blocks.data_ptr()))
+            for rows in (128, 256):
+                fc1, fc2 = ctypes.c_void_p(), ctypes.c_void_p()
+                _lib.check(lib.gpu_kernels_nvfp4_grouped_plan_create(
+                    ctypes.byref(fc1), self.pool_rows, two_i, self.hidden, self.local_experts, rows,
+                    self.pool_packed.data_ptr(), self.w1q.data_ptr(), self.pool_scales.data_ptr(), self.w1s.data_ptr(),
+                    self.block_expert.data_ptr(), self.num_blocks.data_ptr()))
+                _lib.check(lib.gpu_kernels_nvfp4_grouped_plan_create(
+                    ctypes.byref(fc2), self.pool_rows, self.hidden, self.inter, self.local_experts, rows,
+                    self.act_packed.data_ptr(), self.w2q.data_ptr(), self.act_scales.data_ptr(), self.w2s.data_ptr(),
+                    self.block_expert.data_ptr(), self.num_blocks.data_ptr()))
+                self._plans[rows] = (fc1, fc2)
+
+    def _mark(self, name):
+        if self.phase_events is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self.phase_events.append((name, ev))
+
+    def phase_times_us(self):
+        """Device time between the marks of the last forward() (needs phase_events = [] before the call)."""
+        torch.cuda.synchronize()
+        ev = self.phase_events or []
+        return {ev[i + 1][0]: 1000.0 * ev[i][1].elapsed_time(ev[i + 1][1]) for i in range(len(ev) - 1)}
 
     # ---- phases ----------------------------------------------------------------------------------
-    def _metadata(self, ids, tokens):
+    def _metadata(self, ids, tokens, block_rows):
         lib, s = _lib.load(), _stream()
         routes = tokens * self.topk
         self.counts.zero_()
@@ -128,15 +150,15 @@ class Nvfp4MoE:
         else:
             self.counts_matrix.copy_(self.counts.view(1, -1))
         _lib.check(lib.gpu_kernels_nvfp4_moe_plan(
-            self.counts_matrix.data_ptr(), self.world, self.rank, self.experts, self.pool_rows,
+            self.counts_matrix.data_ptr(), self.world, self.rank, self.experts, self.pool_rows, block_rows,
             self.send_offset.data_ptr(), self.seg_src.data_ptr(), self.seg_pool.data_ptr(),
             self.block_expert.data_ptr(), self.num_blocks.data_ptr(), self.totals.data_ptr(), s))
-        if self.world == 1 and self.pool_rows >= routes + self.local_experts * 127:
+        if self.world == 1 and self.pool_rows >= routes + self.local_experts * (block_rows - 1):
             # one rank, pool sized for the worst case: nothing to exchange and nothing can overflow, so the
             # host never has to look at the counts and the whole forward stays asynchronous
             return [routes], [routes]
         # the split sizes of the all-to-all have to be host integers: one small D2H copy per call
-        send_splits, recv_splits, need = exchange_splits(self.counts_matrix.cpu(), self.rank, self.local_experts)
+        send_splits, recv_splits, need = exchange_splits(self.counts_matrix.cpu(), self.rank, self.local_experts, block_rows)
         if need > self.pool_rows:
             raise RuntimeError(f"expert pool overflow: {need} rows needed, {self.pool_rows} allocated")
         return send_splits, recv_splits
@@ -152,9 +174,15 @@ class Nvfp4MoE:
         with torch.cuda.device(self.device):
             s = _stream()
             # quantise the tokens once; rows are padded to whole 128-row scale atoms
+            self._mark("start")
             self.x_pad[:tokens].copy_(x)
             xq, xs = quantize(self.x_pad)
-            send_splits, recv_splits = self._metadata(ids, tokens)
+            self._mark("quantise tokens")
+            # rows an expert of this rank sees on average decide the block size (and with it single CTAs or pairs)
+            block_rows = self.block_rows or (256 if tokens * self.topk * self.world >= 160 * self.experts else 128)
+            fc1, fc2 = self._plans[block_rows]
+            send_splits, recv_splits = self._metadata(ids, tokens, block_rows)
+            self._mark("metadata (counts, all-gather, plan, host split sizes)")
             self.cursor.zero_()
             self.pool_scales.zero_()
             self.pool_weight.zero_()
@@ -170,22 +198,27 @@ class Nvfp4MoE:
                     xq.data_ptr(), xs.data_ptr(), ids.data_ptr(), weights.data_ptr(), tokens, self.topk, self.hidden,
                     self.send_offset.data_ptr(), self.cursor.data_ptr(), self.send_rows.data_ptr(),
                     self.send_pos.data_ptr(), s))
+                self._mark("pack")
                 dist.all_to_all_single(self.recv_rows[:total_recv], self.send_rows[:tokens * self.topk],
                                        recv_splits, send_splits, group=self.group)
+                self._mark("dispatch all-to-all")
                 _lib.check(lib.gpu_kernels_nvfp4_moe_unpack(
                     self.recv_rows.data_ptr(), self.recv_cap, self.totals.data_ptr(), self.world, self.local_experts,
                     self.hidden, self.seg_src.data_ptr(), self.seg_pool.data_ptr(), self.pool_packed.data_ptr(),
                     self.pool_scales.data_ptr(), self.pool_weight.data_ptr(), self.pool_of_recv.data_ptr(), s))
+            self._mark("pool filled")
             if self.fused:
                 _lib.check(lib.gpu_kernels_nvfp4_grouped_run_swiglu(
-                    self._fc1, self.pool_weight.data_ptr(), self.clamp, self.act_packed.data_ptr(),
+                    fc1, self.pool_weight.data_ptr(), self.clamp, self.act_packed.data_ptr(),
                     self.act_scales.data_ptr(), s))
             else:
-                _lib.check(lib.gpu_kernels_nvfp4_grouped_run(self._fc1, self.gate_up.data_ptr(), 1, s))
+                _lib.check(lib.gpu_kernels_nvfp4_grouped_run(fc1, self.gate_up.data_ptr(), 1, s))
                 _lib.check(lib.gpu_kernels_nvfp4_moe_swiglu_quant(
-                    self.gate_up.data_ptr(), self.pool_weight.data_ptr(), self.num_blocks.data_ptr(), self.pool_rows,
+                    self.gate_up.data_ptr(), self.pool_weight.data_ptr(), self.num_blocks.data_ptr(), block_rows, self.pool_rows,
                     self.inter, self.clamp, self.act_packed.data_ptr(), self.act_scales.data_ptr(), s))
-            _lib.check(lib.gpu_kernels_nvfp4_grouped_run(self._fc2, self.out_pool.data_ptr(), 1, s))
+            self._mark("FC1 + SwiGLU + quantise")
+            _lib.check(lib.gpu_kernels_nvfp4_grouped_run(fc2, self.out_pool.data_ptr(), 1, s))
+            self._mark("FC2")
             if self.world == 1:
                 # send_pos holds pool rows: the reduce reads the second GEMM's output in place
                 _lib.check(lib.gpu_kernels_nvfp4_moe_reduce(
@@ -195,22 +228,26 @@ class Nvfp4MoE:
                 _lib.check(lib.gpu_kernels_nvfp4_moe_return_rows(
                     self.out_pool.data_ptr(), self.pool_of_recv.data_ptr(), self.totals.data_ptr(), self.recv_cap,
                     self.hidden, self.ret_send.data_ptr(), s))
+                self._mark("return_rows")
                 dist.all_to_all_single(self.ret_recv[:tokens * self.topk].view(torch.uint8),
                                        self.ret_send[:total_recv].view(torch.uint8),
                                        send_splits, recv_splits, group=self.group)
+                self._mark("combine all-to-all")
                 _lib.check(lib.gpu_kernels_nvfp4_moe_reduce(
                     self.ret_recv.data_ptr(), self.send_pos.data_ptr(), tokens, self.topk, self.hidden,
                     self.y.data_ptr(), s))
+            self._mark("reduce")
         return self.y[:tokens]
 
     __call__ = forward
 
     def close(self) -> None:
         lib = _lib.load()
-        for plan in (self._fc1, self._fc2):
-            if plan:
-                lib.gpu_kernels_nvfp4_grouped_plan_destroy(plan)
-        self._fc1, self._fc2 = ctypes.c_void_p(), ctypes.c_void_p()
+        for pair in getattr(self, "_plans", {}).values():
+            for plan in pair:
+                if plan:
+                    lib.gpu_kernels_nvfp4_grouped_plan_destroy(plan)
+        self._plans = {}
 
     def __del__(self):
         try:

@@ -82,12 +82,13 @@ int gpu_kernels_nvfp4_gemm_host(int M, int N, int K, const void* A, const void* 
  *      kernels are BF16 for sm_90a and move tokens through peer pointers, these move quantised rows
  *      through an all-to-all the caller runs between pack and unpack). All pointers are device pointers. ---- */
 
-/* Grouped GEMM: pool A [pool_rows, K/2] of 128-row blocks, stacked weights B [experts*n, K/2] (+ scales);
- * block i multiplies expert block_expert[i]; *num_blocks blocks are live (device values, read by the kernel).
- * C [pool_rows, n], fp16 or bf16. Replaces the two WGMMA phases of kernels/moe/fused/sm90.cu:209-550. */
-int gpu_kernels_nvfp4_grouped_plan_create(void** plan, int pool_rows, int n, int k, int experts, const void* A,
-                                          const void* B, const void* SFA, const void* SFB, const void* block_expert,
-                                          const void* num_blocks);
+/* Grouped GEMM: pool A [pool_rows, K/2] of blocks of block_rows (128 or 256) rows, stacked weights
+ * B [experts*n, K/2] (+ scales); block i multiplies expert block_expert[i]; *num_blocks blocks are live (device
+ * values, read by the kernel). 128-row blocks run on single CTAs, 256-row blocks on CTA pairs (for experts with
+ * many rows). C [pool_rows, n], fp16 or bf16. Replaces the two WGMMA phases of kernels/moe/fused/sm90.cu:209-550. */
+int gpu_kernels_nvfp4_grouped_plan_create(void** plan, int pool_rows, int n, int k, int experts, int block_rows,
+                                          const void* A, const void* B, const void* SFA, const void* SFB,
+                                          const void* block_expert, const void* num_blocks);
 void gpu_kernels_nvfp4_grouped_plan_destroy(void* plan);
 int gpu_kernels_nvfp4_grouped_run(void* plan, void* C, int out_bf16, void* stream);
 
@@ -105,9 +106,9 @@ int gpu_kernels_nvfp4_moe_payload_bytes(int hidden);
 int gpu_kernels_nvfp4_moe_route_count(const void* ids, int routes, int experts, void* counts, void* stream);
 /* replaces offsets_kernel (sm90.cu:103-119): counts_matrix int32 [world, experts] (all ranks' counts) ->
  * send_offset [experts+1], seg_src_offset [world*local+1], seg_pool_offset [world*local],
- * block_expert [capacity_rows/128], num_blocks [1], totals [3] = {rows received, pool rows used, overflow}. */
+ * block_expert [capacity_rows/block_rows], num_blocks [1], totals [3] = {rows received, pool rows used, overflow}. */
 int gpu_kernels_nvfp4_moe_plan(const void* counts_matrix, int world, int rank, int experts, int capacity_rows,
-                               void* send_offset, void* seg_src_offset, void* seg_pool_offset, void* block_expert,
+                               int block_rows, void* send_offset, void* seg_src_offset, void* seg_pool_offset, void* block_expert,
                                void* num_blocks, void* totals, void* stream);
 /* quantised tokens (xq [T_pad, hidden/2], xs VEC16 scales), ids int64 [T, topk], weights f32 [T, topk] ->
  * send_rows [T*topk, payload] ordered by destination expert; send_pos [T*topk] = row of each route;
@@ -131,7 +132,7 @@ int gpu_kernels_nvfp4_moe_unpack(const void* recv_rows, int recv_capacity, const
 /* replaces kernels/moe/swiglu.cu:12-26 fused with the re-quantisation for the second GEMM:
  * gate_up bf16 [pool_rows, 2*intermediate] -> NVFP4 activation [pool_rows, intermediate/2] + scales. */
 int gpu_kernels_nvfp4_moe_swiglu_quant(const void* gate_up, const void* pool_weight, const void* num_blocks,
-                                       int pool_rows, int intermediate, float clamp, void* act_packed,
+                                       int block_rows, int pool_rows, int intermediate, float clamp, void* act_packed,
                                        void* act_scales, void* stream);
 /* expert outputs bf16 [pool_rows, hidden] -> rows in the order they were received (for the all-to-all back). */
 int gpu_kernels_nvfp4_moe_return_rows(const void* out_pool, const void* pool_of_recv, const void* totals, int capacity,

@@ -61,11 +61,11 @@ def assert_layer_close(y, ref, what):
     (200, 256, 512, 16, 6, False),       # top-6 as in the benchmark layer
     (300, 512, 256, 8, 2, True),         # skewed routing: one expert spans several 128-row blocks, others empty
 ])
-@pytest.mark.parametrize("fused", [True, False])
-def test_layer_against_oracle(g, tokens, hidden, inter, experts, topk, skew, fused):
+@pytest.mark.parametrize("fused,block_rows", [(True, 128), (False, 128), (True, 256), (False, 256)])
+def test_layer_against_oracle(g, tokens, hidden, inter, experts, topk, skew, fused, block_rows):
     x, logits, w1, w2 = make_layer(tokens + hidden, tokens, hidden, inter, experts, topk, skew)
     ids, wts = g.route(logits, topk)
-    layer = g.Nvfp4MoE(w1, w2, experts, topk, clamp=10.0, max_tokens=max(tokens, 64), fused=fused)
+    layer = g.Nvfp4MoE(w1, w2, experts, topk, clamp=10.0, max_tokens=max(tokens, 64), fused=fused, block_rows=block_rows)
     y = layer(x, ids, wts).clone()
     torch.cuda.synchronize()
     assert_layer_close(y, oracle_layer(x, ids, wts, w1, w2, 10.0), f"T={tokens} H={hidden} I={inter} E={experts} k={topk}")
@@ -106,7 +106,7 @@ def test_routing_plan_pack_unpack_exact(g):
     tokens, hidden, inter, experts, topk = 150, 512, 256, 8, 3
     x, logits, w1, w2 = make_layer(5, tokens, hidden, inter, experts, topk, skew=True)
     ids, wts = g.route(logits, topk)
-    layer = g.Nvfp4MoE(w1, w2, experts, topk, max_tokens=256)
+    layer = g.Nvfp4MoE(w1, w2, experts, topk, max_tokens=256, block_rows=128)
     layer(x, ids, wts)
     torch.cuda.synchronize()
     ids_np, w_np = to_np(ids), to_np(wts)
@@ -158,7 +158,7 @@ def test_reduce_order_exact(g):
 def test_pool_overflow_is_reported(g):
     x, logits, w1, w2 = make_layer(3, 64, 256, 256, 4, 2)
     ids, wts = g.route(logits, 2)
-    layer = g.Nvfp4MoE(w1, w2, 4, 2, max_tokens=64, pool_rows=128)
+    layer = g.Nvfp4MoE(w1, w2, 4, 2, max_tokens=64, pool_rows=256)
     with pytest.raises(RuntimeError, match="overflow"):
         layer(x, ids, wts)
     layer.close()

@@ -34,10 +34,11 @@ def _worker(rank, world, port, out_dir):
         w2 = (torch.randn((experts, hidden, inter), generator=gen, device="cuda") * 0.02).bfloat16()
         layer = g.Nvfp4MoE(w1[rank * local:(rank + 1) * local], w2[rank * local:(rank + 1) * local], experts, topk,
                            max_tokens=128)
-        for call, tokens in enumerate((50 + 30 * rank, 7)):                   # ragged token counts, two calls
+        for call, tokens in enumerate((50 + 30 * rank, 7, 128)):               # ragged token counts; the last call uses 256-row blocks
             gen_r = torch.Generator(device="cuda").manual_seed(1000 * call + rank)
             x = torch.randn((tokens, hidden), generator=gen_r, device="cuda").bfloat16()
             ids, wts = g.route(torch.randn((tokens, experts), generator=gen_r, device="cuda"), topk)
+            layer.block_rows = 256 if call == 2 else None
             y = layer(x, ids, wts)
             torch.cuda.synchronize()
             ref = MO.moe_forward_nvfp4(x.float().cpu().numpy(), ids.cpu().numpy(), wts.cpu().numpy(),
