@@ -411,7 +411,7 @@ struct Roles {
                                     const uint32_t gb = v[b * 32 + 2 * i + h], ub = v[b * 32 + 16 + 2 * i + h];
                                     const float gate = fminf(__uint_as_float((gb + 0x7FFFu + ((gb >> 16) & 1u)) & 0xFFFF0000u), c);
                                     const float up = fminf(fmaxf(__uint_as_float((ub + 0x7FFFu + ((ub >> 16) & 1u)) & 0xFFFF0000u), -c), c);
-                                    a2[h] = gate / (1.0f + expf(-gate)) * up * w;
+                                    a2[h] = silu_fast(gate) * up * w;
                                 }
                                 const __nv_bfloat162 p = __floats2bfloat162_rn(a2[0], a2[1]);
                                 act[i] = *reinterpret_cast<const uint32_t*>(&p);

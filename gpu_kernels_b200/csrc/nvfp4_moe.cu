@@ -221,8 +221,7 @@ swiglu_quant_kernel(const __nv_bfloat16* __restrict__ gate_up, const float* __re
                 const uint32_t ubits = h ? (uw[i] & 0xFFFF0000u) : (uw[i] << 16);
                 const float gate = fminf(__uint_as_float(gbits), clamp);
                 const float upv = fminf(fmaxf(__uint_as_float(ubits), -clamp), clamp);
-                const float silu = gate / (1.0f + expf(-gate));
-                a2[h] = silu * upv * w;
+                a2[h] = silu_fast(gate) * upv * w;
             }
             const __nv_bfloat162 p = __floats2bfloat162_rn(a2[0], a2[1]);
             act[i] = *reinterpret_cast<const uint32_t*>(&p);

@@ -102,6 +102,12 @@ __device__ __forceinline__ uint32_t quantise_block(const float (&v)[16], uint2& 
     return sbyte;
 }
 
+// silu(x) = x / (1 + e^-x) with the hardware exponential and reciprocal (a few ulp of FP32). The
+// result is multiplied and then rounded to bf16 (8 significant bits) before it is quantised, so the
+// approximation almost never survives the rounding; the exact expf + IEEE division cost ten times the
+// instructions and made the fused FC1 epilogue the bottleneck of compute-dense expert GEMMs.
+__device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+
 // ---- 16-bit inputs: two values per instruction, no division -----------------------------------
 //
 // For a bf16 or fp16 input the E2M1 code of x/s can be read off x itself: RN(x/s) lies above,
