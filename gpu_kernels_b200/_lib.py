@@ -37,7 +37,7 @@ SIGNATURES = {
     "gpu_kernels_nvfp4_grouped_run_swiglu": ([P, P, F, P, P, P], I),
     "gpu_kernels_nvfp4_moe_payload_bytes": ([I], I),
     "gpu_kernels_nvfp4_moe_route_count": ([P, I, I, P, P], I),
-    "gpu_kernels_nvfp4_moe_plan": ([P, I, I, I, I, I, P, P, P, P, P, P, P], I),
+    "gpu_kernels_nvfp4_moe_plan": ([P, I, I, I, I, I, P, P, P, P, P, P, P, P], I),
     "gpu_kernels_nvfp4_moe_pack": ([P, P, P, P, I, I, I, P, P, P, P, P], I),
     "gpu_kernels_nvfp4_moe_pack_to_pool": ([P, P, P, P, I, I, I, P, P, P, P, P, P, P], I),
     "gpu_kernels_nvfp4_moe_unpack": ([P, I, P, I, I, I, P, P, P, P, P, P, P], I),
@@ -45,6 +45,12 @@ SIGNATURES = {
     "gpu_kernels_nvfp4_moe_return_rows": ([P, P, P, I, I, P, P], I),
     "gpu_kernels_nvfp4_moe_reduce": ([P, P, I, I, I, P, P], I),
     "gpu_kernels_nvfp4_gemm_host_static": ([I, I, I, P, P, P, P, P, F, P], I),
+    "gpu_kernels_nvfp4_moe_pack_peer": ([P, P, P, P, I, I, I, I, I, P, P, ctypes.POINTER(P), I, P, P], I),
+    "gpu_kernels_nvfp4_moe_return_peer": ([P, P, P, P, P, I, I, I, I, ctypes.POINTER(P), I, P, P], I),
+    "gpu_kernels_nvfp4_ipc_alloc": ([ctypes.c_size_t, ctypes.POINTER(P), P], I),
+    "gpu_kernels_nvfp4_ipc_open": ([P, ctypes.POINTER(P)], I),
+    "gpu_kernels_nvfp4_ipc_close": ([P], I),
+    "gpu_kernels_nvfp4_ipc_free": ([P], I),
     "gpu_kernels_nvfp4_version": ([], ctypes.c_char_p),
     "gpu_kernels_nvfp4_launch_count": ([], ctypes.c_ulonglong),
 }

@@ -374,13 +374,14 @@ int gpu_kernels_nvfp4_moe_route_count(const void* ids, int routes, int experts, 
 
 int gpu_kernels_nvfp4_moe_plan(const void* counts_matrix, int world, int rank, int experts, int capacity_rows,
                                int block_rows, void* send_offset, void* seg_src_offset, void* seg_pool_offset, void* block_expert,
-                               void* num_blocks, void* totals, void* stream) {
+                               void* num_blocks, void* totals, void* peer_offset, void* stream) {
     return guarded([&] {
         nvfp4_b200::require_sm100();
         nvfp4_b200::moe_plan(static_cast<const int*>(counts_matrix), world, rank, experts, capacity_rows, block_rows,
                              static_cast<int*>(send_offset), static_cast<int*>(seg_src_offset),
                              static_cast<int*>(seg_pool_offset), static_cast<int*>(block_expert),
-                             static_cast<int*>(num_blocks), static_cast<int*>(totals), static_cast<cudaStream_t>(stream));
+                             static_cast<int*>(num_blocks), static_cast<int*>(totals), static_cast<int*>(peer_offset),
+                             static_cast<cudaStream_t>(stream));
         nvfp4_b200::g_launches.fetch_add(1, std::memory_order_relaxed);
     });
 }
@@ -494,6 +495,68 @@ int gpu_kernels_nvfp4_gemm_host_static(int M, int N, int K, const void* A, const
         cuda_check(cudaMemcpyAsync(C, dC, c_bytes, cudaMemcpyDeviceToHost, stream));
         cuda_check(cudaStreamSynchronize(stream));
     });
+}
+
+int gpu_kernels_nvfp4_moe_pack_peer(const void* xq, const void* xs, const void* ids, const void* weights, int tokens,
+                                    int topk, int hidden, int world, int local_experts, const void* peer_offset,
+                                    void* cursor, void* const* peer_recv, int recv_capacity, void* error, void* stream) {
+    return guarded([&] {
+        nvfp4_b200::moe_pack_peer(static_cast<const uint8_t*>(xq), static_cast<const uint8_t*>(xs),
+                                  static_cast<const long long*>(ids), static_cast<const float*>(weights), tokens, topk,
+                                  hidden, world, local_experts, static_cast<const int*>(peer_offset),
+                                  static_cast<int*>(cursor), peer_recv, recv_capacity, static_cast<int*>(error),
+                                  static_cast<cudaStream_t>(stream));
+        nvfp4_b200::g_launches.fetch_add(1, std::memory_order_relaxed);
+    });
+}
+
+int gpu_kernels_nvfp4_moe_return_peer(const void* out_pool, const void* recv_rows, const void* pool_of_recv,
+                                      const void* totals, const void* seg_src_offset, int world, int local_experts,
+                                      int hidden, int recv_capacity, void* const* peer_slots, int slot_capacity,
+                                      void* error, void* stream) {
+    return guarded([&] {
+        nvfp4_b200::moe_return_peer(out_pool, static_cast<const uint8_t*>(recv_rows), static_cast<const int*>(pool_of_recv),
+                                    static_cast<const int*>(totals), static_cast<const int*>(seg_src_offset), world,
+                                    local_experts, hidden, recv_capacity, peer_slots, slot_capacity,
+                                    static_cast<int*>(error), static_cast<cudaStream_t>(stream));
+        nvfp4_b200::g_launches.fetch_add(1, std::memory_order_relaxed);
+    });
+}
+
+/* ---- device buffers that other processes of the box can map (CUDA IPC) ---- */
+
+int gpu_kernels_nvfp4_ipc_alloc(size_t bytes, void** ptr, void* handle64) {
+    return guarded([&] {
+        static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+        if (!ptr || !handle64 || bytes == 0) throw std::invalid_argument("ipc_alloc: bad argument");
+        void* p = nullptr;
+        nvfp4_b200::cuda_check(cudaMalloc(&p, bytes));
+        cudaIpcMemHandle_t h{};
+        const cudaError_t e = cudaIpcGetMemHandle(&h, p);
+        if (e != cudaSuccess) { cudaFree(p); nvfp4_b200::cuda_check(e); }
+        nvfp4_b200::cuda_check(cudaMemset(p, 0, bytes));
+        std::memcpy(handle64, &h, sizeof(h));
+        *ptr = p;
+    });
+}
+
+int gpu_kernels_nvfp4_ipc_open(const void* handle64, void** ptr) {
+    return guarded([&] {
+        if (!ptr || !handle64) throw std::invalid_argument("ipc_open: bad argument");
+        cudaIpcMemHandle_t h{};
+        std::memcpy(&h, handle64, sizeof(h));
+        void* p = nullptr;
+        nvfp4_b200::cuda_check(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+        *ptr = p;
+    });
+}
+
+int gpu_kernels_nvfp4_ipc_close(void* ptr) {
+    return guarded([&] { if (ptr) nvfp4_b200::cuda_check(cudaIpcCloseMemHandle(ptr)); });
+}
+
+int gpu_kernels_nvfp4_ipc_free(void* ptr) {
+    return guarded([&] { if (ptr) nvfp4_b200::cuda_check(cudaFree(ptr)); });
 }
 
 const char* gpu_kernels_nvfp4_version(void) { return "nvfp4-b200 0.1 (sm_100a)"; }

@@ -51,7 +51,14 @@ struct MoeShape {
 void moe_route_count(const long long* ids, int routes, int experts, int* counts, cudaStream_t stream);
 void moe_plan(const int* counts_matrix, int world, int rank, int experts, int pool_capacity_rows, int block_rows,
               int* send_offset, int* seg_src_offset, int* seg_pool_offset, int* block_expert, int* num_blocks,
-              int* totals, cudaStream_t stream);
+              int* totals, int* peer_offset, cudaStream_t stream);
+// Expert parallelism over peer memory (NVLink stores into buffers of the other ranks' processes).
+void moe_pack_peer(const uint8_t* xq, const uint8_t* xs, const long long* ids, const float* weights, int tokens,
+                   int topk, int hidden, int world, int local_experts, const int* peer_offset, int* cursor,
+                   void* const* peer_recv, int recv_capacity, int* error, cudaStream_t stream);
+void moe_return_peer(const void* out_pool_bf16, const uint8_t* recv_rows, const int* pool_of_recv, const int* totals,
+                     const int* seg_src_offset, int world, int local_experts, int hidden, int recv_capacity,
+                     void* const* peer_slots, int slot_capacity, int* error, cudaStream_t stream);
 void moe_pack(const uint8_t* xq, const uint8_t* xs, const long long* ids, const float* weights, int tokens, int topk,
               int hidden, const int* send_offset, int* cursor, uint8_t* send_rows, int* send_pos, cudaStream_t stream);
 // Single-rank shortcut: rows go straight into the expert-major pool (no send buffer, no unpack);

@@ -68,7 +68,7 @@ __global__ void plan_kernel(const int* __restrict__ counts, int world, int rank,
                             int block_rows,
                             int* __restrict__ send_offset, int* __restrict__ seg_src_offset,
                             int* __restrict__ seg_pool_offset, int* __restrict__ block_expert,
-                            int* __restrict__ num_blocks, int* __restrict__ totals) {
+                            int* __restrict__ num_blocks, int* __restrict__ totals, int* __restrict__ peer_offset) {
     extern __shared__ int sh[];
     const int local_experts = experts / world;
     const int segments = world * local_experts;          // == experts
@@ -81,6 +81,18 @@ __global__ void plan_kernel(const int* __restrict__ counts, int world, int rank,
     block_exclusive_scan(scan, experts, chunk);
     for (int ge = threadIdx.x; ge < experts; ge += blockDim.x) send_offset[ge] = scan[ge];
     if (threadIdx.x == 0) send_offset[experts] = chunk[blockDim.x];
+    if (peer_offset) {
+        // Where this rank's rows for global expert ge start in the RECEIVE buffer of the rank that owns ge
+        // (source-major there): rows of lower-ranked sources for that destination, then this rank's rows
+        // for the destination's earlier experts. Lets pack write straight into the peer's buffer.
+        for (int ge = threadIdx.x; ge < experts; ge += blockDim.x) {
+            const int d = ge / local_experts;
+            int base = 0;
+            for (int r = 0; r < rank; ++r)
+                for (int e = 0; e < local_experts; ++e) base += counts[r * experts + d * local_experts + e];
+            peer_offset[ge] = base + scan[ge] - scan[d * local_experts];
+        }
+    }
     __syncthreads();
     // 2. segments (source rank r, local expert e) in the receive buffer: source-major, expert order inside
     //    a source, which is the order pack() wrote them
@@ -274,6 +286,67 @@ __global__ void reduce_kernel(const uint4* __restrict__ returned, const int* __r
     }
 }
 
+// ---- expert parallelism over peer memory ----------------------------------------------------
+// Instead of packing into a send buffer and letting a library all-to-all move it, each route's row
+// is stored directly into the receive buffer of the rank that owns its expert (NVLink peer store),
+// and each expert output row directly into the [T, topk, H] slot buffer of the rank the token came
+// from. Every peer write is bounds-checked against the capacity the peers agreed on; a violation is
+// recorded in `error` and the write is skipped. The caller separates the phases with a collective
+// (a stream-ordered barrier): nothing here waits on another GPU.
+struct PeerBuffers {
+    void* ptr[8];
+};
+
+__global__ void pack_peer_kernel(const uint8_t* __restrict__ xq, const uint8_t* __restrict__ xs,
+                                 const long long* __restrict__ ids, const float* __restrict__ weights, int routes,
+                                 int topk, int hidden, int local_experts, const int* __restrict__ peer_offset,
+                                 int* __restrict__ cursor, PeerBuffers recv, int recv_capacity, int* __restrict__ error) {
+    const int lane = threadIdx.x & 31;
+    const int route = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (route >= routes) return;
+    const int token = route / topk;
+    const int expert = int(ids[route]);
+    int dst = 0;
+    if (lane == 0) dst = peer_offset[expert] + atomicAdd(&cursor[expert], 1);
+    dst = __shfl_sync(0xFFFFFFFFu, dst, 0);
+    if (dst < 0 || dst >= recv_capacity) {
+        if (lane == 0) atomicOr(error, 1);
+        return;
+    }
+    uint8_t* out = static_cast<uint8_t*>(recv.ptr[expert / local_experts]) + size_t(dst) * payload_bytes(hidden);
+    const uint4* src = reinterpret_cast<const uint4*>(xq + size_t(token) * (hidden / 2));
+    for (int i = lane; i < hidden / 32; i += 32) reinterpret_cast<uint4*>(out)[i] = __ldg(src + i);
+    for (int b = lane; b < hidden / 16; b += 32) out[hidden / 2 + b] = xs[scale_byte_offset(token, b, hidden)];
+    if (lane == 0) {
+        *reinterpret_cast<float*>(out + hidden / 2 + hidden / 16) = weights[route];
+        *reinterpret_cast<int*>(out + hidden / 2 + hidden / 16 + 4) = route;       // where the result goes back to
+    }
+}
+
+// One CTA per received row: expert output -> slot `route` of the source rank's [T*topk, H] buffer.
+__global__ void return_peer_kernel(const uint4* __restrict__ out_pool, const uint8_t* __restrict__ recv_rows,
+                                   const int* __restrict__ pool_of_recv, const int* __restrict__ totals,
+                                   const int* __restrict__ seg_src_offset, int segments, int local_experts, int hidden,
+                                   PeerBuffers slots, int slot_capacity, int* __restrict__ error) {
+    const int p = blockIdx.x;
+    if (p >= totals[0] || totals[2]) return;
+    int lo = 0, hi = segments;
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (seg_src_offset[mid] <= p) lo = mid; else hi = mid;
+    }
+    const int src_rank = lo / local_experts;
+    const int route = *reinterpret_cast<const int*>(recv_rows + size_t(p) * payload_bytes(hidden) + hidden / 2 + hidden / 16 + 4);
+    if (route < 0 || route >= slot_capacity) {
+        if (threadIdx.x == 0) atomicOr(error, 2);
+        return;
+    }
+    const int row_vec = hidden / 8;
+    const uint4* src = out_pool + size_t(pool_of_recv[p]) * row_vec;
+    uint4* dst = static_cast<uint4*>(slots.ptr[src_rank]) + size_t(route) * row_vec;
+    for (int i = threadIdx.x; i < row_vec; i += blockDim.x) dst[i] = __ldg(src + i);
+}
+
 void check_hidden(int hidden, const char* what) {
     if (hidden <= 0 || hidden % 256) throw std::invalid_argument(std::string(what) + ": width must be a positive multiple of 256");
 }
@@ -290,7 +363,7 @@ void moe_route_count(const long long* ids, int routes, int experts, int* counts,
 
 void moe_plan(const int* counts_matrix, int world, int rank, int experts, int pool_capacity_rows, int block_rows,
               int* send_offset, int* seg_src_offset, int* seg_pool_offset, int* block_expert, int* num_blocks,
-              int* totals, cudaStream_t stream) {
+              int* totals, int* peer_offset, cudaStream_t stream) {
     if (world <= 0 || rank < 0 || rank >= world || experts <= 0 || experts % world || experts > 4096)
         throw std::invalid_argument("moe plan: experts must divide over the ranks (and be <= 4096)");
     if (block_rows != 128 && block_rows != 256) throw std::invalid_argument("moe plan: block rows must be 128 or 256");
@@ -298,7 +371,7 @@ void moe_plan(const int* counts_matrix, int world, int rank, int experts, int po
     const int local = experts / world;
     plan_kernel<<<1, 256, (experts + local + 257) * sizeof(int), stream>>>(counts_matrix, world, rank, experts, pool_capacity_rows, block_rows,
                                                                    send_offset, seg_src_offset, seg_pool_offset,
-                                                                   block_expert, num_blocks, totals);
+                                                                   block_expert, num_blocks, totals, peer_offset);
     cuda_check(cudaGetLastError());
 }
 
@@ -361,6 +434,41 @@ void moe_reduce(const void* returned_bf16, const int* send_pos, int tokens, int 
     if (tokens <= 0) return;
     reduce_kernel<<<tokens, 128, 0, stream>>>(static_cast<const uint4*>(returned_bf16), send_pos, topk, hidden / 8,
                                               static_cast<uint4*>(y_bf16));
+    cuda_check(cudaGetLastError());
+}
+
+void moe_pack_peer(const uint8_t* xq, const uint8_t* xs, const long long* ids, const float* weights, int tokens,
+                   int topk, int hidden, int world, int local_experts, const int* peer_offset, int* cursor,
+                   void* const* peer_recv, int recv_capacity, int* error, cudaStream_t stream) {
+    check_hidden(hidden, "moe pack_peer");
+    if (world < 1 || world > 8 || !peer_recv) throw std::invalid_argument("moe pack_peer: 1..8 ranks");
+    const int routes = tokens * topk;
+    if (routes == 0) return;
+    PeerBuffers recv{};
+    for (int r = 0; r < world; ++r) {
+        if (!peer_recv[r]) throw std::invalid_argument("moe pack_peer: null peer buffer");
+        recv.ptr[r] = peer_recv[r];
+    }
+    pack_peer_kernel<<<(routes * 32 + 255) / 256, 256, 0, stream>>>(xq, xs, ids, weights, routes, topk, hidden,
+                                                                    local_experts, peer_offset, cursor, recv,
+                                                                    recv_capacity, error);
+    cuda_check(cudaGetLastError());
+}
+
+void moe_return_peer(const void* out_pool_bf16, const uint8_t* recv_rows, const int* pool_of_recv, const int* totals,
+                     const int* seg_src_offset, int world, int local_experts, int hidden, int recv_capacity,
+                     void* const* peer_slots, int slot_capacity, int* error, cudaStream_t stream) {
+    check_hidden(hidden, "moe return_peer");
+    if (world < 1 || world > 8 || !peer_slots) throw std::invalid_argument("moe return_peer: 1..8 ranks");
+    if (recv_capacity <= 0) return;
+    PeerBuffers slots{};
+    for (int r = 0; r < world; ++r) {
+        if (!peer_slots[r]) throw std::invalid_argument("moe return_peer: null peer buffer");
+        slots.ptr[r] = peer_slots[r];
+    }
+    return_peer_kernel<<<recv_capacity, 128, 0, stream>>>(static_cast<const uint4*>(out_pool_bf16), recv_rows, pool_of_recv,
+                                                          totals, seg_src_offset, world * local_experts, local_experts,
+                                                          hidden, slots, slot_capacity, error);
     cuda_check(cudaGetLastError());
 }
 

@@ -47,7 +47,7 @@ def exchange_splits(counts_matrix: torch.Tensor, rank: int, local_experts: int, 
 class Nvfp4MoE:
     def __init__(self, w1: torch.Tensor, w2: torch.Tensor, num_experts: int, topk: int, clamp: float = 10.0,
                  max_tokens: int = 4096, group=None, pool_rows: int | None = None, fused: bool = True,
-                 block_rows: int | None = None):
+                 block_rows: int | None = None, exchange: str = "peer"):
         """w1 [E_local, 2I, H], w2 [E_local, H, I]: this rank's experts (bf16/fp16/fp32 CUDA tensors)."""
         if not (w1.is_cuda and w2.is_cuda):
             raise ValueError("expert weights must be CUDA tensors: this package has no CPU path")
@@ -70,6 +70,12 @@ class Nvfp4MoE:
         # For the fused FC1 epilogue W1's rows are interleaved 16 gate rows / 16 up rows, so that one lane's
         # accumulator chunk holds whole (gate, up) block pairs.
         self.fused = fused
+        # exchange between ranks: "peer" = rows are stored straight into the other ranks' buffers over NVLink
+        # (buffers shared through CUDA IPC, no library all-to-all, no host synchronisation); "nccl" = pack,
+        # all_to_all_single, unpack (needs the split sizes on the host every call)
+        if exchange not in ("peer", "nccl"):
+            raise ValueError("exchange must be 'peer' or 'nccl'")
+        self.exchange = exchange if self.world > 1 else "local"
         self.phase_events = None        # set to [] to record (name, cuda event) pairs during forward()
         if fused:
             w1 = (w1.reshape(self.local_experts, 2, self.inter // 16, 16, self.hidden)
@@ -102,6 +108,10 @@ class Nvfp4MoE:
         recv_cap = self.world * routes
         self.recv_cap = recv_cap
         self.recv_rows = self.send_rows if self.world == 1 else torch.empty((recv_cap, self.payload), dtype=u8, device=d)
+        self.recv_ptr = self.recv_rows.data_ptr()
+        self._peer = None
+        if self.exchange == "peer":
+            self._setup_peer_buffers(routes, recv_cap)
         self.pool_packed = torch.zeros((self.pool_rows, self.hidden // 2), dtype=u8, device=d)
         self.pool_scales = torch.zeros(self.pool_rows * self.hidden // 16, dtype=u8, device=d)
         self.pool_weight = torch.zeros(self.pool_rows, dtype=torch.float32, device=d)
@@ -126,6 +136,53 @@ class Nvfp4MoE:
                     self.act_packed.data_ptr(), self.w2q.data_ptr(), self.act_scales.data_ptr(), self.w2s.data_ptr(),
                     self.block_expert.data_ptr(), self.num_blocks.data_ptr()))
                 self._plans[rows] = (fc1, fc2)
+
+    def _setup_peer_buffers(self, routes, recv_cap):
+        """Receive and result-slot buffers that every rank of the group can write (CUDA IPC)."""
+        lib = _lib.load()
+        sizes = (recv_cap * self.payload, routes * self.hidden * 2)
+        own, handles = [], []
+        with torch.cuda.device(self.device):
+            for nbytes in sizes:
+                ptr, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+                _lib.check(lib.gpu_kernels_nvfp4_ipc_alloc(nbytes, ctypes.byref(ptr), handle))
+                own.append(ptr.value)
+                handles.append(handle.raw)
+            gathered = [None] * self.world
+            dist.all_gather_object(gathered, handles, group=self.group)
+            tables, opened = [], []
+            for which in range(2):
+                table = (ctypes.c_void_p * self.world)()
+                for r in range(self.world):
+                    if r == self.rank:
+                        table[r] = own[which]
+                    else:
+                        ptr = ctypes.c_void_p()
+                        _lib.check(lib.gpu_kernels_nvfp4_ipc_open(gathered[r][which], ctypes.byref(ptr)))
+                        table[r] = ptr.value
+                        opened.append(ptr.value)
+                tables.append(table)
+        self._peer = {"own": own, "opened": opened, "recv": tables[0], "slots": tables[1]}
+        self.recv_ptr = own[0]
+        self.slots_ptr = own[1]
+        d = self.device
+        self.peer_offset = torch.zeros(self.experts, dtype=torch.int32, device=d)
+        self.peer_error = torch.zeros(1, dtype=torch.int32, device=d)
+        self.identity = torch.arange(routes, dtype=torch.int32, device=d)
+        self._fence = torch.zeros(1, dtype=torch.int32, device=d)
+
+    def _barrier(self):
+        # a stream-ordered collective: it completes on a rank only after every rank's earlier work on its
+        # stream (the peer stores) has finished, and nothing on the host waits for it
+        dist.all_reduce(self._fence, group=self.group)
+
+    def check(self) -> None:
+        """Synchronises and raises if a peer store was out of bounds or the pool overflowed in the last calls."""
+        torch.cuda.synchronize(self.device)
+        if self._peer is not None and int(self.peer_error.item()):
+            raise RuntimeError(f"expert exchange: a peer store was outside the agreed capacity (code {int(self.peer_error.item())})")
+        if int(self.totals[2].item()):
+            raise RuntimeError("expert pool overflow")
 
     def _mark(self, name):
         if self.phase_events is not None:
@@ -152,7 +209,11 @@ class Nvfp4MoE:
         _lib.check(lib.gpu_kernels_nvfp4_moe_plan(
             self.counts_matrix.data_ptr(), self.world, self.rank, self.experts, self.pool_rows, block_rows,
             self.send_offset.data_ptr(), self.seg_src.data_ptr(), self.seg_pool.data_ptr(),
-            self.block_expert.data_ptr(), self.num_blocks.data_ptr(), self.totals.data_ptr(), s))
+            self.block_expert.data_ptr(), self.num_blocks.data_ptr(), self.totals.data_ptr(),
+            self.peer_offset.data_ptr() if self._peer is not None else None, s))
+        if self._peer is not None and self.pool_rows >= self.world * self.max_tokens * self.topk + self.local_experts * (block_rows - 1):
+            # peer exchange with a worst-case pool: the host needs nothing from the counts
+            return None, None
         if self.world == 1 and self.pool_rows >= routes + self.local_experts * (block_rows - 1):
             # one rank, pool sized for the worst case: nothing to exchange and nothing can overflow, so the
             # host never has to look at the counts and the whole forward stays asynchronous
@@ -186,8 +247,20 @@ class Nvfp4MoE:
             self.cursor.zero_()
             self.pool_scales.zero_()
             self.pool_weight.zero_()
-            total_recv = sum(recv_splits)
-            if self.world == 1:
+            total_recv = sum(recv_splits) if recv_splits is not None else 0
+            if self.world > 1 and send_splits is None:
+                _lib.check(lib.gpu_kernels_nvfp4_moe_pack_peer(
+                    xq.data_ptr(), xs.data_ptr(), ids.data_ptr(), weights.data_ptr(), tokens, self.topk, self.hidden,
+                    self.world, self.local_experts, self.peer_offset.data_ptr(), self.cursor.data_ptr(),
+                    self._peer["recv"], self.recv_cap, self.peer_error.data_ptr(), s))
+                self._mark("pack into the peers' receive buffers")
+                self._barrier()
+                self._mark("barrier")
+                _lib.check(lib.gpu_kernels_nvfp4_moe_unpack(
+                    self.recv_ptr, self.recv_cap, self.totals.data_ptr(), self.world, self.local_experts,
+                    self.hidden, self.seg_src.data_ptr(), self.seg_pool.data_ptr(), self.pool_packed.data_ptr(),
+                    self.pool_scales.data_ptr(), self.pool_weight.data_ptr(), self.pool_of_recv.data_ptr(), s))
+            elif self.world == 1:
                 # nothing to exchange: rows go straight into the expert-major pool
                 _lib.check(lib.gpu_kernels_nvfp4_moe_pack_to_pool(
                     xq.data_ptr(), xs.data_ptr(), ids.data_ptr(), weights.data_ptr(), tokens, self.topk, self.hidden,
@@ -219,7 +292,17 @@ class Nvfp4MoE:
             self._mark("FC1 + SwiGLU + quantise")
             _lib.check(lib.gpu_kernels_nvfp4_grouped_run(fc2, self.out_pool.data_ptr(), 1, s))
             self._mark("FC2")
-            if self.world == 1:
+            if self.world > 1 and send_splits is None:
+                _lib.check(lib.gpu_kernels_nvfp4_moe_return_peer(
+                    self.out_pool.data_ptr(), self.recv_ptr, self.pool_of_recv.data_ptr(), self.totals.data_ptr(),
+                    self.seg_src.data_ptr(), self.world, self.local_experts, self.hidden, self.recv_cap,
+                    self._peer["slots"], self.max_tokens * self.topk, self.peer_error.data_ptr(), s))
+                self._mark("expert outputs into the sources' slot buffers")
+                self._barrier()
+                self._mark("barrier")
+                _lib.check(lib.gpu_kernels_nvfp4_moe_reduce(
+                    self.slots_ptr, self.identity.data_ptr(), tokens, self.topk, self.hidden, self.y.data_ptr(), s))
+            elif self.world == 1:
                 # send_pos holds pool rows: the reduce reads the second GEMM's output in place
                 _lib.check(lib.gpu_kernels_nvfp4_moe_reduce(
                     self.out_pool.data_ptr(), self.send_pos.data_ptr(), tokens, self.topk, self.hidden,
@@ -243,6 +326,15 @@ class Nvfp4MoE:
 
     def close(self) -> None:
         lib = _lib.load()
+        if self._peer is not None:
+            torch.cuda.synchronize(self.device)
+            for ptr in self._peer["opened"]:
+                lib.gpu_kernels_nvfp4_ipc_close(ptr)
+            if dist.is_initialized():
+                dist.barrier(group=self.group)          # nobody still maps this rank's buffers
+            for ptr in self._peer["own"]:
+                lib.gpu_kernels_nvfp4_ipc_free(ptr)
+            self._peer = None
         for pair in getattr(self, "_plans", {}).values():
             for plan in pair:
                 if plan:

@@ -106,10 +106,12 @@ int gpu_kernels_nvfp4_moe_payload_bytes(int hidden);
 int gpu_kernels_nvfp4_moe_route_count(const void* ids, int routes, int experts, void* counts, void* stream);
 /* replaces offsets_kernel (sm90.cu:103-119): counts_matrix int32 [world, experts] (all ranks' counts) ->
  * send_offset [experts+1], seg_src_offset [world*local+1], seg_pool_offset [world*local],
- * block_expert [capacity_rows/block_rows], num_blocks [1], totals [3] = {rows received, pool rows used, overflow}. */
+ * block_expert [capacity_rows/block_rows], num_blocks [1], totals [3] = {rows received, pool rows used, overflow};
+ * peer_offset [experts] (may be null): where this rank's rows for each global expert start in the receive
+ * buffer of the rank that owns it, for gpu_kernels_nvfp4_moe_pack_peer. */
 int gpu_kernels_nvfp4_moe_plan(const void* counts_matrix, int world, int rank, int experts, int capacity_rows,
                                int block_rows, void* send_offset, void* seg_src_offset, void* seg_pool_offset, void* block_expert,
-                               void* num_blocks, void* totals, void* stream);
+                               void* num_blocks, void* totals, void* peer_offset, void* stream);
 /* quantised tokens (xq [T_pad, hidden/2], xs VEC16 scales), ids int64 [T, topk], weights f32 [T, topk] ->
  * send_rows [T*topk, payload] ordered by destination expert; send_pos [T*topk] = row of each route;
  * cursor int32 [experts] zeroed by the caller. */
@@ -154,6 +156,30 @@ int gpu_kernels_nvfp4_moe_reduce(const void* returned, const void* send_pos, int
  * synchronises `stream` before it returns. */
 int gpu_kernels_nvfp4_gemm_host_static(int M, int N, int K, const void* A, const void* B, const void* SFA,
                                        const void* SFB, void* C, float alpha, void* stream);
+
+/* Expert parallelism over peer memory: the fused replacement of pack + all-to-all and of return_rows +
+ * all-to-all. The reference moves tokens the same way, by device-initiated peer loads and stores
+ * (kernels/moe/fused/sm90.cu:296-319 pulls, :532-541 pushes); here both directions are stores.
+ * pack_peer writes each route's quantised row (+ weight and route index) straight into the receive buffer
+ * of the rank that owns its expert; return_peer writes each expert output row straight into slot
+ * [route] of the [T*topk, hidden] bf16 buffer of the rank the token came from. peer_recv / peer_slots are
+ * host arrays of `world` device pointers (this process's mappings of every rank's buffer, own included).
+ * Every peer write is bounds-checked against the capacities (rows); a violation sets *error (device int)
+ * and skips the write. The caller must put a stream-ordered collective between pack_peer and unpack, and
+ * between return_peer and reduce (and nothing here waits on another GPU). */
+int gpu_kernels_nvfp4_moe_pack_peer(const void* xq, const void* xs, const void* ids, const void* weights, int tokens,
+                                    int topk, int hidden, int world, int local_experts, const void* peer_offset,
+                                    void* cursor, void* const* peer_recv, int recv_capacity, void* error, void* stream);
+int gpu_kernels_nvfp4_moe_return_peer(const void* out_pool, const void* recv_rows, const void* pool_of_recv,
+                                      const void* totals, const void* seg_src_offset, int world, int local_experts,
+                                      int hidden, int recv_capacity, void* const* peer_slots, int slot_capacity,
+                                      void* error, void* stream);
+/* Device memory that the other processes of the box can map: ipc_alloc = cudaMalloc (zeroed) + a 64-byte handle
+ * to hand to the peers; ipc_open maps a peer's handle (lazy peer access); ipc_close / ipc_free undo them. */
+int gpu_kernels_nvfp4_ipc_alloc(size_t bytes, void** ptr, void* handle64);
+int gpu_kernels_nvfp4_ipc_open(const void* handle64, void** ptr);
+int gpu_kernels_nvfp4_ipc_close(void* ptr);
+int gpu_kernels_nvfp4_ipc_free(void* ptr);
 
 /* Library version string and the number of kernels this library has launched so far in this process. */
 const char* gpu_kernels_nvfp4_version(void);

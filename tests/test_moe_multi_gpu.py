@@ -32,21 +32,23 @@ def _worker(rank, world, port, out_dir):
         gen = torch.Generator(device="cuda").manual_seed(100)                # same weights on every rank
         w1 = (torch.randn((experts, 2 * inter, hidden), generator=gen, device="cuda") * 0.02).bfloat16()
         w2 = (torch.randn((experts, hidden, inter), generator=gen, device="cuda") * 0.02).bfloat16()
-        layer = g.Nvfp4MoE(w1[rank * local:(rank + 1) * local], w2[rank * local:(rank + 1) * local], experts, topk,
-                           max_tokens=128)
-        for call, tokens in enumerate((50 + 30 * rank, 7, 128)):               # ragged token counts; the last call uses 256-row blocks
-            gen_r = torch.Generator(device="cuda").manual_seed(1000 * call + rank)
-            x = torch.randn((tokens, hidden), generator=gen_r, device="cuda").bfloat16()
-            ids, wts = g.route(torch.randn((tokens, experts), generator=gen_r, device="cuda"), topk)
-            layer.block_rows = 256 if call == 2 else None
-            y = layer(x, ids, wts)
-            torch.cuda.synchronize()
-            ref = MO.moe_forward_nvfp4(x.float().cpu().numpy(), ids.cpu().numpy(), wts.cpu().numpy(),
-                                       w1.float().cpu().numpy(), w2.float().cpu().numpy(), 10.0)
-            got = y.float().cpu().numpy()
-            rel = np.linalg.norm(got - ref) / np.linalg.norm(ref)
-            assert not np.isnan(got).any() and rel <= 2e-2, f"rank {rank} call {call}: rel {rel:.3e}"
-        layer.close()
+        for exchange in ("peer", "nccl"):
+            layer = g.Nvfp4MoE(w1[rank * local:(rank + 1) * local], w2[rank * local:(rank + 1) * local], experts, topk,
+                               max_tokens=128, exchange=exchange)
+            for call, tokens in enumerate((50 + 30 * rank, 7, 128)):               # ragged token counts; the last call uses 256-row blocks
+                gen_r = torch.Generator(device="cuda").manual_seed(1000 * call + rank)
+                x = torch.randn((tokens, hidden), generator=gen_r, device="cuda").bfloat16()
+                ids, wts = g.route(torch.randn((tokens, experts), generator=gen_r, device="cuda"), topk)
+                layer.block_rows = 256 if call == 2 else None
+                y = layer(x, ids, wts)
+                torch.cuda.synchronize()
+                ref = MO.moe_forward_nvfp4(x.float().cpu().numpy(), ids.cpu().numpy(), wts.cpu().numpy(),
+                                           w1.float().cpu().numpy(), w2.float().cpu().numpy(), 10.0)
+                got = y.float().cpu().numpy()
+                rel = np.linalg.norm(got - ref) / np.linalg.norm(ref)
+                assert not np.isnan(got).any() and rel <= 2e-2, f"rank {rank} {exchange} call {call}: rel {rel:.3e}"
+            layer.check()
+            layer.close()
         open(os.path.join(out_dir, f"ok{rank}"), "w").close()
     finally:
         dist.destroy_process_group()
