@@ -422,6 +422,25 @@ def run_moe(args, rank, world, local_rank):
     barrier()
     t1 = time.perf_counter()
     launches = _lib.launch_count() - launches0
+    ms_eager = start.elapsed_time(stop)
+    # the same forward recorded once as a CUDA graph and replayed (inputs copied into the graph's buffers on
+    # the device inside the timed region): no per-kernel launch cost on the host
+    gx, gids, gwts, gy, graph = layer.capture(tokens)
+
+    def replay(i):
+        x_, ids_, wts_ = sets[i % 4]
+        gx.copy_(x_); gids.copy_(ids_); gwts.copy_(wts_)
+        graph.replay()
+
+    for i in range(3):
+        replay(i)
+    barrier()
+    start.record()
+    for i in range(args.steps):
+        replay(i)
+    stop.record()
+    barrier()
+    t1 = time.perf_counter()
     ms = start.elapsed_time(stop)
     clocks = sampler.stop(t0, t1) if sampler is not None else None
     # end to end: inputs from pinned host memory, result back to the host, every step
@@ -437,9 +456,12 @@ def run_moe(args, rank, world, local_rank):
     barrier()
     e2e_ms = start.elapsed_time(stop)
     if world > 1:
-        t = torch.tensor([ms, e2e_ms], device=dev)
+        t = torch.tensor([ms, e2e_ms, ms_eager], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_ms = (float(v) for v in t.tolist())
+        ms, e2e_ms, ms_eager = (float(v) for v in t.tolist())
+    filler = torch.empty(1 << 28, dtype=torch.uint8, device=dev)
+    for _ in range(24):                                         # ~2 ms of device work, so that the host runs ahead and
+        filler.zero_()                                          # the marks below time the device, not the launches
     layer.phase_events = []
     layer(*sets[0])
     phases = {k_: round(v_, 1) for k_, v_ in layer.phase_times_us().items()}
@@ -463,7 +485,7 @@ def run_moe(args, rank, world, local_rank):
         roofline = {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
                     "peak_source": f"{peaks['source']} copy bandwidth", "traffic": None,
                     "algorithmic_bytes_per_step": alg_bytes, "kernel": "nvfp4_gemm_kernel<1,256> grouped (FC1 + FC2)",
-                    "note": "whole-step time (8 kernels + 2 all-to-alls + one host sync) against the bytes of the two grouped GEMMs"}
+                    "note": "whole-step time (every kernel and collective of the forward) against the bytes of the two grouped GEMMs"}
     else:
         roofline = {"bound": "tensor", "achieved": value / world, "peak": tensor_peak, "unit": "TFLOP/s",
                     "frac": value / world / tensor_peak, "peak_source": f"4 x {peaks['source']} cuBLAS bf16 (burst)",
@@ -474,7 +496,8 @@ def run_moe(args, rank, world, local_rank):
         "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "nvfp4 operands, f32 accumulate, bf16 activations and output", "data": "synthetic",
         "config": {"workload": args.workload, "tokens_per_gpu": tokens, **MOE_SHAPE, "expert_parallel": world,
-                   "experts_touched_rank0": touched, "phases_us_rank0": phases, "l2": "expert weights (3.6 GB per 256 experts) far exceed L2; inputs rotate over 4 sets"},
+                   "experts_touched_rank0": touched, "launch": "one CUDA graph per forward (Nvfp4MoE.capture)",
+                   "ms_per_step_eager": ms_eager / args.steps, "phases_us_rank0_eager": phases, "l2": "expert weights (3.6 GB per 256 experts) far exceed L2; inputs rotate over 4 sets"},
         "clocks": clocks,
         "e2e": {"value": flops / (e2e_ms / e2e_steps * 1e-3) / 1e12, "unit": UNIT,
                 "h2d_bytes_per_step": tokens * (H * 2 + topk * 12), "d2h_bytes_per_step": tokens * H * 2, "steps": e2e_steps,

@@ -35,12 +35,13 @@ SIGNATURES = {
     "gpu_kernels_nvfp4_grouped_plan_destroy": ([P], None),
     "gpu_kernels_nvfp4_grouped_run": ([P, P, I, P], I),
     "gpu_kernels_nvfp4_grouped_run_swiglu": ([P, P, F, P, P, P], I),
+    "gpu_kernels_nvfp4_grouped_run_scatter": ([P, P, P, P, I, I, I, P], I),
     "gpu_kernels_nvfp4_moe_payload_bytes": ([I], I),
     "gpu_kernels_nvfp4_moe_route_count": ([P, I, I, P, P], I),
     "gpu_kernels_nvfp4_moe_plan": ([P, I, I, I, I, I, P, P, P, P, P, P, P, P], I),
     "gpu_kernels_nvfp4_moe_pack": ([P, P, P, P, I, I, I, P, P, P, P, P], I),
     "gpu_kernels_nvfp4_moe_pack_to_pool": ([P, P, P, P, I, I, I, P, P, P, P, P, P, P], I),
-    "gpu_kernels_nvfp4_moe_unpack": ([P, I, P, I, I, I, P, P, P, P, P, P, P], I),
+    "gpu_kernels_nvfp4_moe_unpack": ([P, I, P, I, I, I, P, P, P, P, P, P, P, P], I),
     "gpu_kernels_nvfp4_moe_swiglu_quant": ([P, P, P, I, I, I, F, P, P, P], I),
     "gpu_kernels_nvfp4_moe_return_rows": ([P, P, P, I, I, P, P], I),
     "gpu_kernels_nvfp4_moe_reduce": ([P, P, I, I, I, P, P], I),

@@ -211,8 +211,9 @@ int gpu_kernels_nvfp4_custom(void* plan, void* C, void* stream) {
 
 int gpu_kernels_nvfp4_validate(void* plan) {
     return guarded([&] {
-        Plan& p = as_plan(plan);
-        p.impl.validate();
+        // the status word is per device, not per plan: a null plan checks the current device (grouped launches)
+        if (!plan) gpu_kernels::nvfp4_sm100_implementation().validate();
+        else as_plan(plan).impl.validate();
     });
 }
 
@@ -357,7 +358,20 @@ int gpu_kernels_nvfp4_grouped_run_swiglu(void* plan, const void* row_weight, flo
         if (!plan) throw std::invalid_argument("null plan");
         nvfp4_b200::grouped_launch_fused(*static_cast<nvfp4_b200::GroupedGemm*>(plan), nullptr, 1,
                                          static_cast<uint8_t*>(act_packed), static_cast<uint8_t*>(act_scales),
-                                         static_cast<const float*>(row_weight), clamp, static_cast<cudaStream_t>(stream));
+                                         static_cast<const float*>(row_weight), clamp, nullptr, nullptr, 0, 0,
+                                         static_cast<cudaStream_t>(stream));
+    });
+}
+
+int gpu_kernels_nvfp4_grouped_run_scatter(void* plan, const void* row_dst, const void* slots, void* own_slots, int world,
+                                          int slot_rows, int out_bf16, void* stream) {
+    return guarded([&] {
+        if (!plan) throw std::invalid_argument("null plan");
+        if (!row_dst) throw std::invalid_argument("grouped_run_scatter: null row_dst");
+        nvfp4_b200::grouped_launch_fused(*static_cast<nvfp4_b200::GroupedGemm*>(plan), own_slots, out_bf16, nullptr, nullptr,
+                                         nullptr, 0.0f, static_cast<const int*>(row_dst),
+                                         static_cast<void* const*>(slots), world, slot_rows,
+                                         static_cast<cudaStream_t>(stream));
     });
 }
 
@@ -417,13 +431,14 @@ int gpu_kernels_nvfp4_moe_pack_to_pool(const void* xq, const void* xs, const voi
 int gpu_kernels_nvfp4_moe_unpack(const void* recv_rows, int recv_capacity, const void* totals, int world,
                                  int local_experts, int hidden, const void* seg_src_offset, const void* seg_pool_offset,
                                  void* pool_packed, void* pool_scales, void* pool_weight, void* pool_of_recv,
-                                 void* stream) {
+                                 void* pool_dst, void* stream) {
     return guarded([&] {
         nvfp4_b200::moe_unpack(static_cast<const uint8_t*>(recv_rows), recv_capacity, static_cast<const int*>(totals),
                                world, local_experts, hidden, static_cast<const int*>(seg_src_offset),
                                static_cast<const int*>(seg_pool_offset), static_cast<uint8_t*>(pool_packed),
                                static_cast<uint8_t*>(pool_scales), static_cast<float*>(pool_weight),
-                               static_cast<int*>(pool_of_recv), static_cast<cudaStream_t>(stream));
+                               static_cast<int*>(pool_of_recv), static_cast<int*>(pool_dst),
+                               static_cast<cudaStream_t>(stream));
         nvfp4_b200::g_launches.fetch_add(1, std::memory_order_relaxed);
     });
 }

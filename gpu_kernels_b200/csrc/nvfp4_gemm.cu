@@ -128,6 +128,13 @@ struct GemmArgs {
     uint8_t* act_scales;            // VEC16 layout of [pool_rows, N/2]
     const float* row_weight;        // [pool_rows]
     float swiglu_clamp;
+    // Fused second expert GEMM + combine (grouped mode, register store route): row r of the pool is not
+    // written to C but to row (row_dst[r] & 0xFFFFFF) - 1 of the [slot_rows, N] buffer of rank row_dst[r] >> 24
+    // (peer memory over NVLink, or this rank's own buffer); row_dst[r] == 0 marks a padding row.
+    const int* row_dst;
+    void* const* slots;             // device array of `world` buffer addresses
+    int world;
+    int slot_rows;
 };
 
 enum ProfSlot { PROF_PROD_WAIT = 0, PROF_PROD_TOTAL, PROF_MMA_WAIT_FULL, PROF_MMA_WAIT_ACC, PROF_MMA_TOTAL,
@@ -425,8 +432,63 @@ struct Roles {
                         static_cast<uint16_t>(sb[0] | (sb[1] << 8));
                     continue;
                 }
+                if (Cfg::STAGED_EPILOGUE && g.row_dst) {
+                    // Scatter through shared memory: every lane stages the 128 bytes of its own row (rows 144
+                    // bytes apart, so that a quarter-warp's 16-byte stores cover all banks) and sends them with
+                    // one bulk copy to the row's destination. Over NVLink this makes 128-byte writes instead of
+                    // the 32-byte ones of register stores, and the warp does not wait for them. Bulk groups are
+                    // per thread and each lane touches only its own row: no warp synchronisation is needed.
+                    const int code = __ldg(g.row_dst + row0 + lane);
+                    const int slot = (code & 0xFFFFFF) - 1, owner = code >> 24;
+                    bool deliver = slot >= 0;
+                    if (deliver && (slot >= g.slot_rows || owner >= g.world)) {
+                        atomicOr(g.status, uint32_t(STATUS_BAD_ARGUMENT));
+                        deliver = false;
+                    }
+                    const uint32_t buf = stage_base + lane * 144;
+                    static_assert(32 * 144 <= 2 * Cfg::EPI_WARP_BYTES || !Cfg::STAGED_EPILOGUE, "row staging");
+                    tma_store_wait_read<0>();                     // this lane's previous copy has read its row
+                    #pragma unroll
+                    for (int q = 0; q < EPI_COLS / 8; ++q) {
+                        uint32_t h[4];
+                        #pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float lo = __uint_as_float(v[q * 8 + 2 * i]) * alpha;
+                            const float hi = __uint_as_float(v[q * 8 + 2 * i + 1]) * alpha;
+                            if (g.out_bf16) {
+                                const __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+                                h[i] = *reinterpret_cast<const uint32_t*>(&p);
+                            } else {
+                                const __half2 p = __floats2half2_rn(lo, hi);
+                                h[i] = *reinterpret_cast<const uint32_t*>(&p);
+                            }
+                        }
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                                     :: "r"(buf + q * 16), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]) : "memory");
+                    }
+                    fence_async_smem();
+                    if (deliver && !(g.debug & 1u)) {
+                        uint16_t* dst = reinterpret_cast<uint16_t*>(__ldg(reinterpret_cast<const unsigned long long*>(g.slots) + owner)) +
+                                        size_t(slot) * g.ldc + col0 + chunk * EPI_COLS;
+                        bulk_store(dst, buf, EPI_COLS * 2);
+                        tma_store_commit();
+                    }
+                    continue;
+                }
                 if (!Cfg::STAGED_EPILOGUE || g.direct_store) {
                     uint16_t* dst = static_cast<uint16_t*>(g.c) + size_t(row0 + lane) * g.ldc + col0 + chunk * EPI_COLS;
+                    bool deliver = true;                          // a lane-wise predicate: the warp stays converged
+                    if (g.row_dst) {
+                        const int code = __ldg(g.row_dst + row0 + lane);
+                        const int slot = (code & 0xFFFFFF) - 1, owner = code >> 24;
+                        deliver = slot >= 0;                      // 0 marks a padding row: nothing to deliver
+                        if (deliver && (slot >= g.slot_rows || owner >= g.world)) {
+                            atomicOr(g.status, uint32_t(STATUS_BAD_ARGUMENT));
+                            deliver = false;
+                        }
+                        if (deliver)
+                            dst = reinterpret_cast<uint16_t*>(__ldg(reinterpret_cast<const unsigned long long*>(g.slots) + owner)) + size_t(slot) * g.ldc + col0 + chunk * EPI_COLS;
+                    }
                     #pragma unroll
                     for (int q = 0; q < EPI_COLS / 16; ++q) {
                         uint32_t h[8];
@@ -442,7 +504,7 @@ struct Roles {
                                 h[i] = *reinterpret_cast<const uint32_t*>(&p);
                             }
                         }
-                        if (!(g.debug & 1u))
+                        if (!(g.debug & 1u) && deliver)
                             asm volatile("st.global.L1::no_allocate.L2::evict_first.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
                                          :: "l"(dst + q * 16), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]),
                                             "r"(h[4]), "r"(h[5]), "r"(h[6]), "r"(h[7]) : "memory");
@@ -484,7 +546,7 @@ struct Roles {
                 ++stores;
             }
         }
-        if (lane == 0) tma_store_wait_all();
+        tma_store_wait_all();                                   // lanes without stores in flight fall through
         if (g.prof && warp == 0 && lane == 0) {
             unsigned long long* out = g.prof + (size_t(unit) * CG + rank) * PROF_WORDS;
             out[PROF_EPI_WAIT_ACC] = wait_acc;
@@ -653,7 +715,7 @@ void launch_variant(const gpu_kernels::Nvfp4Params& p, const CUtensorMap& tmC, v
     using Cfg = Config<CG, UN>;
     GemmArgs g{p.M, p.N, p.K, p.M / Cfg::TILE_M, p.N / UN, std::max(1, p.group_m), p.alpha, status, prof,
                uint32_t(env_int("NVFP4_B200_DEBUG", 0)), p.c_evict_first, 0, nullptr, nullptr, 0,
-               p.direct_store, c, p.N, nullptr, nullptr, nullptr, 0.0f};
+               p.direct_store, c, p.N, nullptr, nullptr, nullptr, 0.0f, nullptr, nullptr, 0, 0};
     cudaLaunchAttribute attr{};
     attr.id = cudaLaunchAttributeClusterDimension;
     attr.val.clusterDim = {unsigned(CG), 1, 1};
@@ -743,8 +805,8 @@ void validate() {
     if (host[0]) {
         const uint32_t zero[4] = {};
         cuda_check(cudaMemcpyToSymbol(g_status, zero, sizeof(zero)));
-        char msg[160];
-        std::snprintf(msg, sizeof(msg), "nvfp4 gemm: a device wait gave up (status 0x%x, first tag 0x%08x); output is invalid",
+        char msg[224];
+        std::snprintf(msg, sizeof(msg), "nvfp4 gemm: the kernel reported an error (status 0x%x: 0x10 = bad destination, else a wait gave up; first tag 0x%08x); output is invalid",
                       host[0], host[1]);
         throw std::runtime_error(msg);
     }
@@ -807,12 +869,18 @@ void grouped_prepare(GroupedGemm& p, const uint8_t* A, const uint8_t* B, const u
 }
 
 void grouped_launch(const GroupedGemm& p, void* C, int out_bf16, cudaStream_t stream) {
-    grouped_launch_fused(p, C, out_bf16, nullptr, nullptr, nullptr, 0.0f, stream);
+    grouped_launch_fused(p, C, out_bf16, nullptr, nullptr, nullptr, 0.0f, nullptr, nullptr, 0, 0, stream);
 }
 
 void grouped_launch_fused(const GroupedGemm& p, void* C, int out_bf16, uint8_t* act_packed, uint8_t* act_scales,
-                          const float* row_weight, float clamp, cudaStream_t stream) {
+                          const float* row_weight, float clamp, const int* row_dst, void* const* slots, int world,
+                          int slot_rows, cudaStream_t stream) {
     const bool fused = act_packed != nullptr;
+    if (row_dst) {
+        if (fused || !slots || !C || world < 1 || world > 128 || slot_rows <= 0)
+            throw std::invalid_argument("grouped gemm: scatter needs a table of 1..128 slot buffers and this rank's own "
+                                        "buffer, and cannot be combined with the fused activation");
+    }
     if (fused && (!act_scales || !row_weight)) throw std::invalid_argument("grouped gemm: fused SwiGLU needs scales and row weights");
     if (!fused && (!C || (reinterpret_cast<uintptr_t>(C) & 15))) throw std::invalid_argument("grouped gemm: C must be 16-byte aligned");
     if (fused) C = act_packed;       // only the tensor map needs a valid address; the fused route never stores C
@@ -821,7 +889,8 @@ void grouped_launch_fused(const GroupedGemm& p, void* C, int out_bf16, uint8_t* 
                                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE);
     const int cg = p.block_rows == 256 ? 2 : 1;
     GemmArgs g{p.pool_rows, p.n, p.k, p.pool_rows / p.block_rows, p.n / 256, 1, 1.0f, status_word(p.device), nullptr,
-               0u, 1, out_bf16, p.block_expert, p.num_blocks, p.n, 1, C, p.n, act_packed, act_scales, row_weight, clamp};
+               0u, 1, out_bf16, p.block_expert, p.num_blocks, p.n, 1, C, p.n, act_packed, act_scales, row_weight, clamp,
+               row_dst, slots, world, slot_rows};
     cudaLaunchAttribute attr{};
     attr.id = cudaLaunchAttributeClusterDimension;
     attr.val.clusterDim = {unsigned(cg), 1, 1};

@@ -40,8 +40,12 @@ void grouped_prepare(GroupedGemm& p, const uint8_t* A, const uint8_t* B, const u
 void grouped_launch(const GroupedGemm& p, void* C, int out_bf16, cudaStream_t stream);
 // First expert GEMM with the SwiGLU + re-quantise epilogue: B's rows must be interleaved 16 gate / 16 up;
 // writes the NVFP4 activation [pool_rows, n/2] instead of C.
+// row_dst != null: the second expert GEMM fused with the combine: pool row r goes to row
+// (row_dst[r] & 0xFFFFFF) - 1 of slots[row_dst[r] >> 24] (a [slot_rows, n] buffer per rank, peer memory
+// included) instead of C; row_dst[r] == 0 is a padding row.
 void grouped_launch_fused(const GroupedGemm& p, void* C, int out_bf16, uint8_t* act_packed, uint8_t* act_scales,
-                          const float* row_weight, float clamp, cudaStream_t stream);
+                          const float* row_weight, float clamp, const int* row_dst, void* const* slots, int world,
+                          int slot_rows, cudaStream_t stream);
 
 // nvfp4_moe.cu: routing metadata, dispatch packing, SwiGLU + re-quantise, top-k reduce.
 struct MoeShape {
@@ -68,7 +72,7 @@ void moe_pack_to_pool(const uint8_t* xq, const uint8_t* xs, const long long* ids
                       uint8_t* pool_scales, float* pool_weight, int* route_row, cudaStream_t stream);
 void moe_unpack(const uint8_t* recv_rows, int recv_count_capacity, const int* totals, int world, int local_experts,
                 int hidden, const int* seg_src_offset, const int* seg_pool_offset, uint8_t* pool_packed,
-                uint8_t* pool_scales, float* pool_weight, int* pool_of_recv, cudaStream_t stream);
+                uint8_t* pool_scales, float* pool_weight, int* pool_of_recv, int* pool_dst, cudaStream_t stream);
 void moe_swiglu_quant(const void* gate_up_bf16, const float* pool_weight, const int* num_blocks, int block_rows, int pool_rows,
                       int intermediate, float clamp, uint8_t* act_packed, uint8_t* act_scales, cudaStream_t stream);
 void moe_return_rows(const void* out_pool_bf16, const int* pool_of_recv, const int* totals, int capacity, int hidden,

@@ -171,7 +171,8 @@ __global__ void pack_kernel(const uint8_t* __restrict__ xq, const uint8_t* __res
 __global__ void unpack_kernel(const uint8_t* __restrict__ recv_rows, const int* __restrict__ totals, int segments,
                               int hidden, const int* __restrict__ seg_src_offset, const int* __restrict__ seg_pool_offset,
                               uint8_t* __restrict__ pool_packed, uint8_t* __restrict__ pool_scales,
-                              float* __restrict__ pool_weight, int* __restrict__ pool_of_recv) {
+                              float* __restrict__ pool_weight, int* __restrict__ pool_of_recv, int local_experts,
+                              int* __restrict__ pool_dst) {
     const int lane = threadIdx.x & 31;
     const int p = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (p >= totals[0] || totals[2]) return;
@@ -189,6 +190,9 @@ __global__ void unpack_kernel(const uint8_t* __restrict__ recv_rows, const int* 
     if (lane == 0) {
         pool_weight[row] = *reinterpret_cast<const float*>(in + hidden / 2 + hidden / 16);
         pool_of_recv[p] = row;
+        // where the result of this row goes: (source rank << 24) | (route index + 1); 0 stays "padding"
+        if (pool_dst)
+            pool_dst[row] = ((lo / local_experts) << 24) | (*reinterpret_cast<const int*>(in + hidden / 2 + hidden / 16 + 4) + 1);
     }
 }
 
@@ -400,12 +404,12 @@ void moe_pack_to_pool(const uint8_t* xq, const uint8_t* xs, const long long* ids
 
 void moe_unpack(const uint8_t* recv_rows, int recv_count_capacity, const int* totals, int world, int local_experts,
                 int hidden, const int* seg_src_offset, const int* seg_pool_offset, uint8_t* pool_packed,
-                uint8_t* pool_scales, float* pool_weight, int* pool_of_recv, cudaStream_t stream) {
+                uint8_t* pool_scales, float* pool_weight, int* pool_of_recv, int* pool_dst, cudaStream_t stream) {
     check_hidden(hidden, "moe unpack");
     if (recv_count_capacity <= 0) return;
     unpack_kernel<<<(recv_count_capacity * 32 + 255) / 256, 256, 0, stream>>>(
         recv_rows, totals, world * local_experts, hidden, seg_src_offset, seg_pool_offset, pool_packed, pool_scales,
-        pool_weight, pool_of_recv);
+        pool_weight, pool_of_recv, local_experts, pool_dst);
     cuda_check(cudaGetLastError());
 }
 

@@ -182,6 +182,12 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t sr
         "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
         :: "l"(map), "r"(src), "r"(x), "r"(y) : "memory");
 }
+// One contiguous run of shared memory to global memory (this GPU's or a peer's); both addresses 16-byte
+// aligned, bytes a multiple of 16. Joins the issuing thread's bulk group like the tensor stores.
+__device__ __forceinline__ void bulk_store(void* dst, uint32_t src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                 :: "l"(dst), "r"(src), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() {
     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }

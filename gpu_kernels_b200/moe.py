@@ -169,6 +169,8 @@ class Nvfp4MoE:
         self.peer_offset = torch.zeros(self.experts, dtype=torch.int32, device=d)
         self.peer_error = torch.zeros(1, dtype=torch.int32, device=d)
         self.identity = torch.arange(routes, dtype=torch.int32, device=d)
+        self.pool_dst = torch.zeros(self.pool_rows, dtype=torch.int32, device=d)
+        self.slot_table = torch.tensor([int(tables[1][r]) for r in range(self.world)], dtype=torch.int64, device=d)
         self._fence = torch.zeros(1, dtype=torch.int32, device=d)
 
     def _barrier(self):
@@ -183,6 +185,8 @@ class Nvfp4MoE:
             raise RuntimeError(f"expert exchange: a peer store was outside the agreed capacity (code {int(self.peer_error.item())})")
         if int(self.totals[2].item()):
             raise RuntimeError("expert pool overflow")
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.load().gpu_kernels_nvfp4_validate(None))
 
     def _mark(self, name):
         if self.phase_events is not None:
@@ -247,6 +251,8 @@ class Nvfp4MoE:
             self.cursor.zero_()
             self.pool_scales.zero_()
             self.pool_weight.zero_()
+            if self._peer is not None:
+                self.pool_dst.zero_()
             total_recv = sum(recv_splits) if recv_splits is not None else 0
             if self.world > 1 and send_splits is None:
                 _lib.check(lib.gpu_kernels_nvfp4_moe_pack_peer(
@@ -259,7 +265,8 @@ class Nvfp4MoE:
                 _lib.check(lib.gpu_kernels_nvfp4_moe_unpack(
                     self.recv_ptr, self.recv_cap, self.totals.data_ptr(), self.world, self.local_experts,
                     self.hidden, self.seg_src.data_ptr(), self.seg_pool.data_ptr(), self.pool_packed.data_ptr(),
-                    self.pool_scales.data_ptr(), self.pool_weight.data_ptr(), self.pool_of_recv.data_ptr(), s))
+                    self.pool_scales.data_ptr(), self.pool_weight.data_ptr(), self.pool_of_recv.data_ptr(),
+                    self.pool_dst.data_ptr(), s))
             elif self.world == 1:
                 # nothing to exchange: rows go straight into the expert-major pool
                 _lib.check(lib.gpu_kernels_nvfp4_moe_pack_to_pool(
@@ -278,7 +285,7 @@ class Nvfp4MoE:
                 _lib.check(lib.gpu_kernels_nvfp4_moe_unpack(
                     self.recv_rows.data_ptr(), self.recv_cap, self.totals.data_ptr(), self.world, self.local_experts,
                     self.hidden, self.seg_src.data_ptr(), self.seg_pool.data_ptr(), self.pool_packed.data_ptr(),
-                    self.pool_scales.data_ptr(), self.pool_weight.data_ptr(), self.pool_of_recv.data_ptr(), s))
+                    self.pool_scales.data_ptr(), self.pool_weight.data_ptr(), self.pool_of_recv.data_ptr(), None, s))
             self._mark("pool filled")
             if self.fused:
                 _lib.check(lib.gpu_kernels_nvfp4_grouped_run_swiglu(
@@ -290,13 +297,16 @@ class Nvfp4MoE:
                     self.gate_up.data_ptr(), self.pool_weight.data_ptr(), self.num_blocks.data_ptr(), block_rows, self.pool_rows,
                     self.inter, self.clamp, self.act_packed.data_ptr(), self.act_scales.data_ptr(), s))
             self._mark("FC1 + SwiGLU + quantise")
-            _lib.check(lib.gpu_kernels_nvfp4_grouped_run(fc2, self.out_pool.data_ptr(), 1, s))
+            peer = self.world > 1 and send_splits is None
+            if peer:
+                # FC2 fused with the combine: every output row leaves the epilogue for its token's rank
+                _lib.check(lib.gpu_kernels_nvfp4_grouped_run_scatter(
+                    fc2, self.pool_dst.data_ptr(), self.slot_table.data_ptr(), self.slots_ptr, self.world,
+                    self.max_tokens * self.topk, 1, s))
+            else:
+                _lib.check(lib.gpu_kernels_nvfp4_grouped_run(fc2, self.out_pool.data_ptr(), 1, s))
             self._mark("FC2")
-            if self.world > 1 and send_splits is None:
-                _lib.check(lib.gpu_kernels_nvfp4_moe_return_peer(
-                    self.out_pool.data_ptr(), self.recv_ptr, self.pool_of_recv.data_ptr(), self.totals.data_ptr(),
-                    self.seg_src.data_ptr(), self.world, self.local_experts, self.hidden, self.recv_cap,
-                    self._peer["slots"], self.max_tokens * self.topk, self.peer_error.data_ptr(), s))
+            if peer:
                 self._mark("expert outputs into the sources' slot buffers")
                 self._barrier()
                 self._mark("barrier")
@@ -323,6 +333,40 @@ class Nvfp4MoE:
         return self.y[:tokens]
 
     __call__ = forward
+
+    def capture(self, tokens: int):
+        """Records forward() for `tokens` tokens as one CUDA graph (kernels, collectives and peer stores).
+
+        Returns (x, ids, weights, y, graph): write the inputs into the first three (device tensors of the shapes
+        forward() takes), call graph.replay(), read y (a view of the layer's output buffer). Possible where
+        forward() needs nothing from the host: one rank, or the peer exchange, with the pool at its worst-case
+        size (the default). Every rank of the group captures (token counts may differ) and then replays the same
+        number of times, as with any collective."""
+        if tokens < 1 or tokens > self.max_tokens:
+            raise ValueError("tokens outside 1..max_tokens")
+        if self.world > 1 and self._peer is None:
+            raise RuntimeError("capture needs exchange='peer': the all-to-all path reads its split sizes on the host")
+        worst = self.world * self.max_tokens * self.topk + self.local_experts * 255
+        if self.pool_rows < worst:
+            raise RuntimeError(f"capture needs a worst-case pool ({worst} rows): a smaller one is checked on the host")
+        if self.phase_events is not None:
+            raise RuntimeError("phase timing marks cannot be captured")
+        d = self.device
+        x = torch.zeros((tokens, self.hidden), dtype=torch.bfloat16, device=d)
+        ids = torch.zeros((tokens, self.topk), dtype=torch.int64, device=d)
+        weights = torch.zeros((tokens, self.topk), dtype=torch.float32, device=d)
+        with torch.cuda.device(d):
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):                       # first calls: library load, communicator, plans
+                for _ in range(2):
+                    self.forward(x, ids, weights)
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize(d)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                y = self.forward(x, ids, weights)
+        return x, ids, weights, y, graph
 
     def close(self) -> None:
         lib = _lib.load()

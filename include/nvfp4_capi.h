@@ -35,7 +35,9 @@ void gpu_kernels_nvfp4_plan_destroy(void* plan);
 int gpu_kernels_nvfp4_cublas(void* plan, void* C, const void* A, const void* B, void* stream);
 /* replaces nvfp4_bridge.cu:112-121: C[M,N] fp16 = A * B^T with this library's kernel; capture-safe */
 int gpu_kernels_nvfp4_custom(void* plan, void* C, void* stream);
-/* replaces nvfp4_bridge.cu:123-132: synchronises and reports a kernel that gave up waiting */
+/* replaces nvfp4_bridge.cu:123-132: synchronises and reports a kernel that gave up waiting or skipped an
+ * out-of-range store. The status is kept per device: plan may be NULL (checks the current device; this is how
+ * grouped launches are checked). */
 int gpu_kernels_nvfp4_validate(void* plan);
 /* replaces nvfp4_bridge.cu:134-139 */
 int gpu_kernels_nvfp4_l2_bytes(void);
@@ -99,6 +101,16 @@ int gpu_kernels_nvfp4_grouped_run(void* plan, void* C, int out_bf16, void* strea
 int gpu_kernels_nvfp4_grouped_run_swiglu(void* plan, const void* row_weight, float clamp, void* act_packed,
                                          void* act_scales, void* stream);
 
+/* The second expert GEMM fused with the combine: instead of C, pool row r is written (bf16 or fp16, from the
+ * epilogue's registers, while the GEMM runs) to row (row_dst[r] & 0xFFFFFF) - 1 of slots[row_dst[r] >> 24], a
+ * [slot_rows, n] buffer per rank: this rank's own, or a peer's mapped through gpu_kernels_nvfp4_ipc_open, in
+ * which case the stores cross NVLink. row_dst[r] == 0 marks a padding row. Out-of-range destinations are
+ * skipped and reported by gpu_kernels_nvfp4_validate. Replaces FC2 + the peer scatter of
+ * kernels/moe/fused/sm90.cu:514-544. slots: DEVICE array of `world` buffer addresses (8 bytes each);
+ * own_slots: this rank's own buffer (= slots[rank]). */
+int gpu_kernels_nvfp4_grouped_run_scatter(void* plan, const void* row_dst, const void* slots, void* own_slots, int world,
+                                          int slot_rows, int out_bf16, void* stream);
+
 /* Bytes of one dispatched token row: hidden/2 packed + hidden/16 scale bytes + 16 (route weight). */
 int gpu_kernels_nvfp4_moe_payload_bytes(int hidden);
 /* replaces metadata_kernel's histogram (kernels/moe/fused/sm90.cu:43-101): counts[e] += routes to global expert e
@@ -126,11 +138,13 @@ int gpu_kernels_nvfp4_moe_pack_to_pool(const void* xq, const void* xs, const voi
                                        void* pool_packed, void* pool_scales, void* pool_weight, void* route_row,
                                        void* stream);
 /* received rows (source-major) -> expert-major pool: packed rows, scale atoms (zeroed by the caller first),
- * per-row route weight, and pool_of_recv [recv_capacity] for the way back. */
+ * per-row route weight, pool_of_recv [recv_capacity] for the way back, and (if not null; rows packed by
+ * pack_peer only) pool_dst [pool_rows] = (source rank << 24) | (route index + 1) for grouped_run_scatter;
+ * the caller zeroes pool_dst first so that padding rows read 0. */
 int gpu_kernels_nvfp4_moe_unpack(const void* recv_rows, int recv_capacity, const void* totals, int world,
                                  int local_experts, int hidden, const void* seg_src_offset, const void* seg_pool_offset,
                                  void* pool_packed, void* pool_scales, void* pool_weight, void* pool_of_recv,
-                                 void* stream);
+                                 void* pool_dst, void* stream);
 /* replaces kernels/moe/swiglu.cu:12-26 fused with the re-quantisation for the second GEMM:
  * gate_up bf16 [pool_rows, 2*intermediate] -> NVFP4 activation [pool_rows, intermediate/2] + scales. */
 int gpu_kernels_nvfp4_moe_swiglu_quant(const void* gate_up, const void* pool_weight, const void* num_blocks,

@@ -102,6 +102,76 @@ def test_fused_and_unfused_first_gemm_agree(g):
     assert same_scale > 0.999 and same_code > 0.999, (same_scale, same_code)
 
 
+def test_second_gemm_scatter_epilogue_exact(g):
+    # FC2 fused with the combine: each pool row must land, bit for bit, in the slot its destination code names
+    # (here two buffers of this GPU stand in for two ranks), and padding rows (code 0) must write nothing
+    import ctypes
+    from gpu_kernels_b200 import _lib
+    tokens, hidden, inter, experts, topk = 300, 512, 256, 4, 2
+    x, logits, w1, w2 = make_layer(5, tokens, hidden, inter, experts, topk)
+    ids, wts = g.route(logits, topk)
+    for block_rows in (128, 256):
+        layer = g.Nvfp4MoE(w1, w2, experts, topk, max_tokens=512, block_rows=block_rows)
+        layer(x, ids, wts)
+        torch.cuda.synchronize()
+        rows = int(layer.totals[1].item())
+        weight = layer.pool_weight[:rows].cpu().numpy()
+        real = np.flatnonzero(weight != 0)
+        rng = np.random.default_rng(block_rows)
+        slot_rows = len(real)
+        slot_of = rng.permutation(slot_rows)
+        owner = rng.integers(0, 2, slot_rows)
+        codes = np.zeros(layer.pool_rows, np.int32)
+        codes[real] = (owner << 24) | (slot_of + 1)
+        row_dst = torch.from_numpy(codes).cuda()
+        slots = [torch.full((slot_rows, hidden), -7.0, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+        table = torch.tensor([t.data_ptr() for t in slots], dtype=torch.int64, device="cuda")
+        fc2 = layer._plans[block_rows][1]
+        _lib.check(_lib.load().gpu_kernels_nvfp4_grouped_run_scatter(
+            fc2, row_dst.data_ptr(), table.data_ptr(), slots[0].data_ptr(), 2, slot_rows, 1,
+            ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        torch.cuda.synchronize()
+        assert _lib.load().gpu_kernels_nvfp4_validate(None) == 0
+        expect = [np.full((slot_rows, hidden), -7.0, np.float32) for _ in range(2)]
+        pool = layer.out_pool.float().cpu().numpy()
+        for r, o, sl in zip(real, owner, slot_of):
+            expect[o][sl] = pool[r]
+        for o in range(2):
+            assert np.array_equal(slots[o].float().cpu().numpy(), expect[o]), (block_rows, o)
+        # a destination outside the buffer is skipped and reported, not written
+        codes[real[0]] = slot_rows + 1
+        row_dst.copy_(torch.from_numpy(codes))
+        _lib.load().gpu_kernels_nvfp4_grouped_run_scatter(
+            fc2, row_dst.data_ptr(), table.data_ptr(), slots[0].data_ptr(), 2, slot_rows, 1,
+            ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()
+        assert _lib.load().gpu_kernels_nvfp4_validate(None) != 0
+        layer.close()
+
+
+def test_captured_forward_replays_exactly(g):
+    # the whole forward as one CUDA graph: replays on new inputs must give the bits of the eager call
+    tokens, hidden, inter, experts, topk = 96, 512, 256, 8, 2
+    x, logits, w1, w2 = make_layer(11, tokens, hidden, inter, experts, topk)
+    layer = g.Nvfp4MoE(w1, w2, experts, topk, max_tokens=128)
+    gx, gids, gwts, gy, graph = layer.capture(tokens)
+    for seed in (1, 2, 3):
+        x, logits, _, _ = make_layer(seed, tokens, hidden, inter, experts, topk)
+        ids, wts = g.route(logits, topk)
+        eager = layer(x, ids, wts).clone()
+        gx.copy_(x); gids.copy_(ids); gwts.copy_(wts)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(gy, eager), seed
+    layer.check()
+    del graph
+    layer.close()
+    small = g.Nvfp4MoE(w1, w2, experts, topk, max_tokens=128, pool_rows=512)
+    with pytest.raises(RuntimeError):
+        small.capture(tokens)
+    small.close()
+
+
 def test_routing_plan_pack_unpack_exact(g):
     tokens, hidden, inter, experts, topk = 150, 512, 256, 8, 3
     x, logits, w1, w2 = make_layer(5, tokens, hidden, inter, experts, topk, skew=True)

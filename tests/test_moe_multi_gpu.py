@@ -32,6 +32,7 @@ def _worker(rank, world, port, out_dir):
         gen = torch.Generator(device="cuda").manual_seed(100)                # same weights on every rank
         w1 = (torch.randn((experts, 2 * inter, hidden), generator=gen, device="cuda") * 0.02).bfloat16()
         w2 = (torch.randn((experts, hidden, inter), generator=gen, device="cuda") * 0.02).bfloat16()
+        outputs = {}
         for exchange in ("peer", "nccl"):
             layer = g.Nvfp4MoE(w1[rank * local:(rank + 1) * local], w2[rank * local:(rank + 1) * local], experts, topk,
                                max_tokens=128, exchange=exchange)
@@ -47,6 +48,17 @@ def _worker(rank, world, port, out_dir):
                 got = y.float().cpu().numpy()
                 rel = np.linalg.norm(got - ref) / np.linalg.norm(ref)
                 assert not np.isnan(got).any() and rel <= 2e-2, f"rank {rank} {exchange} call {call}: rel {rel:.3e}"
+                # both exchanges deliver the same rows and the reduce adds them in the same order: identical bits
+                assert np.array_equal(outputs.setdefault(call, got), got), f"rank {rank} call {call}: peer != nccl"
+            if exchange == "peer":
+                # the same forward, collectives and peer stores included, replayed from a CUDA graph
+                gx, gids, gwts, gy, graph = layer.capture(tokens)
+                for _ in range(2):
+                    gx.copy_(x); gids.copy_(ids); gwts.copy_(wts)
+                    graph.replay()
+                    torch.cuda.synchronize()
+                    assert np.array_equal(gy.float().cpu().numpy(), outputs[2]), f"rank {rank}: graph replay differs"
+                del graph
             layer.check()
             layer.close()
         open(os.path.join(out_dir, f"ok{rank}"), "w").close()
