@@ -192,6 +192,13 @@ def run_ours(args, rank, world, local_rank):
     rotations = min(rotations, 64)
     sets = [(pa, sa, pb, sb)] + [tuple(t.clone() for t in (pa, sa, pb, sb)) for _ in range(rotations - 1)]
     plans = [g.Nvfp4Gemm(x[0], x[2], x[1], x[3]) for x in sets]
+    for plan in plans:
+        # four units per tile where the library offers it (a slab with far fewer tiles than SMs); this
+        # process owns the GPU, which is what the option needs
+        try:
+            plan.set_option("split_k", 1)
+        except RuntimeError:
+            break
     out = torch.empty((m, n_local), dtype=torch.float16, device=dev)
     full = torch.empty((m, n), dtype=torch.float16, device=dev) if (world > 1 and args.gather) else None
 

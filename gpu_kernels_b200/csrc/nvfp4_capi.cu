@@ -105,6 +105,14 @@ struct Plan {
     void* workspace = nullptr;
     size_t workspace_bytes = 0;
     std::unique_ptr<LtMatmul> lt;
+    void* split_k_workspace = nullptr;      // owned
+    size_t split_k_bytes = 0;
+    int whole_tile_units = 0;                // params.clusters and direct_store of the unsplit schedule
+    int whole_tile_direct_store = 0;
+    Plan() = default;
+    Plan(const Plan&) = delete;
+    Plan& operator=(const Plan&) = delete;
+    ~Plan() { if (split_k_workspace) cudaFree(split_k_workspace); }
 };
 
 Plan& as_plan(void* p) {
@@ -186,6 +194,16 @@ int gpu_kernels_nvfp4_plan_create(void** out, int M, int N, int K, const void* A
         plan->sfb = SFB;
         plan->workspace = workspace;
         plan->workspace_bytes = workspace_bytes;
+        plan->whole_tile_units = plan->params.clusters;
+        plan->whole_tile_direct_store = plan->params.direct_store;
+        // off unless asked for: its units wait for each other, which needs the GPU's SMs free of other kernels
+        const char* on = std::getenv("NVFP4_B200_SPLIT_K");
+        plan->split_k_bytes = gpu_kernels::nvfp4_split_k_workspace_bytes(plan->params);
+        if (plan->split_k_bytes && on && on[0] == '1') {
+            nvfp4_b200::cuda_check(cudaMalloc(&plan->split_k_workspace, plan->split_k_bytes));
+            gpu_kernels::nvfp4_enable_split_k(plan->params, plan->split_k_workspace, plan->split_k_bytes,
+                                               static_cast<cudaStream_t>(stream));
+        }
         *out = plan.release();
     });
 }
@@ -257,7 +275,22 @@ int gpu_kernels_nvfp4_plan_set_option(void* plan, const char* key, int value) {
         } else if (std::strcmp(key, "c_evict_first") == 0) {
             p.params.c_evict_first = value ? 1 : 0;
         } else if (std::strcmp(key, "direct_store") == 0) {
+            if (p.params.split_k > 1 && !value) throw std::invalid_argument("set_option: split-K writes C from registers");
             p.params.direct_store = value ? 1 : 0;
+            p.whole_tile_direct_store = p.params.direct_store;
+        } else if (std::strcmp(key, "k_skew") == 0) {
+            if (value < 0) throw std::invalid_argument("set_option: k_skew must be >= 0");
+            p.params.k_skew = value;
+        } else if (std::strcmp(key, "split_k") == 0) {
+            if (!value) {
+                p.params.split_k = 0;
+                p.params.clusters = p.whole_tile_units;
+                p.params.direct_store = p.whole_tile_direct_store;
+            } else if (p.params.split_k <= 1) {
+                if (!p.split_k_bytes) throw std::invalid_argument("set_option: split_k does not apply to this shape");
+                if (!p.split_k_workspace) nvfp4_b200::cuda_check(cudaMalloc(&p.split_k_workspace, p.split_k_bytes));
+                gpu_kernels::nvfp4_enable_split_k(p.params, p.split_k_workspace, p.split_k_bytes, nullptr);
+            }
         } else {
             throw std::invalid_argument(std::string("set_option: unknown key ") + key);
         }
@@ -269,8 +302,8 @@ int gpu_kernels_nvfp4_plan_info(void* plan, int* info) {
         Plan& p = as_plan(plan);
         if (!info) throw std::invalid_argument("plan_info: null output");
         const auto& q = p.params;
-        const int values[8] = {q.M, q.N, q.K, q.clusters, q.cta_group, q.tile_n, q.group_m,
-                               nvfp4_b200::gemm_stage_count(q.cta_group, q.tile_n)};
+        const int values[10] = {q.M, q.N, q.K, q.clusters, q.cta_group, q.tile_n, q.group_m,
+                                nvfp4_b200::gemm_stage_count(q.cta_group, q.tile_n), q.split_k, q.k_skew};
         std::memcpy(info, values, sizeof(values));
     });
 }

@@ -135,6 +135,40 @@ struct GemmArgs {
     void* const* slots;             // device array of `world` buffer addresses
     int world;
     int slot_rows;
+    // Tile t walks K starting at step (t * k_skew) % ksteps and wraps: the CTAs then do not all ask HBM for
+    // the same 128-byte column of their rows at the same time. 0 = every tile starts at K = 0.
+    int k_skew;
+    // Split-K (dense mode, shapes with far fewer tiles than SMs): unit u works on K steps
+    // [slice * steps / S, (slice + 1) * steps / S) of tile u / S, slice = u % S, and writes FP32 partial sums
+    // to its slot of sk_partials. When the S slices of a tile are there (flags), slice j adds them up, in
+    // slice order, for the column chunks c with c % S == j and writes those columns of C. One item per
+    // unit: the grid is tiles * S CTAs (or pairs), all resident at once.
+    int split_k;                    // S; 0 or 1 = off
+    float* sk_partials;             // [units][CG][4 warps][UN/64 chunks][16][32 lanes] float4
+    uint32_t* sk_flags;             // [units][CG][4 warps]: partial sums published
+    uint32_t* sk_done;              // [tiles][CG][4 warps]: readers finished (the last one lowers the flags)
+};
+
+struct Segment {
+    uint32_t tile, item;            // item = position in the work sequence (tile * S + slice)
+    int k0, k1;                     // ring steps [k0, k1) of the tile
+};
+// The sequence of segments one unit works through; every role of the unit builds the same one.
+struct Walk {
+    uint32_t next, stride, tiles;
+    int ksteps, split;
+    __device__ Walk(const GemmArgs& g, uint32_t unit, uint32_t units, uint32_t tiles_, int ksteps_)
+        : next(unit), stride(units), tiles(tiles_), ksteps(ksteps_), split(g.split_k > 1 ? g.split_k : 1) {}
+    __device__ bool get(Segment& s) {
+        if (next >= tiles * uint32_t(split)) return false;
+        s.item = next;
+        s.tile = next / uint32_t(split);
+        const int slice = int(next - s.tile * uint32_t(split)), len = ksteps / split;
+        s.k0 = slice * len;
+        s.k1 = s.k0 + len;
+        next += stride;
+        return true;
+    }
 };
 
 enum ProfSlot { PROF_PROD_WAIT = 0, PROF_PROD_TOTAL, PROF_MMA_WAIT_FULL, PROF_MMA_WAIT_ACC, PROF_MMA_TOTAL,
@@ -144,6 +178,7 @@ enum ProfSlot { PROF_PROD_WAIT = 0, PROF_PROD_TOTAL, PROF_MMA_WAIT_FULL, PROF_MM
 // next tile issued, 3 leader epilogue warp 0: acc_full seen, 4 same: first chunk loaded,
 // 5 same: acc_free arrival sent, 6 peer CTA epilogue warp 0: acc_full seen, 7 peer: arrival sent}.
 constexpr int TR_TILES = 16;
+constexpr size_t SPLIT_K_FLAG_BYTES = 8192;    // [0, 4096): 4 flags per CTA, up to 256 CTAs; [4096, 8192): readers' counters per tile
 
 
 // Shared-memory matrix descriptors (built in Roles::issue from two 32-bit halves):
@@ -205,14 +240,20 @@ struct Roles {
         const int sf_rows_per_block = (g.K / 64) * 4;          // 128-byte rows of the scale map per 128 tensor rows
         long long waited = 0;
         const long long born = clock64();
-        for (uint32_t t = unit; t < tiles; t += units) {
+        Walk walk(g, unit, units, tiles, ksteps);
+        Segment seg;
+        while (walk.get(seg)) {
+            const uint32_t t = seg.tile;
             int tm, tn, b_base;
             tile_coords(int(t), g, tm, tn, b_base);
             const int a_row = tm * Cfg::TILE_M + int(rank) * BLOCK_M;
             const int b_row = b_base + tn * UN + int(rank) * Cfg::B_ROWS;
             const int sfa_row0 = (a_row / 128) * sf_rows_per_block;
             const int sfb_row0 = ((b_base + tn * UN) / 128) * sf_rows_per_block;
-            for (int ks = 0; ks < ksteps; ++ks) {
+            // whole tiles may start anywhere in K and wrap; slices of a tile are walked in order
+            const int k_first = (g.k_skew && g.split_k <= 1) ? int((t * uint32_t(g.k_skew)) % uint32_t(ksteps)) : 0;
+            for (int step = seg.k0; step < seg.k1; ++step) {
+                const int ks = step + k_first < ksteps ? step + k_first : step + k_first - ksteps;
                 const long long w0 = g.prof ? clock64() : 0;
                 const bool ok = wait(&ctrl->empty[stage], phase ^ 1u, lane == 0 ? STATUS_TIMEOUT_PRODUCER : 0u,
                                      0x10000000u | (stage << 16) | ks);
@@ -278,12 +319,14 @@ struct Roles {
         const uint32_t ring_lo = (smem & 0x3FFFFu) >> 4;
         const uint32_t sf_tmem = tmem + Cfg::SF_BASE;
         bool landed = false;                                    // the probe of this step's barrier succeeded
-        for (uint32_t t = unit; t < tiles; t += units, ++iter) {
+        Walk walk(g, unit, units, tiles, ksteps);
+        Segment seg;
+        for (; walk.get(seg); ++iter) {
             const uint32_t acc = tmem + (iter & 1u) * Cfg::ACC_STRIDE;
             unsigned long long* tr = nullptr;
             if (g.prof && unit == 0 && lane == 0 && iter > 0 && iter <= TR_TILES)
                 tr = g.prof + size_t(units) * CG * PROF_WORDS + size_t(iter - 1) * 8;
-            for (int ks = 0; ks < ksteps; ++ks) {
+            for (int ks = seg.k0; ks < seg.k1; ++ks) {
                 if (!landed) {
                     const long long w0 = g.prof ? clock64() : 0;
                     const bool ok = wait(&ctrl->full[stage], phase, lane == 0 ? STATUS_TIMEOUT_MMA : 0u,
@@ -297,7 +340,7 @@ struct Roles {
                 const bool probe = mbar_test_wait(bar(&ctrl->full[next_stage]), next_phase);
                 const uint32_t lo = ring_lo + uint32_t(stage) * (Cfg::STAGE_BYTES >> 4);
                 const uint32_t empty = bar(&ctrl->empty[stage]);
-                const uint32_t first = ks != 0 ? 1u : 0u;
+                const uint32_t first = ks != seg.k0 ? 1u : 0u;   // 0: the first MMA of the segment overwrites the accumulator
                 auto copies = [&](int j) {
                     const uint32_t sf = sf_tmem + j * Cfg::SF_COLS_PER_MMA;
                     tmem_copy_scales<CG>(sf, (lo + ((Cfg::OFF_SFA + j * SF_ATOM_BYTES) >> 4)) | SCALE_LBO, SCALE_HI);
@@ -313,7 +356,7 @@ struct Roles {
                     mma_nvfp4<CG>(acc, lo + ((j * (MMA_K / 2)) >> 4), lo + ((Cfg::OFF_B + j * (MMA_K / 2)) >> 4),
                                   OPERAND_HI, Cfg::IDESC, sf, sf + 4, j != 0 ? 1u : first);
                 };
-                const bool handover = ks == 0 && iter > 0;
+                const bool handover = ks == seg.k0 && iter > 0;
                 if (handover) {
                     // First step of a tile: the scale copies do not touch the accumulators, so they go out
                     // before the wait for the epilogue to pull the columns this tile shares with the last one.
@@ -336,9 +379,9 @@ struct Roles {
                         if (do_mma) mma(j);
                     }
                     mma_commit<CG>(empty);                      // stage reusable once these MMAs retire
-                    if (ks == ksteps - 1) mma_commit<CG>(bar(&ctrl->acc_full));
+                    if (ks == seg.k1 - 1) mma_commit<CG>(bar(&ctrl->acc_full));
                 }
-                if (tr && ks == 0) tr[2] = clock64();
+                if (tr && ks == seg.k0) tr[2] = clock64();
                 landed = __all_sync(0xFFFFFFFFu, probe);
                 stage = next_stage;
                 phase = next_phase;
@@ -352,6 +395,84 @@ struct Roles {
         }
     }
 
+    // 64 accumulator columns of this lane's row: x alpha, to FP16/BF16, 128 bytes in four 32-byte stores.
+    __device__ __forceinline__ void store_row_chunk(uint16_t* dst, const uint32_t (&v)[EPI_COLS], float alpha, bool deliver) const {
+        #pragma unroll
+        for (int q = 0; q < EPI_COLS / 16; ++q) {
+            uint32_t h[8];
+            #pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float lo = __uint_as_float(v[q * 16 + 2 * i]) * alpha;
+                const float hi = __uint_as_float(v[q * 16 + 2 * i + 1]) * alpha;
+                if (g.out_bf16) {
+                    const __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+                    h[i] = *reinterpret_cast<const uint32_t*>(&p);
+                } else {
+                    const __half2 p = __floats2half2_rn(lo, hi);
+                    h[i] = *reinterpret_cast<const uint32_t*>(&p);
+                }
+            }
+            if (!(g.debug & 1u) && deliver)
+                asm volatile("st.global.L1::no_allocate.L2::evict_first.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                             :: "l"(dst + q * 16), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]),
+                                "r"(h[4]), "r"(h[5]), "r"(h[6]), "r"(h[7]) : "memory");
+        }
+    }
+
+    // Split-K, once a unit's partial sums are stored: publish them, wait for the other slices of the tile, add
+    // up, in slice order, this slice's share of the column chunks and write those columns of C. (Measured:
+    // reading the slices with plain L2 loads, sixteen in flight per lane, takes 3.7k cycles per chunk of four
+    // slices; staging them in shared memory with bulk copies took 11.6k.)
+    __device__ bool split_k_finish(const Segment& seg, int warp, int lane, int row0, int col0, float alpha) const {
+        const uint32_t S = uint32_t(g.split_k), first = seg.tile * S, slice = seg.item - first;
+        __threadfence();
+        __syncwarp();
+        bool ok = true;
+        if (lane == 0) {
+            flag_publish(g.sk_flags + (seg.item * CG + rank) * 4 + warp, 1u);
+            for (uint32_t i = 0; i < S && ok; ++i)
+                ok = flag_wait(g.sk_flags + ((first + i) * CG + rank) * 4 + warp, &ctrl->wait, g.status,
+                               STATUS_TIMEOUT_EPILOGUE, peer_abort);
+            if (!ok) atomicCAS(g.status + 1, 0u, 0x31000000u | seg.item);
+        }
+        if (!__all_sync(0xFFFFFFFFu, ok)) return false;
+        constexpr uint32_t CHUNK_FLOAT4 = 32 * EPI_COLS / 4;   // one warp's 32 rows x 64 columns of FP32
+        constexpr uint32_t WARP_FLOATS = UN * 32;
+        #pragma unroll 1
+        for (uint32_t chunk = slice; chunk < UN / EPI_COLS; chunk += S) {
+            uint32_t v[EPI_COLS];
+            #pragma unroll 1
+            for (uint32_t i = 0; i < S; ++i) {
+                const float4* in = reinterpret_cast<const float4*>(g.sk_partials + ((size_t(first + i) * CG + rank) * 4 + warp) * WARP_FLOATS) +
+                                   size_t(chunk) * CHUNK_FLOAT4 + lane;
+                float4 part[EPI_COLS / 4];
+                #pragma unroll
+                for (int q = 0; q < EPI_COLS / 4; ++q) part[q] = __ldcg(in + q * 32);      // sixteen loads in flight per lane
+                #pragma unroll
+                for (int q = 0; q < EPI_COLS / 4; ++q) {
+                    if (i == 0) {
+                        v[4 * q] = __float_as_uint(part[q].x); v[4 * q + 1] = __float_as_uint(part[q].y);
+                        v[4 * q + 2] = __float_as_uint(part[q].z); v[4 * q + 3] = __float_as_uint(part[q].w);
+                    } else {
+                        v[4 * q] = __float_as_uint(__uint_as_float(v[4 * q]) + part[q].x);
+                        v[4 * q + 1] = __float_as_uint(__uint_as_float(v[4 * q + 1]) + part[q].y);
+                        v[4 * q + 2] = __float_as_uint(__uint_as_float(v[4 * q + 2]) + part[q].z);
+                        v[4 * q + 3] = __float_as_uint(__uint_as_float(v[4 * q + 3]) + part[q].w);
+                    }
+                }
+            }
+            store_row_chunk(static_cast<uint16_t*>(g.c) + size_t(row0 + lane) * g.ldc + col0 + chunk * EPI_COLS, v, alpha, true);
+        }
+        if (lane == 0) {
+            uint32_t* done = g.sk_done + (seg.tile * CG + rank) * 4 + warp;
+            if (atomicAdd(done, 1u) == S - 1) {                 // the last reader of this warp's rows lowers the flags
+                for (uint32_t i = 0; i < S; ++i) g.sk_flags[((first + i) * CG + rank) * 4 + warp] = 0u;
+                *done = 0u;
+            }
+        }
+        return true;
+    }
+
     // ---- warps 0-3: drain accumulators to C ---------------------------------------
     __device__ void drain(uint32_t tmem, const CUtensorMap* tmC, int warp, int lane) const {
         const uint32_t stage_base = smem + Cfg::STAGES * Cfg::STAGE_BYTES + warp * 2 * Cfg::EPI_WARP_BYTES;
@@ -361,7 +482,11 @@ struct Roles {
         const uint64_t c_policy = policy_evict_first();
         long long wait_acc = 0, wait_store = 0;
         const long long born = clock64();
-        for (uint32_t t = unit; t < tiles; t += units, ++iter) {
+        Walk walk(g, unit, units, tiles, g.K / STAGE_K);
+        Segment seg;
+        constexpr uint32_t SK_WARP_FLOATS = UN * 32;            // one warp's 32 rows of a tile
+        for (; walk.get(seg); ++iter) {
+            const uint32_t t = seg.tile;
             int tm, tn, b_base;
             tile_coords(int(t), g, tm, tn, b_base);
             const int row0 = tm * Cfg::TILE_M + int(rank) * BLOCK_M + warp * 32;
@@ -393,6 +518,16 @@ struct Roles {
                     if (tr) tr[rank ? 1 : 2] = clock64();
                 }
                 if (g.debug & 8u) continue;                      // diagnostic: drain only
+                if (g.split_k > 1) {
+                    // FP32 partial sums to this unit's slot: 16 bytes per lane, 512 contiguous bytes per store
+                    float4* out = reinterpret_cast<float4*>(g.sk_partials + ((size_t(seg.item) * CG + rank) * 4 + warp) * SK_WARP_FLOATS) +
+                                  size_t(chunk) * (EPI_COLS / 4) * 32 + lane;
+                    #pragma unroll
+                    for (int q = 0; q < EPI_COLS / 4; ++q)
+                        __stcg(out + q * 32, make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]),
+                                                         __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3])));
+                    continue;
+                }
                 if (g.act_packed) {
                     const int inter = g.N / 2;
                     const int row = row0 + lane;
@@ -489,26 +624,7 @@ struct Roles {
                         if (deliver)
                             dst = reinterpret_cast<uint16_t*>(__ldg(reinterpret_cast<const unsigned long long*>(g.slots) + owner)) + size_t(slot) * g.ldc + col0 + chunk * EPI_COLS;
                     }
-                    #pragma unroll
-                    for (int q = 0; q < EPI_COLS / 16; ++q) {
-                        uint32_t h[8];
-                        #pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const float lo = __uint_as_float(v[q * 16 + 2 * i]) * alpha;
-                            const float hi = __uint_as_float(v[q * 16 + 2 * i + 1]) * alpha;
-                            if (g.out_bf16) {
-                                const __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
-                                h[i] = *reinterpret_cast<const uint32_t*>(&p);
-                            } else {
-                                const __half2 p = __floats2half2_rn(lo, hi);
-                                h[i] = *reinterpret_cast<const uint32_t*>(&p);
-                            }
-                        }
-                        if (!(g.debug & 1u) && deliver)
-                            asm volatile("st.global.L1::no_allocate.L2::evict_first.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
-                                         :: "l"(dst + q * 16), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]),
-                                            "r"(h[4]), "r"(h[5]), "r"(h[6]), "r"(h[7]) : "memory");
-                    }
+                    store_row_chunk(dst, v, alpha, deliver);
                     continue;
                 }
                 const uint32_t buf = stage_base + (stores & 1u) * Cfg::EPI_WARP_BYTES;
@@ -544,6 +660,9 @@ struct Roles {
                     tma_store_commit();
                 }
                 ++stores;
+            }
+            if (g.split_k > 1) {
+                if (!split_k_finish(seg, warp, lane, row0, col0, alpha)) break;
             }
         }
         tma_store_wait_all();                                   // lanes without stores in flight fall through
@@ -715,7 +834,11 @@ void launch_variant(const gpu_kernels::Nvfp4Params& p, const CUtensorMap& tmC, v
     using Cfg = Config<CG, UN>;
     GemmArgs g{p.M, p.N, p.K, p.M / Cfg::TILE_M, p.N / UN, std::max(1, p.group_m), p.alpha, status, prof,
                uint32_t(env_int("NVFP4_B200_DEBUG", 0)), p.c_evict_first, 0, nullptr, nullptr, 0,
-               p.direct_store, c, p.N, nullptr, nullptr, nullptr, 0.0f, nullptr, nullptr, 0, 0};
+               p.direct_store, c, p.N, nullptr, nullptr, nullptr, 0.0f, nullptr, nullptr, 0, 0, p.k_skew,
+               p.split_k, p.split_k > 1 ? reinterpret_cast<float*>(static_cast<uint8_t*>(p.split_k_workspace) + SPLIT_K_FLAG_BYTES) : nullptr,
+               p.split_k > 1 ? static_cast<uint32_t*>(p.split_k_workspace) : nullptr,
+               p.split_k > 1 ? static_cast<uint32_t*>(p.split_k_workspace) + SPLIT_K_FLAG_BYTES / 8 : nullptr};
+    if (p.split_k > 1 && !p.direct_store) throw std::logic_error("nvfp4 gemm: split-K writes C from registers");
     cudaLaunchAttribute attr{};
     attr.id = cudaLaunchAttributeClusterDimension;
     attr.val.clusterDim = {unsigned(CG), 1, 1};
@@ -784,7 +907,48 @@ void prepare(gpu_kernels::Nvfp4Params& p, const uint8_t* A, const uint8_t* B, co
     // at 8192^3 (everything L2-resident) the band height does not matter.
     if (M / (128 * p.cta_group) >= 48) gm = std::max(gm, 16);
     p.group_m = std::max(1, std::min(env_int("NVFP4_B200_GROUP_M", gm), M / (128 * p.cta_group)));
+    // Measured: 128x28672x8192 30.2 -> 28.9 us, 8192^3 199.8 -> 199.0 us with the tiles' K walks de-phased.
+    p.k_skew = env_int("NVFP4_B200_K_SKEW", 11);
+    p.split_k = 0;
+    p.split_k_workspace = nullptr;
     (void)status_word(device);
+}
+
+// Split-K can pay when whole tiles would leave most SMs idle and every tile's K loop is long: four units per
+// tile, each with a quarter of the K steps, as long as all tiles * 4 units are resident at once and a slice
+// keeps at least four ring steps. Measured (us, split / whole): 128x3584x8192 18.2 / 20.9, 256x256x8192
+// 14.6 / 16.3, 128x7168x8192 20.9 / 21.2; two slices per tile lost everywhere (128x14336x8192 26.5 / 22.5,
+// 1024x2048x4096 18.1 / 12.9): publishing, waiting for the slowest slice and re-reading the partial sums cost
+// about 17k cycles, which is what a quarter of a 32-step K loop saves.
+int split_k_factor(const gpu_kernels::Nvfp4Params& p) {
+    const int tiles = (p.M / (128 * p.cta_group)) * (p.N / p.tile_n);
+    const int fit = p.cta_group == 2 ? max_units<2, 256>(p.device)
+                  : p.tile_n == 256 ? max_units<1, 256>(p.device) : max_units<1, 128>(p.device);
+    const int ksteps = p.K / STAGE_K, chunks = p.tile_n / EPI_COLS;
+    for (int s : {4})
+        if (s <= chunks && tiles * s <= fit && ksteps % s == 0 && ksteps / s >= 4 &&
+            size_t(tiles) * s * p.cta_group * 4 * sizeof(uint32_t) <= SPLIT_K_FLAG_BYTES / 2)
+            return s;
+    return 0;
+}
+
+size_t split_k_workspace_bytes(const gpu_kernels::Nvfp4Params& p) {
+    const int s = split_k_factor(p);
+    if (!s) return 0;
+    const size_t tiles = size_t(p.M / (128 * p.cta_group)) * (p.N / p.tile_n);
+    return SPLIT_K_FLAG_BYTES + tiles * s * p.cta_group * 128 * p.tile_n * sizeof(float);
+}
+
+void enable_split_k(gpu_kernels::Nvfp4Params& p, void* workspace, size_t bytes, cudaStream_t stream) {
+    const int s = split_k_factor(p);
+    if (!s) throw std::invalid_argument("nvfp4 gemm: split-K does not apply to this shape");
+    if (!workspace || bytes < split_k_workspace_bytes(p) || (reinterpret_cast<uintptr_t>(workspace) & 255))
+        throw std::invalid_argument("nvfp4 gemm: split-K workspace missing, too small or not 256-byte aligned");
+    cuda_check(cudaMemsetAsync(workspace, 0, SPLIT_K_FLAG_BYTES, stream));
+    p.split_k = s;
+    p.split_k_workspace = workspace;
+    p.direct_store = 1;
+    p.clusters = (p.M / (128 * p.cta_group)) * (p.N / p.tile_n) * s;     // one (tile, slice) per unit
 }
 
 void launch_with(const gpu_kernels::Nvfp4Params& p, __half* C, cudaStream_t stream, unsigned long long* prof) {
@@ -890,7 +1054,7 @@ void grouped_launch_fused(const GroupedGemm& p, void* C, int out_bf16, uint8_t* 
     const int cg = p.block_rows == 256 ? 2 : 1;
     GemmArgs g{p.pool_rows, p.n, p.k, p.pool_rows / p.block_rows, p.n / 256, 1, 1.0f, status_word(p.device), nullptr,
                0u, 1, out_bf16, p.block_expert, p.num_blocks, p.n, 1, C, p.n, act_packed, act_scales, row_weight, clamp,
-               row_dst, slots, world, slot_rows};
+               row_dst, slots, world, slot_rows, 0, 0, nullptr, nullptr, nullptr};
     cudaLaunchAttribute attr{};
     attr.id = cudaLaunchAttributeClusterDimension;
     attr.val.clusterDim = {unsigned(cg), 1, 1};
@@ -919,5 +1083,11 @@ Nvfp4Implementation nvfp4_sm100_implementation() {
 }
 
 void nvfp4_set_alpha(Nvfp4Params& p, float alpha) { p.alpha = alpha; }
+
+size_t nvfp4_split_k_workspace_bytes(const Nvfp4Params& p) { return nvfp4_b200::split_k_workspace_bytes(p); }
+
+void nvfp4_enable_split_k(Nvfp4Params& p, void* workspace, size_t bytes, cudaStream_t stream) {
+    nvfp4_b200::enable_split_k(p, workspace, bytes, stream);
+}
 
 }  // namespace gpu_kernels

@@ -145,6 +145,31 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, WaitCtl
     }
 }
 
+// Wait (one lane) until a word in global memory that another CTA publishes with flag_publish() is
+// non-zero; same limits and abort protocol as mbar_wait.
+__device__ __forceinline__ bool flag_wait(const uint32_t* flag, WaitCtl* ctl, uint32_t* status, uint32_t who,
+                                          uint32_t peer_abort_addr) {
+    const uint64_t start = globaltimer_ns();
+    #pragma unroll 1
+    while (true) {
+        uint32_t v;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        if (v) return true;
+        if (ctl->abort) return false;
+        if (globaltimer_ns() - start > WAIT_LIMIT_NS) {
+            ctl->abort = 1;
+            if (peer_abort_addr)
+                asm volatile("st.shared::cluster.u32 [%0], %1;" :: "r"(peer_abort_addr), "r"(1u) : "memory");
+            atomicOr(status, who);
+            return false;
+        }
+        __nanosleep(200);
+    }
+}
+__device__ __forceinline__ void flag_publish(uint32_t* flag, uint32_t value) {
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" :: "l"(flag), "r"(value) : "memory");
+}
+
 // ---- TMA ------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* m) {
     asm volatile("prefetch.tensormap [%0];" :: "l"(m) : "memory");

@@ -51,9 +51,9 @@ class Nvfp4Gemm:
         _lib.check(_lib.load().gpu_kernels_nvfp4_plan_set_option(self._plan, key.encode(), int(value)))
 
     def info(self) -> dict:
-        buf = (ctypes.c_int * 8)()
+        buf = (ctypes.c_int * 10)()
         _lib.check(_lib.load().gpu_kernels_nvfp4_plan_info(self._plan, buf))
-        keys = ("M", "N", "K", "units", "cta_group", "tile_n", "group_m", "stages")
+        keys = ("M", "N", "K", "units", "cta_group", "tile_n", "group_m", "stages", "split_k", "k_skew")
         return dict(zip(keys, list(buf)))
 
     def run(self, out: torch.Tensor | None = None) -> torch.Tensor:
@@ -77,6 +77,7 @@ class Nvfp4Gemm:
                 "epi_wait_acc", "epi_wait_store", "epi_total", "smid")
         ctas = (written.value - 128) // 16
         self.handover = [tuple(buf[ctas * 16 + 8 * i: ctas * 16 + 8 * i + 8]) for i in range(16)]
+        self.raw_profile = [tuple(buf[i:i + 16]) for i in range(0, ctas * 16, 16)]
         return [dict(zip(keys, buf[i:i + len(keys)])) for i in range(0, ctas * 16, 16)]
 
     def run_cublaslt(self, out: torch.Tensor) -> torch.Tensor:

@@ -54,11 +54,18 @@ def gather_columns(local: torch.Tensor, group=None, out: torch.Tensor | None = N
 class ShardedNvfp4Gemm:
     """C[:, slab] = alpha * A @ B_slab.T on this rank; `run(gather=True)` returns the full C."""
 
-    def __init__(self, a_packed, sfa, b_slab, sfb_slab, group=None, alpha: float = 1.0):
+    def __init__(self, a_packed, sfa, b_slab, sfb_slab, group=None, alpha: float = 1.0, split_k: bool = False):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.plan = Nvfp4Gemm(a_packed, b_slab, sfa, sfb_slab, alpha=alpha)
+        if split_k:
+            # a thin slab leaves most SMs without a tile; the library offers four units per tile for such
+            # shapes (only for a process that has the GPU to itself: the units wait for each other)
+            try:
+                self.plan.set_option("split_k", 1)
+            except RuntimeError:
+                pass
         self.local = torch.empty((self.plan.m, self.plan.n), dtype=torch.float16, device=a_packed.device)
         self.full = None
 

@@ -39,6 +39,9 @@ struct Nvfp4Params {
     int device;                     // device the plan was prepared on
     int c_evict_first;              // 1: C is stored with the evict-first L2 policy
     int direct_store;               // 1: epilogue writes C from registers instead of TMA stores
+    int k_skew;                     // tile t starts its K walk at step (t * k_skew) % steps and wraps; 0 = off
+    int split_k;                    // S > 1: S units per tile, each with 1/S of the K steps (see below)
+    void* split_k_workspace;        // flags + FP32 partial tiles, owned by the caller
 };
 
 struct Nvfp4Implementation {
@@ -59,5 +62,18 @@ Nvfp4Implementation nvfp4_sm100_implementation();
 
 // Extension: set the FP32 global scale of a prepared plan (takes effect at the next launch).
 void nvfp4_set_alpha(Nvfp4Params&, float alpha);
+
+// Extension: split-K (off unless enabled). For shapes with at most a quarter as many tiles as SMs and a long
+// K loop (decode-like: M = 128, a slab of N) the K steps of every tile can be dealt to 4 units; each writes FP32 partial sums to a
+// workspace, and once a tile's slices are there every slice adds them up, in slice order, for its share of
+// the columns and writes that part of C. nvfp4_split_k_workspace_bytes returns 0 when the shape would not
+// gain. The workspace (256-byte aligned device memory) belongs to the caller, must outlive the plan, and
+// serves one plan: launches of that plan must not overlap each other. The grid then has one unit per
+// (tile, slice) and they wait for each other, so all of them must be resident: launch it on a GPU whose SMs
+// are not held by other kernels (a wait that runs out is reported by validate()). Results are reproducible
+// but differ in the last bits from the unsplit schedule. After validate() has reported an error, enable it
+// again (the flag area is cleared on `stream`).
+size_t nvfp4_split_k_workspace_bytes(const Nvfp4Params&);
+void nvfp4_enable_split_k(Nvfp4Params&, void* workspace, size_t bytes, cudaStream_t stream);
 
 }  // namespace gpu_kernels

@@ -56,9 +56,15 @@ int gpu_kernels_nvfp4_dequantize(const void* packed, const void* scales, void* o
 /* FP32 global scale: C = fp16(alpha * accumulator). The reference fixes alpha = 1 (nvfp4_bridge.cu:101). */
 int gpu_kernels_nvfp4_plan_set_alpha(void* plan, float alpha);
 /* Tuning knobs. key: "group_m" (tile rows per rasterisation band, >= 1); "c_evict_first" (0/1: L2 policy
- * of the C stores); "direct_store" (0/1: epilogue writes C from registers instead of staging it for TMA stores). */
+ * of the C stores); "direct_store" (0/1: epilogue writes C from registers instead of staging it for TMA stores);
+ * "k_skew" (>= 0: tile t starts its K walk at step (t * k_skew) % steps; 0 = every tile at K = 0);
+ * "split_k" (0/1, default 0: four units per tile, each with a quarter of the K steps, partial sums combined
+ * through a workspace the plan allocates. Offered for shapes with at most a quarter as many tiles as SMs and
+ * at least 16 K steps of 256 (10-13 % faster there); refused for others. The units of such a launch wait
+ * for each other, so the GPU's SMs must not be held by other kernels; a wait that runs out is reported by
+ * validate. Not inside stream capture: switching it on may allocate and clears flags). */
 int gpu_kernels_nvfp4_plan_set_option(void* plan, const char* key, int value);
-/* Fills info[0..7] = {M, N, K, units, cta_group, tile_n, group_m, stages}. */
+/* Fills info[0..9] = {M, N, K, units, cta_group, tile_n, group_m, stages, split_k, k_skew}. */
 int gpu_kernels_nvfp4_plan_info(void* plan, int* info);
 
 /* Diagnostic: one launch with per-role wait counters on; writes 16 words per CTA

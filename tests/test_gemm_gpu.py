@@ -226,3 +226,73 @@ def test_full_size_skinny(g):
     out, info = run_plan(g, pa, sa, pb, sb)
     assert info["cta_group"] == 1
     assert_gemm_close(out, fp32_reference_on_gpu(g, pa, sa, pb, sb), "skinny vs FP32 dequantise-then-matmul")
+
+
+SPLIT_K_SHAPES = [
+    # (M, N, K, S): far fewer tiles than SMs and a long K loop
+    (128, 512, 4096, 4),            # 2 tiles: 8 units of 4 ring steps
+    (128, 3584, 8192, 4),           # the decode shape's slab on one of eight GPUs
+    (256, 256, 8192, 4),            # CTA pairs, one tile
+    (512, 512, 4096, 4),            # CTA pairs, 4 tiles
+]
+
+
+@pytest.mark.parametrize("m,n,k,split", SPLIT_K_SHAPES)
+def test_split_k_against_whole_tiles(g, m, n, k, split):
+    # S units per tile: same result as the unsplit schedule up to FP32 summation order, reproducible from
+    # launch to launch (the slices are added in a fixed order), flags lowered again after every launch
+    a = random_operand(m, k, seed=11 + m + n + k)
+    b = random_operand(n, k, seed=12 + m + n + k, scale=0.02)
+    pa, sa = g.quantize(a)
+    pb, sb = g.quantize(b)
+    plan = g.Nvfp4Gemm(pa, pb, sa, sb)
+    assert plan.info()["split_k"] == 0                  # opt-in
+    plan.set_option("split_k", 1)
+    info = plan.info()
+    assert info["split_k"] == split, info
+    outs = [plan.run(nan_output(m, n)).clone() for _ in range(3)]
+    plan.validate()
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    plan.set_option("split_k", 0)
+    assert plan.info()["split_k"] == 0 and plan.info()["units"] * split == info["units"]
+    whole = plan.run(nan_output(m, n)).clone()
+    plan.set_option("split_k", 1)
+    again = plan.run(nan_output(m, n))
+    plan.validate()
+    assert torch.equal(again, outs[0])
+    ref = g.dequantize(pa, sa) @ g.dequantize(pb, sb).T
+    assert_gemm_close(outs[0], to_np(ref), f"split-K {m}x{n}x{k}")
+    assert_gemm_close(whole, to_np(ref), f"whole tiles {m}x{n}x{k}")
+    diff = (outs[0].float() - whole.float()).abs().max().item()
+    assert diff <= 2e-3 * ref.abs().max().item(), diff
+    # inside a CUDA graph, replayed
+    graph = torch.cuda.CUDAGraph()
+    out = nan_output(m, n)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        plan.run(out)
+    torch.cuda.current_stream().wait_stream(side)
+    with torch.cuda.graph(graph):
+        plan.run(out)
+    for _ in range(2):
+        out.fill_(float("nan"))
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, outs[0])
+    plan.validate()
+    del graph
+    plan.close()
+
+
+def test_split_k_is_left_off_where_it_cannot_gain(g):
+    for m, n, k in ((256, 256, 256), (8192, 8192, 256), (128, 28672, 1024), (384, 640, 2048), (1024, 2048, 4096)):
+        a = random_operand(m, k, seed=5)
+        b = random_operand(n, k, seed=6, scale=0.02)
+        pa, sa = g.quantize(a)
+        pb, sb = g.quantize(b)
+        plan = g.Nvfp4Gemm(pa, pb, sa, sb)
+        assert plan.info()["split_k"] == 0
+        with pytest.raises(RuntimeError):
+            plan.set_option("split_k", 1)
+        plan.close()
