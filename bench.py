@@ -200,11 +200,19 @@ def run_ours(args, rank, world, local_rank):
         except RuntimeError:
             break
     out = torch.empty((m, n_local), dtype=torch.float16, device=dev)
-    full = torch.empty((m, n), dtype=torch.float16, device=dev) if (world > 1 and args.gather) else None
+    full = torch.empty((m, n), dtype=torch.float16, device=dev) if (world > 1 and args.gather == "nccl") else None
+    shared = None
+    if world > 1 and args.gather == "fused":
+        # every rank's full C is mapped into all ranks; the GEMM's epilogue writes the slab into all of them
+        shared = g.GatheredOutput(m, n, dev)
+        for plan in plans:
+            shared.attach(plan, lo)
 
     def step(i):
         plans[i % rotations].run(out)
-        if full is not None:
+        if shared is not None:
+            shared.barrier()
+        elif full is not None:
             g.gather_columns(out, None, full)
 
     def barrier():
@@ -285,6 +293,8 @@ def run_ours(args, rank, world, local_rank):
     del te
     h2d = sum(t.numel() * t.element_size() for t in host)
     d2h = host_c.numel() * 2
+    if shared is not None:
+        shared.close()                                          # collective: before any rank leaves
 
     if rank != 0:
         return
@@ -326,7 +336,7 @@ def run_ours(args, rank, world, local_rank):
         "vs_baseline": None, "dtype": "nvfp4 (e2m1 x ue4m3), f32 accumulate, f16 out", "data": "synthetic",
         "config": {"workload": args.workload, "M": m, "N": n, "K": k, "layout": "TN",
                    "sharding": f"B rows over {world} rank(s), {n_local} columns of C per rank",
-                   "gather": bool(full is not None),
+                   "gather": args.gather if world > 1 else "none",
                    "l2": f"operand rotation over {rotations} copies ({rotations * in_bytes >> 20} MiB > 2 x L2 {l2 >> 20} MiB)",
                    "plan": info},
         "clocks": clocks,
@@ -521,7 +531,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="gemm8192", choices=sorted(WORKLOADS) + sorted(MOE_WORKLOADS) + sorted(QUANT_WORKLOADS))
-    ap.add_argument("--gather", action="store_true", help="N>1: include the all-gather of C in every step")
+    ap.add_argument("--gather", nargs="?", const="fused", default="none", choices=["none", "fused", "nccl"],
+                    help="N>1: every step also leaves the full C on every rank: 'fused' = the GEMM's epilogue stores the "
+                         "slab into all ranks' buffers over NVLink + a barrier; 'nccl' = all-gather + strided copy")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

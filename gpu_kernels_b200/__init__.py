@@ -5,5 +5,5 @@ Everything here drives hand-written sm_100a kernels through a C ABI
 """
 from .nvfp4 import dequantize, pack_scales, quantize, unpack_scales  # noqa: F401
 from .gemm import Nvfp4Gemm, gemm_host  # noqa: F401
-from .sharded import ShardedNvfp4Gemm, gather_columns, shard_b, slab_rows  # noqa: F401
+from .sharded import GatheredOutput, ShardedNvfp4Gemm, gather_columns, shard_b, slab_rows  # noqa: F401
 from .moe import Nvfp4MoE, route  # noqa: F401

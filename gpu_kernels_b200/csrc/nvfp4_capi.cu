@@ -105,6 +105,7 @@ struct Plan {
     void* workspace = nullptr;
     size_t workspace_bytes = 0;
     std::unique_ptr<LtMatmul> lt;
+    void* gather_table = nullptr;           // owned
     void* split_k_workspace = nullptr;      // owned
     size_t split_k_bytes = 0;
     int whole_tile_units = 0;                // params.clusters and direct_store of the unsplit schedule
@@ -112,7 +113,10 @@ struct Plan {
     Plan() = default;
     Plan(const Plan&) = delete;
     Plan& operator=(const Plan&) = delete;
-    ~Plan() { if (split_k_workspace) cudaFree(split_k_workspace); }
+    ~Plan() {
+        if (split_k_workspace) cudaFree(split_k_workspace);
+        if (gather_table) cudaFree(gather_table);
+    }
 };
 
 Plan& as_plan(void* p) {
@@ -294,6 +298,16 @@ int gpu_kernels_nvfp4_plan_set_option(void* plan, const char* key, int value) {
         } else {
             throw std::invalid_argument(std::string("set_option: unknown key ") + key);
         }
+    });
+}
+
+int gpu_kernels_nvfp4_plan_set_gather(void* plan, void* const* buffers, int world, int col0, int n_total) {
+    return guarded([&] {
+        Plan& p = as_plan(plan);
+        if (world > 0 && !p.gather_table) {
+            nvfp4_b200::cuda_check(cudaMalloc(&p.gather_table, gpu_kernels::nvfp4_gather_table_bytes(64)));
+        }
+        gpu_kernels::nvfp4_set_gather(p.params, buffers, world, col0, n_total, p.gather_table, nullptr);
     });
 }
 

@@ -28,6 +28,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <vector>
 
 namespace nvfp4_b200 {
 
@@ -147,6 +148,15 @@ struct GemmArgs {
     float* sk_partials;             // [units][CG][4 warps][UN/64 chunks][16][32 lanes] float4
     uint32_t* sk_flags;             // [units][CG][4 warps]: partial sums published
     uint32_t* sk_done;              // [tiles][CG][4 warps]: readers finished (the last one lowers the flags)
+    // GEMM fused with the all-gather of C (dense mode, N sharded over ranks): this rank's column slab is
+    // written into the full [M, gather_ldc] C of EVERY rank, its own and its peers' (NVLink), from the
+    // epilogue: TMA stores through one tensor map per destination (staged route) or register stores (direct
+    // route). 0 destinations = plain C.
+    int gather_world;
+    int gather_col0;                // first column of this rank's slab in the full C
+    int gather_ldc;                 // columns of the full C
+    const CUtensorMap* gather_maps; // [gather_world] in device memory, written by the host before any launch
+    void* const* gather_ptrs;       // [gather_world] bases of the full C buffers
 };
 
 struct Segment {
@@ -461,7 +471,14 @@ struct Roles {
                     }
                 }
             }
-            store_row_chunk(static_cast<uint16_t*>(g.c) + size_t(row0 + lane) * g.ldc + col0 + chunk * EPI_COLS, v, alpha, true);
+            if (g.gather_world) {
+                const size_t at = size_t(row0 + lane) * g.gather_ldc + g.gather_col0 + col0 + chunk * EPI_COLS;
+                for (int r = 0; r < g.gather_world; ++r)
+                    store_row_chunk(reinterpret_cast<uint16_t*>(__ldg(reinterpret_cast<const unsigned long long*>(g.gather_ptrs) + r)) + at,
+                                    v, alpha, true);
+            } else {
+                store_row_chunk(static_cast<uint16_t*>(g.c) + size_t(row0 + lane) * g.ldc + col0 + chunk * EPI_COLS, v, alpha, true);
+            }
         }
         if (lane == 0) {
             uint32_t* done = g.sk_done + (seg.tile * CG + rank) * 4 + warp;
@@ -624,6 +641,13 @@ struct Roles {
                         if (deliver)
                             dst = reinterpret_cast<uint16_t*>(__ldg(reinterpret_cast<const unsigned long long*>(g.slots) + owner)) + size_t(slot) * g.ldc + col0 + chunk * EPI_COLS;
                     }
+                    if (g.gather_world) {
+                        const size_t at = size_t(row0 + lane) * g.gather_ldc + g.gather_col0 + col0 + chunk * EPI_COLS;
+                        for (int r = 0; r < g.gather_world; ++r)
+                            store_row_chunk(reinterpret_cast<uint16_t*>(__ldg(reinterpret_cast<const unsigned long long*>(g.gather_ptrs) + r)) + at,
+                                            v, alpha, true);
+                        continue;
+                    }
                     store_row_chunk(dst, v, alpha, deliver);
                     continue;
                 }
@@ -655,7 +679,12 @@ struct Roles {
                 fence_async_smem();
                 __syncwarp();
                 if (lane == 0 && !(g.debug & 1u)) {
-                    if (g.c_evict_first) tma_store_2d_hint(tmC, buf, col0 + chunk * EPI_COLS, row0, c_policy);
+                    if (g.gather_world) {
+                        // the same staged tile to every rank's full C; one bulk group, so the buffer is reused
+                        // only after all of them have read it
+                        for (int r = 0; r < g.gather_world; ++r)
+                            tma_store_2d(g.gather_maps + r, buf, g.gather_col0 + col0 + chunk * EPI_COLS, row0);
+                    } else if (g.c_evict_first) tma_store_2d_hint(tmC, buf, col0 + chunk * EPI_COLS, row0, c_policy);
                     else tma_store_2d(tmC, buf, col0 + chunk * EPI_COLS, row0);
                     tma_store_commit();
                 }
@@ -837,7 +866,9 @@ void launch_variant(const gpu_kernels::Nvfp4Params& p, const CUtensorMap& tmC, v
                p.direct_store, c, p.N, nullptr, nullptr, nullptr, 0.0f, nullptr, nullptr, 0, 0, p.k_skew,
                p.split_k, p.split_k > 1 ? reinterpret_cast<float*>(static_cast<uint8_t*>(p.split_k_workspace) + SPLIT_K_FLAG_BYTES) : nullptr,
                p.split_k > 1 ? static_cast<uint32_t*>(p.split_k_workspace) : nullptr,
-               p.split_k > 1 ? static_cast<uint32_t*>(p.split_k_workspace) + SPLIT_K_FLAG_BYTES / 8 : nullptr};
+               p.split_k > 1 ? static_cast<uint32_t*>(p.split_k_workspace) + SPLIT_K_FLAG_BYTES / 8 : nullptr,
+               p.gather_world, p.gather_col0, p.gather_ldc, static_cast<const CUtensorMap*>(p.gather_maps),
+               static_cast<void* const*>(p.gather_ptrs)};
     if (p.split_k > 1 && !p.direct_store) throw std::logic_error("nvfp4 gemm: split-K writes C from registers");
     cudaLaunchAttribute attr{};
     attr.id = cudaLaunchAttributeClusterDimension;
@@ -911,7 +942,40 @@ void prepare(gpu_kernels::Nvfp4Params& p, const uint8_t* A, const uint8_t* B, co
     p.k_skew = env_int("NVFP4_B200_K_SKEW", 11);
     p.split_k = 0;
     p.split_k_workspace = nullptr;
+    p.gather_world = 0;
+    p.gather_col0 = 0;
+    p.gather_ldc = 0;
+    p.gather_maps = nullptr;
+    p.gather_ptrs = nullptr;
     (void)status_word(device);
+}
+
+// table: device memory of gather_table_bytes(world), filled here (on `stream`) with one tensor map and one
+// base pointer per destination; buffers: host array of `world` device pointers to the full [M, n_total] C.
+size_t gather_table_bytes(int world) { return size_t(world) * (sizeof(CUtensorMap) + sizeof(void*)); }
+
+void set_gather(gpu_kernels::Nvfp4Params& p, void* const* buffers, int world, int col0, int n_total, void* table,
+                cudaStream_t stream) {
+    if (world == 0) { p.gather_world = 0; p.gather_maps = nullptr; p.gather_ptrs = nullptr; return; }
+    if (!buffers || !table || world < 1 || world > 64) throw std::invalid_argument("nvfp4 gemm gather: 1..64 destination buffers and a table");
+    if (col0 < 0 || col0 % 64 || n_total % 8 || col0 + p.N > n_total)
+        throw std::invalid_argument("nvfp4 gemm gather: the slab [col0, col0 + N) must lie inside the full C, col0 a multiple of 64");
+    if (reinterpret_cast<uintptr_t>(table) & 127) throw std::invalid_argument("nvfp4 gemm gather: table must be 128-byte aligned");
+    std::vector<uint8_t> host(gather_table_bytes(world));
+    auto* maps = reinterpret_cast<CUtensorMap*>(host.data());
+    auto* ptrs = reinterpret_cast<void**>(host.data() + size_t(world) * sizeof(CUtensorMap));
+    for (int r = 0; r < world; ++r) {
+        if (!buffers[r] || (reinterpret_cast<uintptr_t>(buffers[r]) & 15)) throw std::invalid_argument("nvfp4 gemm gather: null or misaligned buffer");
+        maps[r] = output_map(static_cast<const __half*>(buffers[r]), p.M, n_total);
+        ptrs[r] = buffers[r];
+    }
+    cuda_check(cudaMemcpyAsync(table, host.data(), host.size(), cudaMemcpyHostToDevice, stream));
+    cuda_check(cudaStreamSynchronize(stream));           // `host` goes out of scope
+    p.gather_world = world;
+    p.gather_col0 = col0;
+    p.gather_ldc = n_total;
+    p.gather_maps = table;
+    p.gather_ptrs = static_cast<uint8_t*>(table) + size_t(world) * sizeof(CUtensorMap);
 }
 
 // Split-K can pay when whole tiles would leave most SMs idle and every tile's K loop is long: four units per
@@ -1054,7 +1118,7 @@ void grouped_launch_fused(const GroupedGemm& p, void* C, int out_bf16, uint8_t* 
     const int cg = p.block_rows == 256 ? 2 : 1;
     GemmArgs g{p.pool_rows, p.n, p.k, p.pool_rows / p.block_rows, p.n / 256, 1, 1.0f, status_word(p.device), nullptr,
                0u, 1, out_bf16, p.block_expert, p.num_blocks, p.n, 1, C, p.n, act_packed, act_scales, row_weight, clamp,
-               row_dst, slots, world, slot_rows, 0, 0, nullptr, nullptr, nullptr};
+               row_dst, slots, world, slot_rows, 0, 0, nullptr, nullptr, nullptr, 0, 0, 0, nullptr, nullptr};
     cudaLaunchAttribute attr{};
     attr.id = cudaLaunchAttributeClusterDimension;
     attr.val.clusterDim = {unsigned(cg), 1, 1};
@@ -1088,6 +1152,13 @@ size_t nvfp4_split_k_workspace_bytes(const Nvfp4Params& p) { return nvfp4_b200::
 
 void nvfp4_enable_split_k(Nvfp4Params& p, void* workspace, size_t bytes, cudaStream_t stream) {
     nvfp4_b200::enable_split_k(p, workspace, bytes, stream);
+}
+
+size_t nvfp4_gather_table_bytes(int world) { return nvfp4_b200::gather_table_bytes(world); }
+
+void nvfp4_set_gather(Nvfp4Params& p, void* const* buffers, int world, int col0, int n_total, void* table,
+                      cudaStream_t stream) {
+    nvfp4_b200::set_gather(p, buffers, world, col0, n_total, table, stream);
 }
 
 }  // namespace gpu_kernels

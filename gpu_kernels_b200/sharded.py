@@ -13,6 +13,7 @@ from __future__ import annotations
 import torch
 import torch.distributed as dist
 
+from . import _lib
 from .gemm import Nvfp4Gemm
 
 
@@ -51,10 +52,80 @@ def gather_columns(local: torch.Tensor, group=None, out: torch.Tensor | None = N
     return out
 
 
-class ShardedNvfp4Gemm:
-    """C[:, slab] = alpha * A @ B_slab.T on this rank; `run(gather=True)` returns the full C."""
+class _DeviceView:
+    """Lets torch wrap device memory this package allocated itself (CUDA array interface)."""
 
-    def __init__(self, a_packed, sfa, b_slab, sfb_slab, group=None, alpha: float = 1.0, split_k: bool = False):
+    def __init__(self, ptr: int, shape, typestr: str):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False), "version": 3}
+
+
+class GatheredOutput:
+    """The full [M, N_total] FP16 C of every rank of the group, each mapped into all the others (CUDA IPC).
+
+    `attach(plan, col0)` makes a plan's epilogue write its column slab into all of them (this rank's own
+    and, over NVLink, the peers'); `barrier()` is the stream-ordered point after which every rank's stores
+    have landed in `full`. All ranks must sit on one NVLink node. Collective: construct and close on every rank.
+    """
+
+    def __init__(self, m: int, n_total: int, device, group=None):
+        import ctypes
+        lib = _lib.load()
+        self.group, self.m, self.n_total = group, m, n_total
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.device = torch.device(device)
+        with torch.cuda.device(self.device):
+            own, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+            _lib.check(lib.gpu_kernels_nvfp4_ipc_alloc(m * n_total * 2, ctypes.byref(own), handle))
+            handles = [None] * self.world
+            dist.all_gather_object(handles, handle.raw, group=group)
+            self._table, self._opened = (ctypes.c_void_p * self.world)(), []
+            for r in range(self.world):
+                if r == self.rank:
+                    self._table[r] = own.value
+                else:
+                    ptr = ctypes.c_void_p()
+                    _lib.check(lib.gpu_kernels_nvfp4_ipc_open(handles[r], ctypes.byref(ptr)))
+                    self._table[r] = ptr.value
+                    self._opened.append(ptr.value)
+        self._own = own.value
+        self.full = torch.as_tensor(_DeviceView(own.value, (m, n_total), "<f2"), device=self.device)
+        self._fence = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+    def attach(self, plan: Nvfp4Gemm, col0: int) -> None:
+        if plan.m != self.m:
+            raise ValueError("plan and output disagree on M")
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.load().gpu_kernels_nvfp4_plan_set_gather(plan._plan, self._table, self.world, col0, self.n_total))
+
+    def barrier(self) -> None:
+        dist.all_reduce(self._fence, group=self.group)
+
+    def close(self) -> None:
+        if self._own is None:
+            return
+        lib = _lib.load()
+        torch.cuda.synchronize(self.device)
+        self.full = None
+        for ptr in self._opened:
+            lib.gpu_kernels_nvfp4_ipc_close(ptr)
+        if dist.is_initialized():
+            dist.barrier(group=self.group)              # nobody still maps this rank's buffer
+        lib.gpu_kernels_nvfp4_ipc_free(self._own)
+        self._own = None
+
+
+class ShardedNvfp4Gemm:
+    """C[:, slab] = alpha * A @ B_slab.T on this rank; `run(gather=True)` returns the full C on every rank.
+
+    fused_gather=True (all ranks on one NVLink node): the full C of every rank lives in a buffer the other
+    ranks map through CUDA IPC, and the GEMM's epilogue writes this rank's slab into all of them while the
+    tiles are computed; run(gather=True) is then that one kernel plus a barrier (a one-element all-reduce,
+    stream-ordered). Otherwise run(gather=True) is the GEMM, an NCCL all-gather and a strided copy.
+    The full C is reused by the next run(): consume it (or copy it) before calling run() again.
+    """
+
+    def __init__(self, a_packed, sfa, b_slab, sfb_slab, group=None, alpha: float = 1.0, split_k: bool = False,
+                 fused_gather: bool = False):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -68,8 +139,22 @@ class ShardedNvfp4Gemm:
                 pass
         self.local = torch.empty((self.plan.m, self.plan.n), dtype=torch.float16, device=a_packed.device)
         self.full = None
+        self._ipc = None
+        if fused_gather and self.world > 1:
+            self._setup_fused_gather()
+
+    def _setup_fused_gather(self):
+        self._ipc = GatheredOutput(self.plan.m, self.plan.n * self.world, self.local.device, self.group)
+        self._ipc.attach(self.plan, self.rank * self.plan.n)
+        self.full = self._ipc.full
 
     def run(self, gather: bool = False) -> torch.Tensor:
+        if self._ipc is not None:
+            if not gather:
+                raise ValueError("this object was built with fused_gather=True: every run writes the full C")
+            self.plan.run(self.local)                   # the slab goes to every rank's full C; `local` stays untouched
+            self._ipc.barrier()                         # all ranks' stores have landed once this completes
+            return self.full
         self.plan.run(self.local)
         if not gather or self.world == 1:
             return self.local
@@ -82,4 +167,8 @@ class ShardedNvfp4Gemm:
         self.plan.validate()
 
     def close(self) -> None:
+        if self._ipc is not None:
+            self.full = None
+            self._ipc.close()
+            self._ipc = None
         self.plan.close()

@@ -42,6 +42,10 @@ struct Nvfp4Params {
     int k_skew;                     // tile t starts its K walk at step (t * k_skew) % steps and wraps; 0 = off
     int split_k;                    // S > 1: S units per tile, each with 1/S of the K steps (see below)
     void* split_k_workspace;        // flags + FP32 partial tiles, owned by the caller
+    int gather_world;               // > 0: C goes to this many full-width buffers instead (see nvfp4_set_gather)
+    int gather_col0, gather_ldc;
+    const void* gather_maps;
+    const void* gather_ptrs;
 };
 
 struct Nvfp4Implementation {
@@ -75,5 +79,16 @@ void nvfp4_set_alpha(Nvfp4Params&, float alpha);
 // again (the flag area is cleared on `stream`).
 size_t nvfp4_split_k_workspace_bytes(const Nvfp4Params&);
 void nvfp4_enable_split_k(Nvfp4Params&, void* workspace, size_t bytes, cudaStream_t stream);
+
+// Extension: the GEMM fused with the all-gather of C, for N sharded over the GPUs of one NVLink node. This
+// rank's [M, N] result is the column slab [col0, col0 + N) of a full [M, n_total] C; with a gather set, the
+// epilogue writes the slab straight into the full C of every rank in `buffers` (this rank's own and its
+// peers', mapped into this process, e.g. through CUDA IPC), so no collective has to move C afterwards: the
+// caller only needs a barrier between the ranks before reading. launch() then writes nothing through its C
+// argument (still a valid device pointer of M * N elements, e.g. this rank's buffer). `table` is device memory of nvfp4_gather_table_bytes(world), 128-byte aligned, owned by the
+// caller and filled here. world = 0 switches the gather off again.
+size_t nvfp4_gather_table_bytes(int world);
+void nvfp4_set_gather(Nvfp4Params&, void* const* buffers, int world, int col0, int n_total, void* table,
+                      cudaStream_t stream);
 
 }  // namespace gpu_kernels

@@ -64,6 +64,15 @@ int gpu_kernels_nvfp4_plan_set_alpha(void* plan, float alpha);
  * for each other, so the GPU's SMs must not be held by other kernels; a wait that runs out is reported by
  * validate. Not inside stream capture: switching it on may allocate and clears flags). */
 int gpu_kernels_nvfp4_plan_set_option(void* plan, const char* key, int value);
+/* The GEMM fused with the all-gather of C (N sharded over the GPUs of one NVLink node; no counterpart in the
+ * reference, whose GEMM is single-GPU): the plan's [M, N] result is the column slab [col0, col0 + N) of a
+ * full [M, n_total] FP16 matrix, and every later gpu_kernels_nvfp4_custom(plan, C, stream) writes that slab
+ * from its epilogue into ALL `world` buffers (host array of device pointers: this rank's full C and the
+ * peers', opened with gpu_kernels_nvfp4_ipc_open); nothing is written through C then (still a valid device
+ * pointer of M * N elements, e.g. this rank's buffer). The caller puts a
+ * barrier between the ranks before reading, and before the next launch overwrites. world = 0 switches it
+ * off. Not inside stream capture (synchronises once). */
+int gpu_kernels_nvfp4_plan_set_gather(void* plan, void* const* buffers, int world, int col0, int n_total);
 /* Fills info[0..9] = {M, N, K, units, cta_group, tile_n, group_m, stages, split_k, k_skew}. */
 int gpu_kernels_nvfp4_plan_info(void* plan, int* info);
 

@@ -1,0 +1,79 @@
+"""N-sharded GEMM on two GPUs: the all-gather fused into the GEMM's epilogue (stores into the peers' full C
+over NVLink) against the NCCL all-gather route and the FP32 reference, one process per GPU."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+# (M, N, K, what it exercises)
+CASES = [
+    (512, 1024, 4096),      # CTA pairs, staged epilogue: one TMA store per destination and chunk
+    (512, 1024, 1024),      # CTA pairs, register stores
+    (128, 1024, 2048),      # single CTAs (the decode shape's kind)
+    (128, 512, 8192),       # single CTAs with split-K: the reducing slices store to every rank
+    (384, 768, 512),        # 128 x 128 tiles
+]
+
+
+def _worker(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    from datetime import timedelta
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank),
+                            timeout=timedelta(seconds=60))
+    try:
+        import gpu_kernels_b200 as g
+        torch.backends.cuda.matmul.allow_tf32 = False
+        for m, n, k in CASES:
+            gen = torch.Generator(device="cuda").manual_seed(m + n + k)              # same operands on every rank
+            a = torch.randn((m, k), generator=gen, device="cuda").bfloat16()
+            b = (torch.randn((n, k), generator=gen, device="cuda") * 0.02).bfloat16()
+            pa, sa = g.quantize(a)
+            pb, sb = g.quantize(b)
+            slab, slab_scales = (t.clone() for t in g.shard_b(pb, sb, world, rank))
+            ref = g.dequantize(pa, sa) @ g.dequantize(pb, sb).T
+            plain = g.ShardedNvfp4Gemm(pa, sa, slab, slab_scales, split_k=True)
+            want = plain.run(gather=True).clone()                                # GEMM + NCCL all-gather + strided copy
+            plain.validate()
+            fused = g.ShardedNvfp4Gemm(pa, sa, slab, slab_scales, split_k=True, fused_gather=True)
+            for call in range(3):
+                fused.full.fill_(float("nan"))
+                dist.barrier()                                                   # nobody clears after a peer has written
+                torch.cuda.synchronize()
+                got = fused.run(gather=True)
+                torch.cuda.synchronize()
+                assert not torch.isnan(got).any(), f"rank {rank} {m}x{n}x{k} call {call}: unwritten part of the full C"
+                assert torch.equal(got, want), f"rank {rank} {m}x{n}x{k} call {call}: fused gather differs from the NCCL route"
+                dist.barrier()
+            fused.validate()
+            err = (want.float() - ref).double()
+            rel = float(err.norm() / ref.double().norm())
+            assert rel <= 1e-3, f"rank {rank} {m}x{n}x{k}: relative Frobenius error {rel:.3e}"
+            with pytest.raises(ValueError):
+                fused.run(gather=False)
+            fused.close()
+            plain.close()
+        open(os.path.join(out_dir, f"ok{rank}"), "w").close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_fused_gather_two_gpus(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world, port = 2, _free_port()
+    mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    assert all((tmp_path / f"ok{r}").exists() for r in range(world))
