@@ -7,3 +7,4 @@ from .nvfp4 import dequantize, pack_scales, quantize, unpack_scales  # noqa: F40
 from .gemm import Nvfp4Gemm, gemm_host  # noqa: F401
 from .sharded import GatheredOutput, ShardedNvfp4Gemm, gather_columns, shard_b, slab_rows  # noqa: F401
 from .moe import Nvfp4MoE, route  # noqa: F401
+from .peer import PeerGroup, SharedBuffer  # noqa: F401

@@ -585,6 +585,21 @@ int gpu_kernels_nvfp4_moe_return_peer(const void* out_pool, const void* recv_row
     });
 }
 
+int gpu_kernels_nvfp4_peer_state_bytes(int world, int max_ints, size_t* bytes) {
+    return guarded([&] {
+        if (!bytes) throw std::invalid_argument("peer_state_bytes: null result pointer");
+        *bytes = nvfp4_b200::peer_state_bytes(world, max_ints);
+    });
+}
+
+int gpu_kernels_nvfp4_peer_exchange(void* own, const void* peers_device, int world, int rank, const void* payload, int ints,
+                                    int max_ints, void* out, void* stream) {
+    return guarded([&] {
+        nvfp4_b200::peer_exchange(own, static_cast<void* const*>(peers_device), world, rank, static_cast<const int*>(payload),
+                                  ints, max_ints, static_cast<int*>(out), static_cast<cudaStream_t>(stream));
+    });
+}
+
 /* ---- device buffers that other processes of the box can map (CUDA IPC) ---- */
 
 int gpu_kernels_nvfp4_ipc_alloc(size_t bytes, void** ptr, void* handle64) {

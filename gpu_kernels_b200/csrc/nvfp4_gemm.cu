@@ -1042,6 +1042,8 @@ void validate() {
 
 }  // namespace
 
+uint32_t* device_status_word(int device) { return status_word(device); }
+
 void require_sm100() {
     int device = 0, major = 0;
     cuda_check(cudaGetDevice(&device));

@@ -78,6 +78,14 @@ void moe_swiglu_quant(const void* gate_up_bf16, const float* pool_weight, const 
 void moe_return_rows(const void* out_pool_bf16, const int* pool_of_recv, const int* totals, int capacity, int hidden,
                      void* return_rows_bf16, cudaStream_t stream);
 int moe_payload_bytes(int hidden);
+// The device's four status words: [0] bits of ptx.cuh's StatusBits, [1] first tag, [2] cycles of the last GEMM.
+uint32_t* device_status_word(int device);
+// Barrier (ints = 0) or barrier + all-gather of `ints` integers per rank between the GPUs of one node, through
+// state blocks (peer_state_bytes each, zeroed) that every rank maps: own = this rank's, peers_device = device
+// array of all ranks' blocks in rank order. out [world][ints].
+size_t peer_state_bytes(int world, int max_ints);
+void peer_exchange(void* own, void* const* peers_device, int world, int rank, const int* payload, int ints, int max_ints,
+                   int* out, cudaStream_t stream);
 void moe_reduce(const void* returned_bf16, const int* send_pos, int tokens, int topk, int hidden, void* y_bf16,
                 cudaStream_t stream);
 

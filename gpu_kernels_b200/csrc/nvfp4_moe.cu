@@ -17,11 +17,13 @@
 // This file keeps those semantics (rounding points, clamp order, fixed-order top-k sum) and the
 // phase structure (metadata / FC1 / FC2 / reduce), with NVFP4 operands and an all-to-all exchange.
 #include "nvfp4_internal.h"
+#include "ptx.cuh"
 #include "quant_device.cuh"
 
 #include <cuda_bf16.h>
 
 #include <algorithm>
+#include <cstddef>
 #include <string>
 
 namespace nvfp4_b200 {
@@ -477,5 +479,85 @@ void moe_return_peer(const void* out_pool_bf16, const uint8_t* recv_rows, const 
 }
 
 int moe_payload_bytes(int hidden) { return payload_bytes(hidden); }
+
+// ---- barrier (+ small all-gather) between the GPUs of one node over peer memory --------------------------
+//
+// Every rank owns one PeerState in memory that all the others map. An exchange with sequence number e (one
+// more than this rank's last): write this rank's payload into row `rank` of slot e & 1 of every rank's
+// payload area, fence, store e into arrived[rank] of every rank, wait until all of this rank's own arrived[]
+// words have reached e, copy the gathered rows out. One CTA per GPU; the kernels of one exchange run on
+// different GPUs, never two on the same one. The wait is bounded: after WAIT_LIMIT_NS the kernel sets
+// STATUS_TIMEOUT_PEER and returns. The payload slots alternate so that a rank already at exchange e + 1
+// cannot overwrite rows a slower rank is still copying out of exchange e; it cannot get to e + 2 before that
+// rank has arrived at e + 1.
+using ptx::globaltimer_ns;
+using ptx::WAIT_LIMIT_NS;
+using ptx::STATUS_TIMEOUT_PEER;
+
+struct PeerState {
+    uint32_t epoch;
+    uint32_t pad0[31];
+    uint32_t arrived[64];
+    uint32_t pad1[32];
+    int payload[1];                 // [2][world][max_ints]
+};
+constexpr size_t PEER_STATE_HEADER = offsetof(PeerState, payload);
+
+__global__ void peer_exchange_kernel(PeerState* own, PeerState* const* peers, int world, int rank,
+                                     const int* __restrict__ payload, int ints, int max_ints, int* __restrict__ out,
+                                     uint32_t* status) {
+    __shared__ uint32_t next_epoch;
+    __shared__ int failed;
+    if (threadIdx.x == 0) { next_epoch = own->epoch + 1u; failed = 0; }
+    __syncthreads();
+    const uint32_t e = next_epoch;
+    const size_t slot = size_t(e & 1u) * world;
+    for (int r = 0; r < world && ints > 0; ++r) {
+        int* dst = peers[r]->payload + (slot + rank) * max_ints;
+        for (int i = threadIdx.x; i < ints; i += blockDim.x) dst[i] = payload[i];
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (int(threadIdx.x) < world) {
+        asm volatile("st.release.sys.global.u32 [%0], %1;" :: "l"(&peers[threadIdx.x]->arrived[rank]), "r"(e) : "memory");
+        const uint64_t start = globaltimer_ns();
+        while (true) {
+            uint32_t seen;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(&own->arrived[threadIdx.x]) : "memory");
+            if (int32_t(seen - e) >= 0) break;
+            if (globaltimer_ns() - start > WAIT_LIMIT_NS) {
+                atomicOr(status, uint32_t(STATUS_TIMEOUT_PEER));
+                atomicCAS(status + 1, 0u, 0x40000000u | (uint32_t(threadIdx.x) << 16) | (e & 0xFFFFu));
+                failed = 1;
+                break;
+            }
+            __nanosleep(100);
+        }
+    }
+    __syncthreads();
+    if (!failed && ints > 0) {
+        const int* src = own->payload + slot * max_ints;
+        for (int r = 0; r < world; ++r)
+            for (int i = threadIdx.x; i < ints; i += blockDim.x) out[r * ints + i] = __ldcg(src + size_t(r) * max_ints + i);
+    }
+    if (threadIdx.x == 0) own->epoch = e;
+}
+
+size_t peer_state_bytes(int world, int max_ints) {
+    if (world < 1 || world > 64 || max_ints < 0) throw std::invalid_argument("peer state: 1..64 ranks");
+    return PEER_STATE_HEADER + size_t(2) * world * std::max(max_ints, 1) * sizeof(int);
+}
+
+void peer_exchange(void* own, void* const* peers_device, int world, int rank, const int* payload, int ints, int max_ints,
+                   int* out, cudaStream_t stream) {
+    if (!own || !peers_device || world < 1 || world > 64 || rank < 0 || rank >= world)
+        throw std::invalid_argument("peer exchange: bad state, table or rank");
+    if (ints < 0 || ints > max_ints || (ints > 0 && (!payload || !out))) throw std::invalid_argument("peer exchange: bad payload");
+    int device = 0;
+    cuda_check(cudaGetDevice(&device));
+    peer_exchange_kernel<<<1, 256, 0, stream>>>(static_cast<PeerState*>(own), reinterpret_cast<PeerState* const*>(peers_device),
+                                                world, rank, payload, ints, max_ints, out, device_status_word(device));
+    cuda_check(cudaGetLastError());
+}
 
 }  // namespace nvfp4_b200

@@ -107,6 +107,7 @@ enum StatusBits : uint32_t {
     STATUS_TIMEOUT_EPILOGUE = 1u << 2,
     STATUS_TIMEOUT_TEARDOWN = 1u << 3,
     STATUS_BAD_ARGUMENT = 1u << 4,
+    STATUS_TIMEOUT_PEER = 1u << 5,       // another GPU of the node did not arrive at a barrier
 };
 
 // Same test, but the hardware may park the warp for up to `hint_ns` nanoseconds while the phase

@@ -19,6 +19,7 @@ import torch
 import torch.distributed as dist
 
 from . import _lib
+from .peer import PeerGroup, SharedBuffer
 from .nvfp4 import quantize
 
 
@@ -138,45 +139,24 @@ class Nvfp4MoE:
                 self._plans[rows] = (fc1, fc2)
 
     def _setup_peer_buffers(self, routes, recv_cap):
-        """Receive and result-slot buffers that every rank of the group can write (CUDA IPC)."""
-        lib = _lib.load()
-        sizes = (recv_cap * self.payload, routes * self.hidden * 2)
-        own, handles = [], []
-        with torch.cuda.device(self.device):
-            for nbytes in sizes:
-                ptr, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
-                _lib.check(lib.gpu_kernels_nvfp4_ipc_alloc(nbytes, ctypes.byref(ptr), handle))
-                own.append(ptr.value)
-                handles.append(handle.raw)
-            gathered = [None] * self.world
-            dist.all_gather_object(gathered, handles, group=self.group)
-            tables, opened = [], []
-            for which in range(2):
-                table = (ctypes.c_void_p * self.world)()
-                for r in range(self.world):
-                    if r == self.rank:
-                        table[r] = own[which]
-                    else:
-                        ptr = ctypes.c_void_p()
-                        _lib.check(lib.gpu_kernels_nvfp4_ipc_open(gathered[r][which], ctypes.byref(ptr)))
-                        table[r] = ptr.value
-                        opened.append(ptr.value)
-                tables.append(table)
-        self._peer = {"own": own, "opened": opened, "recv": tables[0], "slots": tables[1]}
-        self.recv_ptr = own[0]
-        self.slots_ptr = own[1]
+        """Receive and result-slot buffers that every rank of the group can write (CUDA IPC), and the barrier."""
         d = self.device
+        recv = SharedBuffer(recv_cap * self.payload, d, self.group)
+        slots = SharedBuffer(routes * self.hidden * 2, d, self.group)
+        self._peers = PeerGroup(d, self.group, max_ints=self.experts)
+        self._peer = {"recv": recv, "slots": slots}
+        self.recv_ptr = recv.own
+        self.slots_ptr = slots.own
+        self.slot_table = slots.device_table
         self.peer_offset = torch.zeros(self.experts, dtype=torch.int32, device=d)
         self.peer_error = torch.zeros(1, dtype=torch.int32, device=d)
         self.identity = torch.arange(routes, dtype=torch.int32, device=d)
         self.pool_dst = torch.zeros(self.pool_rows, dtype=torch.int32, device=d)
-        self.slot_table = torch.tensor([int(tables[1][r]) for r in range(self.world)], dtype=torch.int64, device=d)
-        self._fence = torch.zeros(1, dtype=torch.int32, device=d)
 
     def _barrier(self):
-        # a stream-ordered collective: it completes on a rank only after every rank's earlier work on its
-        # stream (the peer stores) has finished, and nothing on the host waits for it
-        dist.all_reduce(self._fence, group=self.group)
+        # one small kernel per rank over peer memory: it completes on a rank only after every rank's earlier
+        # work on its stream (the peer stores) has finished, and nothing on the host waits for it
+        self._peers.barrier()
 
     def check(self) -> None:
         """Synchronises and raises if a peer store was out of bounds or the pool overflowed in the last calls."""
@@ -206,7 +186,9 @@ class Nvfp4MoE:
         routes = tokens * self.topk
         self.counts.zero_()
         _lib.check(lib.gpu_kernels_nvfp4_moe_route_count(ids.data_ptr(), routes, self.experts, self.counts.data_ptr(), s))
-        if self.world > 1:
+        if self._peer is not None:
+            self._peers.all_gather_ints(self.counts, self.counts_matrix)      # peer stores + barrier, one kernel
+        elif self.world > 1:
             dist.all_gather_into_tensor(self.counts_matrix.view(-1), self.counts, group=self.group)
         else:
             self.counts_matrix.copy_(self.counts.view(1, -1))
@@ -258,7 +240,7 @@ class Nvfp4MoE:
                 _lib.check(lib.gpu_kernels_nvfp4_moe_pack_peer(
                     xq.data_ptr(), xs.data_ptr(), ids.data_ptr(), weights.data_ptr(), tokens, self.topk, self.hidden,
                     self.world, self.local_experts, self.peer_offset.data_ptr(), self.cursor.data_ptr(),
-                    self._peer["recv"], self.recv_cap, self.peer_error.data_ptr(), s))
+                    self._peer["recv"].table, self.recv_cap, self.peer_error.data_ptr(), s))
                 self._mark("pack into the peers' receive buffers")
                 self._barrier()
                 self._mark("barrier")
@@ -371,13 +353,9 @@ class Nvfp4MoE:
     def close(self) -> None:
         lib = _lib.load()
         if self._peer is not None:
-            torch.cuda.synchronize(self.device)
-            for ptr in self._peer["opened"]:
-                lib.gpu_kernels_nvfp4_ipc_close(ptr)
-            if dist.is_initialized():
-                dist.barrier(group=self.group)          # nobody still maps this rank's buffers
-            for ptr in self._peer["own"]:
-                lib.gpu_kernels_nvfp4_ipc_free(ptr)
+            self._peers.close()
+            self._peer["slots"].close()
+            self._peer["recv"].close()
             self._peer = None
         for pair in getattr(self, "_plans", {}).values():
             for plan in pair:

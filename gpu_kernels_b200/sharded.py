@@ -15,6 +15,7 @@ import torch.distributed as dist
 
 from . import _lib
 from .gemm import Nvfp4Gemm
+from .peer import DeviceView, PeerGroup, SharedBuffer
 
 
 def slab_rows(n: int, world: int, rank: int) -> tuple[int, int]:
@@ -52,13 +53,6 @@ def gather_columns(local: torch.Tensor, group=None, out: torch.Tensor | None = N
     return out
 
 
-class _DeviceView:
-    """Lets torch wrap device memory this package allocated itself (CUDA array interface)."""
-
-    def __init__(self, ptr: int, shape, typestr: str):
-        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False), "version": 3}
-
-
 class GatheredOutput:
     """The full [M, N_total] FP16 C of every rank of the group, each mapped into all the others (CUDA IPC).
 
@@ -68,50 +62,28 @@ class GatheredOutput:
     """
 
     def __init__(self, m: int, n_total: int, device, group=None):
-        import ctypes
-        lib = _lib.load()
-        self.group, self.m, self.n_total = group, m, n_total
-        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
-        self.device = torch.device(device)
-        with torch.cuda.device(self.device):
-            own, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
-            _lib.check(lib.gpu_kernels_nvfp4_ipc_alloc(m * n_total * 2, ctypes.byref(own), handle))
-            handles = [None] * self.world
-            dist.all_gather_object(handles, handle.raw, group=group)
-            self._table, self._opened = (ctypes.c_void_p * self.world)(), []
-            for r in range(self.world):
-                if r == self.rank:
-                    self._table[r] = own.value
-                else:
-                    ptr = ctypes.c_void_p()
-                    _lib.check(lib.gpu_kernels_nvfp4_ipc_open(handles[r], ctypes.byref(ptr)))
-                    self._table[r] = ptr.value
-                    self._opened.append(ptr.value)
-        self._own = own.value
-        self.full = torch.as_tensor(_DeviceView(own.value, (m, n_total), "<f2"), device=self.device)
-        self._fence = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.m, self.n_total = m, n_total
+        self.buffer = SharedBuffer(m * n_total * 2, device, group)
+        self.peers = PeerGroup(device, group, max_ints=0)
+        self.device = self.buffer.device
+        self.full = torch.as_tensor(DeviceView(self.buffer.own, (m, n_total), "<f2"), device=self.device)
 
     def attach(self, plan: Nvfp4Gemm, col0: int) -> None:
         if plan.m != self.m:
             raise ValueError("plan and output disagree on M")
         with torch.cuda.device(self.device):
-            _lib.check(_lib.load().gpu_kernels_nvfp4_plan_set_gather(plan._plan, self._table, self.world, col0, self.n_total))
+            _lib.check(_lib.load().gpu_kernels_nvfp4_plan_set_gather(plan._plan, self.buffer.table, self.buffer.world, col0,
+                                                                     self.n_total))
 
     def barrier(self) -> None:
-        dist.all_reduce(self._fence, group=self.group)
+        self.peers.barrier()
 
     def close(self) -> None:
-        if self._own is None:
+        if self.full is None:
             return
-        lib = _lib.load()
-        torch.cuda.synchronize(self.device)
         self.full = None
-        for ptr in self._opened:
-            lib.gpu_kernels_nvfp4_ipc_close(ptr)
-        if dist.is_initialized():
-            dist.barrier(group=self.group)              # nobody still maps this rank's buffer
-        lib.gpu_kernels_nvfp4_ipc_free(self._own)
-        self._own = None
+        self.peers.close()
+        self.buffer.close()
 
 
 class ShardedNvfp4Gemm:
@@ -119,8 +91,8 @@ class ShardedNvfp4Gemm:
 
     fused_gather=True (all ranks on one NVLink node): the full C of every rank lives in a buffer the other
     ranks map through CUDA IPC, and the GEMM's epilogue writes this rank's slab into all of them while the
-    tiles are computed; run(gather=True) is then that one kernel plus a barrier (a one-element all-reduce,
-    stream-ordered). Otherwise run(gather=True) is the GEMM, an NCCL all-gather and a strided copy.
+    tiles are computed; run(gather=True) is then that one kernel plus a barrier kernel over peer memory
+    (stream-ordered, nothing for the host to wait on). Otherwise run(gather=True) is the GEMM, an NCCL all-gather and a strided copy.
     The full C is reused by the next run(): consume it (or copy it) before calling run() again.
     """
 

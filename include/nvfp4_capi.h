@@ -203,6 +203,19 @@ int gpu_kernels_nvfp4_moe_return_peer(const void* out_pool, const void* recv_row
                                       const void* totals, const void* seg_src_offset, int world, int local_experts,
                                       int hidden, int recv_capacity, void* const* peer_slots, int slot_capacity,
                                       void* error, void* stream);
+/* Barrier, or barrier plus all-gather of a few integers, between the GPUs of one NVLink node without a
+ * collective library: one small kernel per rank that stores into the peers' memory and waits (at most 2 s,
+ * then validate reports it) for their stores. Every rank owns a state block of peer_state_bytes(world,
+ * max_ints) bytes from gpu_kernels_nvfp4_ipc_alloc (zeroed) that all ranks map; `peers_device` is a DEVICE
+ * array of the world blocks' addresses in rank order (own = entry `rank`). After the call completes on a
+ * rank's stream, everything every rank had stored into peer memory before ITS call (on its stream) is visible
+ * there. ints > 0: `payload` [ints] of each rank arrives in `out` [world][ints] on every rank. All ranks call
+ * it the same number of times, each on its own GPU (never two ranks on one GPU). Capturable in a CUDA graph.
+ * No counterpart in the reference (its peer signalling is inside kernels/moe/fused/sm90.cu:296-319). */
+int gpu_kernels_nvfp4_peer_state_bytes(int world, int max_ints, size_t* bytes);
+int gpu_kernels_nvfp4_peer_exchange(void* own, const void* peers_device, int world, int rank, const void* payload, int ints,
+                                    int max_ints, void* out, void* stream);
+
 /* Device memory that the other processes of the box can map: ipc_alloc = cudaMalloc (zeroed) + a 64-byte handle
  * to hand to the peers; ipc_open maps a peer's handle (lazy peer access); ipc_close / ipc_free undo them. */
 int gpu_kernels_nvfp4_ipc_alloc(size_t bytes, void** ptr, void* handle64);

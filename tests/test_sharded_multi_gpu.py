@@ -71,6 +71,59 @@ def _worker(rank, world, port, out_dir):
         dist.destroy_process_group()
 
 
+def _peer_worker(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    from datetime import timedelta
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank),
+                            timeout=timedelta(seconds=60))
+    try:
+        import gpu_kernels_b200 as g
+        peers = g.PeerGroup(torch.device("cuda", rank), max_ints=300)
+        box = g.SharedBuffer(4 * 1024, torch.device("cuda", rank))
+        mine = torch.as_tensor(g.peer.DeviceView(box.own, (1024,), "<i4"), device="cuda")
+        theirs = [torch.as_tensor(g.peer.DeviceView(p, (1024,), "<i4"), device="cuda") for p in box.ptrs]
+        out = torch.empty((world, 300), dtype=torch.int32, device="cuda")
+        results = []
+        for i in range(200):                                  # no host synchronisation inside the loop
+            payload = torch.arange(300, dtype=torch.int32, device="cuda") + 1000 * rank + i
+            peers.all_gather_ints(payload, out)
+            # a plain store into every peer's buffer, then a barrier: the peers' values must be there after it
+            for r in range(world):
+                theirs[r][rank * 8:(rank + 1) * 8] = i + 1
+            peers.barrier()
+            results.append(mine[:world * 8].clone())
+            peers.barrier()                                   # nobody overwrites before everyone has read
+        torch.cuda.synchronize()
+        for i, seen in enumerate(results):
+            assert torch.equal(seen, torch.full((world * 8,), i + 1, dtype=torch.int32, device="cuda")), (rank, i)
+        # all-gather payloads, checked with synchronisation
+        for i in range(20):
+            n = 1 + (i * 37) % 300
+            payload = torch.arange(n, dtype=torch.int32, device="cuda") + 1000 * rank + i
+            gathered = torch.empty((world, n), dtype=torch.int32, device="cuda")
+            peers.all_gather_ints(payload, gathered)
+            torch.cuda.synchronize()
+            for r in range(world):
+                assert torch.equal(gathered[r].cpu(), torch.arange(n, dtype=torch.int32) + 1000 * r + i), (rank, i, r)
+        import ctypes
+        from gpu_kernels_b200 import _lib
+        assert _lib.load().gpu_kernels_nvfp4_validate(None) == 0
+        box.close()
+        peers.close()
+        open(os.path.join(out_dir, f"ok{rank}"), "w").close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_peer_barrier_and_gather_two_gpus(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world, port = 2, _free_port()
+    mp.spawn(_peer_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    assert all((tmp_path / f"ok{r}").exists() for r in range(world))
+
+
 def test_fused_gather_two_gpus(tmp_path):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
