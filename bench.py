@@ -36,7 +36,10 @@ WORKLOADS = {
     "gemm256": (256, 256, 256, 1.0),
 }
 # Routed-MoE expert layer (H=4096, I=2048, 256 experts, top-6), tokens PER GPU; experts are split over the ranks.
-MOE_WORKLOADS = {"moe_t1": 1, "moe_t64": 64, "moe_t1024": 1024, "moe_t4096": 4096}
+MOE_WORKLOADS = {"moe_t1": 1, "moe_t64": 64, "moe_t1024": 1024, "moe_t4096": 4096,
+                 # a quarter of the experts at the row count per expert of moe_t4096: small enough for an ncu capture
+                 "moe_t1024_e64": 1024}
+MOE_EXPERTS = {"moe_t1024_e64": 64}
 MOE_SHAPE = {"hidden": 4096, "inter": 2048, "experts": 256, "topk": 6, "clamp": 10.0}
 # Stand-alone quantise/pack kernel: (rows, K) of a bf16 operand.
 QUANT_WORKLOADS = {"quantise8192": (8192, 8192), "quantise16384": (16384, 16384), "quantise_skinny_b": (28672, 8192)}
@@ -425,6 +428,7 @@ def run_moe(args, rank, world, local_rank):
     dev = torch.device("cuda", local_rank)
     tokens = MOE_WORKLOADS[args.workload]
     H, I, E, topk, clamp = (MOE_SHAPE[k] for k in ("hidden", "inter", "experts", "topk", "clamp"))
+    E = MOE_EXPERTS.get(args.workload, E)
     local = E // world
     gen = torch.Generator(device=dev).manual_seed(rank)
     w1 = torch.empty((local, 2 * I, H), dtype=torch.bfloat16, device=dev)
@@ -533,9 +537,9 @@ def run_moe(args, rank, world, local_rank):
         "metric": "nvfp4_moe_tflops", "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "nvfp4 operands, f32 accumulate, bf16 activations and output", "data": "synthetic",
-        "config": {"workload": args.workload, "tokens_per_gpu": tokens, **MOE_SHAPE, "expert_parallel": world,
+        "config": {"workload": args.workload, "tokens_per_gpu": tokens, **{**MOE_SHAPE, "experts": E}, "expert_parallel": world,
                    "experts_touched_rank0": touched, "launch": "one CUDA graph per forward (Nvfp4MoE.capture)",
-                   "ms_per_step_eager": ms_eager / args.steps, "phases_us_rank0_eager": phases, "l2": "expert weights (3.6 GB per 256 experts) far exceed L2; inputs rotate over 4 sets"},
+                   "ms_per_step_eager": ms_eager / args.steps, "phases_us_rank0_eager": phases, "l2": f"expert weights ({E * 14.2e-3:.1f} GB for {E} experts) far exceed L2; inputs rotate over 4 sets"},
         "clocks": clocks,
         "e2e": {"value": flops / (e2e_ms / e2e_steps * 1e-3) / 1e12, "unit": UNIT,
                 "h2d_bytes_per_step": tokens * (H * 2 + topk * 12), "d2h_bytes_per_step": tokens * H * 2, "steps": e2e_steps,
