@@ -509,6 +509,8 @@ def run_moe(args, rank, world, local_rank):
     phases = {k_: round(v_, 1) for k_, v_ in layer.phase_times_us().items()}
     layer.phase_events = None
     touched = int((layer.counts_matrix.sum(0)[rank * local:(rank + 1) * local] > 0).sum().item())
+    del graph
+    layer.close()                                               # collective (unmaps the peers' buffers): every rank
     if rank != 0:
         return
     routes = world * tokens * topk
@@ -546,7 +548,6 @@ def run_moe(args, rank, world, local_rank):
                 "call": "Nvfp4MoE.forward on tensors copied from pinned host memory, result copied back"},
         "gpu_launches": int(launches), "roofline": roofline, "cpu_baseline": None,
     }))
-    layer.close()
 
 
 def main():

@@ -585,6 +585,20 @@ int gpu_kernels_nvfp4_moe_return_peer(const void* out_pool, const void* recv_row
     });
 }
 
+int gpu_kernels_nvfp4_moe_quantise_route(const void* x_bf16, const void* ids, const void* weights, int tokens, int topk,
+                                         int hidden, int experts, const void* offsets, void* cursor, void* const* peer_recv,
+                                         int world, int local_experts, int recv_capacity, void* error, void* pool_packed,
+                                         void* pool_scales, void* pool_weight, void* route_row, void* stream) {
+    return guarded([&] {
+        nvfp4_b200::moe_quantise_route(x_bf16, static_cast<const long long*>(ids), static_cast<const float*>(weights), tokens,
+                                       topk, hidden, experts, static_cast<const int*>(offsets), static_cast<int*>(cursor),
+                                       peer_recv, world, local_experts, recv_capacity, static_cast<int*>(error),
+                                       static_cast<uint8_t*>(pool_packed), static_cast<uint8_t*>(pool_scales),
+                                       static_cast<float*>(pool_weight), static_cast<int*>(route_row),
+                                       static_cast<cudaStream_t>(stream));
+    });
+}
+
 int gpu_kernels_nvfp4_peer_state_bytes(int world, int max_ints, size_t* bytes) {
     return guarded([&] {
         if (!bytes) throw std::invalid_argument("peer_state_bytes: null result pointer");

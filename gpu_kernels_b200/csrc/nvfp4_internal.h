@@ -77,6 +77,13 @@ void moe_swiglu_quant(const void* gate_up_bf16, const float* pool_weight, const 
                       int intermediate, float clamp, uint8_t* act_packed, uint8_t* act_scales, cudaStream_t stream);
 void moe_return_rows(const void* out_pool_bf16, const int* pool_of_recv, const int* totals, int capacity, int hidden,
                      void* return_rows_bf16, cudaStream_t stream);
+// Token quantisation fused with the dispatch: x [tokens, hidden] bf16 -> each route's quantised row delivered
+// to its expert, world > 0: into peer_recv[owner] at offsets[expert] + arrival order (bounds-checked against
+// recv_capacity); world == 0: into this rank's pool at row offsets[expert] + arrival order (route_row gets it).
+void moe_quantise_route(const void* x_bf16, const long long* ids, const float* weights, int tokens, int topk, int hidden,
+                        int experts, const int* offsets, int* cursor, void* const* peer_recv, int world, int local_experts,
+                        int recv_capacity, int* error, uint8_t* pool_packed, uint8_t* pool_scales, float* pool_weight,
+                        int* route_row, cudaStream_t stream);
 int moe_payload_bytes(int hidden);
 // The device's four status words: [0] bits of ptx.cuh's StatusBits, [1] first tag, [2] cycles of the last GEMM.
 uint32_t* device_status_word(int device);

@@ -188,7 +188,10 @@ __global__ void unpack_kernel(const uint8_t* __restrict__ recv_rows, const int* 
     const uint8_t* in = recv_rows + size_t(p) * payload_bytes(hidden);
     uint4* dst = reinterpret_cast<uint4*>(pool_packed + size_t(row) * (hidden / 2));
     for (int i = lane; i < hidden / 32; i += 32) dst[i] = reinterpret_cast<const uint4*>(in)[i];
-    for (int b = lane; b < hidden / 16; b += 32) pool_scales[scale_byte_offset(row, b, hidden)] = in[hidden / 2 + b];
+    // four scale bytes (64 K-values) are contiguous in the atom layout, and 4-byte aligned in the dispatch row
+    for (int q = lane; q < hidden / 64; q += 32)
+        *reinterpret_cast<uint32_t*>(pool_scales + scale_byte_offset(row, 4 * q, hidden)) =
+            *reinterpret_cast<const uint32_t*>(in + hidden / 2 + 4 * q);
     if (lane == 0) {
         pool_weight[row] = *reinterpret_cast<const float*>(in + hidden / 2 + hidden / 16);
         pool_of_recv[p] = row;
@@ -326,6 +329,67 @@ __global__ void pack_peer_kernel(const uint8_t* __restrict__ xq, const uint8_t* 
     if (lane == 0) {
         *reinterpret_cast<float*>(out + hidden / 2 + hidden / 16) = weights[route];
         *reinterpret_cast<int*>(out + hidden / 2 + hidden / 16 + 4) = route;       // where the result goes back to
+    }
+}
+
+// One CTA per token: quantise the token's row once (bf16 -> E2M1 codes + UE4M3 scale bytes, bit for bit what
+// quantise_kernel writes), keep it in shared memory as one dispatch row, and deliver it to the token's topk
+// experts: into the receive buffers of the ranks that own them (world > 0: peer stores over NVLink, each
+// bounds-checked), or straight into this rank's expert-major pool (world == 0). Replaces the stand-alone
+// quantiser, its padded input copy and the pack kernel: the quantised tokens never go through global memory.
+__global__ void __launch_bounds__(256)
+quantise_route_kernel(const __nv_bfloat16* __restrict__ x, const long long* __restrict__ ids,
+                      const float* __restrict__ weights, int topk, int hidden, int experts,
+                      const int* __restrict__ offsets, int* __restrict__ cursor,
+                      PeerBuffers recv, int world, int local_experts, int recv_capacity, int* __restrict__ error,
+                      uint8_t* __restrict__ pool_packed, uint8_t* __restrict__ pool_scales,
+                      float* __restrict__ pool_weight, int* __restrict__ route_row) {
+    extern __shared__ __align__(16) uint8_t row[];              // codes [hidden/2] | scale bytes [hidden/16] | int dst[topk]
+    const int token = blockIdx.x;
+    const int row_bytes = hidden / 2 + hidden / 16;
+    int* dst = reinterpret_cast<int*>(row + ((row_bytes + 15) & ~15));
+    const uint4* src = reinterpret_cast<const uint4*>(x + size_t(token) * hidden);
+    for (int b = threadIdx.x; b < hidden / 16; b += blockDim.x) {
+        const uint4 lo = __ldg(src + 2 * b), hi = __ldg(src + 2 * b + 1);
+        const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+        uint2 codes;
+        const uint32_t sbyte = quantise_block_pairs<Bf16Pairs>(w, codes);
+        *reinterpret_cast<uint2*>(row + b * 8) = codes;
+        row[hidden / 2 + b] = static_cast<uint8_t>(sbyte);
+    }
+    if (int(threadIdx.x) < topk) {
+        const long long e = ids[size_t(token) * topk + threadIdx.x];
+        dst[threadIdx.x] = (e >= 0 && e < experts) ? offsets[e] + atomicAdd(&cursor[e], 1) : -1;
+    }
+    __syncthreads();
+    for (int j = 0; j < topk; ++j) {
+        const int route = token * topk + j, d = dst[j];
+        if (world > 0) {
+            if (d < 0 || d >= recv_capacity) {
+                if (threadIdx.x == 0) atomicOr(error, 1);
+                continue;
+            }
+            const int owner = int(ids[route]) / local_experts;
+            uint8_t* out = static_cast<uint8_t*>(recv.ptr[owner]) + size_t(d) * payload_bytes(hidden);
+            for (int i = threadIdx.x; i < row_bytes / 16; i += blockDim.x)
+                reinterpret_cast<uint4*>(out)[i] = reinterpret_cast<const uint4*>(row)[i];
+            if (threadIdx.x == 0) {
+                *reinterpret_cast<float*>(out + row_bytes) = weights[route];
+                *reinterpret_cast<int*>(out + row_bytes + 4) = route;           // where the result goes back to
+            }
+        } else {
+            if (d < 0) continue;                                            // an id outside the expert range: dropped, as pack does not
+            uint4* packed = reinterpret_cast<uint4*>(pool_packed + size_t(d) * (hidden / 2));
+            for (int i = threadIdx.x; i < hidden / 32; i += blockDim.x) packed[i] = reinterpret_cast<const uint4*>(row)[i];
+            // four scale bytes (64 K-values) are contiguous in the atom layout
+            for (int q = threadIdx.x; q < hidden / 64; q += blockDim.x)
+                *reinterpret_cast<uint32_t*>(pool_scales + scale_byte_offset(d, 4 * q, hidden)) =
+                    *reinterpret_cast<const uint32_t*>(row + hidden / 2 + 4 * q);
+            if (threadIdx.x == 0) {
+                pool_weight[d] = weights[route];
+                route_row[route] = d;
+            }
+        }
     }
 }
 
@@ -475,6 +539,31 @@ void moe_return_peer(const void* out_pool_bf16, const uint8_t* recv_rows, const 
     return_peer_kernel<<<recv_capacity, 128, 0, stream>>>(static_cast<const uint4*>(out_pool_bf16), recv_rows, pool_of_recv,
                                                           totals, seg_src_offset, world * local_experts, local_experts,
                                                           hidden, slots, slot_capacity, error);
+    cuda_check(cudaGetLastError());
+}
+
+void moe_quantise_route(const void* x_bf16, const long long* ids, const float* weights, int tokens, int topk, int hidden,
+                        int experts, const int* offsets, int* cursor, void* const* peer_recv, int world, int local_experts,
+                        int recv_capacity, int* error, uint8_t* pool_packed, uint8_t* pool_scales, float* pool_weight,
+                        int* route_row, cudaStream_t stream) {
+    check_hidden(hidden, "moe quantise_route");
+    if (tokens <= 0) return;
+    if (topk < 1 || topk > 256 || experts < 1 || !x_bf16 || !ids || !weights || !offsets || !cursor)
+        throw std::invalid_argument("moe quantise_route: bad argument");
+    PeerBuffers recv{};
+    if (world > 0) {
+        if (world > 8 || !peer_recv || !error || local_experts < 1) throw std::invalid_argument("moe quantise_route: 1..8 ranks");
+        for (int r = 0; r < world; ++r) {
+            if (!peer_recv[r]) throw std::invalid_argument("moe quantise_route: null peer buffer");
+            recv.ptr[r] = peer_recv[r];
+        }
+    } else if (!pool_packed || !pool_scales || !pool_weight || !route_row) {
+        throw std::invalid_argument("moe quantise_route: null pool");
+    }
+    const size_t smem = ((size_t(hidden) / 2 + hidden / 16 + 15) & ~size_t(15)) + size_t(topk) * sizeof(int);
+    quantise_route_kernel<<<tokens, 256, smem, stream>>>(static_cast<const __nv_bfloat16*>(x_bf16), ids, weights, topk, hidden,
+                                                        experts, offsets, cursor, recv, world, local_experts, recv_capacity,
+                                                        error, pool_packed, pool_scales, pool_weight, route_row);
     cuda_check(cudaGetLastError());
 }
 

@@ -48,7 +48,7 @@ def exchange_splits(counts_matrix: torch.Tensor, rank: int, local_experts: int, 
 class Nvfp4MoE:
     def __init__(self, w1: torch.Tensor, w2: torch.Tensor, num_experts: int, topk: int, clamp: float = 10.0,
                  max_tokens: int = 4096, group=None, pool_rows: int | None = None, fused: bool = True,
-                 block_rows: int | None = None, exchange: str = "peer"):
+                 block_rows: int | None = None, exchange: str = "peer", fused_dispatch: bool = True):
         """w1 [E_local, 2I, H], w2 [E_local, H, I]: this rank's experts (bf16/fp16/fp32 CUDA tensors)."""
         if not (w1.is_cuda and w2.is_cuda):
             raise ValueError("expert weights must be CUDA tensors: this package has no CPU path")
@@ -87,6 +87,10 @@ class Nvfp4MoE:
         # block_rows: rows per pool block, 128 (single-CTA tiles) or 256 (CTA pairs); None = per call, 256 once
         # an expert sees about 160 rows or more
         self.block_rows = block_rows
+        # fused_dispatch: tokens are quantised inside the dispatch kernel (one CTA per token, row kept in shared
+        # memory, stored straight to the experts' ranks or into the pool) instead of by the stand-alone quantiser
+        # followed by a pack kernel. Same bits. Not for the all-to-all route, which packs a send buffer.
+        self.fused_dispatch = fused_dispatch
         worst = self.world * max_tokens * topk + self.local_experts * 255
         self.pool_rows = pool_rows if pool_rows is not None else -(-worst // 256) * 256
         if self.pool_rows % 256:
@@ -220,23 +224,49 @@ class Nvfp4MoE:
         weights = weights.contiguous().to(torch.float32)
         with torch.cuda.device(self.device):
             s = _stream()
-            # quantise the tokens once; rows are padded to whole 128-row scale atoms
+            fused_dispatch = self.fused_dispatch and (self.world == 1 or self._peer is not None) and x.dtype == torch.bfloat16
             self._mark("start")
-            self.x_pad[:tokens].copy_(x)
-            xq, xs = quantize(self.x_pad)
-            self._mark("quantise tokens")
+            if not fused_dispatch:
+                # quantise the tokens once; rows are padded to whole 128-row scale atoms
+                self.x_pad[:tokens].copy_(x)
+                xq, xs = quantize(self.x_pad)
+                self._mark("quantise tokens")
             # rows an expert of this rank sees on average decide the block size (and with it single CTAs or pairs)
             block_rows = self.block_rows or (256 if tokens * self.topk * self.world >= 160 * self.experts else 128)
             fc1, fc2 = self._plans[block_rows]
             send_splits, recv_splits = self._metadata(ids, tokens, block_rows)
             self._mark("metadata (counts, all-gather, plan, host split sizes)")
+            if fused_dispatch and self.world > 1 and send_splits is not None:
+                # a pool below the worst case sends this call through the all-to-all route, which packs a send buffer
+                fused_dispatch = False
+                self.x_pad[:tokens].copy_(x)
+                xq, xs = quantize(self.x_pad)
             self.cursor.zero_()
             self.pool_scales.zero_()
             self.pool_weight.zero_()
             if self._peer is not None:
                 self.pool_dst.zero_()
             total_recv = sum(recv_splits) if recv_splits is not None else 0
-            if self.world > 1 and send_splits is None:
+            if fused_dispatch and (self.world == 1 or send_splits is None):
+                x = x.contiguous()
+                peer = self.world > 1
+                _lib.check(lib.gpu_kernels_nvfp4_moe_quantise_route(
+                    x.data_ptr(), ids.data_ptr(), weights.data_ptr(), tokens, self.topk, self.hidden, self.experts,
+                    (self.peer_offset if peer else self.seg_pool).data_ptr(), self.cursor.data_ptr(),
+                    self._peer["recv"].table if peer else None, self.world if peer else 0, self.local_experts,
+                    self.recv_cap, self.peer_error.data_ptr() if peer else None,
+                    None if peer else self.pool_packed.data_ptr(), None if peer else self.pool_scales.data_ptr(),
+                    None if peer else self.pool_weight.data_ptr(), None if peer else self.send_pos.data_ptr(), s))
+                if peer:
+                    self._mark("quantise + pack into the peers' receive buffers")
+                    self._barrier()
+                    self._mark("barrier")
+                    _lib.check(lib.gpu_kernels_nvfp4_moe_unpack(
+                        self.recv_ptr, self.recv_cap, self.totals.data_ptr(), self.world, self.local_experts,
+                        self.hidden, self.seg_src.data_ptr(), self.seg_pool.data_ptr(), self.pool_packed.data_ptr(),
+                        self.pool_scales.data_ptr(), self.pool_weight.data_ptr(), self.pool_of_recv.data_ptr(),
+                        self.pool_dst.data_ptr(), s))
+            elif self.world > 1 and send_splits is None:
                 _lib.check(lib.gpu_kernels_nvfp4_moe_pack_peer(
                     xq.data_ptr(), xs.data_ptr(), ids.data_ptr(), weights.data_ptr(), tokens, self.topk, self.hidden,
                     self.world, self.local_experts, self.peer_offset.data_ptr(), self.cursor.data_ptr(),

@@ -196,6 +196,16 @@ int gpu_kernels_nvfp4_gemm_host_static(int M, int N, int K, const void* A, const
  * Every peer write is bounds-checked against the capacities (rows); a violation sets *error (device int)
  * and skips the write. The caller must put a stream-ordered collective between pack_peer and unpack, and
  * between return_peer and reduce (and nothing here waits on another GPU). */
+/* Token quantisation fused with the dispatch (one CTA per token; replaces quantize + pack_peer, or quantize +
+ * pack_to_pool, with the same bits): x [tokens, hidden] bf16 is quantised row by row in shared memory and each
+ * route's row (codes, scale bytes, weight, route index) goes straight to its expert. world > 0: into
+ * peer_recv[expert / local_experts] (host array of `world` device pointers) at row offsets[expert] + arrival
+ * order, refused and flagged in `error` beyond recv_capacity. world == 0: into this rank's pool (packed rows,
+ * VEC16 scale atoms, weights) at row offsets[expert] + arrival order, which route_row [tokens * topk] records. */
+int gpu_kernels_nvfp4_moe_quantise_route(const void* x_bf16, const void* ids, const void* weights, int tokens, int topk,
+                                         int hidden, int experts, const void* offsets, void* cursor, void* const* peer_recv,
+                                         int world, int local_experts, int recv_capacity, void* error, void* pool_packed,
+                                         void* pool_scales, void* pool_weight, void* route_row, void* stream);
 int gpu_kernels_nvfp4_moe_pack_peer(const void* xq, const void* xs, const void* ids, const void* weights, int tokens,
                                     int topk, int hidden, int world, int local_experts, const void* peer_offset,
                                     void* cursor, void* const* peer_recv, int recv_capacity, void* error, void* stream);

@@ -172,6 +172,30 @@ def test_captured_forward_replays_exactly(g):
     small.close()
 
 
+def test_fused_dispatch_matches_quantise_then_pack(g):
+    # tokens quantised inside the dispatch kernel (one CTA per token) against the stand-alone quantiser
+    # followed by the pack kernel: the same pool rows, hence the same output bits
+    for tokens, hidden, inter, experts, topk, skew in ((300, 512, 256, 8, 2, False), (64, 1024, 256, 16, 6, True), (1, 512, 256, 4, 2, False)):
+        x, logits, w1, w2 = make_layer(21 + tokens, tokens, hidden, inter, experts, topk, skew)
+        ids, wts = g.route(logits, topk)
+        outs, pools = [], []
+        for fused_dispatch in (True, False):
+            layer = g.Nvfp4MoE(w1, w2, experts, topk, max_tokens=512, fused_dispatch=fused_dispatch)
+            outs.append(layer(x, ids, wts).clone())
+            torch.cuda.synchronize()
+            rows = int(layer.totals[1].item())
+            weight = layer.pool_weight[:rows].cpu().numpy()
+            order = np.lexsort((to_np(layer.pool_packed[:rows]).view(np.uint8)[:, 0], weight))
+            pools.append((to_np(layer.pool_packed[:rows])[order], O.unpack_scales_u8(to_np(layer.pool_scales), layer.pool_rows, hidden)[:rows][order], weight[order]))
+            layer.check()
+            layer.close()
+        assert torch.equal(outs[0], outs[1]), (tokens, hidden)
+        # the pools hold the same rows (the order inside an expert's group is arrival order)
+        assert np.array_equal(pools[0][2], pools[1][2])
+        real = pools[0][2] != 0
+        assert np.array_equal(pools[0][1][real], pools[1][1][real])
+
+
 def test_routing_plan_pack_unpack_exact(g):
     tokens, hidden, inter, experts, topk = 150, 512, 256, 8, 3
     x, logits, w1, w2 = make_layer(5, tokens, hidden, inter, experts, topk, skew=True)

@@ -33,9 +33,9 @@ def _worker(rank, world, port, out_dir):
         w1 = (torch.randn((experts, 2 * inter, hidden), generator=gen, device="cuda") * 0.02).bfloat16()
         w2 = (torch.randn((experts, hidden, inter), generator=gen, device="cuda") * 0.02).bfloat16()
         outputs = {}
-        for exchange in ("peer", "nccl"):
+        for exchange, fused_dispatch in (("peer", True), ("peer", False), ("nccl", False)):
             layer = g.Nvfp4MoE(w1[rank * local:(rank + 1) * local], w2[rank * local:(rank + 1) * local], experts, topk,
-                               max_tokens=128, exchange=exchange)
+                               max_tokens=128, exchange=exchange, fused_dispatch=fused_dispatch)
             for call, tokens in enumerate((50 + 30 * rank, 7, 128)):               # ragged token counts; the last call uses 256-row blocks
                 gen_r = torch.Generator(device="cuda").manual_seed(1000 * call + rank)
                 x = torch.randn((tokens, hidden), generator=gen_r, device="cuda").bfloat16()
@@ -49,8 +49,8 @@ def _worker(rank, world, port, out_dir):
                 rel = np.linalg.norm(got - ref) / np.linalg.norm(ref)
                 assert not np.isnan(got).any() and rel <= 2e-2, f"rank {rank} {exchange} call {call}: rel {rel:.3e}"
                 # both exchanges deliver the same rows and the reduce adds them in the same order: identical bits
-                assert np.array_equal(outputs.setdefault(call, got), got), f"rank {rank} call {call}: peer != nccl"
-            if exchange == "peer":
+                assert np.array_equal(outputs.setdefault(call, got), got), f"rank {rank} call {call}: {exchange} fused_dispatch={fused_dispatch} differs"
+            if exchange == "peer" and fused_dispatch:
                 # the same forward, collectives and peer stores included, replayed from a CUDA graph
                 gx, gids, gwts, gy, graph = layer.capture(tokens)
                 for _ in range(2):
