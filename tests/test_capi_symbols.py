@@ -57,3 +57,38 @@ def test_host_layer_rejects_cpu_tensors():
         g.quantize(torch.zeros(128, 64))
     with pytest.raises(ValueError):
         g.Nvfp4Gemm(*(torch.zeros(128, 128, dtype=torch.uint8),) * 2, *(torch.zeros(2048, dtype=torch.uint8),) * 2)
+
+
+BRIDGE_LIKE_CONSUMER = r"""
+// What a host written against the reference's include/nvfp4.h does with it (benchmarks/bindings/
+// nvfp4_bridge.cu:19-21, 83-85, 115 in the reference): value-initialise the params, fetch the
+// implementation, call prepare / launch / validate through the function pointers.
+#include "nvfp4.h"
+#include "nvfp4_capi.h"
+struct Plan {
+    gpu_kernels::Nvfp4Params params{};
+    gpu_kernels::Nvfp4Implementation impl{};
+};
+int run(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb, __half* c, int m, int n, int k,
+        cudaStream_t stream) {
+    Plan plan;
+    plan.impl = gpu_kernels::nvfp4_sm100_implementation();
+    plan.impl.prepare(plan.params, a, b, sfa, sfb, m, n, k, stream);
+    plan.impl.launch(plan.params, c, stream);
+    plan.impl.validate();
+    static_assert(offsetof(gpu_kernels::Nvfp4Params, A) == 0, "the tensor maps lead the struct");
+    static_assert(offsetof(gpu_kernels::Nvfp4Params, M) == 4 * sizeof(CUtensorMap), "then M, N, K, clusters");
+    return plan.params.M + plan.params.N + plan.params.K + plan.params.clusters + gpu_kernels_nvfp4_l2_bytes();
+}
+"""
+
+
+def test_headers_compile_for_a_reference_style_host(tmp_path):
+    import shutil
+    import subprocess
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    src = tmp_path / "consumer.cu"
+    src.write_text("#include <cstddef>\n" + BRIDGE_LIKE_CONSUMER)
+    done = subprocess.run([nvcc, "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-I", str(ROOT / "include"),
+                           "-c", str(src), "-o", str(tmp_path / "consumer.o")], capture_output=True, text=True)
+    assert done.returncode == 0, done.stderr
