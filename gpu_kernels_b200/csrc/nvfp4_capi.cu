@@ -12,6 +12,7 @@
 #include <cstring>
 #include <memory>
 #include <mutex>
+#include <vector>
 #include <string>
 
 namespace nvfp4_b200 {
@@ -130,10 +131,22 @@ struct HostGemm {
     uint8_t *A = nullptr, *B = nullptr, *SFA = nullptr, *SFB = nullptr;
     __half* C = nullptr;
     Plan plan;
+    // Row pieces of the product, so that the copy of one piece's result to the host overlaps the next
+    // piece's operand copy and kernel (the two directions of the host link run at the same time).
+    std::vector<gpu_kernels::Nvfp4Params> pieces;
+    int piece_rows = 0;
+    cudaStream_t out_stream = nullptr;
+    std::vector<cudaEvent_t> piece_done;
     void release() {
         for (void* p : {static_cast<void*>(A), static_cast<void*>(B), static_cast<void*>(SFA), static_cast<void*>(SFB),
                         static_cast<void*>(C)})
             if (p) cudaFree(p);
+        for (cudaEvent_t e : piece_done) cudaEventDestroy(e);
+        if (out_stream) cudaStreamDestroy(out_stream);
+        piece_done.clear();
+        pieces.clear();
+        out_stream = nullptr;
+        piece_rows = 0;
         A = B = SFA = SFB = nullptr;
         C = nullptr;
         M = N = K = 0;
@@ -344,15 +357,44 @@ int gpu_kernels_nvfp4_gemm_host(int M, int N, int K, const void* A, const void* 
             cuda_check(cudaMalloc(&h.C, c_bytes));
             h.plan.impl = gpu_kernels::nvfp4_sm100_implementation();
             h.plan.impl.prepare(h.plan.params, h.A, h.B, h.SFA, h.SFB, M, N, K, stream);
+            // large products go in 4 (or 2) row pieces of whole 256-row tiles
+            const int count = (M >= 2048 && M % 1024 == 0) ? 4 : (M >= 1024 && M % 512 == 0) ? 2 : 1;
+            if (count > 1) {
+                h.piece_rows = M / count;
+                h.pieces.resize(count);
+                h.piece_done.resize(count);
+                cuda_check(cudaStreamCreateWithFlags(&h.out_stream, cudaStreamNonBlocking));
+                for (int i = 0; i < count; ++i) {
+                    const size_t row0 = size_t(i) * h.piece_rows;
+                    h.plan.impl.prepare(h.pieces[i], h.A + row0 * K / 2, h.B, h.SFA + row0 * K / 16, h.SFB, h.piece_rows, N, K, stream);
+                    cuda_check(cudaEventCreateWithFlags(&h.piece_done[i], cudaEventDisableTiming));
+                }
+            }
             h.M = M; h.N = N; h.K = K;
         }
-        h.plan.params.alpha = alpha;
-        cuda_check(cudaMemcpyAsync(h.A, A, a_bytes, cudaMemcpyHostToDevice, stream));
         cuda_check(cudaMemcpyAsync(h.B, B, b_bytes, cudaMemcpyHostToDevice, stream));
-        cuda_check(cudaMemcpyAsync(h.SFA, SFA, sfa_bytes, cudaMemcpyHostToDevice, stream));
         cuda_check(cudaMemcpyAsync(h.SFB, SFB, sfb_bytes, cudaMemcpyHostToDevice, stream));
-        h.plan.impl.launch(h.plan.params, h.C, stream);
-        cuda_check(cudaMemcpyAsync(C, h.C, c_bytes, cudaMemcpyDeviceToHost, stream));
+        cuda_check(cudaMemcpyAsync(h.SFA, SFA, sfa_bytes, cudaMemcpyHostToDevice, stream));
+        if (h.pieces.empty()) {
+            h.plan.params.alpha = alpha;
+            cuda_check(cudaMemcpyAsync(h.A, A, a_bytes, cudaMemcpyHostToDevice, stream));
+            h.plan.impl.launch(h.plan.params, h.C, stream);
+            cuda_check(cudaMemcpyAsync(C, h.C, c_bytes, cudaMemcpyDeviceToHost, stream));
+            cuda_check(cudaStreamSynchronize(stream));
+            return;
+        }
+        const size_t a_piece = size_t(h.piece_rows) * K / 2, c_piece = size_t(h.piece_rows) * N;      // bytes, elements
+        for (size_t i = 0; i < h.pieces.size(); ++i) {
+            h.pieces[i].alpha = alpha;
+            cuda_check(cudaMemcpyAsync(h.A + i * a_piece, static_cast<const uint8_t*>(A) + i * a_piece, a_piece,
+                                       cudaMemcpyHostToDevice, stream));
+            h.plan.impl.launch(h.pieces[i], h.C + i * c_piece, stream);
+            cuda_check(cudaEventRecord(h.piece_done[i], stream));
+            cuda_check(cudaStreamWaitEvent(h.out_stream, h.piece_done[i], 0));
+            cuda_check(cudaMemcpyAsync(static_cast<__half*>(C) + i * c_piece, h.C + i * c_piece, c_piece * 2,
+                                       cudaMemcpyDeviceToHost, h.out_stream));
+        }
+        cuda_check(cudaStreamSynchronize(h.out_stream));
         cuda_check(cudaStreamSynchronize(stream));
     });
 }

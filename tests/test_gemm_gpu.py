@@ -183,6 +183,23 @@ def test_host_entry_point(g):
     assert_gemm_close(out, O.gemm_f32(to_np(pa), to_np(sa), to_np(pb), to_np(sb)), "host entry point")
 
 
+@pytest.mark.parametrize("m,n,k", [(2048, 512, 512), (1024, 384, 768), (4096, 256, 256)])
+def test_host_entry_point_in_row_pieces(g, m, n, k):
+    # large M: the host entry point computes and copies back in 4 (or 2) row pieces on two streams; against
+    # one plan over the whole product (tiles start their K walk elsewhere, so single FP16 roundings may
+    # differ) and the FP32 reference, also on a second call with other operands
+    for seed in (71, 72):
+        pa, sa = g.quantize(random_operand(m, k, seed=seed))
+        pb, sb = g.quantize(random_operand(n, k, seed=seed + 10, scale=0.02))
+        host = [t.cpu().pin_memory() for t in (pa, pb, sa, sb)]
+        out = torch.full((m, n), float("nan"), dtype=torch.float16).pin_memory()
+        g.gemm_host(*host, out, alpha=0.5)
+        whole, _ = run_plan(g, pa, sa, pb, sb, alpha=0.5)
+        assert not torch.isnan(out).any()
+        assert (out == whole.cpu()).float().mean() > 0.99, (m, n, k, seed)
+        assert_gemm_close(out, 0.5 * fp32_reference_on_gpu(g, pa, sa, pb, sb), f"host pieces {m}x{n}x{k}")
+
+
 def test_argument_errors(g):
     from gpu_kernels_b200._lib import Nvfp4Error
     z = lambda *s: torch.zeros(*s, dtype=torch.uint8, device="cuda")
