@@ -38,8 +38,8 @@ WORKLOADS = {
 # Routed-MoE expert layer (H=4096, I=2048, 256 experts, top-6), tokens PER GPU; experts are split over the ranks.
 MOE_WORKLOADS = {"moe_t1": 1, "moe_t64": 64, "moe_t1024": 1024, "moe_t4096": 4096,
                  # a quarter of the experts at the row count per expert of moe_t4096: small enough for an ncu capture
-                 "moe_t1024_e64": 1024}
-MOE_EXPERTS = {"moe_t1024_e64": 64}
+                 "moe_t1024_e64": 1024, "moe_t4096_e64": 4096}
+MOE_EXPERTS = {"moe_t1024_e64": 64, "moe_t4096_e64": 64}
 MOE_SHAPE = {"hidden": 4096, "inter": 2048, "experts": 256, "topk": 6, "clamp": 10.0}
 # Stand-alone quantise/pack kernel: (rows, K) of a bf16 operand.
 QUANT_WORKLOADS = {"quantise8192": (8192, 8192), "quantise16384": (16384, 16384), "quantise_skinny_b": (28672, 8192)}
