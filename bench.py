@@ -49,7 +49,9 @@ NOMINAL_FP4_TFLOPS = 9000.0
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of nvfp4_gemm_kernel, from the
 # ncu captures summarised under profiles/ (None until a capture of that workload exists).
-NCU_DRAM_BYTES_PER_LAUNCH = {"gemm8192": 226_928_896, "gemm16384": None, "skinny": None}
+NCU_DRAM_BYTES_PER_LAUNCH = {"gemm8192": 226_928_896, "gemm16384": None, "skinny": 136_602_624,
+                             # quantise_kernel<bf16>: part of the output was still in L2 when the capture ended
+                             "quantise8192": 155_176_960}
 
 
 def algorithmic_bytes(m, n, k):
@@ -405,6 +407,21 @@ def run_quantise(args, rank, world, local_rank):
     alg = rows * k * 2 + rows * k // 2 + rows * k // 16
     gbs = alg / (ms * 1e-3) / 1e9
     peaks = measured_peaks()
+    cpu = None
+    if not args.no_cpu:
+        # the same operand through the CPU restatement of the reference's quantiser (numpy, one thread),
+        # on a bounded sample of its rows
+        from oracle import nvfp4_oracle as O
+        sample_rows = 128
+        while sample_rows * 2 <= rows and sample_rows * k < (1 << 24):
+            sample_rows *= 2
+        host = xs[0][:sample_rows].float().cpu().numpy()
+        O.quantize(host[:128])
+        t0 = time.perf_counter()
+        O.quantize(host)
+        dt = time.perf_counter() - t0
+        cpu = {"value": (alg * sample_rows / rows) / dt / 1e9, "unit": "GB/s", "cores": 1, "kind": "port",
+               "sample": f"rows 0..{sample_rows - 1} of the operand ({sample_rows}x{k}), {dt:.1f} s"}
     print(json.dumps({
         "metric": "nvfp4_quantise_gbs", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
         "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -413,8 +430,39 @@ def run_quantise(args, rank, world, local_rank):
         "gpu_launches": int(_lib.launch_count() - n0),
         "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
                      "peak_source": f"{peaks['source']} copy bandwidth", "kernel": "quantise_kernel<bf16>",
-                     "algorithmic_bytes_per_launch": alg, "traffic": None},
-        "cpu_baseline": None, "e2e": None}))
+                     "algorithmic_bytes_per_launch": alg, "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(args.workload)},
+        "cpu_baseline": cpu, "e2e": None}))
+
+
+def moe_cpu_baseline(layer, g, sample, hidden, inter, topk, clamp):
+    """The reference's CPU statement of the layer (moe_forward: FP32 matmuls with its bf16 rounding points) on the
+    dequantised expert weights, for the first tokens of one input set."""
+    import numpy as np
+    from oracle import moe_oracle as MO
+    x, ids, wts = sample
+    count = min(2, x.shape[0])
+    x, ids, wts = x[:count].float().cpu().numpy(), ids[:count].cpu().numpy(), wts[:count].cpu().numpy()
+    used = np.unique(ids)
+    two_i = 2 * inter
+    w1 = np.empty((len(used), two_i, hidden), np.float32)
+    w2 = np.empty((len(used), hidden, inter), np.float32)
+    for i, e in enumerate(used):
+        r0 = int(e) * two_i
+        d = g.dequantize(layer.w1q[r0:r0 + two_i], layer.w1s[r0 * hidden // 16:(r0 + two_i) * hidden // 16])
+        if layer.fused:                                         # rows are stored 16 gate / 16 up interleaved
+            d = d.reshape(inter // 16, 2, 16, hidden).permute(1, 0, 2, 3).reshape(two_i, hidden)
+        w1[i] = d.cpu().numpy()
+        r0 = int(e) * hidden
+        w2[i] = g.dequantize(layer.w2q[r0:r0 + hidden], layer.w2s[r0 * inter // 16:(r0 + hidden) * inter // 16]).cpu().numpy()
+    local_ids = np.searchsorted(used, ids)
+    MO.moe_forward(x[:1], local_ids[:1], wts[:1], w1, w2, clamp)
+    t0 = time.perf_counter()
+    MO.moe_forward(x, local_ids, wts, w1, w2, clamp)
+    dt = time.perf_counter() - t0
+    flops = count * topk * 2.0 * (two_i * hidden + hidden * inter)
+    return {"value": flops / dt / 1e12, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
+            "sample": f"the first {count} token(s) of one input set ({count * topk} routes, {len(used)} experts) through "
+                      f"moe_forward on the dequantised weights, numpy BLAS threads, {dt:.3f} s"}
 
 
 def run_moe(args, rank, world, local_rank):
@@ -509,6 +557,9 @@ def run_moe(args, rank, world, local_rank):
     phases = {k_: round(v_, 1) for k_, v_ in layer.phase_times_us().items()}
     layer.phase_events = None
     touched = int((layer.counts_matrix.sum(0)[rank * local:(rank + 1) * local] > 0).sum().item())
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cpu = moe_cpu_baseline(layer, g, sets[0], H, I, topk, clamp)
     del graph
     layer.close()                                               # collective (unmaps the peers' buffers): every rank
     if rank != 0:
@@ -546,7 +597,7 @@ def run_moe(args, rank, world, local_rank):
         "e2e": {"value": flops / (e2e_ms / e2e_steps * 1e-3) / 1e12, "unit": UNIT,
                 "h2d_bytes_per_step": tokens * (H * 2 + topk * 12), "d2h_bytes_per_step": tokens * H * 2, "steps": e2e_steps,
                 "call": "Nvfp4MoE.forward on tensors copied from pinned host memory, result copied back"},
-        "gpu_launches": int(launches), "roofline": roofline, "cpu_baseline": None,
+        "gpu_launches": int(launches), "roofline": roofline, "cpu_baseline": cpu,
     }))
 
 

@@ -52,7 +52,7 @@ constexpr int SMEM_LIMIT = 232448;  // 227 KiB opt-in maximum per CTA
 // [2] SM cycles the first CTA of the most recent GEMM launch was resident (diagnostic).
 __device__ uint32_t g_status[4];
 
-template <int CG, int UN>
+template <int CG, int UN, bool RS = false>
 struct Config {
     static_assert(CG == 1 || CG == 2, "cta group");
     static_assert(UN == 128 || UN == 256, "tile width");
@@ -72,7 +72,12 @@ struct Config {
     // Single-CTA tiles write C straight from registers, so they keep no staging and get a deeper
     // ring instead (their workloads stream weights from HBM and live on bytes in flight).
     static constexpr bool STAGED_EPILOGUE = CG == 2;
-    static constexpr int EPI_BYTES = STAGED_EPILOGUE ? 4 * 2 * EPI_WARP_BYTES : 0;   // 4 warps, double-buffered
+    // RS (row staging, the scatter epilogue of the second expert GEMM): instead of two 32 x 64 chunk buffers
+    // per warp, every epilogue warp keeps its 32 whole rows of the tile (UN columns, 16 bytes of padding per
+    // row so that a quarter-warp's 16-byte stores cover all banks); the ring gives up a stage for it.
+    static constexpr bool ROW_STAGING = RS;
+    static constexpr int ROW_PITCH = UN * 2 + 16;
+    static constexpr int EPI_BYTES = RS ? 4 * 32 * ROW_PITCH : STAGED_EPILOGUE ? 4 * 2 * EPI_WARP_BYTES : 0;
     static constexpr int CTRL_BYTES = 1024;
     static constexpr int STAGES = (SMEM_LIMIT - 1024 - CTRL_BYTES - EPI_BYTES) / STAGE_BYTES;
     static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + CTRL_BYTES;
@@ -219,9 +224,9 @@ __device__ __forceinline__ void tile_coords(int t, const GemmArgs& g, int& tm, i
     tn = (band & 1) ? g.tiles_n - 1 - c : c;
 }
 
-template <int CG, int UN>
+template <int CG, int UN, bool RS = false>
 struct Roles {
-    using Cfg = Config<CG, UN>;
+    using Cfg = Config<CG, UN, RS>;
 
     uint32_t smem;            // 1024-aligned shared-window address of stage 0
     Control* ctrl;
@@ -584,22 +589,15 @@ struct Roles {
                         static_cast<uint16_t>(sb[0] | (sb[1] << 8));
                     continue;
                 }
-                if (Cfg::STAGED_EPILOGUE && g.row_dst) {
-                    // Scatter through shared memory: every lane stages the 128 bytes of its own row (rows 144
-                    // bytes apart, so that a quarter-warp's 16-byte stores cover all banks) and sends them with
-                    // one bulk copy to the row's destination. Over NVLink this makes 128-byte writes instead of
-                    // the 32-byte ones of register stores, and the warp does not wait for them. Bulk groups are
-                    // per thread and each lane touches only its own row: no warp synchronisation is needed.
-                    const int code = __ldg(g.row_dst + row0 + lane);
-                    const int slot = (code & 0xFFFFFF) - 1, owner = code >> 24;
-                    bool deliver = slot >= 0;
-                    if (deliver && (slot >= g.slot_rows || owner >= g.world)) {
-                        atomicOr(g.status, uint32_t(STATUS_BAD_ARGUMENT));
-                        deliver = false;
-                    }
-                    const uint32_t buf = stage_base + lane * 144;
-                    static_assert(32 * 144 <= 2 * Cfg::EPI_WARP_BYTES || !Cfg::STAGED_EPILOGUE, "row staging");
-                    tma_store_wait_read<0>();                     // this lane's previous copy has read its row
+                if constexpr (Cfg::ROW_STAGING) {
+                    // Scatter through shared memory: every lane stages its own row of the tile, chunk by chunk,
+                    // and after the last chunk sends the UN columns (512 bytes) with ONE bulk copy to the row's
+                    // destination. Over NVLink this makes 512-byte writes (register stores make 32-byte ones,
+                    // which took 381 us for FC2 at 4096 tokens per GPU on two GPUs; one 128-byte copy per chunk
+                    // took 233 us), and the warp does not wait for them. Bulk groups are per thread and each
+                    // lane touches only its own row: no warp synchronisation is needed.
+                    const uint32_t rowbuf = smem + Cfg::STAGES * Cfg::STAGE_BYTES + uint32_t(warp * 32 + lane) * Cfg::ROW_PITCH;
+                    if (c == 0) tma_store_wait_read<0>();         // this lane's copy of the previous tile has read the row
                     #pragma unroll
                     for (int q = 0; q < EPI_COLS / 8; ++q) {
                         uint32_t h[4];
@@ -616,14 +614,20 @@ struct Roles {
                             }
                         }
                         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
-                                     :: "r"(buf + q * 16), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]) : "memory");
+                                     :: "r"(rowbuf + chunk * (EPI_COLS * 2) + q * 16), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]) : "memory");
                     }
-                    fence_async_smem();
-                    if (deliver && !(g.debug & 1u)) {
-                        uint16_t* dst = reinterpret_cast<uint16_t*>(__ldg(reinterpret_cast<const unsigned long long*>(g.slots) + owner)) +
-                                        size_t(slot) * g.ldc + col0 + chunk * EPI_COLS;
-                        bulk_store(dst, buf, EPI_COLS * 2);
-                        tma_store_commit();
+                    if (c == UN / EPI_COLS - 1) {
+                        fence_async_smem();
+                        const int code = g.row_dst ? __ldg(g.row_dst + row0 + lane) : 0;
+                        const int slot = (code & 0xFFFFFF) - 1, owner = code >> 24;
+                        if (slot >= 0 && (slot >= g.slot_rows || owner >= g.world)) {
+                            atomicOr(g.status, uint32_t(STATUS_BAD_ARGUMENT));
+                        } else if (slot >= 0 && !(g.debug & 1u)) {   // slot < 0: a padding row, nothing to deliver
+                            uint16_t* dst = reinterpret_cast<uint16_t*>(__ldg(reinterpret_cast<const unsigned long long*>(g.slots) + owner)) +
+                                            size_t(slot) * g.ldc + col0;
+                            bulk_store(dst, rowbuf, UN * 2);
+                            tma_store_commit();
+                        }
                     }
                     continue;
                 }
@@ -707,12 +711,12 @@ struct Roles {
     }
 };
 
-template <int CG, int UN>
+template <int CG, int UN, bool RS = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB,
                   const __grid_constant__ CUtensorMap tmC, const GemmArgs g) {
-    using Cfg = Config<CG, UN>;
+    using Cfg = Config<CG, UN, RS>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t smem = (raw + 1023u) & ~1023u;
@@ -744,7 +748,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     tc_fence_after_sync();
     const uint32_t tmem = ctrl->tmem_base;
 
-    Roles<CG, UN> roles{smem, ctrl, rank,
+    Roles<CG, UN, RS> roles{smem, ctrl, rank,
                         CG == 2 ? blockIdx.x / 2u : blockIdx.x, gridDim.x / CG,
                         uint32_t(g.block_expert ? __ldg(g.num_blocks) : g.tiles_m) * uint32_t(g.tiles_n),
                         CG == 2 ? map_to_cta(smem_u32(const_cast<uint32_t*>(&ctrl->wait.abort)), rank ^ 1u) : 0u, g};
@@ -828,12 +832,12 @@ int env_int(const char* name, int fallback) {
     return v && *v ? std::atoi(v) : fallback;
 }
 
-template <int CG, int UN>
+template <int CG, int UN, bool RS = false>
 int max_units(int device) {
-    using Cfg = Config<CG, UN>;
+    using Cfg = Config<CG, UN, RS>;
     static int cached[64] = {};
     if (device < 64 && cached[device]) return cached[device];
-    auto kernel = nvfp4_gemm_kernel<CG, UN>;
+    auto kernel = nvfp4_gemm_kernel<CG, UN, RS>;
     cuda_check(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
     int sms = 0;
     cuda_check(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
@@ -1127,11 +1131,14 @@ void grouped_launch_fused(const GroupedGemm& p, void* C, int out_bf16, uint8_t* 
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(unsigned(p.units) * cg);
     cfg.blockDim = dim3(NUM_THREADS);
-    cfg.dynamicSmemBytes = cg == 2 ? Config<2, 256>::SMEM_BYTES : Config<1, 256>::SMEM_BYTES;
+    const bool row_staging = cg == 2 && row_dst != nullptr;
+    if (row_staging) (void)max_units<2, 256, true>(p.device);              // sets that instance's shared-memory limit once
+    cfg.dynamicSmemBytes = row_staging ? Config<2, 256, true>::SMEM_BYTES : cg == 2 ? Config<2, 256>::SMEM_BYTES : Config<1, 256>::SMEM_BYTES;
     cfg.stream = stream;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    if (cg == 2) cuda_check(cudaLaunchKernelEx(&cfg, nvfp4_gemm_kernel<2, 256>, p.A, p.B, p.SFA, p.SFB, tmC, g));
+    if (row_staging) cuda_check(cudaLaunchKernelEx(&cfg, nvfp4_gemm_kernel<2, 256, true>, p.A, p.B, p.SFA, p.SFB, tmC, g));
+    else if (cg == 2) cuda_check(cudaLaunchKernelEx(&cfg, nvfp4_gemm_kernel<2, 256>, p.A, p.B, p.SFA, p.SFB, tmC, g));
     else cuda_check(cudaLaunchKernelEx(&cfg, nvfp4_gemm_kernel<1, 256>, p.A, p.B, p.SFA, p.SFB, tmC, g));
     g_launches.fetch_add(1, std::memory_order_relaxed);
 }
