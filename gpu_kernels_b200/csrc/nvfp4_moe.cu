@@ -361,36 +361,45 @@ quantise_route_kernel(const __nv_bfloat16* __restrict__ x, const long long* __re
         const long long e = ids[size_t(token) * topk + threadIdx.x];
         dst[threadIdx.x] = (e >= 0 && e < experts) ? offsets[e] + atomicAdd(&cursor[e], 1) : -1;
     }
+    ptx::fence_async_smem();                                    // the row, written above, is read by bulk copies below
     __syncthreads();
-    for (int j = 0; j < topk; ++j) {
-        const int route = token * topk + j, d = dst[j];
-        if (world > 0) {
+    const uint32_t row_smem = ptx::smem_u32(row);
+    if (world > 0) {
+        // thread j sends route j: one bulk copy of the whole row (codes + scale bytes), then the 8-byte tail
+        if (int(threadIdx.x) < topk) {
+            const int route = token * topk + threadIdx.x, d = dst[threadIdx.x];
             if (d < 0 || d >= recv_capacity) {
-                if (threadIdx.x == 0) atomicOr(error, 1);
-                continue;
-            }
-            const int owner = int(ids[route]) / local_experts;
-            uint8_t* out = static_cast<uint8_t*>(recv.ptr[owner]) + size_t(d) * payload_bytes(hidden);
-            for (int i = threadIdx.x; i < row_bytes / 16; i += blockDim.x)
-                reinterpret_cast<uint4*>(out)[i] = reinterpret_cast<const uint4*>(row)[i];
-            if (threadIdx.x == 0) {
+                atomicOr(error, 1);
+            } else {
+                const int owner = int(ids[route]) / local_experts;
+                uint8_t* out = static_cast<uint8_t*>(recv.ptr[owner]) + size_t(d) * payload_bytes(hidden);
+                ptx::bulk_store(out, row_smem, uint32_t(row_bytes));
+                ptx::tma_store_commit();
                 *reinterpret_cast<float*>(out + row_bytes) = weights[route];
                 *reinterpret_cast<int*>(out + row_bytes + 4) = route;           // where the result goes back to
             }
-        } else {
-            if (d < 0) continue;                                            // an id outside the expert range: dropped, as pack does not
-            uint4* packed = reinterpret_cast<uint4*>(pool_packed + size_t(d) * (hidden / 2));
-            for (int i = threadIdx.x; i < hidden / 32; i += blockDim.x) packed[i] = reinterpret_cast<const uint4*>(row)[i];
-            // four scale bytes (64 K-values) are contiguous in the atom layout
-            for (int q = threadIdx.x; q < hidden / 64; q += blockDim.x)
-                *reinterpret_cast<uint32_t*>(pool_scales + scale_byte_offset(d, 4 * q, hidden)) =
-                    *reinterpret_cast<const uint32_t*>(row + hidden / 2 + 4 * q);
-            if (threadIdx.x == 0) {
-                pool_weight[d] = weights[route];
-                route_row[route] = d;
-            }
+            ptx::tma_store_wait_read<0>();                      // the copies have read the row: the CTA may go
+        }
+        return;
+    }
+    if (int(threadIdx.x) < topk) {
+        const int route = token * topk + threadIdx.x, d = dst[threadIdx.x];
+        if (d >= 0) {                                           // an id outside the expert range is dropped, as pack does
+            ptx::bulk_store(pool_packed + size_t(d) * (hidden / 2), row_smem, uint32_t(hidden / 2));
+            ptx::tma_store_commit();
+            pool_weight[d] = weights[route];
+            route_row[route] = d;
         }
     }
+    for (int j = 0; j < topk; ++j) {
+        const int d = dst[j];
+        if (d < 0) continue;
+        // four scale bytes (64 K-values) are contiguous in the atom layout
+        for (int q = threadIdx.x; q < hidden / 64; q += blockDim.x)
+            *reinterpret_cast<uint32_t*>(pool_scales + scale_byte_offset(d, 4 * q, hidden)) =
+                *reinterpret_cast<const uint32_t*>(row + hidden / 2 + 4 * q);
+    }
+    if (int(threadIdx.x) < topk) ptx::tma_store_wait_read<0>();
 }
 
 // One CTA per received row: expert output -> slot `route` of the source rank's [T*topk, H] buffer.
