@@ -480,11 +480,37 @@ int gpu_kernels_nvfp4_moe_plan(const void* counts_matrix, int world, int rank, i
                                void* num_blocks, void* totals, void* peer_offset, void* stream) {
     return guarded([&] {
         nvfp4_b200::require_sm100();
-        nvfp4_b200::moe_plan(static_cast<const int*>(counts_matrix), world, rank, experts, capacity_rows, block_rows,
-                             static_cast<int*>(send_offset), static_cast<int*>(seg_src_offset),
+        nvfp4_b200::moe_plan(const_cast<int*>(static_cast<const int*>(counts_matrix)), world, rank, experts, capacity_rows,
+                             block_rows, static_cast<int*>(send_offset), static_cast<int*>(seg_src_offset),
                              static_cast<int*>(seg_pool_offset), static_cast<int*>(block_expert),
                              static_cast<int*>(num_blocks), static_cast<int*>(totals), static_cast<int*>(peer_offset),
+                             nullptr, 0, nullptr, static_cast<cudaStream_t>(stream));
+        nvfp4_b200::g_launches.fetch_add(1, std::memory_order_relaxed);
+    });
+}
+
+int gpu_kernels_nvfp4_moe_route_plan(const void* ids, int routes, void* counts, int experts, int capacity_rows, int block_rows,
+                                     void* send_offset, void* seg_src_offset, void* seg_pool_offset, void* block_expert,
+                                     void* num_blocks, void* totals, void* cursor, void* stream) {
+    return guarded([&] {
+        nvfp4_b200::require_sm100();
+        if (!ids || !counts || !cursor) throw std::invalid_argument("moe route_plan: null pointer");
+        nvfp4_b200::moe_plan(static_cast<int*>(counts), 1, 0, experts, capacity_rows, block_rows,
+                             static_cast<int*>(send_offset), static_cast<int*>(seg_src_offset),
+                             static_cast<int*>(seg_pool_offset), static_cast<int*>(block_expert),
+                             static_cast<int*>(num_blocks), static_cast<int*>(totals), nullptr,
+                             static_cast<const long long*>(ids), routes, static_cast<int*>(cursor),
                              static_cast<cudaStream_t>(stream));
+        nvfp4_b200::g_launches.fetch_add(1, std::memory_order_relaxed);
+    });
+}
+
+int gpu_kernels_nvfp4_moe_clear_live(const void* num_blocks, int block_rows, int pool_rows, int hidden, void* pool_scales,
+                                     void* pool_weight, void* pool_dst, void* stream) {
+    return guarded([&] {
+        nvfp4_b200::moe_clear_live(static_cast<const int*>(num_blocks), block_rows, pool_rows, hidden,
+                                   static_cast<uint8_t*>(pool_scales), static_cast<float*>(pool_weight),
+                                   static_cast<int*>(pool_dst), static_cast<cudaStream_t>(stream));
         nvfp4_b200::g_launches.fetch_add(1, std::memory_order_relaxed);
     });
 }

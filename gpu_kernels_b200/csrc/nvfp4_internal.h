@@ -53,9 +53,11 @@ struct MoeShape {
     float clamp;
 };
 void moe_route_count(const long long* ids, int routes, int experts, int* counts, cudaStream_t stream);
-void moe_plan(const int* counts_matrix, int world, int rank, int experts, int pool_capacity_rows, int block_rows,
+void moe_plan(int* counts_matrix, int world, int rank, int experts, int pool_capacity_rows, int block_rows,
               int* send_offset, int* seg_src_offset, int* seg_pool_offset, int* block_expert, int* num_blocks,
-              int* totals, int* peer_offset, cudaStream_t stream);
+              int* totals, int* peer_offset, const long long* ids, int routes, int* cursor, cudaStream_t stream);
+void moe_clear_live(const int* num_blocks, int block_rows, int pool_rows, int hidden, uint8_t* pool_scales,
+                    float* pool_weight, int* pool_dst, cudaStream_t stream);
 // Expert parallelism over peer memory (NVLink stores into buffers of the other ranks' processes).
 void moe_pack_peer(const uint8_t* xq, const uint8_t* xs, const long long* ids, const float* weights, int tokens,
                    int topk, int hidden, int world, int local_experts, const int* peer_offset, int* cursor,

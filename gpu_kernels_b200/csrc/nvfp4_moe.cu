@@ -66,17 +66,33 @@ __device__ void block_exclusive_scan(int* data, int n, int* chunk_sums) {
 }
 
 // counts[r * experts + ge]: routes rank r sends to global expert ge. One CTA of 256 threads; experts <= 4096.
-__global__ void plan_kernel(const int* __restrict__ counts, int world, int rank, int experts, int capacity_rows,
+__global__ void plan_kernel(int* counts, int world, int rank, int experts, int capacity_rows,
                             int block_rows,
                             int* __restrict__ send_offset, int* __restrict__ seg_src_offset,
                             int* __restrict__ seg_pool_offset, int* __restrict__ block_expert,
-                            int* __restrict__ num_blocks, int* __restrict__ totals, int* __restrict__ peer_offset) {
+                            int* __restrict__ num_blocks, int* __restrict__ totals, int* __restrict__ peer_offset,
+                            const long long* __restrict__ ids, int routes, int* __restrict__ cursor) {
     extern __shared__ int sh[];
     const int local_experts = experts / world;
     const int segments = world * local_experts;          // == experts
     int* scan = sh;                                       // [experts] scratch for the three scans
     int* pool_off = sh + experts;                         // [local_experts] padded start of each expert
     int* chunk = pool_off + local_experts;                // [blockDim.x + 1]
+    if (ids) {
+        // One rank: nothing to exchange, so the histogram of the routes is taken right here (the counts row is
+        // this kernel's own output) instead of by a zeroing memset and a counting kernel before it.
+        for (int e = threadIdx.x; e < experts; e += blockDim.x) scan[e] = 0;
+        __syncthreads();
+        for (int i = threadIdx.x; i < routes; i += blockDim.x) {
+            const long long e = ids[i];
+            if (e >= 0 && e < experts) atomicAdd(&scan[int(e)], 1);
+        }
+        __syncthreads();
+        for (int e = threadIdx.x; e < experts; e += blockDim.x) counts[e] = scan[e];
+        __syncthreads();
+    }
+    if (cursor)
+        for (int e = threadIdx.x; e < experts; e += blockDim.x) cursor[e] = 0;    // arrival counters of the dispatch
     // 1. where this rank's routes go in its send buffer (ordered by global expert = by destination rank)
     for (int ge = threadIdx.x; ge < experts; ge += blockDim.x) scan[ge] = counts[rank * experts + ge];
     __syncthreads();
@@ -440,9 +456,10 @@ void moe_route_count(const long long* ids, int routes, int experts, int* counts,
     cuda_check(cudaGetLastError());
 }
 
-void moe_plan(const int* counts_matrix, int world, int rank, int experts, int pool_capacity_rows, int block_rows,
+void moe_plan(int* counts_matrix, int world, int rank, int experts, int pool_capacity_rows, int block_rows,
               int* send_offset, int* seg_src_offset, int* seg_pool_offset, int* block_expert, int* num_blocks,
-              int* totals, int* peer_offset, cudaStream_t stream) {
+              int* totals, int* peer_offset, const long long* ids, int routes, int* cursor, cudaStream_t stream) {
+    if (ids && (world != 1 || routes < 0)) throw std::invalid_argument("moe plan: counting the routes in the plan kernel is for one rank");
     if (world <= 0 || rank < 0 || rank >= world || experts <= 0 || experts % world || experts > 4096)
         throw std::invalid_argument("moe plan: experts must divide over the ranks (and be <= 4096)");
     if (block_rows != 128 && block_rows != 256) throw std::invalid_argument("moe plan: block rows must be 128 or 256");
@@ -450,7 +467,7 @@ void moe_plan(const int* counts_matrix, int world, int rank, int experts, int po
     const int local = experts / world;
     plan_kernel<<<1, 256, (experts + local + 257) * sizeof(int), stream>>>(counts_matrix, world, rank, experts, pool_capacity_rows, block_rows,
                                                                    send_offset, seg_src_offset, seg_pool_offset,
-                                                                   block_expert, num_blocks, totals, peer_offset);
+                                                                   block_expert, num_blocks, totals, peer_offset, ids, routes, cursor);
     cuda_check(cudaGetLastError());
 }
 
@@ -573,6 +590,33 @@ void moe_quantise_route(const void* x_bf16, const long long* ids, const float* w
     quantise_route_kernel<<<tokens, 256, smem, stream>>>(static_cast<const __nv_bfloat16*>(x_bf16), ids, weights, topk, hidden,
                                                         experts, offsets, cursor, recv, world, local_experts, recv_capacity,
                                                         error, pool_packed, pool_scales, pool_weight, route_row);
+    cuda_check(cudaGetLastError());
+}
+
+// One CTA per 128 pool rows: if the rows belong to a live block, clear their scale bytes (whole atoms, one
+// contiguous run), route weights and destination codes, so that the padding rows of every expert's last block
+// contribute nothing. Only the blocks of this forward are touched: the pool is sized for the worst case and
+// clearing all of it every call costs more than the small-batch kernels themselves.
+__global__ void __launch_bounds__(256)
+clear_live_kernel(const int* __restrict__ num_blocks, int block_rows, int hidden, uint8_t* __restrict__ pool_scales,
+                  float* __restrict__ pool_weight, int* __restrict__ pool_dst) {
+    const int row0 = blockIdx.x * 128;
+    if (row0 >= *num_blocks * block_rows) return;
+    const size_t bytes = size_t(hidden / 64) * 512;            // the scale atoms of 128 rows
+    uint4* scales = reinterpret_cast<uint4*>(pool_scales + size_t(blockIdx.x) * bytes);
+    for (size_t i = threadIdx.x; i < bytes / 16; i += blockDim.x) scales[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (threadIdx.x < 128) {
+        pool_weight[row0 + threadIdx.x] = 0.0f;
+        if (pool_dst) pool_dst[row0 + threadIdx.x] = 0;
+    }
+}
+
+void moe_clear_live(const int* num_blocks, int block_rows, int pool_rows, int hidden, uint8_t* pool_scales,
+                    float* pool_weight, int* pool_dst, cudaStream_t stream) {
+    check_hidden(hidden, "moe clear_live");
+    if (!num_blocks || !pool_scales || !pool_weight || pool_rows <= 0 || pool_rows % 128 || (block_rows != 128 && block_rows != 256))
+        throw std::invalid_argument("moe clear_live: bad argument");
+    clear_live_kernel<<<pool_rows / 128, 256, 0, stream>>>(num_blocks, block_rows, hidden, pool_scales, pool_weight, pool_dst);
     cuda_check(cudaGetLastError());
 }
 

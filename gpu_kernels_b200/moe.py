@@ -188,19 +188,33 @@ class Nvfp4MoE:
     def _metadata(self, ids, tokens, block_rows):
         lib, s = _lib.load(), _stream()
         routes = tokens * self.topk
-        self.counts.zero_()
-        _lib.check(lib.gpu_kernels_nvfp4_moe_route_count(ids.data_ptr(), routes, self.experts, self.counts.data_ptr(), s))
-        if self._peer is not None:
-            self._peers.all_gather_ints(self.counts, self.counts_matrix)      # peer stores + barrier, one kernel
-        elif self.world > 1:
-            dist.all_gather_into_tensor(self.counts_matrix.view(-1), self.counts, group=self.group)
+        if self.world == 1 and routes <= 4096:
+            # one launch: histogram of the routes (by the plan's single CTA: for small batches), plan, arrival
+            # counters cleared
+            _lib.check(lib.gpu_kernels_nvfp4_moe_route_plan(
+                ids.data_ptr(), routes, self.counts_matrix.data_ptr(), self.experts, self.pool_rows, block_rows,
+                self.send_offset.data_ptr(), self.seg_src.data_ptr(), self.seg_pool.data_ptr(),
+                self.block_expert.data_ptr(), self.num_blocks.data_ptr(), self.totals.data_ptr(),
+                self.cursor.data_ptr(), s))
         else:
-            self.counts_matrix.copy_(self.counts.view(1, -1))
-        _lib.check(lib.gpu_kernels_nvfp4_moe_plan(
-            self.counts_matrix.data_ptr(), self.world, self.rank, self.experts, self.pool_rows, block_rows,
-            self.send_offset.data_ptr(), self.seg_src.data_ptr(), self.seg_pool.data_ptr(),
-            self.block_expert.data_ptr(), self.num_blocks.data_ptr(), self.totals.data_ptr(),
-            self.peer_offset.data_ptr() if self._peer is not None else None, s))
+            self.counts.zero_()
+            self.cursor.zero_()
+            _lib.check(lib.gpu_kernels_nvfp4_moe_route_count(ids.data_ptr(), routes, self.experts, self.counts.data_ptr(), s))
+            if self._peer is not None:
+                self._peers.all_gather_ints(self.counts, self.counts_matrix)      # peer stores + barrier, one kernel
+            elif self.world > 1:
+                dist.all_gather_into_tensor(self.counts_matrix.view(-1), self.counts, group=self.group)
+            else:
+                self.counts_matrix.copy_(self.counts.view(1, -1))
+            _lib.check(lib.gpu_kernels_nvfp4_moe_plan(
+                self.counts_matrix.data_ptr(), self.world, self.rank, self.experts, self.pool_rows, block_rows,
+                self.send_offset.data_ptr(), self.seg_src.data_ptr(), self.seg_pool.data_ptr(),
+                self.block_expert.data_ptr(), self.num_blocks.data_ptr(), self.totals.data_ptr(),
+                self.peer_offset.data_ptr() if self._peer is not None else None, s))
+        # padding rows of the live blocks must contribute nothing: clear their scale bytes, weights and codes
+        _lib.check(lib.gpu_kernels_nvfp4_moe_clear_live(
+            self.num_blocks.data_ptr(), block_rows, self.pool_rows, self.hidden, self.pool_scales.data_ptr(),
+            self.pool_weight.data_ptr(), self.pool_dst.data_ptr() if self._peer is not None else None, s))
         if self._peer is not None and self.pool_rows >= self.world * self.max_tokens * self.topk + self.local_experts * (block_rows - 1):
             # peer exchange with a worst-case pool: the host needs nothing from the counts
             return None, None
@@ -241,11 +255,6 @@ class Nvfp4MoE:
                 fused_dispatch = False
                 self.x_pad[:tokens].copy_(x)
                 xq, xs = quantize(self.x_pad)
-            self.cursor.zero_()
-            self.pool_scales.zero_()
-            self.pool_weight.zero_()
-            if self._peer is not None:
-                self.pool_dst.zero_()
             total_recv = sum(recv_splits) if recv_splits is not None else 0
             if fused_dispatch and (self.world == 1 or send_splits is None):
                 x = x.contiguous()

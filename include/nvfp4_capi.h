@@ -139,6 +139,17 @@ int gpu_kernels_nvfp4_moe_route_count(const void* ids, int routes, int experts, 
 int gpu_kernels_nvfp4_moe_plan(const void* counts_matrix, int world, int rank, int experts, int capacity_rows,
                                int block_rows, void* send_offset, void* seg_src_offset, void* seg_pool_offset, void* block_expert,
                                void* num_blocks, void* totals, void* peer_offset, void* stream);
+/* One rank (nothing to exchange): histogram of the routes (ids int64 [routes] -> counts int32 [experts], written
+ * here) and the plan above in ONE launch, which also zeroes cursor [experts], the arrival counters of the
+ * dispatch kernels. Replaces a memset, route_count, a copy, plan and another memset. */
+int gpu_kernels_nvfp4_moe_route_plan(const void* ids, int routes, void* counts, int experts, int capacity_rows, int block_rows,
+                                     void* send_offset, void* seg_src_offset, void* seg_pool_offset, void* block_expert,
+                                     void* num_blocks, void* totals, void* cursor, void* stream);
+/* Clears scale bytes, route weights and (if not null) destination codes of the pool rows of the live blocks
+ * (num_blocks [1] on the device, from the plan), so that padding rows contribute nothing; rows beyond the live
+ * blocks are not touched. pool_rows: allocated rows (multiple of 128). Run between the plan and the dispatch. */
+int gpu_kernels_nvfp4_moe_clear_live(const void* num_blocks, int block_rows, int pool_rows, int hidden, void* pool_scales,
+                                     void* pool_weight, void* pool_dst, void* stream);
 /* quantised tokens (xq [T_pad, hidden/2], xs VEC16 scales), ids int64 [T, topk], weights f32 [T, topk] ->
  * send_rows [T*topk, payload] ordered by destination expert; send_pos [T*topk] = row of each route;
  * cursor int32 [experts] zeroed by the caller. */

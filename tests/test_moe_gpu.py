@@ -205,7 +205,7 @@ def test_routing_plan_pack_unpack_exact(g):
     torch.cuda.synchronize()
     ids_np, w_np = to_np(ids), to_np(wts)
     counts = np.bincount(ids_np.reshape(-1), minlength=experts)
-    assert np.array_equal(to_np(layer.counts), counts)
+    assert np.array_equal(to_np(layer.counts_matrix[0]), counts)
     # plan: expert-major pool, each expert padded to 128 rows
     padded = (counts + 127) // 128 * 128
     assert int(layer.num_blocks.item()) == padded.sum() // 128
