@@ -44,7 +44,8 @@ SIGNATURES = {
     "gpu_kernels_nvfp4_moe_route_count": ([P, I, I, P, P], I),
     "gpu_kernels_nvfp4_moe_route_plan": ([P, I, P, I, I, I, P, P, P, P, P, P, P, P], I),
     "gpu_kernels_nvfp4_moe_clear_live": ([P, I, I, I, P, P, P, P], I),
-    "gpu_kernels_nvfp4_moe_plan": ([P, I, I, I, I, I, P, P, P, P, P, P, P, P], I),
+    "gpu_kernels_nvfp4_moe_plan": ([P, I, I, I, I, I, P, P, P, P, P, P, P, P, P], I),
+    "gpu_kernels_nvfp4_moe_count_exchange": ([P, I, I, P, P, I, I, I, P, P], I),
     "gpu_kernels_nvfp4_moe_pack": ([P, P, P, P, I, I, I, P, P, P, P, P], I),
     "gpu_kernels_nvfp4_moe_pack_to_pool": ([P, P, P, P, I, I, I, P, P, P, P, P, P, P], I),
     "gpu_kernels_nvfp4_moe_unpack": ([P, I, P, I, I, I, P, P, P, P, P, P, P, P], I),

@@ -477,14 +477,14 @@ int gpu_kernels_nvfp4_moe_route_count(const void* ids, int routes, int experts, 
 
 int gpu_kernels_nvfp4_moe_plan(const void* counts_matrix, int world, int rank, int experts, int capacity_rows,
                                int block_rows, void* send_offset, void* seg_src_offset, void* seg_pool_offset, void* block_expert,
-                               void* num_blocks, void* totals, void* peer_offset, void* stream) {
+                               void* num_blocks, void* totals, void* peer_offset, void* cursor, void* stream) {
     return guarded([&] {
         nvfp4_b200::require_sm100();
         nvfp4_b200::moe_plan(const_cast<int*>(static_cast<const int*>(counts_matrix)), world, rank, experts, capacity_rows,
                              block_rows, static_cast<int*>(send_offset), static_cast<int*>(seg_src_offset),
                              static_cast<int*>(seg_pool_offset), static_cast<int*>(block_expert),
                              static_cast<int*>(num_blocks), static_cast<int*>(totals), static_cast<int*>(peer_offset),
-                             nullptr, 0, nullptr, static_cast<cudaStream_t>(stream));
+                             nullptr, 0, static_cast<int*>(cursor), static_cast<cudaStream_t>(stream));
         nvfp4_b200::g_launches.fetch_add(1, std::memory_order_relaxed);
     });
 }
@@ -678,7 +678,18 @@ int gpu_kernels_nvfp4_peer_exchange(void* own, const void* peers_device, int wor
                                     int max_ints, void* out, void* stream) {
     return guarded([&] {
         nvfp4_b200::peer_exchange(own, static_cast<void* const*>(peers_device), world, rank, static_cast<const int*>(payload),
-                                  ints, max_ints, static_cast<int*>(out), static_cast<cudaStream_t>(stream));
+                                  ints, max_ints, static_cast<int*>(out), nullptr, 0, static_cast<cudaStream_t>(stream));
+    });
+}
+
+int gpu_kernels_nvfp4_moe_count_exchange(const void* ids, int routes, int experts, void* own, const void* peers_device, int world,
+                                         int rank, int max_ints, void* counts_matrix, void* stream) {
+    return guarded([&] {
+        if (!ids) throw std::invalid_argument("moe count_exchange: null ids");
+        nvfp4_b200::peer_exchange(own, static_cast<void* const*>(peers_device), world, rank, nullptr, experts, max_ints,
+                                  static_cast<int*>(counts_matrix), static_cast<const long long*>(ids), routes,
+                                  static_cast<cudaStream_t>(stream));
+        nvfp4_b200::g_launches.fetch_add(1, std::memory_order_relaxed);
     });
 }
 

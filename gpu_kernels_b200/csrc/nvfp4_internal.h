@@ -93,8 +93,9 @@ uint32_t* device_status_word(int device);
 // state blocks (peer_state_bytes each, zeroed) that every rank maps: own = this rank's, peers_device = device
 // array of all ranks' blocks in rank order. out [world][ints].
 size_t peer_state_bytes(int world, int max_ints);
+// ids != null: the payload is the histogram of ids [routes] over `ints` bins, taken inside the kernel.
 void peer_exchange(void* own, void* const* peers_device, int world, int rank, const int* payload, int ints, int max_ints,
-                   int* out, cudaStream_t stream);
+                   int* out, const long long* ids, int routes, cudaStream_t stream);
 void moe_reduce(const void* returned_bf16, const int* send_pos, int tokens, int topk, int hidden, void* y_bf16,
                 cudaStream_t stream);
 

@@ -647,10 +647,22 @@ constexpr size_t PEER_STATE_HEADER = offsetof(PeerState, payload);
 
 __global__ void peer_exchange_kernel(PeerState* own, PeerState* const* peers, int world, int rank,
                                      const int* __restrict__ payload, int ints, int max_ints, int* __restrict__ out,
-                                     uint32_t* status) {
+                                     uint32_t* status, const long long* __restrict__ ids, int routes) {
+    extern __shared__ int histogram[];                          // [ints], only when ids are given
     __shared__ uint32_t next_epoch;
     __shared__ int failed;
     if (threadIdx.x == 0) { next_epoch = own->epoch + 1u; failed = 0; }
+    if (ids) {
+        // the payload is the histogram of this rank's routes over the experts, taken here (small batches):
+        // saves the memset and the counting kernel in front of the exchange
+        for (int e = threadIdx.x; e < ints; e += blockDim.x) histogram[e] = 0;
+        __syncthreads();
+        for (int i = threadIdx.x; i < routes; i += blockDim.x) {
+            const long long e = ids[i];
+            if (e >= 0 && e < ints) atomicAdd(&histogram[int(e)], 1);
+        }
+        payload = histogram;
+    }
     __syncthreads();
     const uint32_t e = next_epoch;
     const size_t slot = size_t(e & 1u) * world;
@@ -691,14 +703,16 @@ size_t peer_state_bytes(int world, int max_ints) {
 }
 
 void peer_exchange(void* own, void* const* peers_device, int world, int rank, const int* payload, int ints, int max_ints,
-                   int* out, cudaStream_t stream) {
+                   int* out, const long long* ids, int routes, cudaStream_t stream) {
     if (!own || !peers_device || world < 1 || world > 64 || rank < 0 || rank >= world)
         throw std::invalid_argument("peer exchange: bad state, table or rank");
-    if (ints < 0 || ints > max_ints || (ints > 0 && (!payload || !out))) throw std::invalid_argument("peer exchange: bad payload");
+    if (ints < 0 || ints > max_ints || (ints > 0 && ((!payload && !ids) || !out))) throw std::invalid_argument("peer exchange: bad payload");
+    if (ids && (ints < 1 || ints > 4096 || routes < 0)) throw std::invalid_argument("peer exchange: a histogram needs 1..4096 bins");
     int device = 0;
     cuda_check(cudaGetDevice(&device));
-    peer_exchange_kernel<<<1, 256, 0, stream>>>(static_cast<PeerState*>(own), reinterpret_cast<PeerState* const*>(peers_device),
-                                                world, rank, payload, ints, max_ints, out, device_status_word(device));
+    peer_exchange_kernel<<<1, 256, ids ? size_t(ints) * sizeof(int) : 0, stream>>>(
+        static_cast<PeerState*>(own), reinterpret_cast<PeerState* const*>(peers_device), world, rank, payload, ints, max_ints, out,
+        device_status_word(device), ids, routes);
     cuda_check(cudaGetLastError());
 }
 

@@ -197,20 +197,26 @@ class Nvfp4MoE:
                 self.block_expert.data_ptr(), self.num_blocks.data_ptr(), self.totals.data_ptr(),
                 self.cursor.data_ptr(), s))
         else:
-            self.counts.zero_()
-            self.cursor.zero_()
-            _lib.check(lib.gpu_kernels_nvfp4_moe_route_count(ids.data_ptr(), routes, self.experts, self.counts.data_ptr(), s))
-            if self._peer is not None:
-                self._peers.all_gather_ints(self.counts, self.counts_matrix)      # peer stores + barrier, one kernel
-            elif self.world > 1:
-                dist.all_gather_into_tensor(self.counts_matrix.view(-1), self.counts, group=self.group)
+            if self._peer is not None and routes <= 4096:
+                # small batch: histogram, peer stores of the counts and the barrier in one kernel
+                st = self._peers.state
+                _lib.check(lib.gpu_kernels_nvfp4_moe_count_exchange(
+                    ids.data_ptr(), routes, self.experts, st.own, st.device_table.data_ptr(), self.world, self.rank,
+                    self._peers.max_ints, self.counts_matrix.data_ptr(), s))
             else:
-                self.counts_matrix.copy_(self.counts.view(1, -1))
+                self.counts.zero_()
+                _lib.check(lib.gpu_kernels_nvfp4_moe_route_count(ids.data_ptr(), routes, self.experts, self.counts.data_ptr(), s))
+                if self._peer is not None:
+                    self._peers.all_gather_ints(self.counts, self.counts_matrix)      # peer stores + barrier, one kernel
+                elif self.world > 1:
+                    dist.all_gather_into_tensor(self.counts_matrix.view(-1), self.counts, group=self.group)
+                else:
+                    self.counts_matrix.copy_(self.counts.view(1, -1))
             _lib.check(lib.gpu_kernels_nvfp4_moe_plan(
                 self.counts_matrix.data_ptr(), self.world, self.rank, self.experts, self.pool_rows, block_rows,
                 self.send_offset.data_ptr(), self.seg_src.data_ptr(), self.seg_pool.data_ptr(),
                 self.block_expert.data_ptr(), self.num_blocks.data_ptr(), self.totals.data_ptr(),
-                self.peer_offset.data_ptr() if self._peer is not None else None, s))
+                self.peer_offset.data_ptr() if self._peer is not None else None, self.cursor.data_ptr(), s))
         # padding rows of the live blocks must contribute nothing: clear their scale bytes, weights and codes
         _lib.check(lib.gpu_kernels_nvfp4_moe_clear_live(
             self.num_blocks.data_ptr(), block_rows, self.pool_rows, self.hidden, self.pool_scales.data_ptr(),

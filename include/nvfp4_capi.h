@@ -135,10 +135,11 @@ int gpu_kernels_nvfp4_moe_route_count(const void* ids, int routes, int experts, 
  * send_offset [experts+1], seg_src_offset [world*local+1], seg_pool_offset [world*local],
  * block_expert [capacity_rows/block_rows], num_blocks [1], totals [3] = {rows received, pool rows used, overflow};
  * peer_offset [experts] (may be null): where this rank's rows for each global expert start in the receive
- * buffer of the rank that owns it, for gpu_kernels_nvfp4_moe_pack_peer. */
+ * buffer of the rank that owns it, for gpu_kernels_nvfp4_moe_pack_peer. cursor [experts] (may be null): the
+ * arrival counters of the dispatch kernels, zeroed here. */
 int gpu_kernels_nvfp4_moe_plan(const void* counts_matrix, int world, int rank, int experts, int capacity_rows,
                                int block_rows, void* send_offset, void* seg_src_offset, void* seg_pool_offset, void* block_expert,
-                               void* num_blocks, void* totals, void* peer_offset, void* stream);
+                               void* num_blocks, void* totals, void* peer_offset, void* cursor, void* stream);
 /* One rank (nothing to exchange): histogram of the routes (ids int64 [routes] -> counts int32 [experts], written
  * here) and the plan above in ONE launch, which also zeroes cursor [experts], the arrival counters of the
  * dispatch kernels. Replaces a memset, route_count, a copy, plan and another memset. */
@@ -234,6 +235,11 @@ int gpu_kernels_nvfp4_moe_return_peer(const void* out_pool, const void* recv_row
  * it the same number of times, each on its own GPU (never two ranks on one GPU). Capturable in a CUDA graph.
  * No counterpart in the reference (its peer signalling is inside kernels/moe/fused/sm90.cu:296-319). */
 int gpu_kernels_nvfp4_peer_state_bytes(int world, int max_ints, size_t* bytes);
+/* The count all-gather of the expert layer in one launch for small batches: the histogram of this rank's routes
+ * (ids int64 [routes], `experts` <= 4096 bins) is taken inside the exchange kernel and arrives, with every
+ * other rank's, in counts_matrix int32 [world, experts]. Arguments as gpu_kernels_nvfp4_peer_exchange. */
+int gpu_kernels_nvfp4_moe_count_exchange(const void* ids, int routes, int experts, void* own, const void* peers_device, int world,
+                                         int rank, int max_ints, void* counts_matrix, void* stream);
 int gpu_kernels_nvfp4_peer_exchange(void* own, const void* peers_device, int world, int rank, const void* payload, int ints,
                                     int max_ints, void* out, void* stream);
 
