@@ -87,17 +87,21 @@ int gpu_kernels_nvfp4_plan_profile(void* plan, void* C, void* stream, unsigned l
  * device spent inside the kernel (synchronising copy of one word); 0 on error. */
 unsigned gpu_kernels_nvfp4_last_kernel_cycles(void);
 
-/* Whole GEMM from HOST buffers: copies the four operands to the device, runs the kernel and copies
- * C back, all on `stream`, then synchronises it. Device staging is cached per (M,N,K) inside the
- * library. This is the end-to-end call a host-side user of the reference path would make in place
- * of its CPU dequantise + matmul (benchmarks/nvfp4.py:41). */
+/* Whole GEMM from HOST buffers (pinned memory recommended): copies the four operands to the device, runs
+ * the kernel and copies C back, then synchronises. From M = 1024 the product goes in 2 or 4 row pieces:
+ * copies in and kernels on `stream`, copies out on a second stream of the library's, so that both directions
+ * of the host link are busy at once. Device staging is cached per (M,N,K) inside the library. This is the
+ * end-to-end call a host-side user of the reference path would make in place of its CPU dequantise + matmul
+ * (benchmarks/nvfp4.py:41). */
 int gpu_kernels_nvfp4_gemm_host(int M, int N, int K, const void* A, const void* B, const void* SFA, const void* SFB,
                                 void* C, float alpha, void* stream);
 
 /* ---- routed-MoE expert path in NVFP4 (phase structure of the reference's gpu_kernels_moe_phase,
  *      benchmarks/bindings/fused_moe_bridge.cu:11-26: metadata / FC1 / FC2 / reduce; the reference's
- *      kernels are BF16 for sm_90a and move tokens through peer pointers, these move quantised rows
- *      through an all-to-all the caller runs between pack and unpack). All pointers are device pointers. ---- */
+ *      kernels are BF16 for sm_90a and move tokens through peer pointers). These move quantised rows, either
+ *      by stores into the peers' memory from the dispatch kernel and from FC2's epilogue (quantise_route /
+ *      pack_peer, grouped_run_scatter, peer_exchange as the barrier), or through an all-to-all that the caller
+ *      runs between pack and unpack. All pointers are device pointers unless said otherwise. ---- */
 
 /* Grouped GEMM: pool A [pool_rows, K/2] of blocks of block_rows (128 or 256) rows, stacked weights
  * B [experts*n, K/2] (+ scales); block i multiplies expert block_expert[i]; *num_blocks blocks are live (device
@@ -117,7 +121,8 @@ int gpu_kernels_nvfp4_grouped_run_swiglu(void* plan, const void* row_weight, flo
                                          void* act_scales, void* stream);
 
 /* The second expert GEMM fused with the combine: instead of C, pool row r is written (bf16 or fp16, from the
- * epilogue's registers, while the GEMM runs) to row (row_dst[r] & 0xFFFFFF) - 1 of slots[row_dst[r] >> 24], a
+ * epilogue while the GEMM runs: register stores for 128-row blocks, one 512-byte bulk copy per row and tile
+ * from shared memory for 256-row blocks) to row (row_dst[r] & 0xFFFFFF) - 1 of slots[row_dst[r] >> 24], a
  * [slot_rows, n] buffer per rank: this rank's own, or a peer's mapped through gpu_kernels_nvfp4_ipc_open, in
  * which case the stores cross NVLink. row_dst[r] == 0 marks a padding row. Out-of-range destinations are
  * skipped and reported by gpu_kernels_nvfp4_validate. Replaces FC2 + the peer scatter of
