@@ -49,7 +49,7 @@ NOMINAL_FP4_TFLOPS = 9000.0
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of nvfp4_gemm_kernel, from the
 # ncu captures summarised under profiles/ (None until a capture of that workload exists).
-NCU_DRAM_BYTES_PER_LAUNCH = {"gemm8192": 226_928_896, "gemm16384": None, "skinny": 136_602_624,
+NCU_DRAM_BYTES_PER_LAUNCH = {"gemm8192": 218_190_336, "gemm16384": None, "skinny": 136_602_624,
                              # quantise_kernel<bf16>: part of the output was still in L2 when the capture ended
                              "quantise8192": 155_176_960}
 
