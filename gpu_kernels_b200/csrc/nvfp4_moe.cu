@@ -194,12 +194,15 @@ __global__ void unpack_kernel(const uint8_t* __restrict__ recv_rows, const int* 
     const int lane = threadIdx.x & 31;
     const int p = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (p >= totals[0] || totals[2]) return;
-    // last segment whose start is <= p (segments may be empty, so starts repeat)
-    int lo = 0, hi = segments;
-    while (hi - lo > 1) {
-        const int mid = (lo + hi) >> 1;
-        if (seg_src_offset[mid] <= p) lo = mid; else hi = mid;
+    // last segment whose start is <= p (segments may be empty, so starts repeat): the starts are
+    // non-decreasing, so it is the number of starts <= p, minus one. The lanes count 32 starts at a
+    // time with independent, coalesced loads (a binary search would be eight dependent loads per row).
+    int below = 0;
+    for (int base = 0; base < segments; base += 32) {
+        const int i = base + lane;
+        below += __popc(__ballot_sync(0xFFFFFFFFu, i < segments && __ldg(seg_src_offset + i) <= p));
     }
+    const int lo = below - 1;
     const int row = seg_pool_offset[lo] + (p - seg_src_offset[lo]);
     const uint8_t* in = recv_rows + size_t(p) * payload_bytes(hidden);
     uint4* dst = reinterpret_cast<uint4*>(pool_packed + size_t(row) * (hidden / 2));
