@@ -98,7 +98,6 @@ class Nvfp4MoE:
         d, u8, i32 = self.device, torch.uint8, torch.int32
         routes = max_tokens * topk
         self.t_pad = -(-max_tokens // 128) * 128
-        self.x_pad = torch.zeros((self.t_pad, self.hidden), dtype=torch.bfloat16, device=d)
         self.counts = torch.zeros(num_experts, dtype=i32, device=d)
         self.counts_matrix = torch.zeros((self.world, num_experts), dtype=i32, device=d)
         self.send_offset = torch.zeros(num_experts + 1, dtype=i32, device=d)
@@ -108,12 +107,22 @@ class Nvfp4MoE:
         self.num_blocks = torch.zeros(1, dtype=i32, device=d)
         self.totals = torch.zeros(4, dtype=i32, device=d)
         self.cursor = torch.zeros(num_experts, dtype=i32, device=d)
-        self.send_rows = torch.empty((routes, self.payload), dtype=u8, device=d)
         self.send_pos = torch.zeros(routes, dtype=i32, device=d)
         recv_cap = self.world * routes
         self.recv_cap = recv_cap
-        self.recv_rows = self.send_rows if self.world == 1 else torch.empty((recv_cap, self.payload), dtype=u8, device=d)
-        self.recv_ptr = self.recv_rows.data_ptr()
+        # Buffers only some routes touch (the all-to-all route's send / receive / return rows, the unfused
+        # routes' intermediates, the stand-alone quantiser's padded input) are created at first use: the
+        # default route of an expert-parallel layer at 4096 tokens would otherwise hold 1.2 GB it never reads.
+        bf16 = torch.bfloat16
+        self._lazy_specs = {
+            "x_pad": ((self.t_pad, self.hidden), bf16, True),
+            "send_rows": ((routes, self.payload), u8, False),
+            "recv_rows": ((recv_cap, self.payload), u8, False),
+            "gate_up": ((self.pool_rows, two_i), bf16, False),
+            "out_pool": ((self.pool_rows, self.hidden), bf16, False),
+            "ret_send": ((recv_cap, self.hidden), bf16, False),
+            "ret_recv": ((routes, self.hidden), bf16, False),
+        }
         self._peer = None
         if self.exchange == "peer":
             self._setup_peer_buffers(routes, recv_cap)
@@ -121,12 +130,8 @@ class Nvfp4MoE:
         self.pool_scales = torch.zeros(self.pool_rows * self.hidden // 16, dtype=u8, device=d)
         self.pool_weight = torch.zeros(self.pool_rows, dtype=torch.float32, device=d)
         self.pool_of_recv = torch.zeros(recv_cap, dtype=i32, device=d)
-        self.gate_up = None if fused else torch.empty((self.pool_rows, two_i), dtype=torch.bfloat16, device=d)
         self.act_packed = torch.empty((self.pool_rows, self.inter // 2), dtype=u8, device=d)
         self.act_scales = torch.empty(self.pool_rows * self.inter // 16, dtype=u8, device=d)
-        self.out_pool = torch.empty((self.pool_rows, self.hidden), dtype=torch.bfloat16, device=d)
-        self.ret_send = torch.empty((recv_cap, self.hidden), dtype=torch.bfloat16, device=d)
-        self.ret_recv = self.ret_send if self.world == 1 else torch.empty((routes, self.hidden), dtype=torch.bfloat16, device=d)
         self.y = torch.empty((max_tokens, self.hidden), dtype=torch.bfloat16, device=d)
         self._plans = {}
         with torch.cuda.device(d):
@@ -141,6 +146,17 @@ class Nvfp4MoE:
                     self.act_packed.data_ptr(), self.w2q.data_ptr(), self.act_scales.data_ptr(), self.w2s.data_ptr(),
                     self.block_expert.data_ptr(), self.num_blocks.data_ptr()))
                 self._plans[rows] = (fc1, fc2)
+
+    def __getattr__(self, name):
+        # only reached for attributes that do not exist yet: the lazily created buffers
+        specs = self.__dict__.get("_lazy_specs")
+        if specs and name in specs:
+            shape, dtype, zero = specs[name]
+            make = torch.zeros if zero else torch.empty
+            tensor = make(shape, dtype=dtype, device=self.__dict__["device"])
+            self.__dict__[name] = tensor
+            return tensor
+        raise AttributeError(name)
 
     def _setup_peer_buffers(self, routes, recv_cap):
         """Receive and result-slot buffers that every rank of the group can write (CUDA IPC), and the barrier."""
