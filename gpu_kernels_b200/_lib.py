@@ -27,7 +27,7 @@ SIGNATURES = {
     "gpu_kernels_nvfp4_dequantize": ([P, P, P, I, I, P], I),
     "gpu_kernels_nvfp4_plan_set_alpha": ([P, F], I),
     "gpu_kernels_nvfp4_plan_set_option": ([P, ctypes.c_char_p, I], I),
-    "gpu_kernels_nvfp4_moe_quantise_route": ([P, P, P, I, I, I, I, P, P, ctypes.POINTER(P), I, I, I, P, P, P, P, P, P], I),
+    "gpu_kernels_nvfp4_moe_quantise_route": ([P, P, P, I, I, I, I, P, P, ctypes.POINTER(P), ctypes.POINTER(P), I, I, I, P, P, P, P, P, P], I),
     "gpu_kernels_nvfp4_peer_state_bytes": ([I, I, ctypes.POINTER(ctypes.c_size_t)], I),
     "gpu_kernels_nvfp4_peer_exchange": ([P, P, I, I, P, I, I, P, P], I),
     "gpu_kernels_nvfp4_plan_set_gather": ([P, ctypes.POINTER(P), I, I, I], I),
@@ -44,7 +44,8 @@ SIGNATURES = {
     "gpu_kernels_nvfp4_moe_route_count": ([P, I, I, P, P], I),
     "gpu_kernels_nvfp4_moe_route_plan": ([P, I, P, I, I, I, P, P, P, P, P, P, P, P], I),
     "gpu_kernels_nvfp4_moe_clear_live": ([P, I, I, I, P, P, P, P], I),
-    "gpu_kernels_nvfp4_moe_plan": ([P, I, I, I, I, I, P, P, P, P, P, P, P, P, P], I),
+    "gpu_kernels_nvfp4_moe_plan": ([P, I, I, I, I, I, P, P, P, P, P, P, P, I, P, P], I),
+    "gpu_kernels_nvfp4_moe_unpack_meta": ([P, I, P, I, I, I, P, P, P, P, P, P], I),
     "gpu_kernels_nvfp4_moe_count_exchange": ([P, I, I, P, P, I, I, I, P, P], I),
     "gpu_kernels_nvfp4_moe_pack": ([P, P, P, P, I, I, I, P, P, P, P, P], I),
     "gpu_kernels_nvfp4_moe_pack_to_pool": ([P, P, P, P, I, I, I, P, P, P, P, P, P, P], I),

@@ -477,14 +477,14 @@ int gpu_kernels_nvfp4_moe_route_count(const void* ids, int routes, int experts, 
 
 int gpu_kernels_nvfp4_moe_plan(const void* counts_matrix, int world, int rank, int experts, int capacity_rows,
                                int block_rows, void* send_offset, void* seg_src_offset, void* seg_pool_offset, void* block_expert,
-                               void* num_blocks, void* totals, void* peer_offset, void* cursor, void* stream) {
+                               void* num_blocks, void* totals, void* peer_offset, int peer_to_pool, void* cursor, void* stream) {
     return guarded([&] {
         nvfp4_b200::require_sm100();
         nvfp4_b200::moe_plan(const_cast<int*>(static_cast<const int*>(counts_matrix)), world, rank, experts, capacity_rows,
                              block_rows, static_cast<int*>(send_offset), static_cast<int*>(seg_src_offset),
                              static_cast<int*>(seg_pool_offset), static_cast<int*>(block_expert),
                              static_cast<int*>(num_blocks), static_cast<int*>(totals), static_cast<int*>(peer_offset),
-                             nullptr, 0, static_cast<int*>(cursor), static_cast<cudaStream_t>(stream));
+                             nullptr, 0, static_cast<int*>(cursor), peer_to_pool, static_cast<cudaStream_t>(stream));
         nvfp4_b200::g_launches.fetch_add(1, std::memory_order_relaxed);
     });
 }
@@ -499,8 +499,21 @@ int gpu_kernels_nvfp4_moe_route_plan(const void* ids, int routes, void* counts, 
                              static_cast<int*>(send_offset), static_cast<int*>(seg_src_offset),
                              static_cast<int*>(seg_pool_offset), static_cast<int*>(block_expert),
                              static_cast<int*>(num_blocks), static_cast<int*>(totals), nullptr,
-                             static_cast<const long long*>(ids), routes, static_cast<int*>(cursor),
+                             static_cast<const long long*>(ids), routes, static_cast<int*>(cursor), 0,
                              static_cast<cudaStream_t>(stream));
+        nvfp4_b200::g_launches.fetch_add(1, std::memory_order_relaxed);
+    });
+}
+
+int gpu_kernels_nvfp4_moe_unpack_meta(const void* side, int recv_capacity, const void* totals, int world, int local_experts,
+                                      int hidden, const void* seg_src_offset, const void* seg_pool_offset, void* pool_scales,
+                                      void* pool_weight, void* pool_dst, void* stream) {
+    return guarded([&] {
+        nvfp4_b200::moe_unpack_meta(static_cast<const uint8_t*>(side), recv_capacity, static_cast<const int*>(totals), world,
+                                    local_experts, hidden, static_cast<const int*>(seg_src_offset),
+                                    static_cast<const int*>(seg_pool_offset), static_cast<uint8_t*>(pool_scales),
+                                    static_cast<float*>(pool_weight), static_cast<int*>(pool_dst),
+                                    static_cast<cudaStream_t>(stream));
         nvfp4_b200::g_launches.fetch_add(1, std::memory_order_relaxed);
     });
 }
@@ -655,12 +668,12 @@ int gpu_kernels_nvfp4_moe_return_peer(const void* out_pool, const void* recv_row
 
 int gpu_kernels_nvfp4_moe_quantise_route(const void* x_bf16, const void* ids, const void* weights, int tokens, int topk,
                                          int hidden, int experts, const void* offsets, void* cursor, void* const* peer_recv,
-                                         int world, int local_experts, int recv_capacity, void* error, void* pool_packed,
-                                         void* pool_scales, void* pool_weight, void* route_row, void* stream) {
+                                         void* const* peer_meta, int world, int local_experts, int recv_capacity, void* error,
+                                         void* pool_packed, void* pool_scales, void* pool_weight, void* route_row, void* stream) {
     return guarded([&] {
         nvfp4_b200::moe_quantise_route(x_bf16, static_cast<const long long*>(ids), static_cast<const float*>(weights), tokens,
                                        topk, hidden, experts, static_cast<const int*>(offsets), static_cast<int*>(cursor),
-                                       peer_recv, world, local_experts, recv_capacity, static_cast<int*>(error),
+                                       peer_recv, peer_meta, world, local_experts, recv_capacity, static_cast<int*>(error),
                                        static_cast<uint8_t*>(pool_packed), static_cast<uint8_t*>(pool_scales),
                                        static_cast<float*>(pool_weight), static_cast<int*>(route_row),
                                        static_cast<cudaStream_t>(stream));

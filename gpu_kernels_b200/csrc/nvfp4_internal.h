@@ -55,7 +55,8 @@ struct MoeShape {
 void moe_route_count(const long long* ids, int routes, int experts, int* counts, cudaStream_t stream);
 void moe_plan(int* counts_matrix, int world, int rank, int experts, int pool_capacity_rows, int block_rows,
               int* send_offset, int* seg_src_offset, int* seg_pool_offset, int* block_expert, int* num_blocks,
-              int* totals, int* peer_offset, const long long* ids, int routes, int* cursor, cudaStream_t stream);
+              int* totals, int* peer_offset, const long long* ids, int routes, int* cursor, int peer_to_pool,
+              cudaStream_t stream);
 void moe_clear_live(const int* num_blocks, int block_rows, int pool_rows, int hidden, uint8_t* pool_scales,
                     float* pool_weight, int* pool_dst, cudaStream_t stream);
 // Expert parallelism over peer memory (NVLink stores into buffers of the other ranks' processes).
@@ -83,9 +84,12 @@ void moe_return_rows(const void* out_pool_bf16, const int* pool_of_recv, const i
 // to its expert, world > 0: into peer_recv[owner] at offsets[expert] + arrival order (bounds-checked against
 // recv_capacity); world == 0: into this rank's pool at row offsets[expert] + arrival order (route_row gets it).
 void moe_quantise_route(const void* x_bf16, const long long* ids, const float* weights, int tokens, int topk, int hidden,
-                        int experts, const int* offsets, int* cursor, void* const* peer_recv, int world, int local_experts,
-                        int recv_capacity, int* error, uint8_t* pool_packed, uint8_t* pool_scales, float* pool_weight,
-                        int* route_row, cudaStream_t stream);
+                        int experts, const int* offsets, int* cursor, void* const* peer_recv, void* const* peer_meta, int world,
+                        int local_experts, int recv_capacity, int* error, uint8_t* pool_packed, uint8_t* pool_scales,
+                        float* pool_weight, int* route_row, cudaStream_t stream);
+void moe_unpack_meta(const uint8_t* side, int recv_count_capacity, const int* totals, int world, int local_experts, int hidden,
+                     const int* seg_src_offset, const int* seg_pool_offset, uint8_t* pool_scales, float* pool_weight,
+                     int* pool_dst, cudaStream_t stream);
 int moe_payload_bytes(int hidden);
 // The device's four status words: [0] bits of ptx.cuh's StatusBits, [1] first tag, [2] cycles of the last GEMM.
 uint32_t* device_status_word(int device);

@@ -71,7 +71,7 @@ __global__ void plan_kernel(int* counts, int world, int rank, int experts, int c
                             int* __restrict__ send_offset, int* __restrict__ seg_src_offset,
                             int* __restrict__ seg_pool_offset, int* __restrict__ block_expert,
                             int* __restrict__ num_blocks, int* __restrict__ totals, int* __restrict__ peer_offset,
-                            const long long* __restrict__ ids, int routes, int* __restrict__ cursor) {
+                            const long long* __restrict__ ids, int routes, int* __restrict__ cursor, int peer_to_pool) {
     extern __shared__ int sh[];
     const int local_experts = experts / world;
     const int segments = world * local_experts;          // == experts
@@ -99,7 +99,7 @@ __global__ void plan_kernel(int* counts, int world, int rank, int experts, int c
     block_exclusive_scan(scan, experts, chunk);
     for (int ge = threadIdx.x; ge < experts; ge += blockDim.x) send_offset[ge] = scan[ge];
     if (threadIdx.x == 0) send_offset[experts] = chunk[blockDim.x];
-    if (peer_offset) {
+    if (peer_offset && !peer_to_pool) {
         // Where this rank's rows for global expert ge start in the RECEIVE buffer of the rank that owns ge
         // (source-major there): rows of lower-ranked sources for that destination, then this rank's rows
         // for the destination's earlier experts. Lets pack write straight into the peer's buffer.
@@ -148,6 +148,24 @@ __global__ void plan_kernel(int* counts, int world, int rank, int experts, int c
         *num_blocks = overflow ? 0 : pool_rows / block_rows;     // an overflowing plan computes nothing; the host reports it
         totals[1] = pool_rows;
         totals[2] = overflow ? 1 : 0;
+    }
+    if (peer_offset && peer_to_pool) {
+        // Where this rank's rows for global expert ge start in the POOL of the rank that owns ge: that rank's
+        // padded expert-major layout (the same arithmetic its own plan does in step 3), then the rows of
+        // lower-ranked sources for that expert. Lets the dispatch write packed rows straight into the pool.
+        __syncthreads();
+        for (int ge = threadIdx.x; ge < experts; ge += blockDim.x) {
+            int sum = 0;
+            for (int r = 0; r < world; ++r) sum += counts[r * experts + ge];
+            scan[ge] = (sum + block_rows - 1) / block_rows * block_rows;
+        }
+        __syncthreads();
+        block_exclusive_scan(scan, experts, chunk);
+        for (int ge = threadIdx.x; ge < experts; ge += blockDim.x) {
+            int before = 0;
+            for (int r = 0; r < rank; ++r) before += counts[r * experts + ge];
+            peer_offset[ge] = scan[ge] - scan[ge / local_experts * local_experts] + before;
+        }
     }
 }
 
@@ -217,6 +235,33 @@ __global__ void unpack_kernel(const uint8_t* __restrict__ recv_rows, const int* 
         // where the result of this row goes: (source rank << 24) | (route index + 1); 0 stays "padding"
         if (pool_dst)
             pool_dst[row] = ((lo / local_experts) << 24) | (*reinterpret_cast<const int*>(in + hidden / 2 + hidden / 16 + 4) + 1);
+    }
+}
+
+// After a dispatch that wrote the packed rows straight into this rank's pool: one warp per received row lays
+// the row's scale bytes (row-major in the side buffer) into the pool's scale atoms and records its route
+// weight and where its result goes. p counts received rows source-major, as the plan's segment tables do.
+__global__ void unpack_meta_kernel(const uint8_t* __restrict__ side, const int* __restrict__ totals, int segments, int hidden,
+                                   const int* __restrict__ seg_src_offset, const int* __restrict__ seg_pool_offset,
+                                   uint8_t* __restrict__ pool_scales, float* __restrict__ pool_weight,
+                                   int* __restrict__ pool_dst, int local_experts) {
+    const int lane = threadIdx.x & 31;
+    const int p = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (p >= totals[0] || totals[2]) return;
+    int below = 0;
+    for (int base = 0; base < segments; base += 32) {
+        const int i = base + lane;
+        below += __popc(__ballot_sync(0xFFFFFFFFu, i < segments && __ldg(seg_src_offset + i) <= p));
+    }
+    const int lo = below - 1;
+    const int row = seg_pool_offset[lo] + (p - seg_src_offset[lo]);
+    const uint8_t* in = side + size_t(row) * (hidden / 16 + PAYLOAD_TAIL);
+    for (int q = lane; q < hidden / 64; q += 32)
+        *reinterpret_cast<uint32_t*>(pool_scales + scale_byte_offset(row, 4 * q, hidden)) =
+            *reinterpret_cast<const uint32_t*>(in + 4 * q);
+    if (lane == 0) {
+        pool_weight[row] = *reinterpret_cast<const float*>(in + hidden / 16);
+        pool_dst[row] = ((lo / local_experts) << 24) | (*reinterpret_cast<const int*>(in + hidden / 16 + 4) + 1);
     }
 }
 
@@ -360,7 +405,8 @@ __global__ void __launch_bounds__(256)
 quantise_route_kernel(const __nv_bfloat16* __restrict__ x, const long long* __restrict__ ids,
                       const float* __restrict__ weights, int topk, int hidden, int experts,
                       const int* __restrict__ offsets, int* __restrict__ cursor,
-                      PeerBuffers recv, int world, int local_experts, int recv_capacity, int* __restrict__ error,
+                      PeerBuffers recv, PeerBuffers meta, int to_pool, int world, int local_experts, int recv_capacity,
+                      int* __restrict__ error,
                       uint8_t* __restrict__ pool_packed, uint8_t* __restrict__ pool_scales,
                       float* __restrict__ pool_weight, int* __restrict__ route_row) {
     extern __shared__ __align__(16) uint8_t row[];              // codes [hidden/2] | scale bytes [hidden/16] | int dst[topk]
@@ -391,11 +437,22 @@ quantise_route_kernel(const __nv_bfloat16* __restrict__ x, const long long* __re
                 atomicOr(error, 1);
             } else {
                 const int owner = int(ids[route]) / local_experts;
-                uint8_t* out = static_cast<uint8_t*>(recv.ptr[owner]) + size_t(d) * payload_bytes(hidden);
-                ptx::bulk_store(out, row_smem, uint32_t(row_bytes));
-                ptx::tma_store_commit();
-                *reinterpret_cast<float*>(out + row_bytes) = weights[route];
-                *reinterpret_cast<int*>(out + row_bytes + 4) = route;           // where the result goes back to
+                if (to_pool) {
+                    // d is a row of the owner's pool: the codes land where FC1 reads them; scale bytes, weight
+                    // and route index go to the owner's side buffer (its scale atoms are laid out there)
+                    uint8_t* side = static_cast<uint8_t*>(meta.ptr[owner]) + size_t(d) * (hidden / 16 + PAYLOAD_TAIL);
+                    ptx::bulk_store(static_cast<uint8_t*>(recv.ptr[owner]) + size_t(d) * (hidden / 2), row_smem, uint32_t(hidden / 2));
+                    ptx::bulk_store(side, row_smem + uint32_t(hidden / 2), uint32_t(hidden / 16));
+                    ptx::tma_store_commit();
+                    *reinterpret_cast<float*>(side + hidden / 16) = weights[route];
+                    *reinterpret_cast<int*>(side + hidden / 16 + 4) = route;
+                } else {
+                    uint8_t* out = static_cast<uint8_t*>(recv.ptr[owner]) + size_t(d) * payload_bytes(hidden);
+                    ptx::bulk_store(out, row_smem, uint32_t(row_bytes));
+                    ptx::tma_store_commit();
+                    *reinterpret_cast<float*>(out + row_bytes) = weights[route];
+                    *reinterpret_cast<int*>(out + row_bytes + 4) = route;       // where the result goes back to
+                }
             }
             ptx::tma_store_wait_read<0>();                      // the copies have read the row: the CTA may go
         }
@@ -461,7 +518,8 @@ void moe_route_count(const long long* ids, int routes, int experts, int* counts,
 
 void moe_plan(int* counts_matrix, int world, int rank, int experts, int pool_capacity_rows, int block_rows,
               int* send_offset, int* seg_src_offset, int* seg_pool_offset, int* block_expert, int* num_blocks,
-              int* totals, int* peer_offset, const long long* ids, int routes, int* cursor, cudaStream_t stream) {
+              int* totals, int* peer_offset, const long long* ids, int routes, int* cursor, int peer_to_pool,
+              cudaStream_t stream) {
     if (ids && (world != 1 || routes < 0)) throw std::invalid_argument("moe plan: counting the routes in the plan kernel is for one rank");
     if (world <= 0 || rank < 0 || rank >= world || experts <= 0 || experts % world || experts > 4096)
         throw std::invalid_argument("moe plan: experts must divide over the ranks (and be <= 4096)");
@@ -470,7 +528,7 @@ void moe_plan(int* counts_matrix, int world, int rank, int experts, int pool_cap
     const int local = experts / world;
     plan_kernel<<<1, 256, (experts + local + 257) * sizeof(int), stream>>>(counts_matrix, world, rank, experts, pool_capacity_rows, block_rows,
                                                                    send_offset, seg_src_offset, seg_pool_offset,
-                                                                   block_expert, num_blocks, totals, peer_offset, ids, routes, cursor);
+                                                                   block_expert, num_blocks, totals, peer_offset, ids, routes, cursor, peer_to_pool);
     cuda_check(cudaGetLastError());
 }
 
@@ -572,27 +630,29 @@ void moe_return_peer(const void* out_pool_bf16, const uint8_t* recv_rows, const 
 }
 
 void moe_quantise_route(const void* x_bf16, const long long* ids, const float* weights, int tokens, int topk, int hidden,
-                        int experts, const int* offsets, int* cursor, void* const* peer_recv, int world, int local_experts,
-                        int recv_capacity, int* error, uint8_t* pool_packed, uint8_t* pool_scales, float* pool_weight,
-                        int* route_row, cudaStream_t stream) {
+                        int experts, const int* offsets, int* cursor, void* const* peer_recv, void* const* peer_meta, int world,
+                        int local_experts, int recv_capacity, int* error, uint8_t* pool_packed, uint8_t* pool_scales,
+                        float* pool_weight, int* route_row, cudaStream_t stream) {
     check_hidden(hidden, "moe quantise_route");
     if (tokens <= 0) return;
     if (topk < 1 || topk > 256 || experts < 1 || !x_bf16 || !ids || !weights || !offsets || !cursor)
         throw std::invalid_argument("moe quantise_route: bad argument");
-    PeerBuffers recv{};
+    PeerBuffers recv{}, meta{};
     if (world > 0) {
         if (world > 8 || !peer_recv || !error || local_experts < 1) throw std::invalid_argument("moe quantise_route: 1..8 ranks");
         for (int r = 0; r < world; ++r) {
-            if (!peer_recv[r]) throw std::invalid_argument("moe quantise_route: null peer buffer");
+            if (!peer_recv[r] || (peer_meta && !peer_meta[r])) throw std::invalid_argument("moe quantise_route: null peer buffer");
             recv.ptr[r] = peer_recv[r];
+            if (peer_meta) meta.ptr[r] = peer_meta[r];
         }
     } else if (!pool_packed || !pool_scales || !pool_weight || !route_row) {
         throw std::invalid_argument("moe quantise_route: null pool");
     }
     const size_t smem = ((size_t(hidden) / 2 + hidden / 16 + 15) & ~size_t(15)) + size_t(topk) * sizeof(int);
     quantise_route_kernel<<<tokens, 256, smem, stream>>>(static_cast<const __nv_bfloat16*>(x_bf16), ids, weights, topk, hidden,
-                                                        experts, offsets, cursor, recv, world, local_experts, recv_capacity,
-                                                        error, pool_packed, pool_scales, pool_weight, route_row);
+                                                        experts, offsets, cursor, recv, meta, peer_meta ? 1 : 0, world,
+                                                        local_experts, recv_capacity, error, pool_packed, pool_scales,
+                                                        pool_weight, route_row);
     cuda_check(cudaGetLastError());
 }
 
@@ -612,6 +672,18 @@ clear_live_kernel(const int* __restrict__ num_blocks, int block_rows, int hidden
         pool_weight[row0 + threadIdx.x] = 0.0f;
         if (pool_dst) pool_dst[row0 + threadIdx.x] = 0;
     }
+}
+
+void moe_unpack_meta(const uint8_t* side, int recv_count_capacity, const int* totals, int world, int local_experts, int hidden,
+                     const int* seg_src_offset, const int* seg_pool_offset, uint8_t* pool_scales, float* pool_weight,
+                     int* pool_dst, cudaStream_t stream) {
+    check_hidden(hidden, "moe unpack_meta");
+    if (recv_count_capacity <= 0) return;
+    if (!side || !pool_scales || !pool_weight || !pool_dst) throw std::invalid_argument("moe unpack_meta: null pointer");
+    unpack_meta_kernel<<<(size_t(recv_count_capacity) * 32 + 255) / 256, 256, 0, stream>>>(
+        side, totals, world * local_experts, hidden, seg_src_offset, seg_pool_offset, pool_scales, pool_weight, pool_dst,
+        local_experts);
+    cuda_check(cudaGetLastError());
 }
 
 void moe_clear_live(const int* num_blocks, int block_rows, int pool_rows, int hidden, uint8_t* pool_scales,

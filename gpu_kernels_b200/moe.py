@@ -19,7 +19,7 @@ import torch
 import torch.distributed as dist
 
 from . import _lib
-from .peer import PeerGroup, SharedBuffer
+from .peer import DeviceView, PeerGroup, SharedBuffer
 from .nvfp4 import quantize
 
 
@@ -124,9 +124,13 @@ class Nvfp4MoE:
             "ret_recv": ((routes, self.hidden), bf16, False),
         }
         self._peer = None
+        # peer exchange with the fused dispatch: packed rows go straight into the owners' pools, so the pool
+        # itself is what the other ranks map, plus a side buffer for each row's scale bytes, weight and route
+        self.to_pool = self.exchange == "peer" and fused_dispatch
         if self.exchange == "peer":
             self._setup_peer_buffers(routes, recv_cap)
-        self.pool_packed = torch.zeros((self.pool_rows, self.hidden // 2), dtype=u8, device=d)
+        if not self.to_pool:
+            self.pool_packed = torch.zeros((self.pool_rows, self.hidden // 2), dtype=u8, device=d)
         self.pool_scales = torch.zeros(self.pool_rows * self.hidden // 16, dtype=u8, device=d)
         self.pool_weight = torch.zeros(self.pool_rows, dtype=torch.float32, device=d)
         self.pool_of_recv = torch.zeros(recv_cap, dtype=i32, device=d)
@@ -161,11 +165,18 @@ class Nvfp4MoE:
     def _setup_peer_buffers(self, routes, recv_cap):
         """Receive and result-slot buffers that every rank of the group can write (CUDA IPC), and the barrier."""
         d = self.device
-        recv = SharedBuffer(recv_cap * self.payload, d, self.group)
+        if self.to_pool:
+            pool = SharedBuffer(self.pool_rows * (self.hidden // 2), d, self.group)
+            side = SharedBuffer(self.pool_rows * (self.hidden // 16 + 16), d, self.group)
+            self.pool_packed = torch.as_tensor(DeviceView(pool.own, (self.pool_rows, self.hidden // 2), "|u1"), device=d)
+            recv = None
+        else:
+            recv = SharedBuffer(recv_cap * self.payload, d, self.group)
+            pool = side = None
         slots = SharedBuffer(routes * self.hidden * 2, d, self.group)
         self._peers = PeerGroup(d, self.group, max_ints=self.experts)
-        self._peer = {"recv": recv, "slots": slots}
-        self.recv_ptr = recv.own
+        self._peer = {"recv": recv, "slots": slots, "pool": pool, "side": side}
+        self.recv_ptr = recv.own if recv is not None else None
         self.slots_ptr = slots.own
         self.slot_table = slots.device_table
         self.peer_offset = torch.zeros(self.experts, dtype=torch.int32, device=d)
@@ -232,7 +243,8 @@ class Nvfp4MoE:
                 self.counts_matrix.data_ptr(), self.world, self.rank, self.experts, self.pool_rows, block_rows,
                 self.send_offset.data_ptr(), self.seg_src.data_ptr(), self.seg_pool.data_ptr(),
                 self.block_expert.data_ptr(), self.num_blocks.data_ptr(), self.totals.data_ptr(),
-                self.peer_offset.data_ptr() if self._peer is not None else None, self.cursor.data_ptr(), s))
+                self.peer_offset.data_ptr() if self._peer is not None else None, 1 if self.to_pool else 0,
+                self.cursor.data_ptr(), s))
         # padding rows of the live blocks must contribute nothing: clear their scale bytes, weights and codes
         _lib.check(lib.gpu_kernels_nvfp4_moe_clear_live(
             self.num_blocks.data_ptr(), block_rows, self.pool_rows, self.hidden, self.pool_scales.data_ptr(),
@@ -260,7 +272,7 @@ class Nvfp4MoE:
         weights = weights.contiguous().to(torch.float32)
         with torch.cuda.device(self.device):
             s = _stream()
-            fused_dispatch = self.fused_dispatch and (self.world == 1 or self._peer is not None) and x.dtype == torch.bfloat16
+            fused_dispatch = self.fused_dispatch and (self.world == 1 or self._peer is not None)
             self._mark("start")
             if not fused_dispatch:
                 # quantise the tokens once; rows are padded to whole 128-row scale atoms
@@ -279,24 +291,37 @@ class Nvfp4MoE:
                 xq, xs = quantize(self.x_pad)
             total_recv = sum(recv_splits) if recv_splits is not None else 0
             if fused_dispatch and (self.world == 1 or send_splits is None):
-                x = x.contiguous()
+                x = x.to(torch.bfloat16).contiguous()             # as the stand-alone route's padded copy does
                 peer = self.world > 1
+                if peer and self.to_pool:
+                    targets, side, capacity = self._peer["pool"].table, self._peer["side"].table, self.pool_rows
+                elif peer:
+                    targets, side, capacity = self._peer["recv"].table, None, self.recv_cap
+                else:
+                    targets, side, capacity = None, None, 0
                 _lib.check(lib.gpu_kernels_nvfp4_moe_quantise_route(
                     x.data_ptr(), ids.data_ptr(), weights.data_ptr(), tokens, self.topk, self.hidden, self.experts,
                     (self.peer_offset if peer else self.seg_pool).data_ptr(), self.cursor.data_ptr(),
-                    self._peer["recv"].table if peer else None, self.world if peer else 0, self.local_experts,
-                    self.recv_cap, self.peer_error.data_ptr() if peer else None,
+                    targets, side, self.world if peer else 0, self.local_experts,
+                    capacity, self.peer_error.data_ptr() if peer else None,
                     None if peer else self.pool_packed.data_ptr(), None if peer else self.pool_scales.data_ptr(),
                     None if peer else self.pool_weight.data_ptr(), None if peer else self.send_pos.data_ptr(), s))
                 if peer:
                     self._mark("quantise + pack into the peers' receive buffers")
                     self._barrier()
                     self._mark("barrier")
-                    _lib.check(lib.gpu_kernels_nvfp4_moe_unpack(
-                        self.recv_ptr, self.recv_cap, self.totals.data_ptr(), self.world, self.local_experts,
-                        self.hidden, self.seg_src.data_ptr(), self.seg_pool.data_ptr(), self.pool_packed.data_ptr(),
-                        self.pool_scales.data_ptr(), self.pool_weight.data_ptr(), self.pool_of_recv.data_ptr(),
-                        self.pool_dst.data_ptr(), s))
+                    if self.to_pool:
+                        # the packed rows are already in place: only scale atoms, weights and destinations are left
+                        _lib.check(lib.gpu_kernels_nvfp4_moe_unpack_meta(
+                            self._peer["side"].own, self.recv_cap, self.totals.data_ptr(), self.world, self.local_experts,
+                            self.hidden, self.seg_src.data_ptr(), self.seg_pool.data_ptr(), self.pool_scales.data_ptr(),
+                            self.pool_weight.data_ptr(), self.pool_dst.data_ptr(), s))
+                    else:
+                        _lib.check(lib.gpu_kernels_nvfp4_moe_unpack(
+                            self.recv_ptr, self.recv_cap, self.totals.data_ptr(), self.world, self.local_experts,
+                            self.hidden, self.seg_src.data_ptr(), self.seg_pool.data_ptr(), self.pool_packed.data_ptr(),
+                            self.pool_scales.data_ptr(), self.pool_weight.data_ptr(), self.pool_of_recv.data_ptr(),
+                            self.pool_dst.data_ptr(), s))
             elif self.world > 1 and send_splits is None:
                 _lib.check(lib.gpu_kernels_nvfp4_moe_pack_peer(
                     xq.data_ptr(), xs.data_ptr(), ids.data_ptr(), weights.data_ptr(), tokens, self.topk, self.hidden,
@@ -414,9 +439,12 @@ class Nvfp4MoE:
     def close(self) -> None:
         lib = _lib.load()
         if self._peer is not None:
+            if self.to_pool:
+                del self.pool_packed                            # a view of the shared pool, freed below
             self._peers.close()
-            self._peer["slots"].close()
-            self._peer["recv"].close()
+            for name in ("slots", "recv", "pool", "side"):
+                if self._peer[name] is not None:
+                    self._peer[name].close()
             self._peer = None
         for pair in getattr(self, "_plans", {}).values():
             for plan in pair:

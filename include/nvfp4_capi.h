@@ -140,11 +140,13 @@ int gpu_kernels_nvfp4_moe_route_count(const void* ids, int routes, int experts, 
  * send_offset [experts+1], seg_src_offset [world*local+1], seg_pool_offset [world*local],
  * block_expert [capacity_rows/block_rows], num_blocks [1], totals [3] = {rows received, pool rows used, overflow};
  * peer_offset [experts] (may be null): where this rank's rows for each global expert start in the receive
- * buffer of the rank that owns it, for gpu_kernels_nvfp4_moe_pack_peer. cursor [experts] (may be null): the
- * arrival counters of the dispatch kernels, zeroed here. */
+ * buffer of the rank that owns it, for gpu_kernels_nvfp4_moe_pack_peer; with peer_to_pool != 0 instead the row of
+ * that rank's POOL where they start (every rank can do the owner's layout arithmetic from the gathered counts), for
+ * the dispatch that writes packed rows straight into the pools. cursor [experts] (may be null): the arrival
+ * counters of the dispatch kernels, zeroed here. */
 int gpu_kernels_nvfp4_moe_plan(const void* counts_matrix, int world, int rank, int experts, int capacity_rows,
                                int block_rows, void* send_offset, void* seg_src_offset, void* seg_pool_offset, void* block_expert,
-                               void* num_blocks, void* totals, void* peer_offset, void* cursor, void* stream);
+                               void* num_blocks, void* totals, void* peer_offset, int peer_to_pool, void* cursor, void* stream);
 /* One rank (nothing to exchange): histogram of the routes (ids int64 [routes] -> counts int32 [experts], written
  * here) and the plan above in ONE launch, which also zeroes cursor [experts], the arrival counters of the
  * dispatch kernels. Replaces a memset, route_count, a copy, plan and another memset. */
@@ -217,12 +219,21 @@ int gpu_kernels_nvfp4_gemm_host_static(int M, int N, int K, const void* A, const
  * pack_to_pool, with the same bits): x [tokens, hidden] bf16 is quantised row by row in shared memory and each
  * route's row (codes, scale bytes, weight, route index) goes straight to its expert. world > 0: into
  * peer_recv[expert / local_experts] (host array of `world` device pointers) at row offsets[expert] + arrival
- * order, refused and flagged in `error` beyond recv_capacity. world == 0: into this rank's pool (packed rows,
- * VEC16 scale atoms, weights) at row offsets[expert] + arrival order, which route_row [tokens * topk] records. */
+ * order, refused and flagged in `error` beyond recv_capacity; with peer_meta (another such array) not null,
+ * peer_recv are the ranks' POOLS (packed rows, hidden/2 bytes each) and the row's scale bytes, weight and route
+ * index go to row offsets[expert] + arrival order of peer_meta[owner] (hidden/16 + 16 bytes per row), for
+ * gpu_kernels_nvfp4_moe_unpack_meta on the owner. world == 0: into this rank's pool (packed rows, VEC16 scale
+ * atoms, weights) at row offsets[expert] + arrival order, which route_row [tokens * topk] records. */
 int gpu_kernels_nvfp4_moe_quantise_route(const void* x_bf16, const void* ids, const void* weights, int tokens, int topk,
                                          int hidden, int experts, const void* offsets, void* cursor, void* const* peer_recv,
-                                         int world, int local_experts, int recv_capacity, void* error, void* pool_packed,
-                                         void* pool_scales, void* pool_weight, void* route_row, void* stream);
+                                         void* const* peer_meta, int world, int local_experts, int recv_capacity, void* error,
+                                         void* pool_packed, void* pool_scales, void* pool_weight, void* route_row, void* stream);
+/* The receiving side of that dispatch: for each received row (recv_capacity bounds their number, totals[0] on the
+ * device gives it) lays the scale bytes from `side` into the pool's scale atoms and fills pool_weight and
+ * pool_dst = (source rank << 24) | (route index + 1). seg_src_offset / seg_pool_offset: the plan's tables. */
+int gpu_kernels_nvfp4_moe_unpack_meta(const void* side, int recv_capacity, const void* totals, int world, int local_experts,
+                                      int hidden, const void* seg_src_offset, const void* seg_pool_offset, void* pool_scales,
+                                      void* pool_weight, void* pool_dst, void* stream);
 int gpu_kernels_nvfp4_moe_pack_peer(const void* xq, const void* xs, const void* ids, const void* weights, int tokens,
                                     int topk, int hidden, int world, int local_experts, const void* peer_offset,
                                     void* cursor, void* const* peer_recv, int recv_capacity, void* error, void* stream);
