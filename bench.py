@@ -532,6 +532,15 @@ def run_moe(args, rank, world, local_rank):
     barrier()
     t1 = time.perf_counter()
     ms = start.elapsed_time(stop)
+    if (t1 - t0) < 0.5:
+        # the timed region is shorter than a few sampling periods of the clock sampler: every rank keeps the same
+        # load running for the same number of further steps (the forward is collective), for the sampler only
+        more = torch.tensor([0.7 / max(ms / args.steps * 1e-3, 1e-6)], device=dev)
+        if world > 1:
+            dist.all_reduce(more, op=dist.ReduceOp.MIN)
+        for i in range(int(min(more.item(), 20000))):
+            replay(i)
+        barrier()
     clocks = sampler.stop(t0, t1) if sampler is not None else None
     # end to end: inputs from pinned host memory, result back to the host, every step
     host = [tuple(t.cpu().pin_memory() for t in s_) for s_ in sets]
