@@ -196,6 +196,47 @@ def test_fused_dispatch_matches_quantise_then_pack(g):
         assert np.array_equal(pools[0][1][real], pools[1][1][real])
 
 
+@pytest.mark.parametrize("world,experts,block_rows", [(2, 8, 128), (4, 32, 256), (8, 256, 128)])
+def test_plan_agrees_across_ranks_on_pool_rows(g, world, experts, block_rows):
+    # every rank derives, from the same gathered counts, where ITS rows start in the pool of each expert's
+    # owner (peer_to_pool) and, as an owner, where every source's rows start in its own pool: the two must
+    # be the same numbers, or a dispatched row would land in another route's place
+    import ctypes
+    from gpu_kernels_b200 import _lib
+    lib = _lib.load()
+    rng = np.random.default_rng(world * 1000 + experts)
+    counts = rng.integers(0, 300, size=(world, experts)).astype(np.int32)
+    counts[rng.random((world, experts)) < 0.3] = 0                         # empty groups
+    local = experts // world
+    dev = lambda a: torch.from_numpy(a).cuda()
+    matrix = dev(counts)
+    capacity = int(((counts.sum(0) + block_rows - 1) // block_rows * block_rows).reshape(world, local).sum(1).max())
+    capacity = -(-capacity // 256) * 256
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    peer_offsets, seg_pools = [], []
+    for rank in range(world):
+        i32 = lambda n: torch.zeros(n, dtype=torch.int32, device="cuda")
+        send_offset, seg_src, seg_pool = i32(experts + 1), i32(experts + 1), i32(experts)
+        block_expert, num_blocks, totals, peer_offset, cursor = i32(capacity // 128), i32(1), i32(4), i32(experts), i32(experts)
+        _lib.check(lib.gpu_kernels_nvfp4_moe_plan(
+            matrix.data_ptr(), world, rank, experts, capacity, block_rows, send_offset.data_ptr(), seg_src.data_ptr(),
+            seg_pool.data_ptr(), block_expert.data_ptr(), num_blocks.data_ptr(), totals.data_ptr(), peer_offset.data_ptr(),
+            1, cursor.data_ptr(), stream))
+        torch.cuda.synchronize()
+        assert int(totals[2].item()) == 0
+        peer_offsets.append(to_np(peer_offset))
+        seg_pools.append(to_np(seg_pool).reshape(world, local))            # [source rank, local expert] on this owner
+    for src in range(world):
+        for ge in range(experts):
+            owner, e = divmod(ge, local)
+            assert peer_offsets[src][ge] == seg_pools[owner][src, e], (src, ge)
+    # and the owner's layout is the padded expert-major one
+    for owner in range(world):
+        padded = (counts[:, owner * local:(owner + 1) * local].sum(0) + block_rows - 1) // block_rows * block_rows
+        starts = np.concatenate(([0], np.cumsum(padded)[:-1]))
+        assert np.array_equal(seg_pools[owner][0], starts)
+
+
 def test_routing_plan_pack_unpack_exact(g):
     tokens, hidden, inter, experts, topk = 150, 512, 256, 8, 3
     x, logits, w1, w2 = make_layer(5, tokens, hidden, inter, experts, topk, skew=True)
