@@ -32,6 +32,9 @@ SIGNATURES = {
     "gpu_kernels_nvfp4_peer_exchange": ([P, P, I, I, P, I, I, P, P], I),
     "gpu_kernels_nvfp4_plan_set_gather": ([P, ctypes.POINTER(P), I, I, I], I),
     "gpu_kernels_nvfp4_plan_info": ([P, ctypes.POINTER(I)], I),
+    "gpu_kernels_nvfp4_plan_placement_misses": ([P, ctypes.POINTER(ctypes.c_uint)], I),
+    "gpu_kernels_nvfp4_side_route": ([ctypes.c_char_p, I, I, ctypes.POINTER(ctypes.c_uint)], I),
+    "gpu_kernels_nvfp4_l2_census": ([ctypes.POINTER(ctypes.c_uint), I, ctypes.POINTER(I)], I),
     "gpu_kernels_nvfp4_plan_profile": ([P, P, P, ctypes.POINTER(ctypes.c_ulonglong), I, ctypes.POINTER(I)], I),
     "gpu_kernels_nvfp4_last_kernel_cycles": ([], ctypes.c_uint),
     "gpu_kernels_nvfp4_gemm_host": ([I, I, I, P, P, P, P, P, F, P], I),
@@ -47,12 +50,12 @@ SIGNATURES = {
     "gpu_kernels_nvfp4_moe_plan": ([P, I, I, I, I, I, P, P, P, P, P, P, P, I, P, P], I),
     "gpu_kernels_nvfp4_moe_unpack_meta": ([P, I, P, I, I, I, P, P, P, P, P, P], I),
     "gpu_kernels_nvfp4_moe_count_exchange": ([P, I, I, P, P, I, I, I, P, P], I),
-    "gpu_kernels_nvfp4_moe_pack": ([P, P, P, P, I, I, I, P, P, P, P, P], I),
-    "gpu_kernels_nvfp4_moe_pack_to_pool": ([P, P, P, P, I, I, I, P, P, P, P, P, P, P], I),
+    "gpu_kernels_nvfp4_moe_pack": ([P, P, P, P, I, I, I, I, P, P, P, P, P], I),
+    "gpu_kernels_nvfp4_moe_pack_to_pool": ([P, P, P, P, I, I, I, I, P, P, P, P, P, P, P], I),
     "gpu_kernels_nvfp4_moe_unpack": ([P, I, P, I, I, I, P, P, P, P, P, P, P, P], I),
     "gpu_kernels_nvfp4_moe_swiglu_quant": ([P, P, P, I, I, I, F, P, P, P], I),
     "gpu_kernels_nvfp4_moe_return_rows": ([P, P, P, I, I, P, P], I),
-    "gpu_kernels_nvfp4_moe_reduce": ([P, P, I, I, I, P, P], I),
+    "gpu_kernels_nvfp4_moe_reduce": ([P, P, I, I, I, P, P, I, P], I),
     "gpu_kernels_nvfp4_gemm_host_static": ([I, I, I, P, P, P, P, P, F, P], I),
     "gpu_kernels_nvfp4_moe_pack_peer": ([P, P, P, P, I, I, I, I, I, P, P, ctypes.POINTER(P), I, P, P], I),
     "gpu_kernels_nvfp4_moe_return_peer": ([P, P, P, P, P, I, I, I, I, ctypes.POINTER(P), I, P, P], I),

@@ -19,7 +19,7 @@ ROOT = Path(__file__).resolve().parents[1]
 CSRC = ROOT / "gpu_kernels_b200" / "csrc"
 OUT_DIR = ROOT / "build"
 LIB_NAME = "libgpu_kernels_nvfp4_bench.so"
-SOURCES = ("nvfp4_quant.cu", "nvfp4_gemm.cu", "nvfp4_moe.cu", "nvfp4_capi.cu")
+SOURCES = ("nvfp4_quant.cu", "nvfp4_gemm.cu", "nvfp4_schedule.cu", "nvfp4_moe.cu", "nvfp4_capi.cu")
 ARCH = ("-gencode", "arch=compute_100a,code=sm_100a")
 
 
@@ -50,12 +50,19 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     if not force and lib.exists() and stamp.exists() and stamp.read_text() == digest:
         return lib
     nvcc = _nvcc()
-    objects = []
-    for src in SOURCES:
+
+    def compile_one(src: str):
         obj = OUT_DIR / (src + ".o")
         cmd = [nvcc, "-std=c++17", "-O3", *ARCH, "-lineinfo", "-Xcompiler", "-fPIC", "-Xptxas", "-v",
                "-I", str(ROOT / "include"), "-I", str(CSRC), "-c", str(CSRC / src), "-o", str(obj)]
         r = subprocess.run(cmd, capture_output=True, text=True)
+        return src, obj, r
+
+    from concurrent.futures import ThreadPoolExecutor
+    with ThreadPoolExecutor(max_workers=min(len(SOURCES), os.cpu_count() or 1)) as pool:
+        results = list(pool.map(compile_one, SOURCES))
+    objects = []
+    for src, obj, r in results:
         if verbose or r.returncode:
             sys.stderr.write(r.stdout + r.stderr)
         if r.returncode:

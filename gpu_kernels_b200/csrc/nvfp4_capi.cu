@@ -10,6 +10,7 @@
 
 #include <atomic>
 #include <cstring>
+#include <map>
 #include <memory>
 #include <mutex>
 #include <vector>
@@ -17,7 +18,8 @@
 
 namespace nvfp4_b200 {
 extern std::atomic<unsigned long long> g_launches;
-int gemm_stage_count(int cta_group, int tile_n);
+int gemm_stage_count(int cta_group, int tile_n, int direct_store);
+void validate_device_slot(int device);
 unsigned last_kernel_cycles();
 int gemm_profile(const gpu_kernels::Nvfp4Params& p, __half* C, cudaStream_t stream, unsigned long long* host, int max_words);
 }
@@ -153,7 +155,7 @@ struct HostGemm {
     }
 };
 std::mutex g_host_lock;
-HostGemm g_host;
+std::map<int, HostGemm> g_host;          // one staging set per device: buffers and tensor maps belong to a GPU
 
 // ---- staging for gpu_kernels_nvfp4_gemm_host_static ---------------------------------------
 // Some hosts of this library may not allocate device memory while they run: a service that sized
@@ -246,9 +248,10 @@ int gpu_kernels_nvfp4_custom(void* plan, void* C, void* stream) {
 
 int gpu_kernels_nvfp4_validate(void* plan) {
     return guarded([&] {
-        // the status word is per device, not per plan: a null plan checks the current device (grouped launches)
+        // a plan reports to its own status slot; a null plan checks every slot of the current device (this is
+        // how grouped launches and the expert-path kernels, which report to the device's own slot, are checked)
         if (!plan) gpu_kernels::nvfp4_sm100_implementation().validate();
-        else as_plan(plan).impl.validate();
+        else gpu_kernels::nvfp4_validate_plan(as_plan(plan).params);
     });
 }
 
@@ -298,6 +301,14 @@ int gpu_kernels_nvfp4_plan_set_option(void* plan, const char* key, int value) {
         } else if (std::strcmp(key, "k_skew") == 0) {
             if (value < 0) throw std::invalid_argument("set_option: k_skew must be >= 0");
             p.params.k_skew = value;
+        } else if (std::strcmp(key, "out_bf16") == 0) {
+            if (p.params.gather_world) throw std::invalid_argument("set_option: choose the output type before set_gather");
+            p.params.out_bf16 = value ? 1 : 0;
+        } else if (std::strcmp(key, "l2_side") == 0) {
+            // value 1: ask for the L2-side-aware order; refused (error) when the census cannot provide it
+            if (!gpu_kernels::nvfp4_set_l2_side_order(p.params, value, nullptr) && value)
+                throw std::runtime_error("set_option: no L2-side order for this plan (grid smaller than the GPU, too few tiles, "
+                                         "or the census did not split the SMs into two sides)");
         } else if (std::strcmp(key, "split_k") == 0) {
             if (!value) {
                 p.params.split_k = 0;
@@ -329,8 +340,9 @@ int gpu_kernels_nvfp4_plan_info(void* plan, int* info) {
         Plan& p = as_plan(plan);
         if (!info) throw std::invalid_argument("plan_info: null output");
         const auto& q = p.params;
-        const int values[10] = {q.M, q.N, q.K, q.clusters, q.cta_group, q.tile_n, q.group_m,
-                                nvfp4_b200::gemm_stage_count(q.cta_group, q.tile_n), q.split_k, q.k_skew};
+        const int values[16] = {q.M, q.N, q.K, q.clusters, q.cta_group, q.tile_n, q.group_m,
+                                nvfp4_b200::gemm_stage_count(q.cta_group, q.tile_n, q.direct_store), q.split_k, q.k_skew,
+                                q.direct_store, q.out_bf16, q.route ? 1 : 0, q.side_units[0], q.side_units[1], q.status_slot};
         std::memcpy(info, values, sizeof(values));
     });
 }
@@ -342,14 +354,16 @@ int gpu_kernels_nvfp4_gemm_host(int M, int N, int K, const void* A, const void* 
         if (!A || !B || !SFA || !SFB || !C) throw std::invalid_argument("gemm_host: null pointer");
         nvfp4_b200::require_sm100();
         auto stream = static_cast<cudaStream_t>(stream_);
+        int device = 0;
+        cuda_check(cudaGetDevice(&device));
         std::lock_guard<std::mutex> hold(g_host_lock);
-        HostGemm& h = g_host;
+        HostGemm& h = g_host[device];
         const size_t a_bytes = size_t(M) * K / 2, b_bytes = size_t(N) * K / 2;
         const size_t sfa_bytes = size_t(M) * K / 16, sfb_bytes = size_t(N) * K / 16, c_bytes = size_t(M) * N * 2;
         if (h.M != M || h.N != N || h.K != K) {
             h.release();
-            if (M <= 0 || N <= 0 || K <= 0 || M % 128 || N % 128 || K % 256)
-                throw std::invalid_argument("gemm_host: M, N multiples of 128 and K a multiple of 256 are required");
+            if (M <= 0 || N <= 0 || K <= 0 || M % 128 || N % 128 || K % 64)
+                throw std::invalid_argument("gemm_host: M, N multiples of 128 and K a multiple of 64 are required");
             cuda_check(cudaMalloc(&h.A, a_bytes));
             cuda_check(cudaMalloc(&h.B, b_bytes));
             cuda_check(cudaMalloc(&h.SFA, sfa_bytes));
@@ -529,12 +543,12 @@ int gpu_kernels_nvfp4_moe_clear_live(const void* num_blocks, int block_rows, int
 }
 
 int gpu_kernels_nvfp4_moe_pack(const void* xq, const void* xs, const void* ids, const void* weights, int tokens,
-                               int topk, int hidden, const void* send_offset, void* cursor, void* send_rows,
+                               int topk, int hidden, int experts, const void* send_offset, void* cursor, void* send_rows,
                                void* send_pos, void* stream) {
     return guarded([&] {
         nvfp4_b200::moe_pack(static_cast<const uint8_t*>(xq), static_cast<const uint8_t*>(xs),
                              static_cast<const long long*>(ids), static_cast<const float*>(weights), tokens, topk, hidden,
-                             static_cast<const int*>(send_offset), static_cast<int*>(cursor),
+                             experts, static_cast<const int*>(send_offset), static_cast<int*>(cursor),
                              static_cast<uint8_t*>(send_rows), static_cast<int*>(send_pos),
                              static_cast<cudaStream_t>(stream));
         nvfp4_b200::g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -542,13 +556,13 @@ int gpu_kernels_nvfp4_moe_pack(const void* xq, const void* xs, const void* ids, 
 }
 
 int gpu_kernels_nvfp4_moe_pack_to_pool(const void* xq, const void* xs, const void* ids, const void* weights, int tokens,
-                                       int topk, int hidden, const void* seg_pool_offset, void* cursor,
+                                       int topk, int hidden, int experts, const void* seg_pool_offset, void* cursor,
                                        void* pool_packed, void* pool_scales, void* pool_weight, void* route_row,
                                        void* stream) {
     return guarded([&] {
         nvfp4_b200::moe_pack_to_pool(static_cast<const uint8_t*>(xq), static_cast<const uint8_t*>(xs),
                                      static_cast<const long long*>(ids), static_cast<const float*>(weights), tokens, topk,
-                                     hidden, static_cast<const int*>(seg_pool_offset), static_cast<int*>(cursor),
+                                     hidden, experts, static_cast<const int*>(seg_pool_offset), static_cast<int*>(cursor),
                                      static_cast<uint8_t*>(pool_packed), static_cast<uint8_t*>(pool_scales),
                                      static_cast<float*>(pool_weight), static_cast<int*>(route_row),
                                      static_cast<cudaStream_t>(stream));
@@ -592,10 +606,10 @@ int gpu_kernels_nvfp4_moe_return_rows(const void* out_pool, const void* pool_of_
 }
 
 int gpu_kernels_nvfp4_moe_reduce(const void* returned, const void* send_pos, int tokens, int topk, int hidden, void* y,
-                                 void* stream) {
+                                 const void* ids, int experts, void* stream) {
     return guarded([&] {
         nvfp4_b200::moe_reduce(returned, static_cast<const int*>(send_pos), tokens, topk, hidden, y,
-                               static_cast<cudaStream_t>(stream));
+                               static_cast<const long long*>(ids), experts, static_cast<cudaStream_t>(stream));
         nvfp4_b200::g_launches.fetch_add(1, std::memory_order_relaxed);
     });
 }
@@ -605,8 +619,8 @@ int gpu_kernels_nvfp4_gemm_host_static(int M, int N, int K, const void* A, const
     return guarded([&] {
         using nvfp4_b200::cuda_check;
         if (!A || !B || !SFA || !SFB || !C) throw std::invalid_argument("gemm_host_static: null pointer");
-        if (M <= 0 || N <= 0 || K <= 0 || M % 128 || N % 128 || K % 256)
-            throw std::invalid_argument("gemm_host_static: M, N multiples of 128 and K a multiple of 256 are required");
+        if (M <= 0 || N <= 0 || K <= 0 || M % 128 || N % 128 || K % 64)
+            throw std::invalid_argument("gemm_host_static: M, N multiples of 128 and K a multiple of 64 are required");
         if (M > STATIC_MAX_M || N > STATIC_MAX_N || K > STATIC_MAX_K)
             throw std::invalid_argument("gemm_host_static: shape " + std::to_string(M) + "x" + std::to_string(N) + "x" +
                                         std::to_string(K) + " exceeds the built-in staging (M <= " +
@@ -742,7 +756,32 @@ int gpu_kernels_nvfp4_ipc_free(void* ptr) {
     return guarded([&] { if (ptr) nvfp4_b200::cuda_check(cudaFree(ptr)); });
 }
 
-const char* gpu_kernels_nvfp4_version(void) { return "nvfp4-b200 0.1 (sm_100a)"; }
+int gpu_kernels_nvfp4_plan_placement_misses(void* plan, unsigned* misses) {
+    return guarded([&] {
+        if (!misses) throw std::invalid_argument("plan_placement_misses: null output");
+        *misses = gpu_kernels::nvfp4_placement_misses(as_plan(plan).params);
+    });
+}
+
+int gpu_kernels_nvfp4_side_route(const unsigned char* unit_side, int units, int tiles, unsigned* route) {
+    return guarded([&] {
+        if (!unit_side || !route || units < 1 || tiles < 0) throw std::invalid_argument("side_route: bad argument");
+        const std::vector<uint8_t> sides(unit_side, unit_side + units);
+        const std::vector<uint32_t> r = nvfp4_b200::build_side_route(sides, tiles);
+        std::memcpy(route, r.data(), r.size() * sizeof(uint32_t));
+    });
+}
+
+int gpu_kernels_nvfp4_l2_census(unsigned* cycles_by_sm, int capacity, int* written) {
+    return guarded([&] {
+        if (!cycles_by_sm || !written) throw std::invalid_argument("l2_census: null output");
+        int device = 0;
+        nvfp4_b200::cuda_check(cudaGetDevice(&device));
+        *written = nvfp4_b200::l2_side_census_cycles(device, cycles_by_sm, capacity);
+    });
+}
+
+const char* gpu_kernels_nvfp4_version(void) { return "nvfp4-b200 0.2 (sm_100a)"; }
 
 unsigned long long gpu_kernels_nvfp4_launch_count(void) {
     return nvfp4_b200::g_launches.load(std::memory_order_relaxed);

@@ -48,11 +48,29 @@ constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 512;
 constexpr int SMEM_LIMIT = 232448;  // 227 KiB opt-in maximum per CTA
 
-// Device-side status: [0] OR of StatusBits, [1] tag of the first wait that gave up,
-// [2] SM cycles the first CTA of the most recent GEMM launch was resident (diagnostic).
-__device__ uint32_t g_status[4];
+// Device-side status, four words per slot: [0] OR of StatusBits, [1] tag of the first wait that gave up,
+// [2] (slot 0 only) SM cycles the first CTA of the most recent GEMM launch was resident (diagnostic),
+// [3] launches-times-clusters that found themselves on the other L2 side than their tile route assumed.
+// Slot 0 is the device's own (grouped launches, the expert-path kernels, the barrier kernel); every dense
+// plan gets one of the other slots, so that validating one plan neither reports nor clears another's error
+// (more than STATUS_SLOTS - 1 live plans share slots, which only merges their reports).
+constexpr int STATUS_SLOTS = 1024;
+__device__ uint32_t g_status[STATUS_SLOTS][4];
 
-template <int CG, int UN, bool RS = false>
+// Epilogue routes, one kernel instance each (the route is a template parameter, so an instance carries
+// only its own epilogue).
+enum Epi : int {
+    EPI_TMA = 0,           // rows staged in swizzled shared memory, C written by TMA stores (CTA pairs)
+    EPI_DIRECT = 1,        // C written from registers with 32-byte global stores
+    EPI_ACT = 2,           // grouped: clamped SwiGLU + route weight + NVFP4 re-quantisation, no C
+    EPI_SCATTER = 3,       // grouped: every row to its own destination buffer, register stores
+    EPI_SCATTER_ROWS = 4,  // grouped, CTA pairs: whole tile rows staged, one bulk copy per row
+    EPI_GATHER_TMA = 5,    // the slab to every rank's full C by TMA stores
+    EPI_GATHER_DIRECT = 6, // the same with register stores
+    EPI_SPLIT_K = 7,       // FP32 partial sums + finish (to C or to every rank's full C)
+};
+
+template <int CG, int UN, int EPI>
 struct Config {
     static_assert(CG == 1 || CG == 2, "cta group");
     static_assert(UN == 128 || UN == 256, "tile width");
@@ -69,15 +87,16 @@ struct Config {
     static constexpr int OFF_SFB = OFF_SFA + SFA_BYTES;
     static constexpr int STAGE_BYTES = OFF_SFB + SFB_BYTES;
     static constexpr int EPI_WARP_BYTES = 32 * EPI_COLS * 2;     // 32 rows x 128 B
-    // Single-CTA tiles write C straight from registers, so they keep no staging and get a deeper
-    // ring instead (their workloads stream weights from HBM and live on bytes in flight).
-    static constexpr bool STAGED_EPILOGUE = CG == 2;
-    // RS (row staging, the scatter epilogue of the second expert GEMM): instead of two 32 x 64 chunk buffers
-    // per warp, every epilogue warp keeps its 32 whole rows of the tile (UN columns, 16 bytes of padding per
-    // row so that a quarter-warp's 16-byte stores cover all banks); the ring gives up a stage for it.
-    static constexpr bool ROW_STAGING = RS;
+    // Routes that write from registers keep no staging and get a deeper ring where it fits (their
+    // workloads stream weights from HBM and live on bytes in flight).
+    static constexpr bool STAGED_EPILOGUE = EPI == EPI_TMA || EPI == EPI_GATHER_TMA;
+    // Row staging (the scatter epilogue of the second expert GEMM on CTA pairs): instead of two 32 x 64
+    // chunk buffers per warp, every epilogue warp keeps its 32 whole rows of the tile (UN columns, 16 bytes
+    // of padding per row so that a quarter-warp's 16-byte stores cover all banks); the ring gives up a
+    // stage for it.
+    static constexpr bool ROW_STAGING = EPI == EPI_SCATTER_ROWS;
     static constexpr int ROW_PITCH = UN * 2 + 16;
-    static constexpr int EPI_BYTES = RS ? 4 * 32 * ROW_PITCH : STAGED_EPILOGUE ? 4 * 2 * EPI_WARP_BYTES : 0;
+    static constexpr int EPI_BYTES = ROW_STAGING ? 4 * 32 * ROW_PITCH : STAGED_EPILOGUE ? 4 * 2 * EPI_WARP_BYTES : 0;
     static constexpr int CTRL_BYTES = 1024;
     static constexpr int STAGES = (SMEM_LIMIT - 1024 - CTRL_BYTES - EPI_BYTES) / STAGE_BYTES;
     static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + CTRL_BYTES;
@@ -90,7 +109,8 @@ struct Config {
     static constexpr int OVERLAP = UN - ACC_STRIDE;              // columns shared by the two accumulators
     static_assert(OVERLAP <= EPI_COLS, "the first epilogue chunk must cover the overlap");
     static_assert(STAGE_BYTES % 1024 == 0, "stages keep the 1024-byte swizzle alignment");
-    static_assert(STAGES >= 3, "ring too shallow");
+    static_assert(STAGES >= 3 && STAGES <= 8, "ring depth");
+    static_assert(!STAGED_EPILOGUE || CG == 2, "single CTAs write C from registers");
     // Instruction descriptor of kind::mxf4nvf4: A and B E2M1 (format 1) at bits 7 and 10,
     // both K-major, N >> 3 at bit 17, UE4M3 scales (bit 23 = 0), M >> 4 at bit 24,
     // scale-factor ids 0 (each MMA reads whole 32-bit scale columns).
@@ -108,11 +128,12 @@ static_assert(sizeof(Control) <= 1024, "control block");
 
 struct GemmArgs {
     int M, N, K;
+    int ksteps;                     // ring steps per tile: ceil(K / 256); a last partial step reads zero fill
     int tiles_m, tiles_n, group_m;
     float alpha;
-    uint32_t* status;
-    unsigned long long* prof;       // optional: per-unit wait/role cycle counters (16 words per CTA)
-    uint32_t debug;                 // diagnostics only (results invalid): 1 skip C stores, 2 skip scale copies, 4 skip MMAs
+    uint32_t* status;               // this plan's four status words ([0] StatusBits, [1] first tag, [3] placement misses)
+    uint32_t* cycles;               // where CTA 0 leaves the SM cycles it was resident (diagnostic)
+    unsigned long long* prof;       // PROF instances only: per-unit wait/role cycle counters (16 words per CTA)
     int c_evict_first;              // store C with the evict-first L2 policy
     int out_bf16;                   // 1: C is bfloat16 instead of float16
     // Grouped mode (routed-MoE experts): A is a pool of 128-row blocks, block i belongs to expert
@@ -121,22 +142,19 @@ struct GemmArgs {
     const int* block_expert;
     const int* num_blocks;
     int b_rows_per_expert;
-    // Epilogue route: 0 = FP16/BF16 rows staged in swizzled shared memory and written by TMA stores,
-    // 1 = written straight from registers with 32-byte global stores (no shared-memory traffic).
-    int direct_store;
-    void* c;                        // C base and leading dimension (elements), used by the direct route
+    void* c;                        // C base and leading dimension (elements), used by the register-store routes
     int ldc;
-    // Fused first expert GEMM (grouped mode only): the weight rows arrive interleaved as 16 gate rows, 16 up
-    // rows, ..., so a lane's 64 accumulator columns are two (gate, up) block pairs; the epilogue rounds them to
-    // bf16, applies the clamped SwiGLU and the row's route weight, rounds to bf16, quantises each 16-value
-    // block to NVFP4 and writes packed codes and scale bytes for the second GEMM. Null act_packed = off.
+    // EPI_ACT (grouped mode only): the weight rows arrive interleaved as 16 gate rows, 16 up rows, ..., so a
+    // lane's 64 accumulator columns are two (gate, up) block pairs; the epilogue rounds them to bf16, applies
+    // the clamped SwiGLU and the row's route weight, rounds to bf16, quantises each 16-value block to NVFP4
+    // and writes packed codes and scale bytes for the second GEMM.
     uint8_t* act_packed;            // [pool_rows, N/4] (N/2 activation columns, two per byte)
     uint8_t* act_scales;            // VEC16 layout of [pool_rows, N/2]
     const float* row_weight;        // [pool_rows]
     float swiglu_clamp;
-    // Fused second expert GEMM + combine (grouped mode, register store route): row r of the pool is not
-    // written to C but to row (row_dst[r] & 0xFFFFFF) - 1 of the [slot_rows, N] buffer of rank row_dst[r] >> 24
-    // (peer memory over NVLink, or this rank's own buffer); row_dst[r] == 0 marks a padding row.
+    // EPI_SCATTER / EPI_SCATTER_ROWS (second expert GEMM + combine): row r of the pool is not written to C but
+    // to row (row_dst[r] & 0xFFFFFF) - 1 of the [slot_rows, N] buffer of rank row_dst[r] >> 24 (peer memory
+    // over NVLink, or this rank's own buffer); row_dst[r] == 0 marks a padding row.
     const int* row_dst;
     void* const* slots;             // device array of `world` buffer addresses
     int world;
@@ -144,7 +162,7 @@ struct GemmArgs {
     // Tile t walks K starting at step (t * k_skew) % ksteps and wraps: the CTAs then do not all ask HBM for
     // the same 128-byte column of their rows at the same time. 0 = every tile starts at K = 0.
     int k_skew;
-    // Split-K (dense mode, shapes with far fewer tiles than SMs): unit u works on K steps
+    // EPI_SPLIT_K (dense mode, shapes with far fewer tiles than SMs): unit u works on K steps
     // [slice * steps / S, (slice + 1) * steps / S) of tile u / S, slice = u % S, and writes FP32 partial sums
     // to its slot of sk_partials. When the S slices of a tile are there (flags), slice j adds them up, in
     // slice order, for the column chunks c with c % S == j and writes those columns of C. One item per
@@ -155,13 +173,20 @@ struct GemmArgs {
     uint32_t* sk_done;              // [tiles][CG][4 warps]: readers finished (the last one lowers the flags)
     // GEMM fused with the all-gather of C (dense mode, N sharded over ranks): this rank's column slab is
     // written into the full [M, gather_ldc] C of EVERY rank, its own and its peers' (NVLink), from the
-    // epilogue: TMA stores through one tensor map per destination (staged route) or register stores (direct
-    // route). 0 destinations = plain C.
+    // epilogue: TMA stores through one tensor map per destination (EPI_GATHER_TMA) or register stores
+    // (EPI_GATHER_DIRECT, and the finish of EPI_SPLIT_K).
     int gather_world;
     int gather_col0;                // first column of this rank's slab in the full C
     int gather_ldc;                 // columns of the full C
     const CUtensorMap* gather_maps; // [gather_world] in device memory, written by the host before any launch
     void* const* gather_ptrs;       // [gather_world] bases of the full C buffers
+    // L2-side-aware order (dense mode): work item w (= unit + trip * units) is tile route[w] of the band order
+    // instead of tile w. The table keeps the clusters that sit on one side of the L2 on one contiguous part
+    // of the band sequence. sm_side[smid] and unit_side[unit] are what the census saw; a cluster that finds
+    // itself on the other side than the table assumed only counts a placement miss (results do not depend on it).
+    const uint32_t* route;
+    const uint8_t* sm_side;
+    const uint8_t* unit_side;
 };
 
 struct Segment {
@@ -172,13 +197,15 @@ struct Segment {
 struct Walk {
     uint32_t next, stride, tiles;
     int ksteps, split;
+    const uint32_t* route;
     __device__ Walk(const GemmArgs& g, uint32_t unit, uint32_t units, uint32_t tiles_, int ksteps_)
-        : next(unit), stride(units), tiles(tiles_), ksteps(ksteps_), split(g.split_k > 1 ? g.split_k : 1) {}
+        : next(unit), stride(units), tiles(tiles_), ksteps(ksteps_), split(g.split_k > 1 ? g.split_k : 1), route(g.route) {}
     __device__ bool get(Segment& s) {
         if (next >= tiles * uint32_t(split)) return false;
         s.item = next;
-        s.tile = next / uint32_t(split);
-        const int slice = int(next - s.tile * uint32_t(split)), len = ksteps / split;
+        const uint32_t whole = next / uint32_t(split);           // the route table is only used with whole tiles
+        s.tile = route ? __ldg(route + next) : whole;
+        const int slice = int(next - whole * uint32_t(split)), len = ksteps / split;
         s.k0 = slice * len;
         s.k1 = s.k0 + len;
         next += stride;
@@ -224,9 +251,9 @@ __device__ __forceinline__ void tile_coords(int t, const GemmArgs& g, int& tm, i
     tn = (band & 1) ? g.tiles_n - 1 - c : c;
 }
 
-template <int CG, int UN, bool RS = false>
+template <int CG, int UN, int EPI, bool PROF>
 struct Roles {
-    using Cfg = Config<CG, UN, RS>;
+    using Cfg = Config<CG, UN, EPI>;
 
     uint32_t smem;            // 1024-aligned shared-window address of stage 0
     Control* ctrl;
@@ -239,6 +266,7 @@ struct Roles {
         if (who) atomicCAS(g.status + 1, 0u, tag);
         return false;
     }
+    static __device__ __forceinline__ long long now() { return PROF ? clock64() : 0; }
 
     // Both single-issuer roles below run their loops with the WHOLE warp in uniform control
     // flow and let one elected lane execute the asynchronous instructions. Addresses,
@@ -247,14 +275,16 @@ struct Roles {
     // inside a one-lane branch costs a register-to-uniform move chain per instruction.
 
     // ---- warp 5: stream operand and scale tiles into the ring ----------------------
+    // The scale maps are three-dimensional {128 bytes, 4 * K/64 rows, row blocks}: one 16-row box is the four
+    // atoms of a K = 256 step, and a last partial step reads zeros beyond the block's own atoms (as the
+    // operand maps do beyond K/2 bytes), so K only has to be a multiple of 64.
     __device__ void produce(const CUtensorMap* tmA, const CUtensorMap* tmB,
                             const CUtensorMap* tmSFA, const CUtensorMap* tmSFB, int lane) const {
         int stage = 0;
         uint32_t phase = 0;
-        const int ksteps = g.K / STAGE_K;
-        const int sf_rows_per_block = (g.K / 64) * 4;          // 128-byte rows of the scale map per 128 tensor rows
+        const int ksteps = g.ksteps;
         long long waited = 0;
-        const long long born = clock64();
+        const long long born = now();
         Walk walk(g, unit, units, tiles, ksteps);
         Segment seg;
         while (walk.get(seg)) {
@@ -263,17 +293,17 @@ struct Roles {
             tile_coords(int(t), g, tm, tn, b_base);
             const int a_row = tm * Cfg::TILE_M + int(rank) * BLOCK_M;
             const int b_row = b_base + tn * UN + int(rank) * Cfg::B_ROWS;
-            const int sfa_row0 = (a_row / 128) * sf_rows_per_block;
-            const int sfb_row0 = ((b_base + tn * UN) / 128) * sf_rows_per_block;
+            const int sfa_block = a_row / 128;
+            const int sfb_block = (b_base + tn * UN) / 128;
             // whole tiles may start anywhere in K and wrap; slices of a tile are walked in order
             const int k_first = (g.k_skew && g.split_k <= 1) ? int((t * uint32_t(g.k_skew)) % uint32_t(ksteps)) : 0;
             for (int step = seg.k0; step < seg.k1; ++step) {
                 const int ks = step + k_first < ksteps ? step + k_first : step + k_first - ksteps;
-                const long long w0 = g.prof ? clock64() : 0;
+                const long long w0 = now();
                 const bool ok = wait(&ctrl->empty[stage], phase ^ 1u, lane == 0 ? STATUS_TIMEOUT_PRODUCER : 0u,
                                      0x10000000u | (stage << 16) | ks);
                 if (!__all_sync(0xFFFFFFFFu, ok)) return;
-                if (g.prof) waited += clock64() - w0;
+                if (PROF) waited += now() - w0;
                 const uint32_t base = smem + stage * Cfg::STAGE_BYTES;
                 const uint32_t own_full = bar(&ctrl->full[stage]);
                 if constexpr (CG == 1) {
@@ -281,11 +311,11 @@ struct Roles {
                         mbar_arrive_expect_tx(own_full, Cfg::STAGE_BYTES);
                         tma_load_2d(base, tmA, ks * ROW_BYTES, a_row, own_full);
                         tma_load_2d(base + Cfg::OFF_B, tmB, ks * ROW_BYTES, b_row, own_full);
-                        tma_load_2d(base + Cfg::OFF_SFA, tmSFA, 0, sfa_row0 + ks * 16, own_full);
+                        tma_load_3d(base + Cfg::OFF_SFA, tmSFA, 0, ks * 16, sfa_block, own_full);
                         #pragma unroll
                         for (int b = 0; b < Cfg::SFB_BLOCKS; ++b)
-                            tma_load_2d(base + Cfg::OFF_SFB + b * Cfg::SFB_BLOCK_BYTES, tmSFB, 0,
-                                        sfb_row0 + b * sf_rows_per_block + ks * 16, own_full);
+                            tma_load_3d(base + Cfg::OFF_SFB + b * Cfg::SFB_BLOCK_BYTES, tmSFB, 0, ks * 16,
+                                        sfb_block + b, own_full);
                     }
                 } else {
                     // Both CTAs of the pair report their bytes to the leader's barrier.
@@ -294,20 +324,20 @@ struct Roles {
                         if (rank == 0) mbar_arrive_expect_tx(own_full, 2 * Cfg::STAGE_BYTES);
                         tma_load_2d_pair(base, tmA, ks * ROW_BYTES, a_row, full);
                         tma_load_2d_pair(base + Cfg::OFF_B, tmB, ks * ROW_BYTES, b_row, full);
-                        tma_load_2d_pair(base + Cfg::OFF_SFA, tmSFA, 0, sfa_row0 + ks * 16, full);
+                        tma_load_3d_pair(base + Cfg::OFF_SFA, tmSFA, 0, ks * 16, sfa_block, full);
                         #pragma unroll
                         for (int b = 0; b < Cfg::SFB_BLOCKS; ++b)
-                            tma_load_2d_pair(base + Cfg::OFF_SFB + b * Cfg::SFB_BLOCK_BYTES, tmSFB, 0,
-                                             sfb_row0 + b * sf_rows_per_block + ks * 16, full);
+                            tma_load_3d_pair(base + Cfg::OFF_SFB + b * Cfg::SFB_BLOCK_BYTES, tmSFB, 0, ks * 16,
+                                             sfb_block + b, full);
                     }
                 }
                 if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
             }
         }
-        if (g.prof && lane == 0) {
+        if (PROF && lane == 0) {
             unsigned long long* out = g.prof + (size_t(unit) * CG + rank) * PROF_WORDS;
             out[PROF_PROD_WAIT] = waited;
-            out[PROF_PROD_TOTAL] = clock64() - born;
+            out[PROF_PROD_TOTAL] = now() - born;
         }
     }
 
@@ -322,10 +352,9 @@ struct Roles {
     __device__ void issue(uint32_t tmem, int lane) const {
         int stage = 0;
         uint32_t phase = 0, iter = 0;
-        const int ksteps = g.K / STAGE_K;
+        const int ksteps = g.ksteps;
         long long wait_full = 0, wait_acc = 0;
-        const long long born = clock64();
-        const bool copy_scales = !(g.debug & 2u), do_mma = !(g.debug & 4u);
+        const long long born = now();
         // Descriptor words. Low word: start address >> 4 (bits 0-13), leading offset >> 4 (bits 16-29).
         // High word: stride >> 4 (bits 0-13), version 1 (bit 14), swizzle mode (bits 29-31).
         constexpr uint32_t OPERAND_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
@@ -339,15 +368,15 @@ struct Roles {
         for (; walk.get(seg); ++iter) {
             const uint32_t acc = tmem + (iter & 1u) * Cfg::ACC_STRIDE;
             unsigned long long* tr = nullptr;
-            if (g.prof && unit == 0 && lane == 0 && iter > 0 && iter <= TR_TILES)
+            if (PROF && unit == 0 && lane == 0 && iter > 0 && iter <= TR_TILES)
                 tr = g.prof + size_t(units) * CG * PROF_WORDS + size_t(iter - 1) * 8;
             for (int ks = seg.k0; ks < seg.k1; ++ks) {
                 if (!landed) {
-                    const long long w0 = g.prof ? clock64() : 0;
+                    const long long w0 = now();
                     const bool ok = wait(&ctrl->full[stage], phase, lane == 0 ? STATUS_TIMEOUT_MMA : 0u,
                                          0x21000000u | (stage << 16) | ks);
                     if (!__all_sync(0xFFFFFFFFu, ok)) return;
-                    if (g.prof) wait_full += clock64() - w0;
+                    if (PROF) wait_full += now() - w0;
                 }
                 tc_fence_after_sync();
                 const int next_stage = stage + 1 == Cfg::STAGES ? 0 : stage + 1;
@@ -375,39 +404,50 @@ struct Roles {
                 if (handover) {
                     // First step of a tile: the scale copies do not touch the accumulators, so they go out
                     // before the wait for the epilogue to pull the columns this tile shares with the last one.
-                    if (copy_scales && elect_one()) {
+                    if (elect_one()) {
                         #pragma unroll
                         for (int j = 0; j < STAGE_K / MMA_K; ++j) copies(j);
                     }
-                    const long long w0 = g.prof ? clock64() : 0;
+                    const long long w0 = now();
                     if (tr) tr[0] = w0;
                     const bool ok = wait(&ctrl->acc_free, (iter - 1u) & 1u, lane == 0 ? STATUS_TIMEOUT_MMA : 0u, 0x20000000u | iter);
                     if (!__all_sync(0xFFFFFFFFu, ok)) return;
-                    if (g.prof) wait_acc += clock64() - w0;
-                    if (tr) tr[1] = clock64();
+                    if (PROF) wait_acc += now() - w0;
+                    if (tr) tr[1] = now();
                     tc_fence_after_sync();
                 }
                 if (elect_one()) {
                     #pragma unroll
                     for (int j = 0; j < STAGE_K / MMA_K; ++j) {
-                        if (copy_scales && !handover) copies(j);
-                        if (do_mma) mma(j);
+                        if (!handover) copies(j);
+                        mma(j);
                     }
                     mma_commit<CG>(empty);                      // stage reusable once these MMAs retire
                     if (ks == seg.k1 - 1) mma_commit<CG>(bar(&ctrl->acc_full));
                 }
-                if (tr && ks == seg.k0) tr[2] = clock64();
+                if (tr && ks == seg.k0) tr[2] = now();
                 landed = __all_sync(0xFFFFFFFFu, probe);
                 stage = next_stage;
                 phase = next_phase;
             }
         }
-        if (g.prof && lane == 0) {
+        if (PROF && lane == 0) {
             unsigned long long* out = g.prof + size_t(unit) * CG * PROF_WORDS;
             out[PROF_MMA_WAIT_FULL] = wait_full;
             out[PROF_MMA_WAIT_ACC] = wait_acc;
-            out[PROF_MMA_TOTAL] = clock64() - born;
+            out[PROF_MMA_TOTAL] = now() - born;
         }
+    }
+
+    // Two accumulator values x alpha -> one packed FP16 (or BF16) pair.
+    __device__ __forceinline__ uint32_t pack_pair(uint32_t lo_bits, uint32_t hi_bits, float alpha) const {
+        const float lo = __uint_as_float(lo_bits) * alpha, hi = __uint_as_float(hi_bits) * alpha;
+        if (g.out_bf16) {
+            const __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+            return *reinterpret_cast<const uint32_t*>(&p);
+        }
+        const __half2 p = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t*>(&p);
     }
 
     // 64 accumulator columns of this lane's row: x alpha, to FP16/BF16, 128 bytes in four 32-byte stores.
@@ -416,22 +456,26 @@ struct Roles {
         for (int q = 0; q < EPI_COLS / 16; ++q) {
             uint32_t h[8];
             #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const float lo = __uint_as_float(v[q * 16 + 2 * i]) * alpha;
-                const float hi = __uint_as_float(v[q * 16 + 2 * i + 1]) * alpha;
-                if (g.out_bf16) {
-                    const __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
-                    h[i] = *reinterpret_cast<const uint32_t*>(&p);
-                } else {
-                    const __half2 p = __floats2half2_rn(lo, hi);
-                    h[i] = *reinterpret_cast<const uint32_t*>(&p);
-                }
-            }
-            if (!(g.debug & 1u) && deliver)
+            for (int i = 0; i < 8; ++i) h[i] = pack_pair(v[q * 16 + 2 * i], v[q * 16 + 2 * i + 1], alpha);
+            if (deliver)
                 asm volatile("st.global.L1::no_allocate.L2::evict_first.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
                              :: "l"(dst + q * 16), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]),
                                 "r"(h[4]), "r"(h[5]), "r"(h[6]), "r"(h[7]) : "memory");
         }
+    }
+
+    // Destination of pool row `row` on the scatter routes: false = nothing to deliver (a padding row, or a
+    // code outside the agreed buffers, which is reported through the status word).
+    __device__ __forceinline__ bool scatter_target(int row, uint16_t*& base) const {
+        const uint32_t code = uint32_t(__ldg(g.row_dst + row));
+        if (code == 0u) return false;
+        const uint32_t slot = (code & 0xFFFFFFu) - 1u, owner = code >> 24;
+        if (slot >= uint32_t(g.slot_rows) || owner >= uint32_t(g.world)) {
+            atomicOr(g.status, uint32_t(STATUS_BAD_ARGUMENT));
+            return false;
+        }
+        base = reinterpret_cast<uint16_t*>(__ldg(reinterpret_cast<const unsigned long long*>(g.slots) + owner)) + size_t(slot) * g.ldc;
+        return true;
     }
 
     // Split-K, once a unit's partial sums are stored: publish them, wait for the other slices of the tile, add
@@ -503,8 +547,8 @@ struct Roles {
         const float alpha = g.alpha;
         const uint64_t c_policy = policy_evict_first();
         long long wait_acc = 0, wait_store = 0;
-        const long long born = clock64();
-        Walk walk(g, unit, units, tiles, g.K / STAGE_K);
+        const long long born = now();
+        Walk walk(g, unit, units, tiles, g.ksteps);
         Segment seg;
         constexpr uint32_t SK_WARP_FLOATS = UN * 32;            // one warp's 32 rows of a tile
         for (; walk.get(seg); ++iter) {
@@ -514,14 +558,14 @@ struct Roles {
             const int row0 = tm * Cfg::TILE_M + int(rank) * BLOCK_M + warp * 32;
             const int col0 = tn * UN;
             // The whole warp leaves together: the Tensor Memory loads below are warp-collective.
-            const long long w0 = g.prof ? clock64() : 0;
+            const long long w0 = now();
             const bool ready = wait(&ctrl->acc_full, iter & 1u, lane == 0 ? STATUS_TIMEOUT_EPILOGUE : 0u, 0x30000000u | iter);
             if (!__all_sync(0xFFFFFFFFu, ready)) break;
-            if (g.prof) wait_acc += clock64() - w0;
+            if (PROF) wait_acc += now() - w0;
             unsigned long long* tr = nullptr;
-            if (g.prof && unit == 0 && warp == 0 && lane == 0 && iter < TR_TILES)
+            if (PROF && unit == 0 && warp == 0 && lane == 0 && iter < TR_TILES)
                 tr = g.prof + size_t(units) * CG * PROF_WORDS + size_t(iter) * 8 + (rank ? 6 : 3);
-            if (tr) tr[0] = clock64();
+            if (tr) tr[0] = now();
             tc_fence_after_sync();
             const uint32_t acc = tmem + (iter & 1u) * Cfg::ACC_STRIDE + (uint32_t(warp * 32) << 16);
             #pragma unroll 1
@@ -533,14 +577,13 @@ struct Roles {
                 tmem_ld_32x32(acc + chunk * EPI_COLS + 32, v + 32);
                 tmem_ld_wait();
                 if (c == 0) {
-                    if (tr && rank == 0) tr[1] = clock64();
+                    if (tr && rank == 0) tr[1] = now();
                     tc_fence_before_sync();
                     __syncwarp();
                     if (lane == 0) mbar_arrive_cluster(acc_free_leader);
-                    if (tr) tr[rank ? 1 : 2] = clock64();
+                    if (tr) tr[rank ? 1 : 2] = now();
                 }
-                if (g.debug & 8u) continue;                      // diagnostic: drain only
-                if (g.split_k > 1) {
+                if constexpr (EPI == EPI_SPLIT_K) {
                     // FP32 partial sums to this unit's slot: 16 bytes per lane, 512 contiguous bytes per store
                     float4* out = reinterpret_cast<float4*>(g.sk_partials + ((size_t(seg.item) * CG + rank) * 4 + warp) * SK_WARP_FLOATS) +
                                   size_t(chunk) * (EPI_COLS / 4) * 32 + lane;
@@ -548,9 +591,7 @@ struct Roles {
                     for (int q = 0; q < EPI_COLS / 4; ++q)
                         __stcg(out + q * 32, make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]),
                                                          __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3])));
-                    continue;
-                }
-                if (g.act_packed) {
+                } else if constexpr (EPI == EPI_ACT) {
                     const int inter = g.N / 2;
                     const int row = row0 + lane;
                     const float w = __ldg(g.row_weight + row);
@@ -562,7 +603,7 @@ struct Roles {
                         codes[0] = codes[1] = make_uint2(0u, 0u);
                         sb[0] = sb[1] = 0x01u;
                     } else {
-                        const float c = g.swiglu_clamp;
+                        const float cl = g.swiglu_clamp;
                         #pragma unroll
                         for (int b = 0; b < 2; ++b) {
                             uint32_t act[8];
@@ -573,12 +614,12 @@ struct Roles {
                                 for (int h = 0; h < 2; ++h) {
                                     // gate_up is rounded to bf16 first, as the unfused pipeline stores it
                                     const uint32_t gb = v[b * 32 + 2 * i + h], ub = v[b * 32 + 16 + 2 * i + h];
-                                    const float gate = fminf(__uint_as_float((gb + 0x7FFFu + ((gb >> 16) & 1u)) & 0xFFFF0000u), c);
-                                    const float up = fminf(fmaxf(__uint_as_float((ub + 0x7FFFu + ((ub >> 16) & 1u)) & 0xFFFF0000u), -c), c);
+                                    const float gate = fminf(__uint_as_float((gb + 0x7FFFu + ((gb >> 16) & 1u)) & 0xFFFF0000u), cl);
+                                    const float up = fminf(fmaxf(__uint_as_float((ub + 0x7FFFu + ((ub >> 16) & 1u)) & 0xFFFF0000u), -cl), cl);
                                     a2[h] = silu_fast(gate) * up * w;
                                 }
-                                const __nv_bfloat162 p = __floats2bfloat162_rn(a2[0], a2[1]);
-                                act[i] = *reinterpret_cast<const uint32_t*>(&p);
+                                const __nv_bfloat162 p2 = __floats2bfloat162_rn(a2[0], a2[1]);
+                                act[i] = *reinterpret_cast<const uint32_t*>(&p2);
                             }
                             sb[b] = quantise_block_pairs<Bf16Pairs>(act, codes[b]);
                         }
@@ -587,9 +628,7 @@ struct Roles {
                         make_uint4(codes[0].x, codes[0].y, codes[1].x, codes[1].y);
                     *reinterpret_cast<uint16_t*>(g.act_scales + scale_byte_offset(row, act_col / 16, inter)) =
                         static_cast<uint16_t>(sb[0] | (sb[1] << 8));
-                    continue;
-                }
-                if constexpr (Cfg::ROW_STAGING) {
+                } else if constexpr (EPI == EPI_SCATTER_ROWS) {
                     // Scatter through shared memory: every lane stages its own row of the tile, chunk by chunk,
                     // and after the last chunk sends the UN columns (512 bytes) with ONE bulk copy to the row's
                     // destination. Over NVLink this makes 512-byte writes (register stores make 32-byte ones,
@@ -602,108 +641,74 @@ struct Roles {
                     for (int q = 0; q < EPI_COLS / 8; ++q) {
                         uint32_t h[4];
                         #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const float lo = __uint_as_float(v[q * 8 + 2 * i]) * alpha;
-                            const float hi = __uint_as_float(v[q * 8 + 2 * i + 1]) * alpha;
-                            if (g.out_bf16) {
-                                const __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
-                                h[i] = *reinterpret_cast<const uint32_t*>(&p);
-                            } else {
-                                const __half2 p = __floats2half2_rn(lo, hi);
-                                h[i] = *reinterpret_cast<const uint32_t*>(&p);
-                            }
-                        }
+                        for (int i = 0; i < 4; ++i) h[i] = pack_pair(v[q * 8 + 2 * i], v[q * 8 + 2 * i + 1], alpha);
                         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
                                      :: "r"(rowbuf + chunk * (EPI_COLS * 2) + q * 16), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]) : "memory");
                     }
                     if (c == UN / EPI_COLS - 1) {
                         fence_async_smem();
-                        const int code = g.row_dst ? __ldg(g.row_dst + row0 + lane) : 0;
-                        const int slot = (code & 0xFFFFFF) - 1, owner = code >> 24;
-                        if (slot >= 0 && (slot >= g.slot_rows || owner >= g.world)) {
-                            atomicOr(g.status, uint32_t(STATUS_BAD_ARGUMENT));
-                        } else if (slot >= 0 && !(g.debug & 1u)) {   // slot < 0: a padding row, nothing to deliver
-                            uint16_t* dst = reinterpret_cast<uint16_t*>(__ldg(reinterpret_cast<const unsigned long long*>(g.slots) + owner)) +
-                                            size_t(slot) * g.ldc + col0;
-                            bulk_store(dst, rowbuf, UN * 2);
+                        uint16_t* dst = nullptr;
+                        if (scatter_target(row0 + lane, dst)) {
+                            bulk_store(dst + col0, rowbuf, UN * 2);
                             tma_store_commit();
                         }
                     }
-                    continue;
-                }
-                if (!Cfg::STAGED_EPILOGUE || g.direct_store) {
-                    uint16_t* dst = static_cast<uint16_t*>(g.c) + size_t(row0 + lane) * g.ldc + col0 + chunk * EPI_COLS;
-                    bool deliver = true;                          // a lane-wise predicate: the warp stays converged
-                    if (g.row_dst) {
-                        const int code = __ldg(g.row_dst + row0 + lane);
-                        const int slot = (code & 0xFFFFFF) - 1, owner = code >> 24;
-                        deliver = slot >= 0;                      // 0 marks a padding row: nothing to deliver
-                        if (deliver && (slot >= g.slot_rows || owner >= g.world)) {
-                            atomicOr(g.status, uint32_t(STATUS_BAD_ARGUMENT));
-                            deliver = false;
-                        }
-                        if (deliver)
-                            dst = reinterpret_cast<uint16_t*>(__ldg(reinterpret_cast<const unsigned long long*>(g.slots) + owner)) + size_t(slot) * g.ldc + col0 + chunk * EPI_COLS;
-                    }
-                    if (g.gather_world) {
-                        const size_t at = size_t(row0 + lane) * g.gather_ldc + g.gather_col0 + col0 + chunk * EPI_COLS;
-                        for (int r = 0; r < g.gather_world; ++r)
-                            store_row_chunk(reinterpret_cast<uint16_t*>(__ldg(reinterpret_cast<const unsigned long long*>(g.gather_ptrs) + r)) + at,
-                                            v, alpha, true);
-                        continue;
-                    }
-                    store_row_chunk(dst, v, alpha, deliver);
-                    continue;
-                }
-                const uint32_t buf = stage_base + (stores & 1u) * Cfg::EPI_WARP_BYTES;
-                const long long s0 = g.prof ? clock64() : 0;
-                if (lane == 0) tma_store_wait_read<1>();        // the store that last read this buffer is done
-                __syncwarp();
-                if (g.prof) wait_store += clock64() - s0;
-                #pragma unroll
-                for (int q = 0; q < EPI_COLS / 8; ++q) {
-                    uint32_t h[4];
+                } else if constexpr (EPI == EPI_SCATTER) {
+                    uint16_t* dst = nullptr;                      // a lane-wise predicate: the warp stays converged
+                    const bool deliver = scatter_target(row0 + lane, dst);
+                    store_row_chunk(dst + col0 + chunk * EPI_COLS, v, alpha, deliver);
+                } else if constexpr (EPI == EPI_GATHER_DIRECT) {
+                    const size_t at = size_t(row0 + lane) * g.gather_ldc + g.gather_col0 + col0 + chunk * EPI_COLS;
+                    for (int r = 0; r < g.gather_world; ++r)
+                        store_row_chunk(reinterpret_cast<uint16_t*>(__ldg(reinterpret_cast<const unsigned long long*>(g.gather_ptrs) + r)) + at,
+                                        v, alpha, true);
+                } else if constexpr (EPI == EPI_DIRECT) {
+                    store_row_chunk(static_cast<uint16_t*>(g.c) + size_t(row0 + lane) * g.ldc + col0 + chunk * EPI_COLS, v, alpha, true);
+                } else {
+                    // EPI_TMA / EPI_GATHER_TMA: the chunk goes through one of the warp's two swizzled buffers
+                    const uint32_t buf = stage_base + (stores & 1u) * Cfg::EPI_WARP_BYTES;
+                    const long long s0 = now();
+                    if (lane == 0) tma_store_wait_read<1>();        // the store that last read this buffer is done
+                    __syncwarp();
+                    if (PROF) wait_store += now() - s0;
                     #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const float lo = __uint_as_float(v[q * 8 + 2 * i]) * alpha;
-                        const float hi = __uint_as_float(v[q * 8 + 2 * i + 1]) * alpha;
-                        if (g.out_bf16) {
-                            const __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
-                            h[i] = *reinterpret_cast<const uint32_t*>(&p);
-                        } else {
-                            const __half2 p = __floats2half2_rn(lo, hi);
-                            h[i] = *reinterpret_cast<const uint32_t*>(&p);
-                        }
+                    for (int q = 0; q < EPI_COLS / 8; ++q) {
+                        uint32_t h[4];
+                        #pragma unroll
+                        for (int i = 0; i < 4; ++i) h[i] = pack_pair(v[q * 8 + 2 * i], v[q * 8 + 2 * i + 1], alpha);
+                        // 128-byte swizzle: 16-byte chunk q of row `lane` lands in chunk q ^ (lane % 8).
+                        const uint32_t dst = buf + lane * 128 + ((q ^ (lane & 7)) << 4);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                                     :: "r"(dst), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]) : "memory");
                     }
-                    // 128-byte swizzle: 16-byte chunk q of row `lane` lands in chunk q ^ (lane % 8).
-                    const uint32_t dst = buf + lane * 128 + ((q ^ (lane & 7)) << 4);
-                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
-                                 :: "r"(dst), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]) : "memory");
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if constexpr (EPI == EPI_GATHER_TMA) {
+                            // the same staged tile to every rank's full C; one bulk group, so the buffer is reused
+                            // only after all of them have read it
+                            for (int r = 0; r < g.gather_world; ++r)
+                                tma_store_2d(g.gather_maps + r, buf, g.gather_col0 + col0 + chunk * EPI_COLS, row0);
+                        } else if (g.c_evict_first) {
+                            tma_store_2d_hint(tmC, buf, col0 + chunk * EPI_COLS, row0, c_policy);
+                        } else {
+                            tma_store_2d(tmC, buf, col0 + chunk * EPI_COLS, row0);
+                        }
+                        tma_store_commit();
+                    }
+                    ++stores;
                 }
-                fence_async_smem();
-                __syncwarp();
-                if (lane == 0 && !(g.debug & 1u)) {
-                    if (g.gather_world) {
-                        // the same staged tile to every rank's full C; one bulk group, so the buffer is reused
-                        // only after all of them have read it
-                        for (int r = 0; r < g.gather_world; ++r)
-                            tma_store_2d(g.gather_maps + r, buf, g.gather_col0 + col0 + chunk * EPI_COLS, row0);
-                    } else if (g.c_evict_first) tma_store_2d_hint(tmC, buf, col0 + chunk * EPI_COLS, row0, c_policy);
-                    else tma_store_2d(tmC, buf, col0 + chunk * EPI_COLS, row0);
-                    tma_store_commit();
-                }
-                ++stores;
             }
-            if (g.split_k > 1) {
+            if constexpr (EPI == EPI_SPLIT_K) {
                 if (!split_k_finish(seg, warp, lane, row0, col0, alpha)) break;
             }
         }
         tma_store_wait_all();                                   // lanes without stores in flight fall through
-        if (g.prof && warp == 0 && lane == 0) {
+        if (PROF && warp == 0 && lane == 0) {
             unsigned long long* out = g.prof + (size_t(unit) * CG + rank) * PROF_WORDS;
             out[PROF_EPI_WAIT_ACC] = wait_acc;
             out[PROF_EPI_WAIT_STORE] = wait_store;
-            out[PROF_EPI_TOTAL] = clock64() - born;
+            out[PROF_EPI_TOTAL] = now() - born;
             uint32_t smid;
             asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
             out[PROF_SMID] = smid;
@@ -711,12 +716,12 @@ struct Roles {
     }
 };
 
-template <int CG, int UN, bool RS = false>
+template <int CG, int UN, int EPI, bool PROF>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB,
                   const __grid_constant__ CUtensorMap tmC, const GemmArgs g) {
-    using Cfg = Config<CG, UN, RS>;
+    using Cfg = Config<CG, UN, EPI>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t smem = (raw + 1023u) & ~1023u;
@@ -741,17 +746,24 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
     if (warp == 5 && lane == 0) {
         prefetch_tensormap(&tmA); prefetch_tensormap(&tmB);
-        prefetch_tensormap(&tmSFA); prefetch_tensormap(&tmSFB); prefetch_tensormap(&tmC);
+        prefetch_tensormap(&tmSFA); prefetch_tensormap(&tmSFB);
+        if constexpr (Cfg::STAGED_EPILOGUE) prefetch_tensormap(&tmC);
+    }
+    const uint32_t unit = CG == 2 ? blockIdx.x / 2u : blockIdx.x;
+    if (g.unit_side && threadIdx.x == 32) {
+        // the tile route was laid out for the L2 side this unit was seen on when the plan was prepared
+        uint32_t smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        if (smid < 256u && __ldg(g.sm_side + smid) != __ldg(g.unit_side + unit)) atomicAdd(g.status + 3, 1u);
     }
     tc_fence_before_sync();
     if constexpr (CG == 2) { cluster_arrive(); cluster_wait(); } else { __syncthreads(); }
     tc_fence_after_sync();
     const uint32_t tmem = ctrl->tmem_base;
 
-    Roles<CG, UN, RS> roles{smem, ctrl, rank,
-                        CG == 2 ? blockIdx.x / 2u : blockIdx.x, gridDim.x / CG,
-                        uint32_t(g.block_expert ? __ldg(g.num_blocks) : g.tiles_m) * uint32_t(g.tiles_n),
-                        CG == 2 ? map_to_cta(smem_u32(const_cast<uint32_t*>(&ctrl->wait.abort)), rank ^ 1u) : 0u, g};
+    Roles<CG, UN, EPI, PROF> roles{smem, ctrl, rank, unit, gridDim.x / CG,
+                                   uint32_t(g.block_expert ? __ldg(g.num_blocks) : g.tiles_m) * uint32_t(g.tiles_n),
+                                   CG == 2 ? map_to_cta(smem_u32(const_cast<uint32_t*>(&ctrl->wait.abort)), rank ^ 1u) : 0u, g};
 
     if (warp == 5) {
         roles.produce(&tmA, &tmB, &tmSFA, &tmSFB, lane);
@@ -773,8 +785,9 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         tc_fence_after_sync();
         tmem_dealloc<CG>(tmem, TMEM_COLS);
     }
-    if (blockIdx.x == 0 && threadIdx.x == 0) g.status[2] = uint32_t(clock64() - entered);
+    if (blockIdx.x == 0 && threadIdx.x == 0) *g.cycles = uint32_t(clock64() - entered);
 }
+
 
 // ---- host side ---------------------------------------------------------------
 
@@ -795,36 +808,45 @@ EncodeTiled encode_tiled() {
     return fn;
 }
 
-CUtensorMap make_map_2d(CUtensorMapDataType type, const void* ptr, uint64_t inner, uint64_t outer,
-                        uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer,
-                        CUtensorMapSwizzle swizzle, CUtensorMapL2promotion promo) {
+// rank 2 or 3; shape[0] is the contiguous dimension, strides are those of dimensions 1.. in bytes
+CUtensorMap make_map(CUtensorMapDataType type, const void* ptr, int rank, const cuuint64_t* shape,
+                     const cuuint64_t* strides, const cuuint32_t* box, CUtensorMapSwizzle swizzle,
+                     CUtensorMapL2promotion promo) {
     CUtensorMap map{};
-    const cuuint64_t shape[2] = {inner, outer};
-    const cuuint64_t strides[1] = {row_stride_bytes};
-    const cuuint32_t box[2] = {box_inner, box_outer};
-    const cuuint32_t steps[2] = {1, 1};
-    const CUresult r = encode_tiled()(&map, type, 2, const_cast<void*>(ptr), shape, strides, box, steps,
+    const cuuint32_t steps[3] = {1, 1, 1};
+    const CUresult r = encode_tiled()(&map, type, cuuint32_t(rank), const_cast<void*>(ptr), shape, strides, box, steps,
                                       CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, promo,
                                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled failed with code " + std::to_string(int(r)));
     return map;
 }
 
-// Packed operand [rows, K/2] bytes, tiles of `box_rows` rows x 128 bytes, 128-byte swizzle.
+// Packed operand [rows, K/2] bytes, tiles of `box_rows` rows x 128 bytes, 128-byte swizzle. A box that
+// reaches beyond K/2 bytes (the last step of a K that is not a multiple of 256) reads zeros there.
 CUtensorMap operand_map(const uint8_t* p, int rows, int K, int box_rows) {
-    return make_map_2d(CU_TENSOR_MAP_DATA_TYPE_UINT8, p, uint64_t(K / 2), uint64_t(rows), uint64_t(K / 2),
-                       ROW_BYTES, uint32_t(box_rows), CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+    const cuuint64_t shape[2] = {cuuint64_t(K / 2), cuuint64_t(rows)};
+    const cuuint64_t strides[1] = {cuuint64_t(K / 2)};
+    const cuuint32_t box[2] = {ROW_BYTES, cuuint32_t(box_rows)};
+    return make_map(CU_TENSOR_MAP_DATA_TYPE_UINT8, p, 2, shape, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
 }
-// The scale bytes seen as rows of 128 bytes: four rows per atom, the four atoms
-// of a K=256 step consecutive, so one 16-row box is one stage's 2 KiB.
+// The scale bytes of one 128-row block are K/64 atoms of 512 bytes = 4 * K/64 rows of 128 bytes; the map is
+// {128 bytes, those rows, row blocks}, and one 16-row box is the four atoms of a K = 256 step (zeros beyond
+// the block's last atom).
 CUtensorMap scale_map(const uint8_t* p, int rows, int K) {
-    const uint64_t total = uint64_t(rows) * uint64_t(K / 16);
-    return make_map_2d(CU_TENSOR_MAP_DATA_TYPE_UINT8, p, 128, total / 128, 128, 128, 16,
-                       CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+    const cuuint64_t per_block = cuuint64_t(K / 64) * 4;
+    const cuuint64_t shape[3] = {128, per_block, cuuint64_t(rows / 128)};
+    const cuuint64_t strides[2] = {128, per_block * 128};
+    const cuuint32_t box[3] = {128, 16, 1};
+    return make_map(CU_TENSOR_MAP_DATA_TYPE_UINT8, p, 3, shape, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
 }
-CUtensorMap output_map(const __half* C, int M, int N) {
-    return make_map_2d(CU_TENSOR_MAP_DATA_TYPE_FLOAT16, C, uint64_t(N), uint64_t(M), uint64_t(N) * 2,
-                       EPI_COLS, 32, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE);
+CUtensorMap output_map(const void* C, int M, int N, bool bf16) {
+    const cuuint64_t shape[2] = {cuuint64_t(N), cuuint64_t(M)};
+    const cuuint64_t strides[1] = {cuuint64_t(N) * 2};
+    const cuuint32_t box[2] = {EPI_COLS, 32};
+    return make_map(bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, C, 2, shape, strides, box,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE);
 }
 
 int env_int(const char* name, int fallback) {
@@ -832,12 +854,46 @@ int env_int(const char* name, int fallback) {
     return v && *v ? std::atoi(v) : fallback;
 }
 
-template <int CG, int UN, bool RS = false>
+std::mutex g_host_state;            // guards the per-device caches below
+
+// One kernel instance: sets its shared-memory limit once per device, then launches.
+template <int CG, int UN, int EPI, bool PROF = false>
+void launch_instance(int device, int units, const CUtensorMap& A, const CUtensorMap& B, const CUtensorMap& SFA,
+                     const CUtensorMap& SFB, const CUtensorMap& tmC, const GemmArgs& g, cudaStream_t stream) {
+    using Cfg = Config<CG, UN, EPI>;
+    auto kernel = nvfp4_gemm_kernel<CG, UN, EPI, PROF>;
+    {
+        static bool ready[64] = {};
+        std::lock_guard<std::mutex> hold(g_host_state);
+        if (device < 0 || device >= 64 || !ready[device]) {
+            cuda_check(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+            if (device >= 0 && device < 64) ready[device] = true;
+        }
+    }
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim = {unsigned(CG), 1, 1};
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(unsigned(units) * CG);
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cfg.stream = stream;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    cuda_check(cudaLaunchKernelEx(&cfg, kernel, A, B, SFA, SFB, tmC, g));
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+}
+
+// Units (CTAs, or CTA pairs) of the persistent grid that fit the device at once. Every instance of a
+// variant holds one CTA per SM (its ring fills the shared memory), so the count is taken once per variant.
+template <int CG, int UN>
 int max_units(int device) {
-    using Cfg = Config<CG, UN, RS>;
+    constexpr int EPI = CG == 2 ? EPI_TMA : EPI_DIRECT;
+    using Cfg = Config<CG, UN, EPI>;
     static int cached[64] = {};
-    if (device < 64 && cached[device]) return cached[device];
-    auto kernel = nvfp4_gemm_kernel<CG, UN, RS>;
+    std::lock_guard<std::mutex> hold(g_host_state);
+    if (device >= 0 && device < 64 && cached[device]) return cached[device];
+    auto kernel = nvfp4_gemm_kernel<CG, UN, EPI, false>;
     cuda_check(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
     int sms = 0;
     cuda_check(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
@@ -857,60 +913,40 @@ int max_units(int device) {
         units = clusters;
     }
     if (units < 1) throw std::runtime_error("nvfp4 gemm: the kernel does not fit on this device");
-    if (device < 64) cached[device] = units;
+    if (device >= 0 && device < 64) cached[device] = units;
     return units;
 }
 
-template <int CG, int UN>
-void launch_variant(const gpu_kernels::Nvfp4Params& p, const CUtensorMap& tmC, void* c, uint32_t* status,
-                    cudaStream_t stream, unsigned long long* prof) {
-    using Cfg = Config<CG, UN>;
-    GemmArgs g{p.M, p.N, p.K, p.M / Cfg::TILE_M, p.N / UN, std::max(1, p.group_m), p.alpha, status, prof,
-               uint32_t(env_int("NVFP4_B200_DEBUG", 0)), p.c_evict_first, 0, nullptr, nullptr, 0,
-               p.direct_store, c, p.N, nullptr, nullptr, nullptr, 0.0f, nullptr, nullptr, 0, 0, p.k_skew,
-               p.split_k, p.split_k > 1 ? reinterpret_cast<float*>(static_cast<uint8_t*>(p.split_k_workspace) + SPLIT_K_FLAG_BYTES) : nullptr,
-               p.split_k > 1 ? static_cast<uint32_t*>(p.split_k_workspace) : nullptr,
-               p.split_k > 1 ? static_cast<uint32_t*>(p.split_k_workspace) + SPLIT_K_FLAG_BYTES / 8 : nullptr,
-               p.gather_world, p.gather_col0, p.gather_ldc, static_cast<const CUtensorMap*>(p.gather_maps),
-               static_cast<void* const*>(p.gather_ptrs)};
-    if (p.split_k > 1 && !p.direct_store) throw std::logic_error("nvfp4 gemm: split-K writes C from registers");
-    cudaLaunchAttribute attr{};
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim = {unsigned(CG), 1, 1};
-    cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(unsigned(p.clusters) * CG);
-    cfg.blockDim = dim3(NUM_THREADS);
-    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
-    cfg.stream = stream;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
-    cuda_check(cudaLaunchKernelEx(&cfg, nvfp4_gemm_kernel<CG, UN>, p.A, p.B, p.SFA, p.SFB, tmC, g));
-    g_launches.fetch_add(1, std::memory_order_relaxed);
+int fit_units(int device, int cta_group, int tile_n) {
+    return cta_group == 2 ? max_units<2, 256>(device) : tile_n == 256 ? max_units<1, 256>(device) : max_units<1, 128>(device);
 }
 
-uint32_t* status_word(int device) {
-    static std::mutex lock;
+uint32_t* status_base(int device) {
     static uint32_t* cached[64] = {};
-    std::lock_guard<std::mutex> hold(lock);
-    if (device < 64 && cached[device]) return cached[device];
+    std::lock_guard<std::mutex> hold(g_host_state);
+    if (device >= 0 && device < 64 && cached[device]) return cached[device];
     uint32_t* p = nullptr;
     cuda_check(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_status));
-    if (device < 64) cached[device] = p;
+    if (device >= 0 && device < 64) cached[device] = p;
     return p;
 }
+uint32_t* status_slot(int device, int slot) { return status_base(device) + size_t(slot) * 4; }
+
+std::atomic<unsigned> g_next_slot{0};
 
 void prepare(gpu_kernels::Nvfp4Params& p, const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB,
              int M, int N, int K, cudaStream_t) {
     require_sm100();
     if (M <= 0 || N <= 0 || K <= 0) throw std::invalid_argument("nvfp4 gemm: M, N, K must be positive");
-    if (M % 128 || N % 128) throw std::invalid_argument("nvfp4 gemm: M and N must be multiples of 128");
-    if (K % STAGE_K) throw std::invalid_argument("nvfp4 gemm: K must be a multiple of 256");
+    if (M % 128 || N % 128) throw std::invalid_argument("nvfp4 gemm: M and N must be multiples of 128 (whole scale atoms)");
+    if (K % 64) throw std::invalid_argument("nvfp4 gemm: K must be a multiple of 64 (whole scale atoms)");
     if (!A || !B || !SFA || !SFB) throw std::invalid_argument("nvfp4 gemm: null operand pointer");
     if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(SFA) |
          reinterpret_cast<uintptr_t>(SFB)) & 15)
         throw std::invalid_argument("nvfp4 gemm: operand pointers must be 16-byte aligned");
     int device = 0;
     cuda_check(cudaGetDevice(&device));
+    p = gpu_kernels::Nvfp4Params{};
     p.M = M; p.N = N; p.K = K;
     p.alpha = 1.0f;
     p.device = device;
@@ -925,16 +961,14 @@ void prepare(gpu_kernels::Nvfp4Params& p, const uint8_t* A, const uint8_t* B, co
     // with the loads either way: 274.8k vs 275.8k cycles at 8192^3) and C goes out by TMA store; when the
     // epilogue is a large share of a tile (short K) or the tile is a single CTA's, writing from registers
     // is faster (4096x4096x1024: 21.8k vs 25.5k cycles; 128x28672x8192: 47.0k vs 48.7k).
-    p.direct_store = env_int("NVFP4_B200_DIRECT_STORE", (K <= 2048 || p.cta_group == 1) ? 1 : 0);
+    p.direct_store = p.cta_group == 1 ? 1 : env_int("NVFP4_B200_DIRECT_STORE", K <= 2048 ? 1 : 0);
     const int box_b = p.tile_n / p.cta_group;
     p.A = operand_map(A, M, K, BLOCK_M);
     p.B = operand_map(B, N, K, box_b);
     p.SFA = scale_map(SFA, M, K);
     p.SFB = scale_map(SFB, N, K);
     const int tiles = (M / (128 * p.cta_group)) * (N / p.tile_n);
-    const int fit = p.cta_group == 2 ? max_units<2, 256>(device)
-                  : p.tile_n == 256 ? max_units<1, 256>(device) : max_units<1, 128>(device);
-    p.clusters = std::min(fit, tiles);
+    p.clusters = std::min(fit_units(device, p.cta_group, p.tile_n), tiles);
     // About sqrt(units) tile rows per band keeps the A and B panels of the tiles in flight balanced.
     int gm = 1;
     while ((gm + 1) * (gm + 1) <= p.clusters) ++gm;
@@ -944,14 +978,8 @@ void prepare(gpu_kernels::Nvfp4Params& p, const uint8_t* A, const uint8_t* B, co
     p.group_m = std::max(1, std::min(env_int("NVFP4_B200_GROUP_M", gm), M / (128 * p.cta_group)));
     // Measured: 128x28672x8192 30.2 -> 28.9 us, 8192^3 199.8 -> 199.0 us with the tiles' K walks de-phased.
     p.k_skew = env_int("NVFP4_B200_K_SKEW", 11);
-    p.split_k = 0;
-    p.split_k_workspace = nullptr;
-    p.gather_world = 0;
-    p.gather_col0 = 0;
-    p.gather_ldc = 0;
-    p.gather_maps = nullptr;
-    p.gather_ptrs = nullptr;
-    (void)status_word(device);
+    p.status_slot = 1 + int(g_next_slot.fetch_add(1, std::memory_order_relaxed) % unsigned(STATUS_SLOTS - 1));
+    (void)status_base(device);
 }
 
 // table: device memory of gather_table_bytes(world), filled here (on `stream`) with one tensor map and one
@@ -970,7 +998,7 @@ void set_gather(gpu_kernels::Nvfp4Params& p, void* const* buffers, int world, in
     auto* ptrs = reinterpret_cast<void**>(host.data() + size_t(world) * sizeof(CUtensorMap));
     for (int r = 0; r < world; ++r) {
         if (!buffers[r] || (reinterpret_cast<uintptr_t>(buffers[r]) & 15)) throw std::invalid_argument("nvfp4 gemm gather: null or misaligned buffer");
-        maps[r] = output_map(static_cast<const __half*>(buffers[r]), p.M, n_total);
+        maps[r] = output_map(buffers[r], p.M, n_total, p.out_bf16 != 0);
         ptrs[r] = buffers[r];
     }
     cuda_check(cudaMemcpyAsync(table, host.data(), host.size(), cudaMemcpyHostToDevice, stream));
@@ -990,11 +1018,10 @@ void set_gather(gpu_kernels::Nvfp4Params& p, void* const* buffers, int world, in
 // about 17k cycles, which is what a quarter of a 32-step K loop saves.
 int split_k_factor(const gpu_kernels::Nvfp4Params& p) {
     const int tiles = (p.M / (128 * p.cta_group)) * (p.N / p.tile_n);
-    const int fit = p.cta_group == 2 ? max_units<2, 256>(p.device)
-                  : p.tile_n == 256 ? max_units<1, 256>(p.device) : max_units<1, 128>(p.device);
-    const int ksteps = p.K / STAGE_K, chunks = p.tile_n / EPI_COLS;
+    const int fit = fit_units(p.device, p.cta_group, p.tile_n);
+    const int ksteps = (p.K + STAGE_K - 1) / STAGE_K, chunks = p.tile_n / EPI_COLS;
     for (int s : {4})
-        if (s <= chunks && tiles * s <= fit && ksteps % s == 0 && ksteps / s >= 4 &&
+        if (p.K % STAGE_K == 0 && s <= chunks && tiles * s <= fit && ksteps % s == 0 && ksteps / s >= 4 &&
             size_t(tiles) * s * p.cta_group * 4 * sizeof(uint32_t) <= SPLIT_K_FLAG_BYTES / 2)
             return s;
     return 0;
@@ -1012,41 +1039,129 @@ void enable_split_k(gpu_kernels::Nvfp4Params& p, void* workspace, size_t bytes, 
     if (!s) throw std::invalid_argument("nvfp4 gemm: split-K does not apply to this shape");
     if (!workspace || bytes < split_k_workspace_bytes(p) || (reinterpret_cast<uintptr_t>(workspace) & 255))
         throw std::invalid_argument("nvfp4 gemm: split-K workspace missing, too small or not 256-byte aligned");
+    // the flags must be zero before the first launch, whatever stream that launch uses
     cuda_check(cudaMemsetAsync(workspace, 0, SPLIT_K_FLAG_BYTES, stream));
+    cuda_check(cudaStreamSynchronize(stream));
     p.split_k = s;
     p.split_k_workspace = workspace;
     p.direct_store = 1;
+    p.route = nullptr;                                                   // slices are dealt in item order
     p.clusters = (p.M / (128 * p.cta_group)) * (p.N / p.tile_n) * s;     // one (tile, slice) per unit
 }
 
-void launch_with(const gpu_kernels::Nvfp4Params& p, __half* C, cudaStream_t stream, unsigned long long* prof) {
+GemmArgs dense_args(const gpu_kernels::Nvfp4Params& p, void* c, unsigned long long* prof) {
+    const int tile_m = 128 * p.cta_group;
+    GemmArgs g{};
+    g.M = p.M; g.N = p.N; g.K = p.K;
+    g.ksteps = (p.K + STAGE_K - 1) / STAGE_K;
+    g.tiles_m = p.M / tile_m;
+    g.tiles_n = p.N / p.tile_n;
+    g.group_m = std::max(1, p.group_m);
+    g.alpha = p.alpha;
+    g.status = status_slot(p.device, p.status_slot);
+    g.cycles = status_slot(p.device, 0) + 2;
+    g.prof = prof;
+    g.c_evict_first = p.c_evict_first;
+    g.out_bf16 = p.out_bf16;
+    g.c = c;
+    g.ldc = p.N;
+    g.k_skew = p.k_skew;
+    g.split_k = p.split_k;
+    if (p.split_k > 1) {
+        auto* ws = static_cast<uint8_t*>(p.split_k_workspace);
+        g.sk_flags = reinterpret_cast<uint32_t*>(ws);
+        g.sk_done = reinterpret_cast<uint32_t*>(ws) + SPLIT_K_FLAG_BYTES / 8;
+        g.sk_partials = reinterpret_cast<float*>(ws + SPLIT_K_FLAG_BYTES);
+    }
+    g.gather_world = p.gather_world;
+    g.gather_col0 = p.gather_col0;
+    g.gather_ldc = p.gather_ldc;
+    g.gather_maps = static_cast<const CUtensorMap*>(p.gather_maps);
+    g.gather_ptrs = static_cast<void* const*>(p.gather_ptrs);
+    if (p.route && p.split_k <= 1) {
+        g.route = static_cast<const uint32_t*>(p.route);
+        g.sm_side = static_cast<const uint8_t*>(p.sm_side);
+        g.unit_side = static_cast<const uint8_t*>(p.unit_side);
+    }
+    return g;
+}
+
+template <int CG, int UN>
+void launch_dense(const gpu_kernels::Nvfp4Params& p, const CUtensorMap& tmC, const GemmArgs& g, cudaStream_t stream) {
+    const bool staged = CG == 2 && !p.direct_store;
+    const int dev = p.device, units = p.clusters;
+    if (p.split_k > 1) {
+        launch_instance<CG, UN, EPI_SPLIT_K>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream);
+    } else if (p.gather_world) {
+        if constexpr (CG == 2) {
+            if (staged) return launch_instance<CG, UN, EPI_GATHER_TMA>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream);
+        }
+        launch_instance<CG, UN, EPI_GATHER_DIRECT>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream);
+    } else if (g.prof) {
+        if constexpr (CG == 2) {
+            if (staged) return launch_instance<CG, UN, EPI_TMA, true>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream);
+        }
+        launch_instance<CG, UN, EPI_DIRECT, true>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream);
+    } else {
+        if constexpr (CG == 2) {
+            if (staged) return launch_instance<CG, UN, EPI_TMA>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream);
+        }
+        launch_instance<CG, UN, EPI_DIRECT>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream);
+    }
+}
+
+void launch_with(const gpu_kernels::Nvfp4Params& p, void* C, cudaStream_t stream, unsigned long long* prof) {
     if (!C || (reinterpret_cast<uintptr_t>(C) & 15)) throw std::invalid_argument("nvfp4 gemm: C must be 16-byte aligned");
-    const CUtensorMap tmC = output_map(C, p.M, p.N);
-    uint32_t* status = status_word(p.device);
-    if (p.cta_group == 2) launch_variant<2, 256>(p, tmC, C, status, stream, prof);
-    else if (p.tile_n == 256) launch_variant<1, 256>(p, tmC, C, status, stream, prof);
-    else launch_variant<1, 128>(p, tmC, C, status, stream, prof);
+    if (prof && (p.split_k > 1 || p.gather_world)) throw std::invalid_argument("nvfp4 gemm profile: plain plans only");
+    const CUtensorMap tmC = output_map(C, p.M, p.N, p.out_bf16 != 0);
+    const GemmArgs g = dense_args(p, C, prof);
+    if (p.cta_group == 2) launch_dense<2, 256>(p, tmC, g, stream);
+    else if (p.tile_n == 256) launch_dense<1, 256>(p, tmC, g, stream);
+    else launch_dense<1, 128>(p, tmC, g, stream);
 }
 
 void launch(const gpu_kernels::Nvfp4Params& p, __half* C, cudaStream_t stream) { launch_with(p, C, stream, nullptr); }
 
+[[noreturn]] void throw_status(const uint32_t* words) {
+    char msg[256];
+    std::snprintf(msg, sizeof(msg), "nvfp4 gemm: the kernel reported an error (status 0x%x: 0x10 = bad destination, else a wait gave up; first tag 0x%08x); output is invalid",
+                  words[0], words[1]);
+    throw std::runtime_error(msg);
+}
+
+// Every slot of the current device: any plan's error is reported (and all are cleared).
 void validate() {
     cuda_check(cudaDeviceSynchronize());
+    static thread_local std::vector<uint32_t> host;
+    host.resize(size_t(STATUS_SLOTS) * 4);
+    cuda_check(cudaMemcpyFromSymbol(host.data(), g_status, host.size() * sizeof(uint32_t)));
+    for (int s = 0; s < STATUS_SLOTS; ++s) {
+        if (!host[size_t(s) * 4]) continue;
+        const uint32_t words[2] = {host[size_t(s) * 4], host[size_t(s) * 4 + 1]};
+        for (int t = 0; t < STATUS_SLOTS; ++t)
+            if (host[size_t(t) * 4]) {
+                const uint32_t zero[2] = {0u, 0u};
+                cuda_check(cudaMemcpyToSymbol(g_status, zero, sizeof(zero), size_t(t) * 16));
+            }
+        throw_status(words);
+    }
+}
+
+void validate_slot(int device, int slot) {
+    cuda_check(cudaDeviceSynchronize());
     uint32_t host[4] = {};
-    cuda_check(cudaMemcpyFromSymbol(host, g_status, sizeof(host)));
+    uint32_t* where = status_slot(device, slot);
+    cuda_check(cudaMemcpy(host, where, sizeof(host), cudaMemcpyDeviceToHost));
     if (host[0]) {
-        const uint32_t zero[4] = {};
-        cuda_check(cudaMemcpyToSymbol(g_status, zero, sizeof(zero)));
-        char msg[224];
-        std::snprintf(msg, sizeof(msg), "nvfp4 gemm: the kernel reported an error (status 0x%x: 0x10 = bad destination, else a wait gave up; first tag 0x%08x); output is invalid",
-                      host[0], host[1]);
-        throw std::runtime_error(msg);
+        const uint32_t zero[2] = {0u, 0u};
+        cuda_check(cudaMemcpy(where, zero, sizeof(zero), cudaMemcpyHostToDevice));
+        throw_status(host);
     }
 }
 
 }  // namespace
 
-uint32_t* device_status_word(int device) { return status_word(device); }
+uint32_t* device_status_word(int device) { return status_slot(device, 0); }
 
 void require_sm100() {
     int device = 0, major = 0;
@@ -1055,6 +1170,12 @@ void require_sm100() {
     if (major != 10) throw std::runtime_error("this library only runs on compute capability 10.x (B200); there is no fallback");
 }
 
+// Plain launch through a pointer that may be FP16 or BF16 storage (the plan's out_bf16 decides).
+void gemm_launch(const gpu_kernels::Nvfp4Params& p, void* C, cudaStream_t stream) { launch_with(p, C, stream, nullptr); }
+
+// The device-wide slot (grouped launches and the expert-path kernels report there).
+void validate_device_slot(int device) { validate_slot(device, 0); }
+
 // One launch with the per-role cycle counters switched on; copies 16 words per CTA to `host`
 // (synchronises). Diagnostic: the counters cost a few clock reads per wait.
 int gemm_profile(const gpu_kernels::Nvfp4Params& p, __half* C, cudaStream_t stream, unsigned long long* host, int max_words) {
@@ -1062,9 +1183,15 @@ int gemm_profile(const gpu_kernels::Nvfp4Params& p, __half* C, cudaStream_t stre
     if (words > max_words) throw std::invalid_argument("nvfp4 gemm profile: output buffer too small");
     unsigned long long* dev = nullptr;
     cuda_check(cudaMalloc(&dev, size_t(words) * 8));
-    cuda_check(cudaMemsetAsync(dev, 0, size_t(words) * 8, stream));
-    launch_with(p, C, stream, dev);
-    cudaError_t e = cudaMemcpyAsync(host, dev, size_t(words) * 8, cudaMemcpyDeviceToHost, stream);
+    cudaError_t e = cudaMemsetAsync(dev, 0, size_t(words) * 8, stream);
+    try {
+        cuda_check(e);
+        launch_with(p, C, stream, dev);
+    } catch (...) {
+        cudaFree(dev);
+        throw;
+    }
+    e = cudaMemcpyAsync(host, dev, size_t(words) * 8, cudaMemcpyDeviceToHost, stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
     cudaFree(dev);
     cuda_check(e);
@@ -1073,9 +1200,11 @@ int gemm_profile(const gpu_kernels::Nvfp4Params& p, __half* C, cudaStream_t stre
 
 // SM cycles the first CTA of the last finished GEMM launch on the current device spent in the kernel.
 unsigned last_kernel_cycles() {
-    uint32_t host[4] = {};
-    cuda_check(cudaMemcpyFromSymbol(host, g_status, sizeof(host)));
-    return host[2];
+    int device = 0;
+    cuda_check(cudaGetDevice(&device));
+    uint32_t cycles = 0;
+    cuda_check(cudaMemcpy(&cycles, status_slot(device, 0) + 2, sizeof(cycles), cudaMemcpyDeviceToHost));
+    return cycles;
 }
 
 void grouped_prepare(GroupedGemm& p, const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB,
@@ -1085,7 +1214,7 @@ void grouped_prepare(GroupedGemm& p, const uint8_t* A, const uint8_t* B, const u
     if (block_rows != 128 && block_rows != 256) throw std::invalid_argument("grouped gemm: block rows must be 128 or 256");
     if (pool_rows <= 0 || pool_rows % block_rows) throw std::invalid_argument("grouped gemm: pool rows must be a positive multiple of the block rows");
     if (n <= 0 || n % 256) throw std::invalid_argument("grouped gemm: N per expert must be a multiple of 256");
-    if (k <= 0 || k % STAGE_K) throw std::invalid_argument("grouped gemm: K must be a multiple of 256");
+    if (k <= 0 || k % 64) throw std::invalid_argument("grouped gemm: K must be a multiple of 64");
     if (experts <= 0 || !A || !B || !SFA || !SFB || !block_expert || !num_blocks)
         throw std::invalid_argument("grouped gemm: null pointer or no experts");
     cuda_check(cudaGetDevice(&p.device));
@@ -1099,7 +1228,7 @@ void grouped_prepare(GroupedGemm& p, const uint8_t* A, const uint8_t* B, const u
     p.SFB = scale_map(SFB, experts * n, k);
     const int fit = block_rows == 256 ? max_units<2, 256>(p.device) : max_units<1, 256>(p.device);
     p.units = std::min(fit, (pool_rows / block_rows) * (n / 256));
-    (void)status_word(p.device);
+    (void)status_base(p.device);
 }
 
 void grouped_launch(const GroupedGemm& p, void* C, int out_bf16, cudaStream_t stream) {
@@ -1111,40 +1240,59 @@ void grouped_launch_fused(const GroupedGemm& p, void* C, int out_bf16, uint8_t* 
                           int slot_rows, cudaStream_t stream) {
     const bool fused = act_packed != nullptr;
     if (row_dst) {
-        if (fused || !slots || !C || world < 1 || world > 128 || slot_rows <= 0)
-            throw std::invalid_argument("grouped gemm: scatter needs a table of 1..128 slot buffers and this rank's own "
-                                        "buffer, and cannot be combined with the fused activation");
+        // a destination code is (rank << 24) | (row + 1) in 32 bits
+        if (fused || !slots || !C || world < 1 || world > 127 || slot_rows <= 0 || slot_rows >= (1 << 24))
+            throw std::invalid_argument("grouped gemm: scatter needs a table of 1..127 slot buffers of fewer than 2^24 rows and "
+                                        "this rank's own buffer, and cannot be combined with the fused activation");
     }
     if (fused && (!act_scales || !row_weight)) throw std::invalid_argument("grouped gemm: fused SwiGLU needs scales and row weights");
     if (!fused && (!C || (reinterpret_cast<uintptr_t>(C) & 15))) throw std::invalid_argument("grouped gemm: C must be 16-byte aligned");
     if (fused) C = act_packed;       // only the tensor map needs a valid address; the fused route never stores C
-    const CUtensorMap tmC = make_map_2d(out_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, C,
-                                        uint64_t(p.n), uint64_t(p.pool_rows), uint64_t(p.n) * 2, EPI_COLS, 32,
-                                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE);
-    const int cg = p.block_rows == 256 ? 2 : 1;
-    GemmArgs g{p.pool_rows, p.n, p.k, p.pool_rows / p.block_rows, p.n / 256, 1, 1.0f, status_word(p.device), nullptr,
-               0u, 1, out_bf16, p.block_expert, p.num_blocks, p.n, 1, C, p.n, act_packed, act_scales, row_weight, clamp,
-               row_dst, slots, world, slot_rows, 0, 0, nullptr, nullptr, nullptr, 0, 0, 0, nullptr, nullptr};
-    cudaLaunchAttribute attr{};
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim = {unsigned(cg), 1, 1};
-    cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(unsigned(p.units) * cg);
-    cfg.blockDim = dim3(NUM_THREADS);
-    const bool row_staging = cg == 2 && row_dst != nullptr;
-    if (row_staging) (void)max_units<2, 256, true>(p.device);              // sets that instance's shared-memory limit once
-    cfg.dynamicSmemBytes = row_staging ? Config<2, 256, true>::SMEM_BYTES : cg == 2 ? Config<2, 256>::SMEM_BYTES : Config<1, 256>::SMEM_BYTES;
-    cfg.stream = stream;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
-    if (row_staging) cuda_check(cudaLaunchKernelEx(&cfg, nvfp4_gemm_kernel<2, 256, true>, p.A, p.B, p.SFA, p.SFB, tmC, g));
-    else if (cg == 2) cuda_check(cudaLaunchKernelEx(&cfg, nvfp4_gemm_kernel<2, 256>, p.A, p.B, p.SFA, p.SFB, tmC, g));
-    else cuda_check(cudaLaunchKernelEx(&cfg, nvfp4_gemm_kernel<1, 256>, p.A, p.B, p.SFA, p.SFB, tmC, g));
-    g_launches.fetch_add(1, std::memory_order_relaxed);
+    const CUtensorMap tmC = output_map(C, p.pool_rows, p.n, out_bf16 != 0);
+    GemmArgs g{};
+    g.M = p.pool_rows; g.N = p.n; g.K = p.k;
+    g.ksteps = (p.k + STAGE_K - 1) / STAGE_K;
+    g.tiles_m = p.pool_rows / p.block_rows;
+    g.tiles_n = p.n / 256;
+    g.group_m = 1;
+    g.alpha = 1.0f;
+    g.status = status_slot(p.device, 0);
+    g.cycles = status_slot(p.device, 0) + 2;
+    g.c_evict_first = 1;
+    g.out_bf16 = out_bf16;
+    g.block_expert = p.block_expert;
+    g.num_blocks = p.num_blocks;
+    g.b_rows_per_expert = p.n;
+    g.c = C;
+    g.ldc = p.n;
+    g.act_packed = act_packed;
+    g.act_scales = act_scales;
+    g.row_weight = row_weight;
+    g.swiglu_clamp = clamp;
+    g.row_dst = row_dst;
+    g.slots = slots;
+    g.world = world;
+    g.slot_rows = slot_rows;
+    const int dev = p.device, units = p.units;
+    if (p.block_rows == 256) {
+        if (fused) launch_instance<2, 256, EPI_ACT>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream);
+        else if (row_dst) launch_instance<2, 256, EPI_SCATTER_ROWS>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream);
+        else launch_instance<2, 256, EPI_DIRECT>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream);
+    } else {
+        if (fused) launch_instance<1, 256, EPI_ACT>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream);
+        else if (row_dst) launch_instance<1, 256, EPI_SCATTER>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream);
+        else launch_instance<1, 256, EPI_DIRECT>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream);
+    }
 }
 
-int gemm_stage_count(int cta_group, int tile_n) {
-    return cta_group == 2 ? Config<2, 256>::STAGES : tile_n == 256 ? Config<1, 256>::STAGES : Config<1, 128>::STAGES;
+int gemm_stage_count(int cta_group, int tile_n, int direct_store) {
+    if (cta_group == 2) return direct_store ? Config<2, 256, EPI_DIRECT>::STAGES : Config<2, 256, EPI_TMA>::STAGES;
+    return tile_n == 256 ? Config<1, 256, EPI_DIRECT>::STAGES : Config<1, 128, EPI_DIRECT>::STAGES;
+}
+
+size_t gemm_smem_bytes(int cta_group, int tile_n) {
+    if (cta_group == 2) return Config<2, 256, EPI_TMA>::SMEM_BYTES;
+    return tile_n == 256 ? Config<1, 256, EPI_DIRECT>::SMEM_BYTES : Config<1, 128, EPI_DIRECT>::SMEM_BYTES;
 }
 
 }  // namespace nvfp4_b200
@@ -1157,6 +1305,8 @@ Nvfp4Implementation nvfp4_sm100_implementation() {
 
 void nvfp4_set_alpha(Nvfp4Params& p, float alpha) { p.alpha = alpha; }
 
+void nvfp4_validate_plan(const Nvfp4Params& p) { nvfp4_b200::validate_slot(p.device, p.status_slot); }
+
 size_t nvfp4_split_k_workspace_bytes(const Nvfp4Params& p) { return nvfp4_b200::split_k_workspace_bytes(p); }
 
 void nvfp4_enable_split_k(Nvfp4Params& p, void* workspace, size_t bytes, cudaStream_t stream) {
@@ -1168,6 +1318,27 @@ size_t nvfp4_gather_table_bytes(int world) { return nvfp4_b200::gather_table_byt
 void nvfp4_set_gather(Nvfp4Params& p, void* const* buffers, int world, int col0, int n_total, void* table,
                       cudaStream_t stream) {
     nvfp4_b200::set_gather(p, buffers, world, col0, n_total, table, stream);
+}
+
+bool nvfp4_set_l2_side_order(Nvfp4Params& p, int on, cudaStream_t stream) {
+    p.route = p.sm_side = p.unit_side = nullptr;
+    p.side_units[0] = p.side_units[1] = 0;
+    if (!on || p.split_k > 1) return false;
+    nvfp4_b200::TileRoute r{};
+    const int tiles_m = p.M / (128 * p.cta_group), tiles_n = p.N / p.tile_n;
+    if (!nvfp4_b200::l2_side_route(p.device, p.cta_group, p.clusters, tiles_m, tiles_n, p.group_m,
+                                   nvfp4_b200::gemm_smem_bytes(p.cta_group, p.tile_n), stream, r))
+        return false;
+    p.route = r.route; p.sm_side = r.sm_side; p.unit_side = r.unit_side;
+    p.side_units[0] = r.side_units[0]; p.side_units[1] = r.side_units[1];
+    return true;
+}
+
+unsigned nvfp4_placement_misses(const Nvfp4Params& p) {
+    uint32_t misses = 0;
+    nvfp4_b200::cuda_check(cudaMemcpy(&misses, nvfp4_b200::device_status_word(p.device) + size_t(p.status_slot) * 4 + 3,
+                                      sizeof(misses), cudaMemcpyDeviceToHost));
+    return misses;
 }
 
 }  // namespace gpu_kernels

@@ -6,6 +6,7 @@
 #include <cstdint>
 #include <stdexcept>
 #include <string>
+#include <vector>
 
 namespace nvfp4_b200 {
 
@@ -18,6 +19,18 @@ inline void cuda_check(cudaError_t e) {
 // Refuse to run on anything but a compute-capability 10.x device: there is no
 // other code path in this library.
 void require_sm100();
+
+// nvfp4_schedule.cu: L2-side-aware tile order (tables live in a per-process cache, per device and shape).
+struct TileRoute {
+    const uint32_t* route;          // [tiles]: work item -> tile of the band order
+    const uint8_t* sm_side;         // [256]: L2 side by SM id
+    const uint8_t* unit_side;       // [units]: side each unit of the grid was seen on
+    int side_units[2];
+};
+bool l2_side_route(int device, int cta_group, int units, int tiles_m, int tiles_n, int group_m, size_t smem_bytes,
+                   cudaStream_t stream, TileRoute& out);
+std::vector<uint32_t> build_side_route(const std::vector<uint8_t>& sides, int tiles);
+int l2_side_census_cycles(int device, unsigned* out, int capacity);
 
 // nvfp4_quant.cu
 void check_quant_shape(int rows, int K);
@@ -67,11 +80,12 @@ void moe_return_peer(const void* out_pool_bf16, const uint8_t* recv_rows, const 
                      const int* seg_src_offset, int world, int local_experts, int hidden, int recv_capacity,
                      void* const* peer_slots, int slot_capacity, int* error, cudaStream_t stream);
 void moe_pack(const uint8_t* xq, const uint8_t* xs, const long long* ids, const float* weights, int tokens, int topk,
-              int hidden, const int* send_offset, int* cursor, uint8_t* send_rows, int* send_pos, cudaStream_t stream);
+              int hidden, int experts, const int* send_offset, int* cursor, uint8_t* send_rows, int* send_pos,
+              cudaStream_t stream);
 // Single-rank shortcut: rows go straight into the expert-major pool (no send buffer, no unpack);
 // route_row[route] is then the pool row, which moe_reduce can read the second GEMM's output by.
 void moe_pack_to_pool(const uint8_t* xq, const uint8_t* xs, const long long* ids, const float* weights, int tokens,
-                      int topk, int hidden, const int* seg_pool_offset, int* cursor, uint8_t* pool_packed,
+                      int topk, int hidden, int experts, const int* seg_pool_offset, int* cursor, uint8_t* pool_packed,
                       uint8_t* pool_scales, float* pool_weight, int* route_row, cudaStream_t stream);
 void moe_unpack(const uint8_t* recv_rows, int recv_count_capacity, const int* totals, int world, int local_experts,
                 int hidden, const int* seg_src_offset, const int* seg_pool_offset, uint8_t* pool_packed,
@@ -100,7 +114,9 @@ size_t peer_state_bytes(int world, int max_ints);
 // ids != null: the payload is the histogram of ids [routes] over `ints` bins, taken inside the kernel.
 void peer_exchange(void* own, void* const* peers_device, int world, int rank, const int* payload, int ints, int max_ints,
                    int* out, const long long* ids, int routes, cudaStream_t stream);
+// ids (may be null) and experts: routes whose expert id lies outside [0, experts) add nothing, as do negative
+// send_pos entries: a dropped route has a defined result on every path.
 void moe_reduce(const void* returned_bf16, const int* send_pos, int tokens, int topk, int hidden, void* y_bf16,
-                cudaStream_t stream);
+                const long long* ids, int experts, cudaStream_t stream);
 
 }  // namespace nvfp4_b200

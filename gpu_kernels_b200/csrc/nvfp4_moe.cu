@@ -172,7 +172,7 @@ __global__ void plan_kernel(int* counts, int world, int rank, int experts, int c
 // One warp per route: copies the token's quantised row and gathers its scale bytes out of the atom layout.
 __global__ void pack_kernel(const uint8_t* __restrict__ xq, const uint8_t* __restrict__ xs,
                             const long long* __restrict__ ids, const float* __restrict__ weights, int routes,
-                            int topk, int hidden, const int* __restrict__ send_offset, int* __restrict__ cursor,
+                            int topk, int hidden, int experts, const int* __restrict__ send_offset, int* __restrict__ cursor,
                             uint8_t* __restrict__ send_rows, int* __restrict__ send_pos,
                             const int* __restrict__ seg_pool_offset, uint8_t* __restrict__ pool_packed,
                             uint8_t* __restrict__ pool_scales, float* __restrict__ pool_weight) {
@@ -180,7 +180,13 @@ __global__ void pack_kernel(const uint8_t* __restrict__ xq, const uint8_t* __res
     const int route = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (route >= routes) return;
     const int token = route / topk;
-    const int expert = int(ids[route]);
+    const long long id = ids[route];
+    if (id < 0 || id >= experts) {
+        // an id outside the expert range (a router's "dropped" mark) takes no row anywhere; the reduce skips it
+        if (lane == 0) send_pos[route] = -1;
+        return;
+    }
+    const int expert = int(id);
     int dst = 0;
     if (lane == 0) {
         const int slot = atomicAdd(&cursor[expert], 1);
@@ -334,14 +340,21 @@ __global__ void return_rows_kernel(const uint4* __restrict__ out_pool, const int
 }
 
 // y[t] = bf16(sum over j of fp32(row of route (t, j))), j ascending: the order of the reference's
-// reduce kernel (kernels/moe/fused/sm90.cu:125-133).
+// reduce kernel (kernels/moe/fused/sm90.cu:125-133). A dropped route (expert id outside [0, experts), or a
+// negative row index) adds nothing.
 __global__ void reduce_kernel(const uint4* __restrict__ returned, const int* __restrict__ send_pos, int topk,
-                              int row_vec, uint4* __restrict__ y) {
+                              int row_vec, uint4* __restrict__ y, const long long* __restrict__ ids, int experts) {
     const int t = blockIdx.x;
     for (int i = threadIdx.x; i < row_vec; i += blockDim.x) {
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         for (int j = 0; j < topk; ++j) {
-            const uint4 v = __ldg(returned + size_t(send_pos[t * topk + j]) * row_vec + i);
+            const int pos = send_pos[t * topk + j];
+            if (pos < 0) continue;
+            if (ids) {
+                const long long id = ids[t * topk + j];
+                if (id < 0 || id >= experts) continue;
+            }
+            const uint4 v = __ldg(returned + size_t(pos) * row_vec + i);
             const uint32_t w[4] = {v.x, v.y, v.z, v.w};
             #pragma unroll
             for (int q = 0; q < 4; ++q) {
@@ -372,13 +385,15 @@ struct PeerBuffers {
 
 __global__ void pack_peer_kernel(const uint8_t* __restrict__ xq, const uint8_t* __restrict__ xs,
                                  const long long* __restrict__ ids, const float* __restrict__ weights, int routes,
-                                 int topk, int hidden, int local_experts, const int* __restrict__ peer_offset,
+                                 int topk, int hidden, int local_experts, int experts, const int* __restrict__ peer_offset,
                                  int* __restrict__ cursor, PeerBuffers recv, int recv_capacity, int* __restrict__ error) {
     const int lane = threadIdx.x & 31;
     const int route = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (route >= routes) return;
     const int token = route / topk;
-    const int expert = int(ids[route]);
+    const long long id = ids[route];
+    if (id < 0 || id >= experts) return;                        // dropped route: no row is sent (see reduce_kernel)
+    const int expert = int(id);
     int dst = 0;
     if (lane == 0) dst = peer_offset[expert] + atomicAdd(&cursor[expert], 1);
     dst = __shfl_sync(0xFFFFFFFFu, dst, 0);
@@ -433,7 +448,9 @@ quantise_route_kernel(const __nv_bfloat16* __restrict__ x, const long long* __re
         // thread j sends route j: one bulk copy of the whole row (codes + scale bytes), then the 8-byte tail
         if (int(threadIdx.x) < topk) {
             const int route = token * topk + threadIdx.x, d = dst[threadIdx.x];
-            if (d < 0 || d >= recv_capacity) {
+            if (d < 0) {
+                // an expert id outside the range: a dropped route, nothing is sent and the reduce skips it
+            } else if (d >= recv_capacity) {
                 atomicOr(error, 1);
             } else {
                 const int owner = int(ids[route]) / local_experts;
@@ -460,12 +477,12 @@ quantise_route_kernel(const __nv_bfloat16* __restrict__ x, const long long* __re
     }
     if (int(threadIdx.x) < topk) {
         const int route = token * topk + threadIdx.x, d = dst[threadIdx.x];
-        if (d >= 0) {                                           // an id outside the expert range is dropped, as pack does
+        if (d >= 0) {
             ptx::bulk_store(pool_packed + size_t(d) * (hidden / 2), row_smem, uint32_t(hidden / 2));
             ptx::tma_store_commit();
             pool_weight[d] = weights[route];
-            route_row[route] = d;
         }
+        route_row[route] = d;                                   // -1: an id outside the expert range, dropped (the reduce skips it)
     }
     for (int j = 0; j < topk; ++j) {
         const int d = dst[j];
@@ -533,23 +550,24 @@ void moe_plan(int* counts_matrix, int world, int rank, int experts, int pool_cap
 }
 
 void moe_pack(const uint8_t* xq, const uint8_t* xs, const long long* ids, const float* weights, int tokens, int topk,
-              int hidden, const int* send_offset, int* cursor, uint8_t* send_rows, int* send_pos, cudaStream_t stream) {
+              int hidden, int experts, const int* send_offset, int* cursor, uint8_t* send_rows, int* send_pos,
+              cudaStream_t stream) {
     check_hidden(hidden, "moe pack");
     const int routes = tokens * topk;
     if (routes == 0) return;
-    pack_kernel<<<(routes * 32 + 255) / 256, 256, 0, stream>>>(xq, xs, ids, weights, routes, topk, hidden, send_offset,
+    pack_kernel<<<(routes * 32 + 255) / 256, 256, 0, stream>>>(xq, xs, ids, weights, routes, topk, hidden, experts, send_offset,
                                                                cursor, send_rows, send_pos, nullptr, nullptr, nullptr, nullptr);
     cuda_check(cudaGetLastError());
 }
 
 void moe_pack_to_pool(const uint8_t* xq, const uint8_t* xs, const long long* ids, const float* weights, int tokens,
-                      int topk, int hidden, const int* seg_pool_offset, int* cursor, uint8_t* pool_packed,
+                      int topk, int hidden, int experts, const int* seg_pool_offset, int* cursor, uint8_t* pool_packed,
                       uint8_t* pool_scales, float* pool_weight, int* route_row, cudaStream_t stream) {
     check_hidden(hidden, "moe pack_to_pool");
     const int routes = tokens * topk;
     if (routes == 0) return;
     if (!pool_packed || !pool_scales || !pool_weight) throw std::invalid_argument("moe pack_to_pool: null pool");
-    pack_kernel<<<(routes * 32 + 255) / 256, 256, 0, stream>>>(xq, xs, ids, weights, routes, topk, hidden, nullptr, cursor,
+    pack_kernel<<<(routes * 32 + 255) / 256, 256, 0, stream>>>(xq, xs, ids, weights, routes, topk, hidden, experts, nullptr, cursor,
                                                                nullptr, route_row, seg_pool_offset, pool_packed,
                                                                pool_scales, pool_weight);
     cuda_check(cudaGetLastError());
@@ -586,11 +604,11 @@ void moe_return_rows(const void* out_pool_bf16, const int* pool_of_recv, const i
 }
 
 void moe_reduce(const void* returned_bf16, const int* send_pos, int tokens, int topk, int hidden, void* y_bf16,
-                cudaStream_t stream) {
+                const long long* ids, int experts, cudaStream_t stream) {
     check_hidden(hidden, "moe reduce");
     if (tokens <= 0) return;
     reduce_kernel<<<tokens, 128, 0, stream>>>(static_cast<const uint4*>(returned_bf16), send_pos, topk, hidden / 8,
-                                              static_cast<uint4*>(y_bf16));
+                                              static_cast<uint4*>(y_bf16), ids, experts);
     cuda_check(cudaGetLastError());
 }
 
@@ -607,8 +625,8 @@ void moe_pack_peer(const uint8_t* xq, const uint8_t* xs, const long long* ids, c
         recv.ptr[r] = peer_recv[r];
     }
     pack_peer_kernel<<<(routes * 32 + 255) / 256, 256, 0, stream>>>(xq, xs, ids, weights, routes, topk, hidden,
-                                                                    local_experts, peer_offset, cursor, recv,
-                                                                    recv_capacity, error);
+                                                                    local_experts, world * local_experts, peer_offset,
+                                                                    cursor, recv, recv_capacity, error);
     cuda_check(cudaGetLastError());
 }
 
@@ -704,7 +722,8 @@ int moe_payload_bytes(int hidden) { return payload_bytes(hidden); }
 // payload area, fence, store e into arrived[rank] of every rank, wait until all of this rank's own arrived[]
 // words have reached e, copy the gathered rows out. One CTA per GPU; the kernels of one exchange run on
 // different GPUs, never two on the same one. The wait is bounded: after WAIT_LIMIT_NS the kernel sets
-// STATUS_TIMEOUT_PEER and returns. The payload slots alternate so that a rank already at exchange e + 1
+// STATUS_TIMEOUT_PEER, leaves its sequence number unchanged (the next call repeats the same exchange) and
+// returns. The payload slots alternate so that a rank already at exchange e + 1
 // cannot overwrite rows a slower rank is still copying out of exchange e; it cannot get to e + 2 before that
 // rank has arrived at e + 1.
 using ptx::globaltimer_ns;
@@ -769,7 +788,9 @@ __global__ void peer_exchange_kernel(PeerState* own, PeerState* const* peers, in
         for (int r = 0; r < world; ++r)
             for (int i = threadIdx.x; i < ints; i += blockDim.x) out[r * ints + i] = __ldcg(src + size_t(r) * max_ints + i);
     }
-    if (threadIdx.x == 0) own->epoch = e;
+    // After a wait that ran out the sequence number stays where it was: the next exchange repeats number e, so a
+    // rank whose partner had not launched yet (and will start from e as well) falls back into step with it.
+    if (threadIdx.x == 0 && !failed) own->epoch = e;
 }
 
 size_t peer_state_bytes(int world, int max_ints) {

@@ -192,6 +192,20 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
         " [%0], [%1, {%3, %4}], [%2];"
         :: "r"(dst), "l"(map), "r"(cluster_bar), "r"(x), "r"(y) : "memory");
 }
+// The 3-D forms (scale maps: byte, row inside the row block, row block).
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5}], [%2];"
+        :: "r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, int z,
+                                                 uint32_t cluster_bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5}], [%2];"
+        :: "r"(dst), "l"(map), "r"(cluster_bar), "r"(x), "r"(y), "r"(z) : "memory");
+}
 // L2 policy for data that is written once and not read again by this kernel.
 __device__ __forceinline__ uint64_t policy_evict_first() {
     uint64_t p;

@@ -33,6 +33,7 @@ class Nvfp4Gemm:
             raise ValueError("scale tensors must hold rows*K/16 bytes")
         self._keep = (a_packed, b_packed, sfa, sfb, workspace)
         self.device = a_packed.device
+        self.out_dtype = torch.float16
         self._plan = ctypes.c_void_p()
         lib = _lib.load()
         with torch.cuda.device(self.device):
@@ -48,19 +49,31 @@ class Nvfp4Gemm:
         _lib.check(_lib.load().gpu_kernels_nvfp4_plan_set_alpha(self._plan, float(alpha)))
 
     def set_option(self, key: str, value: int) -> None:
-        _lib.check(_lib.load().gpu_kernels_nvfp4_plan_set_option(self._plan, key.encode(), int(value)))
+        # some options allocate or launch (split_k, l2_side): on the plan's own device
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.load().gpu_kernels_nvfp4_plan_set_option(self._plan, key.encode(), int(value)))
+        if key == "out_bf16":
+            self.out_dtype = torch.bfloat16 if value else torch.float16
 
     def info(self) -> dict:
-        buf = (ctypes.c_int * 10)()
+        buf = (ctypes.c_int * 16)()
         _lib.check(_lib.load().gpu_kernels_nvfp4_plan_info(self._plan, buf))
-        keys = ("M", "N", "K", "units", "cta_group", "tile_n", "group_m", "stages", "split_k", "k_skew")
+        keys = ("M", "N", "K", "units", "cta_group", "tile_n", "group_m", "stages", "split_k", "k_skew",
+                "direct_store", "out_bf16", "l2_side", "side0_units", "side1_units", "status_slot")
         return dict(zip(keys, list(buf)))
+
+    def placement_misses(self) -> int:
+        """Clusters (summed over launches) that ran on the other L2 side than the tile route assumed."""
+        n = ctypes.c_uint()
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.load().gpu_kernels_nvfp4_plan_placement_misses(self._plan, ctypes.byref(n)))
+        return int(n.value)
 
     def run(self, out: torch.Tensor | None = None) -> torch.Tensor:
         if out is None:
-            out = torch.empty((self.m, self.n), dtype=torch.float16, device=self.device)
-        if not (out.is_cuda and out.dtype == torch.float16 and out.is_contiguous() and out.shape == (self.m, self.n)):
-            raise ValueError("out must be a contiguous CUDA fp16 tensor [M, N]")
+            out = torch.empty((self.m, self.n), dtype=self.out_dtype, device=self.device)
+        if not (out.is_cuda and out.dtype == self.out_dtype and out.is_contiguous() and out.shape == (self.m, self.n)):
+            raise ValueError(f"out must be a contiguous CUDA {self.out_dtype} tensor [M, N]")
         with torch.cuda.device(self.device):
             _lib.check(_lib.load().gpu_kernels_nvfp4_custom(self._plan, out.data_ptr(), _stream()))
         return out
@@ -114,3 +127,12 @@ def gemm_host(a_packed, b_packed, sfa, sfb, out, alpha: float = 1.0) -> torch.Te
         m, n, 2 * half_k, a_packed.data_ptr(), b_packed.data_ptr(), sfa.data_ptr(), sfb.data_ptr(),
         out.data_ptr(), float(alpha), _stream()))
     return out
+
+
+def l2_census() -> list[int]:
+    """Cycles per dependent atomic that each SM of the current device measured in the L2-side census,
+    by SM id; empty before the first plan asked for the "l2_side" order on this device."""
+    buf = (ctypes.c_uint * 256)()
+    n = ctypes.c_int()
+    _lib.check(_lib.load().gpu_kernels_nvfp4_l2_census(buf, 256, ctypes.byref(n)))
+    return list(buf[:n.value])

@@ -339,12 +339,12 @@ class Nvfp4MoE:
                 # nothing to exchange: rows go straight into the expert-major pool
                 _lib.check(lib.gpu_kernels_nvfp4_moe_pack_to_pool(
                     xq.data_ptr(), xs.data_ptr(), ids.data_ptr(), weights.data_ptr(), tokens, self.topk, self.hidden,
-                    self.seg_pool.data_ptr(), self.cursor.data_ptr(), self.pool_packed.data_ptr(),
+                    self.experts, self.seg_pool.data_ptr(), self.cursor.data_ptr(), self.pool_packed.data_ptr(),
                     self.pool_scales.data_ptr(), self.pool_weight.data_ptr(), self.send_pos.data_ptr(), s))
             else:
                 _lib.check(lib.gpu_kernels_nvfp4_moe_pack(
                     xq.data_ptr(), xs.data_ptr(), ids.data_ptr(), weights.data_ptr(), tokens, self.topk, self.hidden,
-                    self.send_offset.data_ptr(), self.cursor.data_ptr(), self.send_rows.data_ptr(),
+                    self.experts, self.send_offset.data_ptr(), self.cursor.data_ptr(), self.send_rows.data_ptr(),
                     self.send_pos.data_ptr(), s))
                 self._mark("pack")
                 dist.all_to_all_single(self.recv_rows[:total_recv], self.send_rows[:tokens * self.topk],
@@ -379,12 +379,13 @@ class Nvfp4MoE:
                 self._barrier()
                 self._mark("barrier")
                 _lib.check(lib.gpu_kernels_nvfp4_moe_reduce(
-                    self.slots_ptr, self.identity.data_ptr(), tokens, self.topk, self.hidden, self.y.data_ptr(), s))
+                    self.slots_ptr, self.identity.data_ptr(), tokens, self.topk, self.hidden, self.y.data_ptr(),
+                    ids.data_ptr(), self.experts, s))
             elif self.world == 1:
                 # send_pos holds pool rows: the reduce reads the second GEMM's output in place
                 _lib.check(lib.gpu_kernels_nvfp4_moe_reduce(
                     self.out_pool.data_ptr(), self.send_pos.data_ptr(), tokens, self.topk, self.hidden,
-                    self.y.data_ptr(), s))
+                    self.y.data_ptr(), ids.data_ptr(), self.experts, s))
             else:
                 _lib.check(lib.gpu_kernels_nvfp4_moe_return_rows(
                     self.out_pool.data_ptr(), self.pool_of_recv.data_ptr(), self.totals.data_ptr(), self.recv_cap,
@@ -396,7 +397,7 @@ class Nvfp4MoE:
                 self._mark("combine all-to-all")
                 _lib.check(lib.gpu_kernels_nvfp4_moe_reduce(
                     self.ret_recv.data_ptr(), self.send_pos.data_ptr(), tokens, self.topk, self.hidden,
-                    self.y.data_ptr(), s))
+                    self.y.data_ptr(), ids.data_ptr(), self.experts, s))
             self._mark("reduce")
         return self.y[:tokens]
 

@@ -46,19 +46,27 @@ struct Nvfp4Params {
     int gather_col0, gather_ldc;
     const void* gather_maps;
     const void* gather_ptrs;
+    int out_bf16;                   // 1: launch() writes bfloat16 instead of FP16 through the same pointer
+    int status_slot;                // which of the device's status slots this plan reports to
+    // L2-side-aware tile order (see nvfp4_set_l2_side_order); device tables owned by a per-process cache
+    const void* route;              // null: arithmetic band order
+    const void* sm_side;
+    const void* unit_side;
+    int side_units[2];              // clusters the census found on either side of the L2
 };
 
 struct Nvfp4Implementation {
     // Builds descriptors for the given device buffers, which must outlive the
     // plan. May query the device; never call it during stream capture.
     // Throws std::invalid_argument on a shape or pointer it cannot serve:
-    // M, N multiples of 128, K a multiple of 256, pointers 16-byte aligned.
+    // M, N multiples of 128 (whole scale atoms), K a multiple of 64 (the quantiser's own rule; the
+    // reference kernel needs multiples of 256 in all three), pointers 16-byte aligned.
     void (*prepare)(Nvfp4Params&, const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB,
                     int M, int N, int K, cudaStream_t);
     // One asynchronous kernel launch on `stream`; safe inside stream capture.
     void (*launch)(const Nvfp4Params&, __half* C, cudaStream_t);
-    // Synchronises the device and throws std::runtime_error if any launch since
-    // the last call reported a wait that timed out.
+    // Synchronises the device and throws std::runtime_error if any launch of any plan since
+    // the last call reported a wait that timed out (nvfp4_validate_plan checks one plan only).
     void (*validate)();
 };
 
@@ -66,6 +74,24 @@ Nvfp4Implementation nvfp4_sm100_implementation();
 
 // Extension: set the FP32 global scale of a prepared plan (takes effect at the next launch).
 void nvfp4_set_alpha(Nvfp4Params&, float alpha);
+
+// Extension: synchronises the device and throws if a launch of THIS plan reported an error since the last
+// check of this plan; other plans' reports are left alone.
+void nvfp4_validate_plan(const Nvfp4Params&);
+
+// Extension: L2-side-aware tile order, the counterpart of the reference's prepare_schedule
+// (kernels/gemm/matmul/sm100.cu:566-673). B200's L2 has two sides; an SM reaches the far one more slowly.
+// on = 1: a census (one short kernel: every SM times a chain of dependent atomics on one line, taking turns
+// with a time limit on every wait; nothing spins without a limit) labels each SM near or far, a second
+// launch with the GEMM's own geometry records which SMs each cluster of the persistent grid lands on, and
+// the tile sequence is dealt so that the clusters of one side work through one contiguous part of the
+// band order (their A and B panels stay in that side's L2). The tables are cached per device and shape for
+// the life of the process. Returns false (and leaves the arithmetic order) when the census does not split
+// the SMs into two groups, when a wait in it ran out, or when the grid is smaller than the GPU. Results never
+// depend on it: a cluster that lands elsewhere than assumed only loses the locality, and is counted
+// (nvfp4_placement_misses). Not during stream capture.
+bool nvfp4_set_l2_side_order(Nvfp4Params&, int on, cudaStream_t stream);
+unsigned nvfp4_placement_misses(const Nvfp4Params&);
 
 // Extension: split-K (off unless enabled). For shapes with at most a quarter as many tiles as SMs and a long
 // K loop (decode-like: M = 128, a slab of N) the K steps of every tile can be dealt to 4 units; each writes FP32 partial sums to a

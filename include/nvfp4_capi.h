@@ -36,8 +36,9 @@ int gpu_kernels_nvfp4_cublas(void* plan, void* C, const void* A, const void* B, 
 /* replaces nvfp4_bridge.cu:112-121: C[M,N] fp16 = A * B^T with this library's kernel; capture-safe */
 int gpu_kernels_nvfp4_custom(void* plan, void* C, void* stream);
 /* replaces nvfp4_bridge.cu:123-132: synchronises and reports a kernel that gave up waiting or skipped an
- * out-of-range store. The status is kept per device: plan may be NULL (checks the current device; this is how
- * grouped launches are checked). */
+ * out-of-range store. Every plan reports to a status slot of its own, so this call neither reports nor clears
+ * another plan's error. plan may be NULL: checks every slot of the current device (this is how grouped
+ * launches and the expert-path kernels, which report to the device's own slot, are checked). */
 int gpu_kernels_nvfp4_validate(void* plan);
 /* replaces nvfp4_bridge.cu:134-139 */
 int gpu_kernels_nvfp4_l2_bytes(void);
@@ -57,6 +58,12 @@ int gpu_kernels_nvfp4_dequantize(const void* packed, const void* scales, void* o
 int gpu_kernels_nvfp4_plan_set_alpha(void* plan, float alpha);
 /* Tuning knobs. key: "group_m" (tile rows per rasterisation band, >= 1); "c_evict_first" (0/1: L2 policy
  * of the C stores); "direct_store" (0/1: epilogue writes C from registers instead of staging it for TMA stores);
+ * "out_bf16" (0/1: C is written as bfloat16 instead of FP16 through the same pointer; the reference's output
+ * is FP16 only, include/nvfp4.h:21); "l2_side" (0/1: L2-side-aware tile order, the counterpart of the
+ * reference's prepare_schedule, kernels/gemm/matmul/sm100.cu:566-673: a census at this call labels the SMs by
+ * the side of the L2 they sit on and deals each side one contiguous part of the tile sequence; fails when the
+ * plan's grid does not fill the GPU or the census finds no two sides; results never depend on it; not inside
+ * stream capture);
  * "k_skew" (>= 0: tile t starts its K walk at step (t * k_skew) % steps; 0 = every tile at K = 0);
  * "split_k" (0/1, default 0: four units per tile, each with a quarter of the K steps, partial sums combined
  * through a workspace the plan allocates. Offered for shapes with at most a quarter as many tiles as SMs and
@@ -73,8 +80,21 @@ int gpu_kernels_nvfp4_plan_set_option(void* plan, const char* key, int value);
  * barrier between the ranks before reading, and before the next launch overwrites. world = 0 switches it
  * off. Not inside stream capture (synchronises once). */
 int gpu_kernels_nvfp4_plan_set_gather(void* plan, void* const* buffers, int world, int col0, int n_total);
-/* Fills info[0..9] = {M, N, K, units, cta_group, tile_n, group_m, stages, split_k, k_skew}. */
+/* Fills info[0..15] = {M, N, K, units, cta_group, tile_n, group_m, stages, split_k, k_skew, direct_store,
+ * out_bf16, l2_side order in use, clusters on L2 side 0, on side 1, status slot}. */
 int gpu_kernels_nvfp4_plan_info(void* plan, int* info);
+
+/* With the "l2_side" order: how many clusters, summed over this plan's launches, found themselves on the
+ * other side of the L2 than the plan's tile route assumed (they lose locality, nothing else). Synchronising copy. */
+int gpu_kernels_nvfp4_plan_placement_misses(void* plan, unsigned* misses);
+/* Host arithmetic of the "l2_side" order (no GPU involved): unit_side[u] in {0, 1} for the `units` persistent
+ * units of a grid; route[w] (w < tiles) = the tile that work item w (= unit + trip * units) computes. The
+ * units of side 0 share the first part of the tile sequence, those of side 1 the rest, each part as long as
+ * its side's share of the work; every trip of a side is a dense run of its part. Always a permutation. */
+int gpu_kernels_nvfp4_side_route(const unsigned char* unit_side, int units, int tiles, unsigned* route);
+/* Diagnostic: cycles per dependent atomic that every SM of the current device measured in the L2-side census,
+ * indexed by SM id (0 = no CTA ran there); *written = 0 when no census has run on this device yet. */
+int gpu_kernels_nvfp4_l2_census(unsigned* cycles_by_sm, int capacity, int* written);
 
 /* Diagnostic: one launch with per-role wait counters on; writes 16 words per CTA
  * {producer wait, producer total, MMA wait-for-data, MMA wait-for-accumulator, MMA total, epilogue
@@ -159,16 +179,17 @@ int gpu_kernels_nvfp4_moe_route_plan(const void* ids, int routes, void* counts, 
 int gpu_kernels_nvfp4_moe_clear_live(const void* num_blocks, int block_rows, int pool_rows, int hidden, void* pool_scales,
                                      void* pool_weight, void* pool_dst, void* stream);
 /* quantised tokens (xq [T_pad, hidden/2], xs VEC16 scales), ids int64 [T, topk], weights f32 [T, topk] ->
- * send_rows [T*topk, payload] ordered by destination expert; send_pos [T*topk] = row of each route;
+ * send_rows [T*topk, payload] ordered by destination expert; send_pos [T*topk] = row of each route (-1 for a
+ * route whose expert id lies outside [0, experts): it is dropped, i.e. adds nothing to its token's result);
  * cursor int32 [experts] zeroed by the caller. */
 int gpu_kernels_nvfp4_moe_pack(const void* xq, const void* xs, const void* ids, const void* weights, int tokens,
-                               int topk, int hidden, const void* send_offset, void* cursor, void* send_rows,
+                               int topk, int hidden, int experts, const void* send_offset, void* cursor, void* send_rows,
                                void* send_pos, void* stream);
 /* Single-rank shortcut (world = 1): the same as pack + unpack in one kernel, rows written straight into the pool;
  * route_row [T*topk] receives each route's pool row, so reduce can read the second GEMM's output directly
  * (pass the output pool as `returned` and route_row as `send_pos`). seg_pool_offset from moe_plan. */
 int gpu_kernels_nvfp4_moe_pack_to_pool(const void* xq, const void* xs, const void* ids, const void* weights, int tokens,
-                                       int topk, int hidden, const void* seg_pool_offset, void* cursor,
+                                       int topk, int hidden, int experts, const void* seg_pool_offset, void* cursor,
                                        void* pool_packed, void* pool_scales, void* pool_weight, void* route_row,
                                        void* stream);
 /* received rows (source-major) -> expert-major pool: packed rows, scale atoms (zeroed by the caller first),
@@ -187,9 +208,10 @@ int gpu_kernels_nvfp4_moe_swiglu_quant(const void* gate_up, const void* pool_wei
 /* expert outputs bf16 [pool_rows, hidden] -> rows in the order they were received (for the all-to-all back). */
 int gpu_kernels_nvfp4_moe_return_rows(const void* out_pool, const void* pool_of_recv, const void* totals, int capacity,
                                       int hidden, void* return_rows, void* stream);
-/* replaces reduce_kernel (sm90.cu:121-139): y[t] = bf16(sum_j fp32(returned[send_pos[t*topk+j]])), j ascending. */
+/* replaces reduce_kernel (sm90.cu:121-139): y[t] = bf16(sum_j fp32(returned[send_pos[t*topk+j]])), j ascending.
+ * Routes with send_pos < 0, or (ids int64 [T*topk] not NULL) an expert id outside [0, experts), are skipped. */
 int gpu_kernels_nvfp4_moe_reduce(const void* returned, const void* send_pos, int tokens, int topk, int hidden, void* y,
-                                 void* stream);
+                                 const void* ids, int experts, void* stream);
 
 /* No counterpart in the reference. The same whole GEMM from HOST buffers as gpu_kernels_nvfp4_gemm_host,
  * for callers that must not allocate device memory while they run (a process whose memory pool owns
