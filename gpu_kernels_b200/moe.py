@@ -63,6 +63,9 @@ class Nvfp4MoE:
             raise ValueError("num_experts must equal E_local * world")
         if self.hidden % 256 or self.inter % 256:
             raise ValueError("H and I must be multiples of 256")
+        if self.world > 127 or max_tokens * topk >= 1 << 24:
+            # a combine destination is (rank << 24) | (route + 1) in 32 bits
+            raise ValueError("at most 127 ranks and fewer than 2^24 routes per rank")
         self.experts, self.topk, self.clamp, self.max_tokens = num_experts, topk, float(clamp), max_tokens
         self.device = w1.device
         lib = _lib.load()
@@ -263,7 +266,10 @@ class Nvfp4MoE:
         return send_splits, recv_splits
 
     def forward(self, x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
-        """x [T, H] bf16, ids [T, topk] int64 global expert ids, weights [T, topk] f32 -> y [T, H] bf16."""
+        """x [T, H] bf16, ids [T, topk] int64 global expert ids, weights [T, topk] f32 -> y [T, H] bf16.
+
+        A route whose id lies outside [0, num_experts) (a router's "dropped" mark such as -1) is dropped: no row
+        is dispatched for it and it adds nothing to its token's sum, on every exchange route."""
         tokens = x.shape[0]
         if tokens > self.max_tokens or x.shape[1] != self.hidden or ids.shape != (tokens, self.topk):
             raise ValueError("shape mismatch with the layer this object was built for")

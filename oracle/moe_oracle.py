@@ -60,6 +60,30 @@ def _quant_dequant_rows(v: np.ndarray) -> np.ndarray:
     return dequantize(*quantize(buf))[:rows]
 
 
+def moe_forward_nvfp4_experts(x, expert_ids, route_weights, dequantised_expert, clamp=10.0):
+    """moe_forward_nvfp4 for layers too large to hold as FP32 arrays: `dequantised_expert(e)` returns the
+    expert's (W1 [2I,H], W2 [H,I]) as FP32 values that are already NVFP4-representable (quantised and
+    dequantised by the caller), and is asked only for the experts some route uses. Ids outside the range of
+    experts the callable knows (it may raise KeyError) must not occur; ids < 0 are dropped routes and add
+    nothing, as in the CUDA path."""
+    tokens, hidden = x.shape
+    topk = expert_ids.shape[1]
+    xq = _quant_dequant_rows(x)
+    slots = np.zeros((tokens, topk, hidden), dtype=np.float32)
+    for e in np.unique(expert_ids):
+        if e < 0:
+            continue
+        tok, choice = np.nonzero(expert_ids == e)
+        w1q, w2q = dequantised_expert(int(e))
+        gate_up = round_bf16(xq[tok] @ w1q.T)
+        act = swiglu(gate_up, route_weights[tok, choice], clamp)
+        slots[tok, choice] = round_bf16(_quant_dequant_rows(act) @ w2q.T)
+    out = np.zeros((tokens, hidden), dtype=np.float32)
+    for j in range(topk):
+        out = (out + slots[:, j]).astype(np.float32)
+    return round_bf16(out)
+
+
 def moe_forward_nvfp4(x, expert_ids, route_weights, w1, w2, clamp=10.0):
     """The same layer with both GEMMs on NVFP4 operands: the FP32 dequantise-then-matmul statement of
     what the CUDA expert path computes. Tokens are quantised along H, each expert's W1 along H and W2

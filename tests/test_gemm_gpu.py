@@ -85,6 +85,91 @@ def test_shapes_against_oracle(g, m, n, k, variant):
     assert_gemm_close(out, ref, f"{m}x{n}x{k}")
 
 
+K_TAIL_SHAPES = [
+    # K is a multiple of 64 but not of the ring's 256: the last ring step reads zero fill beyond K
+    (256, 256, 64, None),
+    (256, 256, 320, None),
+    (128, 512, 1088, None),
+    (384, 640, 832, None),
+    (2048, 1024, 2240, None),       # ring wraps with a partial last step, K walks that start anywhere
+    (512, 512, 1472, 1256),
+    (512, 512, 1472, 1128),
+]
+
+
+@pytest.mark.parametrize("m,n,k,variant", K_TAIL_SHAPES)
+def test_k_multiple_of_64_against_oracle(g, m, n, k, variant):
+    # the reference kernel assumes K % 256 == 0 (kernels/gemm/matmul/sm100.cu:403); its quantiser only needs
+    # K % 64 == 0 (reference/python/nvfp4.py:20), which is what this kernel accepts
+    a = random_operand(m, k, seed=3 + m + n + k)
+    b = random_operand(n, k, seed=4 + m + n + k, scale=0.02)
+    pa, sa = g.quantize(a)
+    pb, sb = g.quantize(b)
+    out, _ = run_plan(g, pa, sa, pb, sb, variant=variant)
+    ref = O.gemm_f32(to_np(pa), to_np(sa), to_np(pb), to_np(sb))
+    assert_gemm_close(out, ref, f"K tail {m}x{n}x{k}")
+
+
+def test_bf16_output(g):
+    # the reference writes FP16 only (include/nvfp4.h:21); "out_bf16" makes the same launch write bfloat16
+    for m, n, k in ((256, 512, 1024), (128, 384, 512), (512, 256, 4096)):
+        pa, sa = g.quantize(random_operand(m, k, seed=81 + m))
+        pb, sb = g.quantize(random_operand(n, k, seed=82 + m, scale=0.02))
+        ref = torch.from_numpy(O.gemm_f32(to_np(pa), to_np(sa), to_np(pb), to_np(sb)))
+        plan = g.Nvfp4Gemm(pa, pb, sa, sb)
+        half = plan.run(nan_output(m, n)).clone()
+        plan.set_option("out_bf16", 1)
+        assert plan.info()["out_bf16"] == 1
+        with pytest.raises(ValueError):
+            plan.run(nan_output(m, n))                          # an FP16 tensor is refused now
+        out = plan.run(torch.full((m, n), float("nan"), device="cuda", dtype=torch.bfloat16))
+        plan.validate()
+        assert not torch.isnan(out).any()
+        # the same accumulators, rounded to 8 significant bits instead of 11
+        want = ref.bfloat16()
+        same = (out.cpu() == want).float().mean().item()
+        assert same > 0.98, f"{m}x{n}x{k}: only {same:.4f} of the bf16 outputs equal the rounded reference"
+        err = (out.float().cpu() - ref).double().norm() / ref.double().norm()
+        assert err < 4e-3, err
+        plan.set_option("out_bf16", 0)
+        assert torch.equal(plan.run(nan_output(m, n)), half)
+        plan.close()
+
+
+def test_l2_side_order_gives_the_same_tiles(g):
+    # the L2-side-aware order is a permutation of the tiles: bit-identical C, whatever the census found
+    m, n, k = 4096, 8192, 512                                 # 16 x 32 tiles of 256 x 256: more than two per unit
+    pa, sa = g.quantize(random_operand(m, k, seed=91))
+    pb, sb = g.quantize(random_operand(n, k, seed=92, scale=0.02))
+    plan = g.Nvfp4Gemm(pa, pb, sa, sb)
+    base = plan.run(nan_output(m, n)).clone()
+    try:
+        plan.set_option("l2_side", 1)
+    except RuntimeError as exc:                              # no two sides found on this device: nothing to compare
+        plan.close()
+        pytest.skip(str(exc))
+    info = plan.info()
+    assert info["l2_side"] == 1 and info["side0_units"] + info["side1_units"] == info["units"]
+    assert info["side0_units"] > 0 and info["side1_units"] > 0
+    for _ in range(3):
+        again = plan.run(nan_output(m, n))
+        assert torch.equal(again, base)
+    plan.validate()
+    misses = plan.placement_misses()
+    assert 0 <= misses <= 3 * info["units"]
+    census = g.gemm.l2_census()
+    assert len(census) >= 100 and max(census) > 0
+    plan.set_option("l2_side", 0)
+    assert plan.info()["l2_side"] == 0
+    assert torch.equal(plan.run(nan_output(m, n)), base)
+    # a plan whose grid does not fill the GPU is refused
+    small = g.Nvfp4Gemm(pa[:256], pb[:256], sa[:256 * k // 16], sb[:256 * k // 16])
+    with pytest.raises(RuntimeError):
+        small.set_option("l2_side", 1)
+    small.close()
+    plan.close()
+
+
 def test_distinct_scale_everywhere(g):
     # every (row, K block) has its own scale byte and codes are random nibbles: a wrong
     # scale column, swizzle or K-slice order cannot cancel out
@@ -203,8 +288,8 @@ def test_host_entry_point_in_row_pieces(g, m, n, k):
 def test_argument_errors(g):
     from gpu_kernels_b200._lib import Nvfp4Error
     z = lambda *s: torch.zeros(*s, dtype=torch.uint8, device="cuda")
-    with pytest.raises(Nvfp4Error):          # K not a multiple of 256
-        g.Nvfp4Gemm(z(128, 64), z(128, 64), z(128 * 8), z(128 * 8))
+    with pytest.raises(Nvfp4Error):          # K not a multiple of 64
+        g.Nvfp4Gemm(z(128, 48), z(128, 48), z(128 * 6), z(128 * 6))
     with pytest.raises(Nvfp4Error):          # M not a multiple of 128
         g.Nvfp4Gemm(z(64, 128), z(128, 128), z(64 * 16), z(128 * 16))
     with pytest.raises(ValueError):

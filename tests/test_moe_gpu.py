@@ -282,12 +282,40 @@ def test_reduce_order_exact(g):
     pos = torch.randperm(tokens * topk, generator=gen, device="cuda").to(torch.int32)
     y = torch.empty((tokens, hidden), dtype=torch.bfloat16, device="cuda")
     _lib.check(_lib.load().gpu_kernels_nvfp4_moe_reduce(rows.data_ptr(), pos.data_ptr(), tokens, topk, hidden,
-                                                        y.data_ptr(), torch.cuda.current_stream().cuda_stream))
+                                                        y.data_ptr(), None, 0, torch.cuda.current_stream().cuda_stream))
     r = to_np(rows.float())[to_np(pos).astype(np.int64)].reshape(tokens, topk, hidden)
     acc = np.zeros((tokens, hidden), dtype=np.float32)
     for j in range(topk):
         acc = (acc + r[:, j]).astype(np.float32)
     assert np.array_equal(to_np(y.float()), MO.round_bf16(acc))
+
+
+@pytest.mark.parametrize("fused_dispatch", [True, False])
+def test_dropped_routes_add_nothing(g, fused_dispatch):
+    # an id outside [0, experts) (a router's "dropped" mark) takes no row and adds nothing: the result equals the
+    # oracle's with that route removed; nothing is read or written out of bounds and no error is reported
+    tokens, hidden, inter, experts, topk = 40, 512, 256, 8, 2
+    x, logits, w1, w2 = make_layer(77, tokens, hidden, inter, experts, topk)
+    ids, wts = g.route(logits, topk)
+    ids = ids.clone()
+    ids[3, 0] = -1
+    ids[17, 1] = experts
+    ids[39, 0] = -7
+    ids[39, 1] = 1 << 40
+    layer = g.Nvfp4MoE(w1, w2, experts, topk, clamp=10.0, max_tokens=64, fused_dispatch=fused_dispatch)
+    for _ in range(2):                                       # the second call must not see rows of the first
+        y = layer(x, ids, wts).clone()
+        torch.cuda.synchronize()
+    layer.check()
+    ids_ref = to_np(ids).copy()
+    ids_ref[(ids_ref < 0) | (ids_ref >= experts)] = -1
+    w1n, w2n = to_np(w1.float()), to_np(w2.float())
+    ref = MO.moe_forward_nvfp4_experts(
+        to_np(x.float()), ids_ref, to_np(wts),
+        lambda e: (MO._quant_dequant_rows(w1n[e]), MO._quant_dequant_rows(w2n[e])), 10.0)
+    assert_layer_close(y, ref, "dropped routes")
+    assert not to_np(y.float())[39].any()                    # both routes of this token were dropped
+    layer.close()
 
 
 def test_pool_overflow_is_reported(g):

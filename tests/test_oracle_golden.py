@@ -97,3 +97,25 @@ def test_moe_oracle_matches_reference_output(golden):
     # floating point with BF16 rounding points: allow one BF16 ulp on a few elements
     assert np.mean(y == ref) > 0.99
     assert np.abs(y - ref).max() <= 2 ** -7 * np.abs(ref).max()
+
+
+def test_expert_streaming_oracle_matches_the_whole_layer_oracle():
+    # moe_forward_nvfp4_experts (weights handed over expert by expert, already NVFP4-representable) is the
+    # same arithmetic as moe_forward_nvfp4; a route with a negative id is dropped
+    from oracle import moe_oracle as MO
+    rng = np.random.default_rng(0)
+    tokens, hidden, inter, experts, topk = 9, 64, 64, 4, 2
+    x = MO.round_bf16(rng.standard_normal((tokens, hidden)).astype(np.float32))
+    w1 = MO.round_bf16((rng.standard_normal((experts, 2 * inter, hidden)) * 0.1).astype(np.float32))
+    w2 = MO.round_bf16((rng.standard_normal((experts, hidden, inter)) * 0.1).astype(np.float32))
+    ids = np.stack([rng.permutation(experts)[:topk] for _ in range(tokens)])
+    wts = rng.random((tokens, topk)).astype(np.float32)
+    pick = lambda e: (MO._quant_dequant_rows(w1[e]), MO._quant_dequant_rows(w2[e]))
+    whole = MO.moe_forward_nvfp4(x, ids, wts, w1, w2)
+    assert np.array_equal(whole, MO.moe_forward_nvfp4_experts(x, ids, wts, pick))
+    dropped = ids.copy()
+    dropped[2, 1] = -1
+    zero_weight = wts.copy()
+    zero_weight[2, 1] = 0.0
+    assert np.array_equal(MO.moe_forward_nvfp4_experts(x, dropped, wts, pick),
+                          MO.moe_forward_nvfp4(x, ids, zero_weight, w1, w2))

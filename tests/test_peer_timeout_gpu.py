@@ -29,6 +29,13 @@ def test_barrier_wait_runs_out_and_is_reported():
     torch.cuda.synchronize()                                               # rank 1 never comes: the wait gives up
     waited = time.perf_counter() - t0
     assert 1.5 < waited < 20.0, waited
+    # the report sits in the device's own status slot: a plan's validate neither sees nor clears it
+    pa, sa = g.quantize(random_operand(256, 512, seed=1))
+    pb, sb = g.quantize(random_operand(256, 512, seed=2, scale=0.02))
+    bystander = g.Nvfp4Gemm(pa, pb, sa, sb)
+    bystander.run()
+    bystander.validate()
+    bystander.close()
     assert lib.gpu_kernels_nvfp4_validate(None) == 1
     message = lib.gpu_kernels_nvfp4_last_error().decode()
     assert "status 0x20" in message, message

@@ -50,7 +50,8 @@ def _worker(rank, world, port, out_dir):
             plain.validate()
             fused = g.ShardedNvfp4Gemm(pa, sa, slab, slab_scales, split_k=True, fused_gather=True)
             for call in range(3):
-                fused.full.fill_(float("nan"))
+                for full in fused._ipc.full:
+                    full.fill_(float("nan"))
                 dist.barrier()                                                   # nobody clears after a peer has written
                 torch.cuda.synchronize()
                 got = fused.run(gather=True)
@@ -59,6 +60,24 @@ def _worker(rank, world, port, out_dir):
                 assert torch.equal(got, want), f"rank {rank} {m}x{n}x{k} call {call}: fused gather differs from the NCCL route"
                 dist.barrier()
             fused.validate()
+            # A rank that lags: the odd ranks keep their stream busy (a bounded spin kernel of a few
+            # milliseconds) between a run and the read of its result, while the others go straight on to the
+            # next run with another alpha. The lagging rank must still read the values of ITS run: the next run
+            # writes the other full-C buffer, and the run after that cannot start before the barrier.
+            seen = []
+            for step in range(4):
+                fused.set_alpha(float(step + 1))
+                got = fused.run(gather=True)
+                if rank % 2:
+                    torch.cuda._sleep(20_000_000)
+                seen.append(got.clone())
+            torch.cuda.synchronize()
+            for step, c in enumerate(seen):
+                plain.set_alpha(float(step + 1))
+                expect = plain.run(gather=True)
+                assert torch.equal(c, expect), f"rank {rank} {m}x{n}x{k} step {step}: a peer that ran ahead overwrote the result"
+            plain.set_alpha(1.0)
+            dist.barrier()
             err = (want.float() - ref).double()
             rel = float(err.norm() / ref.double().norm())
             assert rel <= 1e-3, f"rank {rank} {m}x{n}x{k}: relative Frobenius error {rel:.3e}"

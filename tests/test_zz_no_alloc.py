@@ -52,3 +52,21 @@ def test_static_rejects_shapes_beyond_its_array():
         with pytest.raises(_lib.Nvfp4Error, match="exceeds the built-in staging"):
             _lib.check(_lib.load().gpu_kernels_nvfp4_gemm_host_static(
                 m, n, k, z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), out.data_ptr(), 1.0, None))
+
+
+def test_static_entry_point_leaves_device_memory_alone():
+    # what the entry point is for: once a shape has been through it (the first call on a device takes the
+    # array's address, and the first launch of a kernel variant lets the driver load that kernel), further
+    # calls neither take nor return device memory: cudaMemGetInfo reads the same free bytes before and after
+    shapes = ((256, 384, 512), (128, 1024, 2048), (512, 256, 256))
+    operands = {s: host_operands(*s, seed=10 + i) for i, s in enumerate(shapes)}
+    for s in shapes:
+        run("gpu_kernels_nvfp4_gemm_host_static", *s, operands[s])
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        for s in shapes:
+            run("gpu_kernels_nvfp4_gemm_host_static", *s, operands[s])
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before, f"free device memory changed by {free_before - free_after} bytes"
