@@ -301,6 +301,11 @@ int gpu_kernels_nvfp4_plan_set_option(void* plan, const char* key, int value) {
         } else if (std::strcmp(key, "k_skew") == 0) {
             if (value < 0) throw std::invalid_argument("set_option: k_skew must be >= 0");
             p.params.k_skew = value;
+        } else if (std::strcmp(key, "pdl") == 0) {
+            p.params.pdl = value ? 1 : 0;
+        } else if (std::strcmp(key, "static_operands") == 0) {
+            if (value < 0 || value > 2) throw std::invalid_argument("set_option: static_operands is 0, 1 or 2");
+            p.params.static_operands = value;
         } else if (std::strcmp(key, "out_bf16") == 0) {
             if (p.params.gather_world) throw std::invalid_argument("set_option: choose the output type before set_gather");
             p.params.out_bf16 = value ? 1 : 0;

@@ -1,7 +1,8 @@
 // NVFP4 block-scaled GEMM for B200 (sm_100a): C[M,N] fp16 = alpha * (A sfA)(B sfB)^T.
 //
-// One persistent kernel, three roles per CTA (192 threads):
-//   warps 0-3  epilogue: TMEM -> registers -> FP16 -> swizzled shared memory -> TMA store
+// One persistent kernel, three roles per CTA (192 or 320 threads):
+//   warps 0-3  epilogue: TMEM -> registers -> FP16 -> swizzled shared memory -> TMA store, or straight to
+//              global memory (then warps 6-9 are a second set, two warps per Tensor Memory lane quarter)
 //   warp  4    MMA issuer (one elected lane): scale copies into TMEM + tcgen05 block-scaled MMAs
 //   warp  5    producer  (one elected lane): TMA tile loads of packed operands and scale atoms
 // A ring stage carries K = 256 of everything one MMA group needs (A rows, B rows,
@@ -44,7 +45,6 @@ constexpr int MMA_K = 64;           // K values per tcgen05.mma of this kind
 constexpr int ROW_BYTES = STAGE_K / 2;
 constexpr int SF_ATOM_BYTES = 512;  // 128 rows x 4 scale bytes (K = 64)
 constexpr int EPI_COLS = 64;        // FP16 columns per epilogue chunk: one 128-byte line per row
-constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 512;
 constexpr int SMEM_LIMIT = 232448;  // 227 KiB opt-in maximum per CTA
 
@@ -95,6 +95,13 @@ struct Config {
     // of padding per row so that a quarter-warp's 16-byte stores cover all banks); the ring gives up a
     // stage for it.
     static constexpr bool ROW_STAGING = EPI == EPI_SCATTER_ROWS;
+    // Epilogue warps. A warp reaches only the Tensor Memory lanes of its quarter (warp % 4), so the routes that
+    // write from registers run two warps per quarter, each with every other 64-column chunk: a 128 x 256
+    // accumulator leaves in half the time, which is what bounds tiles with a short K loop and the tail of a
+    // launch with one tile per CTA. The routes that stage in shared memory keep one warp per quarter (a second
+    // set of staging buffers would cost a ring stage), as does split-K.
+    static constexpr int EPI_WARPS = (EPI == EPI_DIRECT || EPI == EPI_ACT || EPI == EPI_SCATTER || EPI == EPI_GATHER_DIRECT) ? 8 : 4;
+    static constexpr int THREADS = (2 + EPI_WARPS) * 32;        // warps 0-3 epilogue, 4 MMA, 5 producer, 6-9 epilogue
     static constexpr int ROW_PITCH = UN * 2 + 16;
     static constexpr int EPI_BYTES = ROW_STAGING ? 4 * 32 * ROW_PITCH : STAGED_EPILOGUE ? 4 * 2 * EPI_WARP_BYTES : 0;
     static constexpr int CTRL_BYTES = 1024;
@@ -187,6 +194,12 @@ struct GemmArgs {
     const uint32_t* route;
     const uint8_t* sm_side;
     const uint8_t* unit_side;
+    // What the launch in front of this one in the stream may still be writing when this kernel starts (it can
+    // start early under programmatic dependent launch): 0 = anything, so every thread waits for that grid before
+    // it touches global memory; 1 = not B and its scales (weights that were there long before): the first ring
+    // stages of B are requested before the wait; 2 = none of the operands: only the epilogue waits, before its
+    // first store, so the tiles of this launch run while the tail of the previous one drains.
+    int static_operands;
 };
 
 struct Segment {
@@ -214,7 +227,10 @@ struct Walk {
 };
 
 enum ProfSlot { PROF_PROD_WAIT = 0, PROF_PROD_TOTAL, PROF_MMA_WAIT_FULL, PROF_MMA_WAIT_ACC, PROF_MMA_TOTAL,
-                PROF_EPI_WAIT_ACC, PROF_EPI_WAIT_STORE, PROF_EPI_TOTAL, PROF_SMID, PROF_WORDS = 16 };
+                PROF_EPI_WAIT_ACC, PROF_EPI_WAIT_STORE, PROF_EPI_TOTAL, PROF_SMID,
+                // %globaltimer (ns) when the CTA entered, when its issuer saw the first stage land, when the issuer
+                // had issued its last step, when epilogue warp 0 had written its last row
+                PROF_T_ENTER, PROF_T_FIRST_DATA, PROF_T_LAST_ISSUE, PROF_T_EPI_DONE, PROF_WORDS = 16 };
 // After the per-CTA counters: for the first TR_TILES tiles of unit 0, eight clock64 stamps around the
 // tile hand-over {0 issuer: last step issued, 1 issuer: acc_free seen, 2 issuer: first step of the
 // next tile issued, 3 leader epilogue warp 0: acc_full seen, 4 same: first chunk loaded,
@@ -285,6 +301,10 @@ struct Roles {
         const int ksteps = g.ksteps;
         long long waited = 0;
         const long long born = now();
+        // static_operands == 1: the A halves of the first ring fill wait for the grid in front of this launch
+        const bool early_b = g.static_operands == 1;
+        Held held[Cfg::STAGES];
+        int issued = 0;
         Walk walk(g, unit, units, tiles, ksteps);
         Segment seg;
         while (walk.get(seg)) {
@@ -306,12 +326,18 @@ struct Roles {
                 if (PROF) waited += now() - w0;
                 const uint32_t base = smem + stage * Cfg::STAGE_BYTES;
                 const uint32_t own_full = bar(&ctrl->full[stage]);
+                // The first ring fill of a launch whose B is static goes out in two halves: B and its scales at
+                // once, A and its scales after the grid in front of this launch has finished (see below).
+                const bool split_issue = early_b && issued < Cfg::STAGES;
+                if (split_issue) held[issued] = {ks, a_row, sfa_block};
                 if constexpr (CG == 1) {
                     if (elect_one()) {
                         mbar_arrive_expect_tx(own_full, Cfg::STAGE_BYTES);
-                        tma_load_2d(base, tmA, ks * ROW_BYTES, a_row, own_full);
+                        if (!split_issue) {
+                            tma_load_2d(base, tmA, ks * ROW_BYTES, a_row, own_full);
+                            tma_load_3d(base + Cfg::OFF_SFA, tmSFA, 0, ks * 16, sfa_block, own_full);
+                        }
                         tma_load_2d(base + Cfg::OFF_B, tmB, ks * ROW_BYTES, b_row, own_full);
-                        tma_load_3d(base + Cfg::OFF_SFA, tmSFA, 0, ks * 16, sfa_block, own_full);
                         #pragma unroll
                         for (int b = 0; b < Cfg::SFB_BLOCKS; ++b)
                             tma_load_3d(base + Cfg::OFF_SFB + b * Cfg::SFB_BLOCK_BYTES, tmSFB, 0, ks * 16,
@@ -322,22 +348,48 @@ struct Roles {
                     const uint32_t full = map_to_cta(own_full, 0);
                     if (elect_one()) {
                         if (rank == 0) mbar_arrive_expect_tx(own_full, 2 * Cfg::STAGE_BYTES);
-                        tma_load_2d_pair(base, tmA, ks * ROW_BYTES, a_row, full);
+                        if (!split_issue) {
+                            tma_load_2d_pair(base, tmA, ks * ROW_BYTES, a_row, full);
+                            tma_load_3d_pair(base + Cfg::OFF_SFA, tmSFA, 0, ks * 16, sfa_block, full);
+                        }
                         tma_load_2d_pair(base + Cfg::OFF_B, tmB, ks * ROW_BYTES, b_row, full);
-                        tma_load_3d_pair(base + Cfg::OFF_SFA, tmSFA, 0, ks * 16, sfa_block, full);
                         #pragma unroll
                         for (int b = 0; b < Cfg::SFB_BLOCKS; ++b)
                             tma_load_3d_pair(base + Cfg::OFF_SFB + b * Cfg::SFB_BLOCK_BYTES, tmSFB, 0, ks * 16,
                                              sfb_block + b, full);
                     }
                 }
+                ++issued;
+                if (early_b && issued == Cfg::STAGES) release_held(tmA, tmSFA, held, Cfg::STAGES);
                 if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
             }
         }
+        if (early_b && issued < Cfg::STAGES) release_held(tmA, tmSFA, held, issued);   // fewer steps than ring stages
         if (PROF && lane == 0) {
             unsigned long long* out = g.prof + (size_t(unit) * CG + rank) * PROF_WORDS;
             out[PROF_PROD_WAIT] = waited;
             out[PROF_PROD_TOTAL] = now() - born;
+        }
+    }
+
+    // The A halves (rows of A and their scale atoms) of the first `count` ring stages, once the grid this launch
+    // depends on has finished: stage i of the ring, in issue order.
+    struct Held { int ks, a_row, sfa_block; };
+    __device__ void release_held(const CUtensorMap* tmA, const CUtensorMap* tmSFA, const Held* held, int count) const {
+        grid_dependency_wait();
+        if (elect_one()) {
+            for (int i = 0; i < count; ++i) {
+                const uint32_t base = smem + i * Cfg::STAGE_BYTES;
+                const uint32_t own_full = bar(&ctrl->full[i]);
+                if constexpr (CG == 1) {
+                    tma_load_2d(base, tmA, held[i].ks * ROW_BYTES, held[i].a_row, own_full);
+                    tma_load_3d(base + Cfg::OFF_SFA, tmSFA, 0, held[i].ks * 16, held[i].sfa_block, own_full);
+                } else {
+                    const uint32_t full = map_to_cta(own_full, 0);
+                    tma_load_2d_pair(base, tmA, held[i].ks * ROW_BYTES, held[i].a_row, full);
+                    tma_load_3d_pair(base + Cfg::OFF_SFA, tmSFA, 0, held[i].ks * 16, held[i].sfa_block, full);
+                }
+            }
         }
     }
 
@@ -378,6 +430,8 @@ struct Roles {
                     if (!__all_sync(0xFFFFFFFFu, ok)) return;
                     if (PROF) wait_full += now() - w0;
                 }
+                if (PROF && iter == 0 && ks == seg.k0 && lane == 0)
+                    g.prof[size_t(unit) * CG * PROF_WORDS + PROF_T_FIRST_DATA] = globaltimer_ns();
                 tc_fence_after_sync();
                 const int next_stage = stage + 1 == Cfg::STAGES ? 0 : stage + 1;
                 const uint32_t next_phase = stage + 1 == Cfg::STAGES ? phase ^ 1u : phase;
@@ -436,6 +490,7 @@ struct Roles {
             out[PROF_MMA_WAIT_FULL] = wait_full;
             out[PROF_MMA_WAIT_ACC] = wait_acc;
             out[PROF_MMA_TOTAL] = now() - born;
+            out[PROF_T_LAST_ISSUE] = globaltimer_ns();
         }
     }
 
@@ -540,7 +595,9 @@ struct Roles {
     }
 
     // ---- warps 0-3: drain accumulators to C ---------------------------------------
-    __device__ void drain(uint32_t tmem, const CUtensorMap* tmC, int warp, int lane) const {
+    // warp: the Tensor Memory lane quarter this warp drains (rows warp * 32 .. + 31 of the CTA's 128);
+    // half: with two warps per quarter, which of the alternating 64-column chunks are this warp's.
+    __device__ void drain(uint32_t tmem, const CUtensorMap* tmC, int warp, int half, int lane) const {
         const uint32_t stage_base = smem + Cfg::STAGES * Cfg::STAGE_BYTES + warp * 2 * Cfg::EPI_WARP_BYTES;
         const uint32_t acc_free_leader = CG == 2 ? map_to_cta(bar(&ctrl->acc_free), 0) : bar(&ctrl->acc_free);
         uint32_t iter = 0, stores = 0;
@@ -548,6 +605,8 @@ struct Roles {
         const uint64_t c_policy = policy_evict_first();
         long long wait_acc = 0, wait_store = 0;
         const long long born = now();
+        // with static operands the prologue did not wait for the grid in front: nothing may be stored before it has finished
+        if (g.static_operands != 0) grid_dependency_wait();
         Walk walk(g, unit, units, tiles, g.ksteps);
         Segment seg;
         constexpr uint32_t SK_WARP_FLOATS = UN * 32;            // one warp's 32 rows of a tile
@@ -563,13 +622,21 @@ struct Roles {
             if (!__all_sync(0xFFFFFFFFu, ready)) break;
             if (PROF) wait_acc += now() - w0;
             unsigned long long* tr = nullptr;
-            if (PROF && unit == 0 && warp == 0 && lane == 0 && iter < TR_TILES)
+            if (PROF && unit == 0 && warp == 0 && half == 0 && lane == 0 && iter < TR_TILES)
                 tr = g.prof + size_t(units) * CG * PROF_WORDS + size_t(iter) * 8 + (rank ? 6 : 3);
             if (tr) tr[0] = now();
             tc_fence_after_sync();
             const uint32_t acc = tmem + (iter & 1u) * Cfg::ACC_STRIDE + (uint32_t(warp * 32) << 16);
+            if (Cfg::EPI_WARPS == 8 && half == 1) {
+                // This warp's chunks never include the columns the two accumulators share (those are chunk 0).
+                // Its arrival says that it has left the previous tile, whose buffer the next tile's MMAs reuse.
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(acc_free_leader);
+            }
             #pragma unroll 1
             for (int c = 0; c < UN / EPI_COLS; ++c) {
+                if (Cfg::EPI_WARPS == 8 && (c & 1) != half) continue;
                 // Columns shared with the other accumulator go first: top of buffer 0, bottom of buffer 1.
                 const int chunk = (iter & 1u) ? c : UN / EPI_COLS - 1 - c;
                 uint32_t v[EPI_COLS];
@@ -704,7 +771,7 @@ struct Roles {
             }
         }
         tma_store_wait_all();                                   // lanes without stores in flight fall through
-        if (PROF && warp == 0 && lane == 0) {
+        if (PROF && warp == 0 && half == 0 && lane == 0) {
             unsigned long long* out = g.prof + (size_t(unit) * CG + rank) * PROF_WORDS;
             out[PROF_EPI_WAIT_ACC] = wait_acc;
             out[PROF_EPI_WAIT_STORE] = wait_store;
@@ -712,12 +779,13 @@ struct Roles {
             uint32_t smid;
             asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
             out[PROF_SMID] = smid;
+            out[PROF_T_EPI_DONE] = globaltimer_ns();
         }
     }
 };
 
 template <int CG, int UN, int EPI, bool PROF>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(Config<CG, UN, EPI>::THREADS, 1)
 nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB,
                   const __grid_constant__ CUtensorMap tmC, const GemmArgs g) {
@@ -730,13 +798,19 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const uint32_t rank = CG == 2 ? cluster_ctarank() : 0u;
     const long long entered = clock64();
 
+    // Programmatic dependent launch: a kernel launched behind this one with the stream-serialisation attribute
+    // may bring its CTAs onto SMs that are free (and set up its barriers and Tensor Memory there) as soon as every
+    // CTA of this grid has got here; it then waits in grid_dependency_wait() until this grid has finished.
+    if (threadIdx.x == 0) grid_launch_dependents();
+    if (PROF && threadIdx.x == 0) g.prof[(size_t(CG == 2 ? blockIdx.x / 2u : blockIdx.x) * CG + rank) * PROF_WORDS + PROF_T_ENTER] = globaltimer_ns();
+
     if (threadIdx.x == 0) {
         for (int s = 0; s < Cfg::STAGES; ++s) {
             mbar_init(smem_u32(&ctrl->full[s]), 1);
             mbar_init(smem_u32(&ctrl->empty[s]), 1);
         }
         mbar_init(smem_u32(&ctrl->acc_full), 1);
-        mbar_init(smem_u32(&ctrl->acc_free), 4 * CG);           // one arrival per epilogue warp of the pair
+        mbar_init(smem_u32(&ctrl->acc_free), Cfg::EPI_WARPS * CG);   // one arrival per epilogue warp of the pair
         ctrl->wait.abort = 0;
         mbar_init_fence();
     }
@@ -760,6 +834,10 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     if constexpr (CG == 2) { cluster_arrive(); cluster_wait(); } else { __syncthreads(); }
     tc_fence_after_sync();
     const uint32_t tmem = ctrl->tmem_base;
+    // Everything above touched only this CTA's own resources. From here on global memory is read and written:
+    // wait for the grid this launch depends on (returns at once when the launch was an ordinary one), unless the
+    // caller has declared operands that the grid in front cannot be writing (then the roles wait where they must).
+    if (g.static_operands == 0) grid_dependency_wait();
 
     Roles<CG, UN, EPI, PROF> roles{smem, ctrl, rank, unit, gridDim.x / CG,
                                    uint32_t(g.block_expert ? __ldg(g.num_blocks) : g.tiles_m) * uint32_t(g.tiles_n),
@@ -770,7 +848,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     } else if (warp == 4) {
         if (rank == 0) roles.issue(tmem, lane);
     } else {
-        roles.drain(tmem, &tmC, warp, lane);
+        roles.drain(tmem, &tmC, warp & 3, warp < 4 ? 0 : 1, lane);
     }
     __syncwarp();
 
@@ -857,9 +935,11 @@ int env_int(const char* name, int fallback) {
 std::mutex g_host_state;            // guards the per-device caches below
 
 // One kernel instance: sets its shared-memory limit once per device, then launches.
+// pdl: launch with the programmatic stream-serialisation attribute, so that the prologue of this launch overlaps
+// the tail of the kernel in front of it in the stream (when that kernel allows it, as this kernel does).
 template <int CG, int UN, int EPI, bool PROF = false>
 void launch_instance(int device, int units, const CUtensorMap& A, const CUtensorMap& B, const CUtensorMap& SFA,
-                     const CUtensorMap& SFB, const CUtensorMap& tmC, const GemmArgs& g, cudaStream_t stream) {
+                     const CUtensorMap& SFB, const CUtensorMap& tmC, const GemmArgs& g, cudaStream_t stream, bool pdl) {
     using Cfg = Config<CG, UN, EPI>;
     auto kernel = nvfp4_gemm_kernel<CG, UN, EPI, PROF>;
     {
@@ -870,16 +950,18 @@ void launch_instance(int device, int units, const CUtensorMap& A, const CUtensor
             if (device >= 0 && device < 64) ready[device] = true;
         }
     }
-    cudaLaunchAttribute attr{};
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim = {unsigned(CG), 1, 1};
+    cudaLaunchAttribute attrs[2]{};
+    attrs[0].id = cudaLaunchAttributeClusterDimension;
+    attrs[0].val.clusterDim = {unsigned(CG), 1, 1};
+    attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[1].val.programmaticStreamSerializationAllowed = 1;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(unsigned(units) * CG);
-    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.blockDim = dim3(Cfg::THREADS);
     cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
     cfg.stream = stream;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
+    cfg.attrs = attrs;
+    cfg.numAttrs = pdl ? 2 : 1;
     cuda_check(cudaLaunchKernelEx(&cfg, kernel, A, B, SFA, SFB, tmC, g));
     g_launches.fetch_add(1, std::memory_order_relaxed);
 }
@@ -904,7 +986,7 @@ int max_units(int device) {
         attr.val.clusterDim = {2, 1, 1};
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3(unsigned(sms / 2) * 2);
-        cfg.blockDim = dim3(NUM_THREADS);
+        cfg.blockDim = dim3(Cfg::THREADS);
         cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
         cfg.attrs = &attr;
         cfg.numAttrs = 1;
@@ -957,11 +1039,11 @@ void prepare(gpu_kernels::Nvfp4Params& p, const uint8_t* A, const uint8_t* B, co
     else if ((force == 0 && N % 256 == 0) || force == 1256) { p.cta_group = 1; p.tile_n = 256; }
     else { p.cta_group = 1; p.tile_n = 128; }
     if (M % (128 * p.cta_group) || N % p.tile_n) throw std::invalid_argument("nvfp4 gemm: forced variant does not divide the shape");
-    // Epilogue route. With a long K loop both routes cost the same (the C bytes share the SM's L2 port
-    // with the loads either way: 274.8k vs 275.8k cycles at 8192^3) and C goes out by TMA store; when the
-    // epilogue is a large share of a tile (short K) or the tile is a single CTA's, writing from registers
-    // is faster (4096x4096x1024: 21.8k vs 25.5k cycles; 128x28672x8192: 47.0k vs 48.7k).
-    p.direct_store = p.cta_group == 1 ? 1 : env_int("NVFP4_B200_DIRECT_STORE", K <= 2048 ? 1 : 0);
+    // Epilogue route. C leaves from registers (32-byte stores, two epilogue warps per Tensor Memory lane
+    // quarter) unless the caller asks for the staged route (rows through swizzled shared memory, TMA stores):
+    // measured by graph replay under sustained load, registers / staged: 8192^3 222.0 / 227.2 us, 16384^3
+    // 1717 / 1753 us, 8192x4096x2048 36.3 / 38.6 us. Single-CTA tiles have no staged route.
+    p.direct_store = p.cta_group == 1 ? 1 : env_int("NVFP4_B200_DIRECT_STORE", 1);
     const int box_b = p.tile_n / p.cta_group;
     p.A = operand_map(A, M, K, BLOCK_M);
     p.B = operand_map(B, N, K, box_b);
@@ -978,6 +1060,7 @@ void prepare(gpu_kernels::Nvfp4Params& p, const uint8_t* A, const uint8_t* B, co
     p.group_m = std::max(1, std::min(env_int("NVFP4_B200_GROUP_M", gm), M / (128 * p.cta_group)));
     // Measured: 128x28672x8192 30.2 -> 28.9 us, 8192^3 199.8 -> 199.0 us with the tiles' K walks de-phased.
     p.k_skew = env_int("NVFP4_B200_K_SKEW", 11);
+    p.pdl = env_int("NVFP4_B200_PDL", 1);
     p.status_slot = 1 + int(g_next_slot.fetch_add(1, std::memory_order_relaxed) % unsigned(STATUS_SLOTS - 1));
     (void)status_base(device);
 }
@@ -1078,6 +1161,8 @@ GemmArgs dense_args(const gpu_kernels::Nvfp4Params& p, void* c, unsigned long lo
     g.gather_ldc = p.gather_ldc;
     g.gather_maps = static_cast<const CUtensorMap*>(p.gather_maps);
     g.gather_ptrs = static_cast<void* const*>(p.gather_ptrs);
+    // split-K launches of one plan share flags and partial sums: they never overlap; profiled launches neither
+    g.static_operands = (p.split_k > 1 || prof) ? 0 : p.static_operands;
     if (p.route && p.split_k <= 1) {
         g.route = static_cast<const uint32_t*>(p.route);
         g.sm_side = static_cast<const uint8_t*>(p.sm_side);
@@ -1089,24 +1174,25 @@ GemmArgs dense_args(const gpu_kernels::Nvfp4Params& p, void* c, unsigned long lo
 template <int CG, int UN>
 void launch_dense(const gpu_kernels::Nvfp4Params& p, const CUtensorMap& tmC, const GemmArgs& g, cudaStream_t stream) {
     const bool staged = CG == 2 && !p.direct_store;
+    const bool pdl = p.pdl != 0 && !g.prof;
     const int dev = p.device, units = p.clusters;
     if (p.split_k > 1) {
-        launch_instance<CG, UN, EPI_SPLIT_K>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream);
+        launch_instance<CG, UN, EPI_SPLIT_K>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream, pdl);
     } else if (p.gather_world) {
         if constexpr (CG == 2) {
-            if (staged) return launch_instance<CG, UN, EPI_GATHER_TMA>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream);
+            if (staged) return launch_instance<CG, UN, EPI_GATHER_TMA>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream, pdl);
         }
-        launch_instance<CG, UN, EPI_GATHER_DIRECT>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream);
+        launch_instance<CG, UN, EPI_GATHER_DIRECT>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream, pdl);
     } else if (g.prof) {
         if constexpr (CG == 2) {
-            if (staged) return launch_instance<CG, UN, EPI_TMA, true>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream);
+            if (staged) return launch_instance<CG, UN, EPI_TMA, true>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream, pdl);
         }
-        launch_instance<CG, UN, EPI_DIRECT, true>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream);
+        launch_instance<CG, UN, EPI_DIRECT, true>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream, pdl);
     } else {
         if constexpr (CG == 2) {
-            if (staged) return launch_instance<CG, UN, EPI_TMA>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream);
+            if (staged) return launch_instance<CG, UN, EPI_TMA>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream, pdl);
         }
-        launch_instance<CG, UN, EPI_DIRECT>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream);
+        launch_instance<CG, UN, EPI_DIRECT>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream, pdl);
     }
 }
 
@@ -1274,14 +1360,15 @@ void grouped_launch_fused(const GroupedGemm& p, void* C, int out_bf16, uint8_t* 
     g.world = world;
     g.slot_rows = slot_rows;
     const int dev = p.device, units = p.units;
+    const bool pdl = env_int("NVFP4_B200_PDL", 1) != 0;
     if (p.block_rows == 256) {
-        if (fused) launch_instance<2, 256, EPI_ACT>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream);
-        else if (row_dst) launch_instance<2, 256, EPI_SCATTER_ROWS>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream);
-        else launch_instance<2, 256, EPI_DIRECT>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream);
+        if (fused) launch_instance<2, 256, EPI_ACT>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream, pdl);
+        else if (row_dst) launch_instance<2, 256, EPI_SCATTER_ROWS>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream, pdl);
+        else launch_instance<2, 256, EPI_DIRECT>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream, pdl);
     } else {
-        if (fused) launch_instance<1, 256, EPI_ACT>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream);
-        else if (row_dst) launch_instance<1, 256, EPI_SCATTER>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream);
-        else launch_instance<1, 256, EPI_DIRECT>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream);
+        if (fused) launch_instance<1, 256, EPI_ACT>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream, pdl);
+        else if (row_dst) launch_instance<1, 256, EPI_SCATTER>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream, pdl);
+        else launch_instance<1, 256, EPI_DIRECT>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream, pdl);
     }
 }
 

@@ -53,6 +53,17 @@ __device__ __forceinline__ void cluster_wait() {
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
+// ---- programmatic dependent launch ---------------------------------------------
+// launch_dependents: once every CTA of this grid has executed it (or exited), a kernel launched behind it with
+// the programmatic stream-serialisation attribute may start. grid_dependency_wait: blocks until the grid this
+// launch depends on has completed and its memory is visible; returns at once for an ordinary launch.
+__device__ __forceinline__ void grid_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void grid_dependency_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // ---- mbarrier -------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t arrivals) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(arrivals) : "memory");

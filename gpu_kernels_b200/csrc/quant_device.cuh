@@ -113,11 +113,20 @@ __device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.0f 
 // For a bf16 or fp16 input the E2M1 code of x/s can be read off x itself: RN(x/s) lies above,
 // on or below a midpoint m exactly when |x| lies above, on or below m*s, and m*s is an exact
 // number with at most 7 significant bits (m has 3, an E4M3 scale 4), i.e. representable in the
-// input's own 16-bit format. So the block routine compares packed pairs of |x| against the seven
-// products m_j*s (strictly for the midpoints whose tie goes down, >= for those whose tie goes
-// up: reference/python/nvfp4.py:8-13) and counts. The count is accumulated on top of a constant
-// whose ulp is 1 (128 in bf16, 1024 in fp16), so the low bits of the sum are the code; the sign
-// bit (x < 0, false for -0.0 as in the reference, where q = -0.0 is not < 0) is added as 8.
+// input's own 16-bit format. The code is the number of the seven midpoints (.25, .75, 1.25, 1.75,
+// 2.5, 3.5, 5) that |x| passes, where a tie passes the midpoints whose even neighbour lies above
+// (.75, 1.75, 3.5: compared with >=) and not the others (>): reference/python/nvfp4.py:8-13.
+// Seven compares per pair made the integer/logic pipe the limit of the kernel (74 % busy at 41 % of
+// the DRAM bandwidth), so the count is taken as a three-step binary search whose thresholds are
+// selected arithmetically on the FMA pipe:
+//   c3 = |x| >= 1.75 s                                        (code bit 2)
+//   c2 = |x| >= .75 s + c3 * 2.75 s                           (.75 s or 3.5 s: both ties go up)
+//   c1 = |x| >  (.25 s + c2 * s) + c3 * (2.25 s + c2 * 1.5 s) (.25, 1.25, 2.5 or 5 s: all ties go down)
+// Every product and sum above is an exact number of at most 8 significant bits (the multipliers have
+// at most 4, the scale 4), so each fused multiply-add returns the exact threshold, in bf16 as in
+// fp16. The code 4 c3 + 2 c2 + c1 is accumulated on top of a constant whose ulp is 1 (128 in bf16,
+// 1024 in fp16), so the low byte of the sum's bit pattern is the code; the sign bit (x < 0, false
+// for -0.0 as in the reference, where q = -0.0 is not < 0) is added as 8.
 // No value of these formats is small enough for a non-zero quotient to round to zero.
 struct Bf16Pairs {
     using pair = __nv_bfloat162;
@@ -162,27 +171,33 @@ __device__ __forceinline__ uint32_t quantise_block_pairs(const uint32_t (&w)[8],
     const float s = ue4m3_to_float(sbyte);
     // one conversion of the scale, then exact 16-bit products (<= 7 significant bits each)
     const pair s2 = F::both(s);
-    const pair t0 = __hmul2(s2, F::both(0.25f)), t1 = __hmul2(s2, F::both(0.75f)), t2 = __hmul2(s2, F::both(1.25f)),
-               t3 = __hmul2(s2, F::both(1.75f)), t4 = __hmul2(s2, F::both(2.5f)), t5 = __hmul2(s2, F::both(3.5f)),
-               t6 = __hmul2(s2, F::both(5.0f));
-    const pair base = F::both(F::count_base()), eight = F::both(8.0f), zero = F::both(0.0f);
-    uint32_t bytes[8];
+    const pair t3 = __hmul2(s2, F::both(1.75f)), t1 = __hmul2(s2, F::both(0.75f)), d51 = __hmul2(s2, F::both(2.75f)),
+               t0 = __hmul2(s2, F::both(0.25f)), d225 = __hmul2(s2, F::both(2.25f)), d150 = __hmul2(s2, F::both(1.5f));
+    const pair base = F::both(F::count_base()), eight = F::both(8.0f), four = F::both(4.0f), two = F::both(2.0f),
+               zero = F::both(0.0f);
+    uint32_t n[8];
     #pragma unroll
     for (int k = 0; k < 8; ++k) {
         const pair mag = F::from_bits(a[k]);
-        pair n = __hadd2(base, __hgt2(mag, t0));
-        n = __hadd2(n, __hge2(mag, t1));
-        n = __hadd2(n, __hgt2(mag, t2));
-        n = __hadd2(n, __hge2(mag, t3));
-        n = __hadd2(n, __hgt2(mag, t4));
-        n = __hadd2(n, __hge2(mag, t5));
-        n = __hadd2(n, __hgt2(mag, t6));
-        n = __hfma2(__hlt2(F::from_bits(w[k]), zero), eight, n);
-        const uint32_t nib = F::bits(n) & 0x000F000Fu;
-        bytes[k] = (nib | (nib >> 12)) & 0xFFu;
+        const pair c3 = __hge2(mag, t3);
+        const pair c2 = __hge2(mag, __hfma2(c3, d51, t1));
+        const pair c1 = __hgt2(mag, __hfma2(c3, __hfma2(c2, d150, d225), __hfma2(c2, s2, t0)));
+        pair count = __hfma2(c3, four, base);
+        count = __hfma2(c2, two, count);
+        count = __hadd2(count, c1);
+        count = __hfma2(__hlt2(F::from_bits(w[k]), zero), eight, count);
+        n[k] = F::bits(count);                               // low byte of each half: the 4-bit code
     }
-    packed = make_uint2(bytes[0] | (bytes[1] << 8) | (bytes[2] << 16) | (bytes[3] << 24),
-                        bytes[4] | (bytes[5] << 8) | (bytes[6] << 16) | (bytes[7] << 24));
+    // codes of values (2k, 2k+1) sit in bytes 0 and 2 of n[k]: gather four codes per word, fold the odd
+    // ones into the high nibbles, gather the four finished bytes
+    uint32_t out[2];
+    #pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const uint32_t x01 = __byte_perm(n[4 * h], n[4 * h + 1], 0x6420), x23 = __byte_perm(n[4 * h + 2], n[4 * h + 3], 0x6420);
+        const uint32_t y01 = x01 | (x01 >> 4), y23 = x23 | (x23 >> 4);
+        out[h] = __byte_perm(y01, y23, 0x6420);
+    }
+    packed = make_uint2(out[0], out[1]);
     return sbyte;
 }
 

@@ -87,7 +87,8 @@ class Nvfp4Gemm:
             _lib.check(_lib.load().gpu_kernels_nvfp4_plan_profile(self._plan, out.data_ptr(), _stream(), buf, n,
                                                                   ctypes.byref(written)))
         keys = ("producer_wait", "producer_total", "mma_wait_data", "mma_wait_acc", "mma_total",
-                "epi_wait_acc", "epi_wait_store", "epi_total", "smid")
+                "epi_wait_acc", "epi_wait_store", "epi_total", "smid",
+                "t_enter_ns", "t_first_data_ns", "t_last_issue_ns", "t_epi_done_ns")
         ctas = (written.value - 128) // 16
         self.handover = [tuple(buf[ctas * 16 + 8 * i: ctas * 16 + 8 * i + 8]) for i in range(16)]
         self.raw_profile = [tuple(buf[i:i + 16]) for i in range(0, ctas * 16, 16)]

@@ -53,6 +53,12 @@ struct Nvfp4Params {
     const void* sm_side;
     const void* unit_side;
     int side_units[2];              // clusters the census found on either side of the L2
+    int pdl;                        // 1: launches carry the programmatic stream-serialisation attribute
+    // What the caller promises about the kernel in front of each launch in the stream (which this launch may
+    // overlap under pdl): 0 = nothing (default): the launch waits for it before touching memory; 1 = it does not
+    // write B or SFB (weights): their first tiles are fetched while it drains; 2 = it writes none of A, B, SFA,
+    // SFB: this launch computes while it drains and only holds back its stores of C until it has finished.
+    int static_operands;
 };
 
 struct Nvfp4Implementation {

@@ -58,6 +58,13 @@ int gpu_kernels_nvfp4_dequantize(const void* packed, const void* scales, void* o
 int gpu_kernels_nvfp4_plan_set_alpha(void* plan, float alpha);
 /* Tuning knobs. key: "group_m" (tile rows per rasterisation band, >= 1); "c_evict_first" (0/1: L2 policy
  * of the C stores); "direct_store" (0/1: epilogue writes C from registers instead of staging it for TMA stores);
+ * "pdl" (0/1, default 1: launches carry the programmatic stream-serialisation attribute, so that this kernel's
+ * set-up overlaps the tail of the kernel in front of it in the stream; 0 = ordinary launches);
+ * "static_operands" (0/1/2, default 0: the caller's promise about the kernel that runs in front of each launch
+ * on the stream, used only with "pdl": 1 = that kernel does not write B or SFB (weights): this launch fetches its
+ * first B tiles while that kernel drains; 2 = it writes none of A, B, SFA, SFB (a chain of independent GEMMs, or
+ * inputs that were produced earlier): this launch computes its tiles while that kernel's last tiles finish and
+ * only holds back its stores of C until that kernel has completed; ignored by split-K launches);
  * "out_bf16" (0/1: C is written as bfloat16 instead of FP16 through the same pointer; the reference's output
  * is FP16 only, include/nvfp4.h:21); "l2_side" (0/1: L2-side-aware tile order, the counterpart of the
  * reference's prepare_schedule, kernels/gemm/matmul/sm100.cu:566-673: a census at this call labels the SMs by

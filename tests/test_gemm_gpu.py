@@ -170,6 +170,55 @@ def test_l2_side_order_gives_the_same_tiles(g):
     plan.close()
 
 
+@pytest.mark.parametrize("mode", [1, 2])
+def test_overlapping_launches_with_static_operands(g, mode):
+    # "static_operands": the caller promises that the kernel in front of a launch does not write B (1) or any
+    # operand (2); under programmatic dependent launch the launch then starts while that kernel's last tiles
+    # finish, and only its stores of C wait. A chain of launches of two plans with different shapes, each into
+    # its own C and, the hard case, all into one shared C (every launch must overwrite the one before it only
+    # after that one has finished): bit-identical to ordinary launches.
+    specs = [(2048, 1024, 1024), (128, 2560, 2048), (512, 768, 512)]
+    plans, wants = [], []
+    for i, (m, n, k) in enumerate(specs):
+        pa, sa = g.quantize(random_operand(m, k, seed=300 + i))
+        pb, sb = g.quantize(random_operand(n, k, seed=310 + i, scale=0.02))
+        plan = g.Nvfp4Gemm(pa, pb, sa, sb)
+        wants.append(plan.run(nan_output(m, n)).clone())
+        plan.set_option("static_operands", mode)
+        plans.append(plan)
+    torch.cuda.synchronize()
+    outs = [nan_output(m, n) for m, n, _ in specs]
+    for _ in range(6):
+        for plan, out in zip(plans, outs):
+            plan.run(out)
+    torch.cuda.synchronize()
+    for plan, out, want in zip(plans, outs, wants):
+        plan.validate()
+        assert torch.equal(out, want)
+    # one shared output buffer, viewed per shape: the last writer wins, and nothing of an earlier launch lands late
+    biggest = max(m * n for m, n, _ in specs)
+    shared = torch.full((biggest,), float("nan"), device="cuda", dtype=torch.float16)
+    views = [shared[:m * n].view(m, n) for m, n, _ in specs]
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            for _ in range(3):
+                for plan, view in zip(plans, views):
+                    plan.run(view)
+            plans[0].run(views[0])
+    torch.cuda.current_stream().wait_stream(side)
+    for _ in range(3):
+        shared.fill_(float("nan"))
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(views[0], wants[0])
+    for plan in plans:
+        plan.validate()
+        plan.close()
+
+
 def test_distinct_scale_everywhere(g):
     # every (row, K block) has its own scale byte and codes are random nibbles: a wrong
     # scale column, swizzle or K-slice order cannot cancel out
