@@ -217,6 +217,14 @@ def time_replays(step, ranks: Ranks, cycle: int, graph_ops: int, warmup_s: float
             "timed_s": t1 - t0, "clocks": clocks}
 
 
+def timing_plan(args, main):
+    """(seconds of warm-up replays, samples, ms per sample): the reference harness's numbers for the workload the
+    line is about, shorter for the other configurations; --capture shrinks everything for a profiler run."""
+    if args.capture:
+        return 0.02, 2, 2.0
+    return (1.0, 9, 20.0) if main else (0.3, 5, 20.0)
+
+
 def timing_note(r, warmup_s, sample_ms):
     return {"method": "CUDA graph replay, median of samples (the reference harness's method)",
             "graph_operations": r["graph_operations"], "warmup_s": warmup_s, "trials": r["trials"],
@@ -420,7 +428,7 @@ def run_gemm(args, ranks: Ranks, workload, sampler, main, gathers=("none",)):
     n_local = hi - lo
     lib = _lib.load()
     l2 = lib.gpu_kernels_nvfp4_l2_bytes()
-    warmup_s, trials, sample_ms = (1.0, 9, 20.0) if main else (0.3, 5, 20.0)
+    warmup_s, trials, sample_ms = timing_plan(args, main)
 
     # Seeded synthetic operands: A on every rank, this rank's row slab of B (drawn with a per-slab seed).
     gen = torch.Generator(device=dev).manual_seed(0)
@@ -612,7 +620,7 @@ def run_quantise(args, ranks: Ranks, workload, sampler, main):
     from gpu_kernels_b200 import _lib
     dev = torch.device("cuda", ranks.local_rank)
     rows, k = QUANT_WORKLOADS[workload]
-    warmup_s, trials, sample_ms = (1.0, 9, 20.0) if main else (0.3, 5, 20.0)
+    warmup_s, trials, sample_ms = timing_plan(args, main)
     copies = max(2, (512 << 20) // (rows * k * 2))
     gen = torch.Generator(device=dev).manual_seed(0)
     xs = []
@@ -737,7 +745,7 @@ class MoeBench:
         tokens = MOE_WORKLOADS[workload]
         H, I, E, topk = (MOE_SHAPE[k] for k in ("hidden", "inter", "experts", "topk"))
         world, rank, local = ranks.world, ranks.rank, self.local
-        warmup_s, trials, sample_ms = (1.0, 9, 20.0) if main else (0.3, 5, 20.0)
+        warmup_s, trials, sample_ms = timing_plan(self.args, main)
         gen = torch.Generator(device=dev).manual_seed(77 * tokens + rank)
         sets = []
         for _ in range(4):                                      # rotating inputs: routing changes every step
@@ -948,6 +956,8 @@ def main():
                     help="tile order of the dense GEMM: the plan's default, or force the L2-side-aware order on / off")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-library-bar", action="store_true", help="skip the cuBLASLt comparison leg")
+    ap.add_argument("--capture", action="store_true",
+                    help="a few launches only (for a run under a profiler; the numbers it prints mean nothing)")
     ap.add_argument("--e2e-all", action="store_true", help="measure the host-buffer entry point for every GEMM config")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

@@ -24,6 +24,7 @@
 
 #include <algorithm>
 #include <cstddef>
+#include <cstdlib>
 #include <string>
 
 namespace nvfp4_b200 {
@@ -33,7 +34,33 @@ constexpr int PAYLOAD_TAIL = 16;          // route weight (float) + padding, kee
 
 __host__ __device__ inline int payload_bytes(int hidden) { return hidden / 2 + hidden / 16 + PAYLOAD_TAIL; }
 
+// Every kernel of this file opens with chain_point(): it lets the kernel behind it in the stream be scheduled
+// early and then waits until the kernel in front of it has finished, so under programmatic dependent launch
+// the launch latencies of the forward's dozen small kernels overlap instead of adding up. Launched through
+// launch_chained() (the attribute that permits the early start); an ordinary launch behaves as before.
+__device__ __forceinline__ void chain_point() {
+    ptx::grid_launch_dependents();
+    ptx::grid_dependency_wait();
+}
+
+template <typename... Params, typename... Args>
+void launch_chained(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    static const bool pdl = [] { const char* v = std::getenv("NVFP4_B200_PDL"); return !(v && v[0] == '0'); }();
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cfg.attrs = &attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    cuda_check(cudaLaunchKernelEx(&cfg, kernel, Params(args)...));
+}
+
 __global__ void route_count_kernel(const long long* __restrict__ ids, int routes, int experts, int* __restrict__ counts) {
+    chain_point();
     extern __shared__ int local[];
     for (int e = threadIdx.x; e < experts; e += blockDim.x) local[e] = 0;
     __syncthreads();
@@ -72,6 +99,7 @@ __global__ void plan_kernel(int* counts, int world, int rank, int experts, int c
                             int* __restrict__ seg_pool_offset, int* __restrict__ block_expert,
                             int* __restrict__ num_blocks, int* __restrict__ totals, int* __restrict__ peer_offset,
                             const long long* __restrict__ ids, int routes, int* __restrict__ cursor, int peer_to_pool) {
+    chain_point();
     extern __shared__ int sh[];
     const int local_experts = experts / world;
     const int segments = world * local_experts;          // == experts
@@ -176,6 +204,7 @@ __global__ void pack_kernel(const uint8_t* __restrict__ xq, const uint8_t* __res
                             uint8_t* __restrict__ send_rows, int* __restrict__ send_pos,
                             const int* __restrict__ seg_pool_offset, uint8_t* __restrict__ pool_packed,
                             uint8_t* __restrict__ pool_scales, float* __restrict__ pool_weight) {
+    chain_point();
     const int lane = threadIdx.x & 31;
     const int route = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (route >= routes) return;
@@ -215,6 +244,7 @@ __global__ void unpack_kernel(const uint8_t* __restrict__ recv_rows, const int* 
                               uint8_t* __restrict__ pool_packed, uint8_t* __restrict__ pool_scales,
                               float* __restrict__ pool_weight, int* __restrict__ pool_of_recv, int local_experts,
                               int* __restrict__ pool_dst) {
+    chain_point();
     const int lane = threadIdx.x & 31;
     const int p = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (p >= totals[0] || totals[2]) return;
@@ -251,6 +281,7 @@ __global__ void unpack_meta_kernel(const uint8_t* __restrict__ side, const int* 
                                    const int* __restrict__ seg_src_offset, const int* __restrict__ seg_pool_offset,
                                    uint8_t* __restrict__ pool_scales, float* __restrict__ pool_weight,
                                    int* __restrict__ pool_dst, int local_experts) {
+    chain_point();
     const int lane = threadIdx.x & 31;
     const int p = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (p >= totals[0] || totals[2]) return;
@@ -278,6 +309,7 @@ __global__ void __launch_bounds__(256)
 swiglu_quant_kernel(const __nv_bfloat16* __restrict__ gate_up, const float* __restrict__ pool_weight,
                     const int* __restrict__ num_blocks, int block_rows, int inter, float clamp,
                     uint8_t* __restrict__ act_packed, uint8_t* __restrict__ act_scales) {
+    chain_point();
     __shared__ __align__(16) uint8_t sf_tile[4 * 512];
     if (int(blockIdx.y) * 128 >= *num_blocks * block_rows) return;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -332,6 +364,7 @@ swiglu_quant_kernel(const __nv_bfloat16* __restrict__ gate_up, const float* __re
 
 __global__ void return_rows_kernel(const uint4* __restrict__ out_pool, const int* __restrict__ pool_of_recv,
                                    const int* __restrict__ totals, int row_vec, uint4* __restrict__ ret) {
+    chain_point();
     const int p = blockIdx.x;
     if (p >= totals[0] || totals[2]) return;
     const uint4* src = out_pool + size_t(pool_of_recv[p]) * row_vec;
@@ -344,6 +377,7 @@ __global__ void return_rows_kernel(const uint4* __restrict__ out_pool, const int
 // negative row index) adds nothing.
 __global__ void reduce_kernel(const uint4* __restrict__ returned, const int* __restrict__ send_pos, int topk,
                               int row_vec, uint4* __restrict__ y, const long long* __restrict__ ids, int experts) {
+    chain_point();
     const int t = blockIdx.x;
     for (int i = threadIdx.x; i < row_vec; i += blockDim.x) {
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -387,6 +421,7 @@ __global__ void pack_peer_kernel(const uint8_t* __restrict__ xq, const uint8_t* 
                                  const long long* __restrict__ ids, const float* __restrict__ weights, int routes,
                                  int topk, int hidden, int local_experts, int experts, const int* __restrict__ peer_offset,
                                  int* __restrict__ cursor, PeerBuffers recv, int recv_capacity, int* __restrict__ error) {
+    chain_point();
     const int lane = threadIdx.x & 31;
     const int route = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (route >= routes) return;
@@ -424,6 +459,7 @@ quantise_route_kernel(const __nv_bfloat16* __restrict__ x, const long long* __re
                       int* __restrict__ error,
                       uint8_t* __restrict__ pool_packed, uint8_t* __restrict__ pool_scales,
                       float* __restrict__ pool_weight, int* __restrict__ route_row) {
+    chain_point();
     extern __shared__ __align__(16) uint8_t row[];              // codes [hidden/2] | scale bytes [hidden/16] | int dst[topk]
     const int token = blockIdx.x;
     const int row_bytes = hidden / 2 + hidden / 16;
@@ -500,6 +536,7 @@ __global__ void return_peer_kernel(const uint4* __restrict__ out_pool, const uin
                                    const int* __restrict__ pool_of_recv, const int* __restrict__ totals,
                                    const int* __restrict__ seg_src_offset, int segments, int local_experts, int hidden,
                                    PeerBuffers slots, int slot_capacity, int* __restrict__ error) {
+    chain_point();
     const int p = blockIdx.x;
     if (p >= totals[0] || totals[2]) return;
     int lo = 0, hi = segments;
@@ -529,8 +566,7 @@ void moe_route_count(const long long* ids, int routes, int experts, int* counts,
     if (!ids || !counts || routes < 0 || experts <= 0 || experts > 4096) throw std::invalid_argument("moe route_count: bad argument");
     if (routes == 0) return;
     const int blocks = std::min(64, (routes + 255) / 256);
-    route_count_kernel<<<blocks, 256, experts * sizeof(int), stream>>>(ids, routes, experts, counts);
-    cuda_check(cudaGetLastError());
+    launch_chained(route_count_kernel, dim3(blocks), dim3(256), size_t(experts * sizeof(int)), stream, ids, routes, experts, counts);
 }
 
 void moe_plan(int* counts_matrix, int world, int rank, int experts, int pool_capacity_rows, int block_rows,
@@ -543,10 +579,9 @@ void moe_plan(int* counts_matrix, int world, int rank, int experts, int pool_cap
     if (block_rows != 128 && block_rows != 256) throw std::invalid_argument("moe plan: block rows must be 128 or 256");
     if (pool_capacity_rows <= 0 || pool_capacity_rows % block_rows) throw std::invalid_argument("moe plan: pool capacity must be a multiple of the block rows");
     const int local = experts / world;
-    plan_kernel<<<1, 256, (experts + local + 257) * sizeof(int), stream>>>(counts_matrix, world, rank, experts, pool_capacity_rows, block_rows,
+    launch_chained(plan_kernel, dim3(1), dim3(256), size_t((experts + local + 257) * sizeof(int)), stream, counts_matrix, world, rank, experts, pool_capacity_rows, block_rows,
                                                                    send_offset, seg_src_offset, seg_pool_offset,
                                                                    block_expert, num_blocks, totals, peer_offset, ids, routes, cursor, peer_to_pool);
-    cuda_check(cudaGetLastError());
 }
 
 void moe_pack(const uint8_t* xq, const uint8_t* xs, const long long* ids, const float* weights, int tokens, int topk,
@@ -555,9 +590,8 @@ void moe_pack(const uint8_t* xq, const uint8_t* xs, const long long* ids, const 
     check_hidden(hidden, "moe pack");
     const int routes = tokens * topk;
     if (routes == 0) return;
-    pack_kernel<<<(routes * 32 + 255) / 256, 256, 0, stream>>>(xq, xs, ids, weights, routes, topk, hidden, experts, send_offset,
+    launch_chained(pack_kernel, dim3((routes * 32 + 255) / 256), dim3(256), size_t(0), stream, xq, xs, ids, weights, routes, topk, hidden, experts, send_offset,
                                                                cursor, send_rows, send_pos, nullptr, nullptr, nullptr, nullptr);
-    cuda_check(cudaGetLastError());
 }
 
 void moe_pack_to_pool(const uint8_t* xq, const uint8_t* xs, const long long* ids, const float* weights, int tokens,
@@ -567,10 +601,9 @@ void moe_pack_to_pool(const uint8_t* xq, const uint8_t* xs, const long long* ids
     const int routes = tokens * topk;
     if (routes == 0) return;
     if (!pool_packed || !pool_scales || !pool_weight) throw std::invalid_argument("moe pack_to_pool: null pool");
-    pack_kernel<<<(routes * 32 + 255) / 256, 256, 0, stream>>>(xq, xs, ids, weights, routes, topk, hidden, experts, nullptr, cursor,
+    launch_chained(pack_kernel, dim3((routes * 32 + 255) / 256), dim3(256), size_t(0), stream, xq, xs, ids, weights, routes, topk, hidden, experts, nullptr, cursor,
                                                                nullptr, route_row, seg_pool_offset, pool_packed,
                                                                pool_scales, pool_weight);
-    cuda_check(cudaGetLastError());
 }
 
 void moe_unpack(const uint8_t* recv_rows, int recv_count_capacity, const int* totals, int world, int local_experts,
@@ -578,10 +611,9 @@ void moe_unpack(const uint8_t* recv_rows, int recv_count_capacity, const int* to
                 uint8_t* pool_scales, float* pool_weight, int* pool_of_recv, int* pool_dst, cudaStream_t stream) {
     check_hidden(hidden, "moe unpack");
     if (recv_count_capacity <= 0) return;
-    unpack_kernel<<<(recv_count_capacity * 32 + 255) / 256, 256, 0, stream>>>(
+    launch_chained(unpack_kernel, dim3((recv_count_capacity * 32 + 255) / 256), dim3(256), size_t(0), stream, 
         recv_rows, totals, world * local_experts, hidden, seg_src_offset, seg_pool_offset, pool_packed, pool_scales,
         pool_weight, pool_of_recv, local_experts, pool_dst);
-    cuda_check(cudaGetLastError());
 }
 
 void moe_swiglu_quant(const void* gate_up_bf16, const float* pool_weight, const int* num_blocks, int block_rows, int pool_rows,
@@ -589,27 +621,24 @@ void moe_swiglu_quant(const void* gate_up_bf16, const float* pool_weight, const 
     check_hidden(intermediate, "moe swiglu_quant");
     if (pool_rows <= 0 || pool_rows % 128) throw std::invalid_argument("moe swiglu_quant: pool rows must be a multiple of 128");
     const dim3 grid(intermediate / 256, pool_rows / 128);
-    swiglu_quant_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(gate_up_bf16), pool_weight, num_blocks, block_rows,
+    launch_chained(swiglu_quant_kernel, dim3(grid), dim3(256), size_t(0), stream, static_cast<const __nv_bfloat16*>(gate_up_bf16), pool_weight, num_blocks, block_rows,
                                                   intermediate, clamp, act_packed, act_scales);
-    cuda_check(cudaGetLastError());
 }
 
 void moe_return_rows(const void* out_pool_bf16, const int* pool_of_recv, const int* totals, int capacity, int hidden,
                      void* return_rows_bf16, cudaStream_t stream) {
     check_hidden(hidden, "moe return_rows");
     if (capacity <= 0) return;
-    return_rows_kernel<<<capacity, 128, 0, stream>>>(static_cast<const uint4*>(out_pool_bf16), pool_of_recv, totals,
+    launch_chained(return_rows_kernel, dim3(capacity), dim3(128), size_t(0), stream, static_cast<const uint4*>(out_pool_bf16), pool_of_recv, totals,
                                                      hidden / 8, static_cast<uint4*>(return_rows_bf16));
-    cuda_check(cudaGetLastError());
 }
 
 void moe_reduce(const void* returned_bf16, const int* send_pos, int tokens, int topk, int hidden, void* y_bf16,
                 const long long* ids, int experts, cudaStream_t stream) {
     check_hidden(hidden, "moe reduce");
     if (tokens <= 0) return;
-    reduce_kernel<<<tokens, 128, 0, stream>>>(static_cast<const uint4*>(returned_bf16), send_pos, topk, hidden / 8,
+    launch_chained(reduce_kernel, dim3(tokens), dim3(128), size_t(0), stream, static_cast<const uint4*>(returned_bf16), send_pos, topk, hidden / 8,
                                               static_cast<uint4*>(y_bf16), ids, experts);
-    cuda_check(cudaGetLastError());
 }
 
 void moe_pack_peer(const uint8_t* xq, const uint8_t* xs, const long long* ids, const float* weights, int tokens,
@@ -624,10 +653,9 @@ void moe_pack_peer(const uint8_t* xq, const uint8_t* xs, const long long* ids, c
         if (!peer_recv[r]) throw std::invalid_argument("moe pack_peer: null peer buffer");
         recv.ptr[r] = peer_recv[r];
     }
-    pack_peer_kernel<<<(routes * 32 + 255) / 256, 256, 0, stream>>>(xq, xs, ids, weights, routes, topk, hidden,
+    launch_chained(pack_peer_kernel, dim3((routes * 32 + 255) / 256), dim3(256), size_t(0), stream, xq, xs, ids, weights, routes, topk, hidden,
                                                                     local_experts, world * local_experts, peer_offset,
                                                                     cursor, recv, recv_capacity, error);
-    cuda_check(cudaGetLastError());
 }
 
 void moe_return_peer(const void* out_pool_bf16, const uint8_t* recv_rows, const int* pool_of_recv, const int* totals,
@@ -641,10 +669,9 @@ void moe_return_peer(const void* out_pool_bf16, const uint8_t* recv_rows, const 
         if (!peer_slots[r]) throw std::invalid_argument("moe return_peer: null peer buffer");
         slots.ptr[r] = peer_slots[r];
     }
-    return_peer_kernel<<<recv_capacity, 128, 0, stream>>>(static_cast<const uint4*>(out_pool_bf16), recv_rows, pool_of_recv,
+    launch_chained(return_peer_kernel, dim3(recv_capacity), dim3(128), size_t(0), stream, static_cast<const uint4*>(out_pool_bf16), recv_rows, pool_of_recv,
                                                           totals, seg_src_offset, world * local_experts, local_experts,
                                                           hidden, slots, slot_capacity, error);
-    cuda_check(cudaGetLastError());
 }
 
 void moe_quantise_route(const void* x_bf16, const long long* ids, const float* weights, int tokens, int topk, int hidden,
@@ -667,11 +694,10 @@ void moe_quantise_route(const void* x_bf16, const long long* ids, const float* w
         throw std::invalid_argument("moe quantise_route: null pool");
     }
     const size_t smem = ((size_t(hidden) / 2 + hidden / 16 + 15) & ~size_t(15)) + size_t(topk) * sizeof(int);
-    quantise_route_kernel<<<tokens, 256, smem, stream>>>(static_cast<const __nv_bfloat16*>(x_bf16), ids, weights, topk, hidden,
+    launch_chained(quantise_route_kernel, dim3(tokens), dim3(256), size_t(smem), stream, static_cast<const __nv_bfloat16*>(x_bf16), ids, weights, topk, hidden,
                                                         experts, offsets, cursor, recv, meta, peer_meta ? 1 : 0, world,
                                                         local_experts, recv_capacity, error, pool_packed, pool_scales,
                                                         pool_weight, route_row);
-    cuda_check(cudaGetLastError());
 }
 
 // One CTA per 128 pool rows: if the rows belong to a live block, clear their scale bytes (whole atoms, one
@@ -681,6 +707,7 @@ void moe_quantise_route(const void* x_bf16, const long long* ids, const float* w
 __global__ void __launch_bounds__(256)
 clear_live_kernel(const int* __restrict__ num_blocks, int block_rows, int hidden, uint8_t* __restrict__ pool_scales,
                   float* __restrict__ pool_weight, int* __restrict__ pool_dst) {
+    chain_point();
     const int row0 = blockIdx.x * 128;
     if (row0 >= *num_blocks * block_rows) return;
     const size_t bytes = size_t(hidden / 64) * 512;            // the scale atoms of 128 rows
@@ -698,10 +725,9 @@ void moe_unpack_meta(const uint8_t* side, int recv_count_capacity, const int* to
     check_hidden(hidden, "moe unpack_meta");
     if (recv_count_capacity <= 0) return;
     if (!side || !pool_scales || !pool_weight || !pool_dst) throw std::invalid_argument("moe unpack_meta: null pointer");
-    unpack_meta_kernel<<<(size_t(recv_count_capacity) * 32 + 255) / 256, 256, 0, stream>>>(
+    launch_chained(unpack_meta_kernel, dim3((size_t(recv_count_capacity) * 32 + 255) / 256), dim3(256), size_t(0), stream, 
         side, totals, world * local_experts, hidden, seg_src_offset, seg_pool_offset, pool_scales, pool_weight, pool_dst,
         local_experts);
-    cuda_check(cudaGetLastError());
 }
 
 void moe_clear_live(const int* num_blocks, int block_rows, int pool_rows, int hidden, uint8_t* pool_scales,
@@ -709,8 +735,7 @@ void moe_clear_live(const int* num_blocks, int block_rows, int pool_rows, int hi
     check_hidden(hidden, "moe clear_live");
     if (!num_blocks || !pool_scales || !pool_weight || pool_rows <= 0 || pool_rows % 128 || (block_rows != 128 && block_rows != 256))
         throw std::invalid_argument("moe clear_live: bad argument");
-    clear_live_kernel<<<pool_rows / 128, 256, 0, stream>>>(num_blocks, block_rows, hidden, pool_scales, pool_weight, pool_dst);
-    cuda_check(cudaGetLastError());
+    launch_chained(clear_live_kernel, dim3(pool_rows / 128), dim3(256), size_t(0), stream, num_blocks, block_rows, hidden, pool_scales, pool_weight, pool_dst);
 }
 
 int moe_payload_bytes(int hidden) { return payload_bytes(hidden); }
@@ -742,6 +767,7 @@ constexpr size_t PEER_STATE_HEADER = offsetof(PeerState, payload);
 __global__ void peer_exchange_kernel(PeerState* own, PeerState* const* peers, int world, int rank,
                                      const int* __restrict__ payload, int ints, int max_ints, int* __restrict__ out,
                                      uint32_t* status, const long long* __restrict__ ids, int routes) {
+    chain_point();
     extern __shared__ int histogram[];                          // [ints], only when ids are given
     __shared__ uint32_t next_epoch;
     __shared__ int failed;
@@ -806,10 +832,9 @@ void peer_exchange(void* own, void* const* peers_device, int world, int rank, co
     if (ids && (ints < 1 || ints > 4096 || routes < 0)) throw std::invalid_argument("peer exchange: a histogram needs 1..4096 bins");
     int device = 0;
     cuda_check(cudaGetDevice(&device));
-    peer_exchange_kernel<<<1, 256, ids ? size_t(ints) * sizeof(int) : 0, stream>>>(
+    launch_chained(peer_exchange_kernel, dim3(1), dim3(256), size_t(ids ? size_t(ints) * sizeof(int) : 0), stream, 
         static_cast<PeerState*>(own), reinterpret_cast<PeerState* const*>(peers_device), world, rank, payload, ints, max_ints, out,
         device_status_word(device), ids, routes);
-    cuda_check(cudaGetLastError());
 }
 
 }  // namespace nvfp4_b200

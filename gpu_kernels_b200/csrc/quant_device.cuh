@@ -153,7 +153,7 @@ __device__ __forceinline__ uint32_t quantise_block_pairs(const uint32_t (&w)[8],
     using pair = typename F::pair;
     uint32_t a[8];
     #pragma unroll
-    for (int k = 0; k < 8; ++k) a[k] = w[k] & 0x7FFF7FFFu;
+    for (int k = 0; k < 8; ++k) a[k] = F::bits(__habs2(F::from_bits(w[k])));   // folds into the users' operand modifiers
     // magnitudes of these formats order like their bit patterns
     uint32_t m = __vimax3_u16x2(__vimax3_u16x2(a[0], a[1], a[2]), __vimax3_u16x2(a[3], a[4], a[5]), __vimax3_u16x2(a[6], a[7], a[7]));
     const uint32_t top = max(m & 0xFFFFu, m >> 16);
