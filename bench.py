@@ -735,8 +735,12 @@ class MoeBench:
         rel = float(np.linalg.norm(got - ref) / max(np.linalg.norm(ref), 1e-30))
         worst = float(np.abs(got - ref).max() / max(np.sqrt((ref ** 2).mean()), 1e-30))
         ok = rel <= LAYER_REL_FROBENIUS and worst <= LAYER_MAX_ABS_OVER_RMS
+        rms = float(np.sqrt((ref ** 2).mean()))
+        ok = ok and rms > 0.0                                   # an all-zero reference would prove nothing
         return bool(ok), {"tokens_checked": len(sample), "experts_rebuilt": len(cache), "rel_frobenius": rel,
-                          "max_abs_over_rms": worst, "bound": [LAYER_REL_FROBENIUS, LAYER_MAX_ABS_OVER_RMS]}
+                          "max_abs_over_rms": worst, "bound": [LAYER_REL_FROBENIUS, LAYER_MAX_ABS_OVER_RMS],
+                          "reference_rms": rms, "output_rms": float(np.sqrt((got ** 2).mean())),
+                          "outputs_equal_to_the_oracle": float((got == ref).mean())}
 
     def run(self, workload, sampler, main):
         import torch

@@ -374,26 +374,49 @@ __global__ void return_rows_kernel(const uint4* __restrict__ out_pool, const int
 
 // y[t] = bf16(sum over j of fp32(row of route (t, j))), j ascending: the order of the reference's
 // reduce kernel (kernels/moe/fused/sm90.cu:125-133). A dropped route (expert id outside [0, experts), or a
-// negative row index) adds nothing.
-__global__ void reduce_kernel(const uint4* __restrict__ returned, const int* __restrict__ send_pos, int topk,
-                              int row_vec, uint4* __restrict__ y, const long long* __restrict__ ids, int experts) {
+// negative row index) adds nothing. TOPK > 0: the route count as a compile-time constant, so that a thread has
+// all of a column's loads in flight before it adds them up (the kernel only moves bytes: 16 bytes x TOPK in
+// flight per thread is what brings it near the memory's speed); TOPK = 0: any count, one load at a time.
+template <int TOPK>
+__global__ void __launch_bounds__(256)
+reduce_kernel(const uint4* __restrict__ returned, const int* __restrict__ send_pos, int topk,
+              int row_vec, uint4* __restrict__ y, const long long* __restrict__ ids, int experts) {
     chain_point();
     const int t = blockIdx.x;
+    constexpr int SLOTS = TOPK > 0 ? TOPK : 1;
+    const int count = TOPK > 0 ? TOPK : topk;
+    __shared__ int rows[64];                                     // row of every route of this token, -1 = skip
+    for (int j = threadIdx.x; j < count && j < 64; j += blockDim.x) {
+        int pos = send_pos[t * count + j];
+        if (ids) {
+            const long long id = ids[t * count + j];
+            if (id < 0 || id >= experts) pos = -1;
+        }
+        rows[j] = pos;
+    }
+    __syncthreads();
     for (int i = threadIdx.x; i < row_vec; i += blockDim.x) {
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        for (int j = 0; j < topk; ++j) {
-            const int pos = send_pos[t * topk + j];
-            if (pos < 0) continue;
-            if (ids) {
-                const long long id = ids[t * topk + j];
-                if (id < 0 || id >= experts) continue;
-            }
-            const uint4 v = __ldg(returned + size_t(pos) * row_vec + i);
+        auto add = [&](const uint4& v) {
             const uint32_t w[4] = {v.x, v.y, v.z, v.w};
             #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 acc[2 * q] += __uint_as_float(w[q] << 16);
                 acc[2 * q + 1] += __uint_as_float(w[q] & 0xFFFF0000u);
+            }
+        };
+        if constexpr (TOPK > 0) {
+            uint4 v[SLOTS];
+            #pragma unroll
+            for (int j = 0; j < SLOTS; ++j)
+                v[j] = rows[j] >= 0 ? __ldg(returned + size_t(rows[j]) * row_vec + i) : make_uint4(0u, 0u, 0u, 0u);
+            #pragma unroll
+            for (int j = 0; j < SLOTS; ++j)
+                if (rows[j] >= 0) add(v[j]);                     // a skipped route adds nothing, not even +0
+        } else {
+            for (int j = 0; j < count; ++j) {
+                const int pos = j < 64 ? rows[j] : -1;
+                if (pos >= 0) add(__ldg(returned + size_t(pos) * row_vec + i));
             }
         }
         uint32_t o[4];
@@ -637,8 +660,19 @@ void moe_reduce(const void* returned_bf16, const int* send_pos, int tokens, int 
                 const long long* ids, int experts, cudaStream_t stream) {
     check_hidden(hidden, "moe reduce");
     if (tokens <= 0) return;
-    launch_chained(reduce_kernel, dim3(tokens), dim3(128), size_t(0), stream, static_cast<const uint4*>(returned_bf16), send_pos, topk, hidden / 8,
-                                              static_cast<uint4*>(y_bf16), ids, experts);
+    if (topk < 1 || topk > 64) throw std::invalid_argument("moe reduce: 1..64 routes per token");
+    auto go = [&](auto kernel) {
+        launch_chained(kernel, dim3(tokens), dim3(256), size_t(0), stream, static_cast<const uint4*>(returned_bf16), send_pos, topk,
+                       hidden / 8, static_cast<uint4*>(y_bf16), ids, experts);
+    };
+    switch (topk) {
+        case 1: go(reduce_kernel<1>); break;
+        case 2: go(reduce_kernel<2>); break;
+        case 4: go(reduce_kernel<4>); break;
+        case 6: go(reduce_kernel<6>); break;
+        case 8: go(reduce_kernel<8>); break;
+        default: go(reduce_kernel<0>); break;
+    }
 }
 
 void moe_pack_peer(const uint8_t* xq, const uint8_t* xs, const long long* ids, const float* weights, int tokens,
