@@ -801,7 +801,9 @@ constexpr size_t PEER_STATE_HEADER = offsetof(PeerState, payload);
 __global__ void peer_exchange_kernel(PeerState* own, PeerState* const* peers, int world, int rank,
                                      const int* __restrict__ payload, int ints, int max_ints, int* __restrict__ out,
                                      uint32_t* status, const long long* __restrict__ ids, int routes) {
-    chain_point();
+    // No chain_point() here, and an ordinary launch: the kernels in front of a barrier store into other GPUs'
+    // memory, and only the ordinary end of a kernel (not the early start of its dependent) is what makes those
+    // stores complete before this kernel tells the peers so.
     extern __shared__ int histogram[];                          // [ints], only when ids are given
     __shared__ uint32_t next_epoch;
     __shared__ int failed;
@@ -866,9 +868,9 @@ void peer_exchange(void* own, void* const* peers_device, int world, int rank, co
     if (ids && (ints < 1 || ints > 4096 || routes < 0)) throw std::invalid_argument("peer exchange: a histogram needs 1..4096 bins");
     int device = 0;
     cuda_check(cudaGetDevice(&device));
-    launch_chained(peer_exchange_kernel, dim3(1), dim3(256), size_t(ids ? size_t(ints) * sizeof(int) : 0), stream, 
-        static_cast<PeerState*>(own), reinterpret_cast<PeerState* const*>(peers_device), world, rank, payload, ints, max_ints, out,
+    peer_exchange_kernel<<<1, 256, ids ? size_t(ints) * sizeof(int) : 0, stream>>>(static_cast<PeerState*>(own), reinterpret_cast<PeerState* const*>(peers_device), world, rank, payload, ints, max_ints, out,
         device_status_word(device), ids, routes);
+    cuda_check(cudaGetLastError());
 }
 
 }  // namespace nvfp4_b200
