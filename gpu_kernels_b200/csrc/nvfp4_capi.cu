@@ -105,6 +105,7 @@ struct Plan {
     gpu_kernels::Nvfp4Implementation impl{};
     const void* sfa = nullptr;
     const void* sfb = nullptr;
+    const void* b = nullptr;
     void* workspace = nullptr;
     size_t workspace_bytes = 0;
     std::unique_ptr<LtMatmul> lt;
@@ -211,6 +212,7 @@ int gpu_kernels_nvfp4_plan_create(void** out, int M, int N, int K, const void* A
                            static_cast<cudaStream_t>(stream));
         plan->sfa = SFA;
         plan->sfb = SFB;
+        plan->b = B;
         plan->workspace = workspace;
         plan->workspace_bytes = workspace_bytes;
         plan->whole_tile_units = plan->params.clusters;
@@ -301,6 +303,11 @@ int gpu_kernels_nvfp4_plan_set_option(void* plan, const char* key, int value) {
         } else if (std::strcmp(key, "k_skew") == 0) {
             if (value < 0) throw std::invalid_argument("set_option: k_skew must be >= 0");
             p.params.k_skew = value;
+        } else if (std::strcmp(key, "ragged_tiles") == 0) {
+            // value tiles over the plan's one tile row (0 = uniform 256-column tiles); refused where it does not apply
+            if (!gpu_kernels::nvfp4_set_ragged_tiles(p.params, static_cast<const uint8_t*>(p.b), value) && value)
+                throw std::invalid_argument("set_option: ragged_tiles needs M = 128, N a multiple of 64 and 2 to 4 units of 64 "
+                                            "columns per tile, more tiles than N / 256");
         } else if (std::strcmp(key, "pdl") == 0) {
             p.params.pdl = value ? 1 : 0;
         } else if (std::strcmp(key, "static_operands") == 0) {
@@ -347,7 +354,8 @@ int gpu_kernels_nvfp4_plan_info(void* plan, int* info) {
         const auto& q = p.params;
         const int values[16] = {q.M, q.N, q.K, q.clusters, q.cta_group, q.tile_n, q.group_m,
                                 nvfp4_b200::gemm_stage_count(q.cta_group, q.tile_n, q.direct_store), q.split_k, q.k_skew,
-                                q.direct_store, q.out_bf16, q.route ? 1 : 0, q.side_units[0], q.side_units[1], q.status_slot};
+                                q.direct_store, q.out_bf16, q.route ? 1 : 0, q.side_units[0], q.side_units[1],
+                                q.ragged_units};
         std::memcpy(info, values, sizeof(values));
     });
 }

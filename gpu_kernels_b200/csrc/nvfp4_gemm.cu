@@ -68,6 +68,7 @@ enum Epi : int {
     EPI_GATHER_TMA = 5,    // the slab to every rank's full C by TMA stores
     EPI_GATHER_DIRECT = 6, // the same with register stores
     EPI_SPLIT_K = 7,       // FP32 partial sums + finish (to C or to every rank's full C)
+    EPI_DIRECT_RAGGED = 8, // EPI_DIRECT on single-CTA tiles of unequal width (see GemmArgs::ragged_base)
 };
 
 template <int CG, int UN, int EPI>
@@ -100,7 +101,10 @@ struct Config {
     // accumulator leaves in half the time, which is what bounds tiles with a short K loop and the tail of a
     // launch with one tile per CTA. The routes that stage in shared memory keep one warp per quarter (a second
     // set of staging buffers would cost a ring stage), as does split-K.
-    static constexpr int EPI_WARPS = (EPI == EPI_DIRECT || EPI == EPI_ACT || EPI == EPI_SCATTER || EPI == EPI_GATHER_DIRECT) ? 8 : 4;
+    static constexpr int EPI_WARPS = (EPI == EPI_DIRECT || EPI == EPI_ACT || EPI == EPI_SCATTER || EPI == EPI_GATHER_DIRECT ||
+                                      EPI == EPI_DIRECT_RAGGED) ? 8 : 4;
+    static constexpr bool RAGGED = EPI == EPI_DIRECT_RAGGED;
+    static_assert(!RAGGED || (CG == 1 && UN == 256), "ragged tiles are single-CTA tiles of up to 256 columns");
     static constexpr int THREADS = (2 + EPI_WARPS) * 32;        // warps 0-3 epilogue, 4 MMA, 5 producer, 6-9 epilogue
     static constexpr int ROW_PITCH = UN * 2 + 16;
     static constexpr int EPI_BYTES = ROW_STAGING ? 4 * 32 * ROW_PITCH : STAGED_EPILOGUE ? 4 * 2 * EPI_WARP_BYTES : 0;
@@ -200,7 +204,25 @@ struct GemmArgs {
     // stages of B are requested before the wait; 2 = none of the operands: only the epilogue waits, before its
     // first store, so the tiles of this launch run while the tail of the previous one drains.
     int static_operands;
+    // EPI_DIRECT_RAGGED (one tile row, M = 128): the N columns are dealt to exactly as many tiles as there are
+    // SMs, in units of 64 columns: the first ragged_extra tiles are ragged_base + 1 units wide, the others
+    // ragged_base (2 or 3), so that no SM is left without a tile when N / 256 is smaller than the SM count. B is
+    // fetched in 64-row boxes; a tile's scale atoms are the two 128-row blocks its columns lie in, and the MMA
+    // reads them from the column (n0 % 128) / 32 on.
+    int ragged_base, ragged_extra;
 };
+
+// First column and width of tile tn of a ragged row of tiles.
+__device__ __forceinline__ void ragged_span(const GemmArgs& g, int tn, int& n0, int& width) {
+    const int wide = g.ragged_base + 1;
+    if (tn < g.ragged_extra) {
+        n0 = tn * wide * 64;
+        width = wide * 64;
+    } else {
+        n0 = (g.ragged_extra * wide + (tn - g.ragged_extra) * g.ragged_base) * 64;
+        width = g.ragged_base * 64;
+    }
+}
 
 struct Segment {
     uint32_t tile, item;            // item = position in the work sequence (tile * S + slice)
@@ -312,9 +334,19 @@ struct Roles {
             int tm, tn, b_base;
             tile_coords(int(t), g, tm, tn, b_base);
             const int a_row = tm * Cfg::TILE_M + int(rank) * BLOCK_M;
-            const int b_row = b_base + tn * UN + int(rank) * Cfg::B_ROWS;
+            int b_row = b_base + tn * UN + int(rank) * Cfg::B_ROWS;
             const int sfa_block = a_row / 128;
-            const int sfb_block = (b_base + tn * UN) / 128;
+            int sfb_block = (b_base + tn * UN) / 128;
+            int b_boxes = 1;                                    // 64-row boxes of B per stage (ragged tiles only)
+            uint32_t stage_bytes = Cfg::STAGE_BYTES;
+            if constexpr (Cfg::RAGGED) {
+                int n0, width;
+                ragged_span(g, tn, n0, width);
+                b_row = n0;
+                sfb_block = n0 / 128;
+                b_boxes = width / 64;
+                stage_bytes = Cfg::A_BYTES + uint32_t(width) * ROW_BYTES + Cfg::SFA_BYTES + Cfg::SFB_BYTES;
+            }
             // whole tiles may start anywhere in K and wrap; slices of a tile are walked in order
             const int k_first = (g.k_skew && g.split_k <= 1) ? int((t * uint32_t(g.k_skew)) % uint32_t(ksteps)) : 0;
             for (int step = seg.k0; step < seg.k1; ++step) {
@@ -332,12 +364,17 @@ struct Roles {
                 if (split_issue) held[issued] = {ks, a_row, sfa_block};
                 if constexpr (CG == 1) {
                     if (elect_one()) {
-                        mbar_arrive_expect_tx(own_full, Cfg::STAGE_BYTES);
+                        mbar_arrive_expect_tx(own_full, stage_bytes);
                         if (!split_issue) {
                             tma_load_2d(base, tmA, ks * ROW_BYTES, a_row, own_full);
                             tma_load_3d(base + Cfg::OFF_SFA, tmSFA, 0, ks * 16, sfa_block, own_full);
                         }
-                        tma_load_2d(base + Cfg::OFF_B, tmB, ks * ROW_BYTES, b_row, own_full);
+                        if constexpr (Cfg::RAGGED) {
+                            for (int u = 0; u < b_boxes; ++u)
+                                tma_load_2d(base + Cfg::OFF_B + u * (64 * ROW_BYTES), tmB, ks * ROW_BYTES, b_row + 64 * u, own_full);
+                        } else {
+                            tma_load_2d(base + Cfg::OFF_B, tmB, ks * ROW_BYTES, b_row, own_full);
+                        }
                         #pragma unroll
                         for (int b = 0; b < Cfg::SFB_BLOCKS; ++b)
                             tma_load_3d(base + Cfg::OFF_SFB + b * Cfg::SFB_BLOCK_BYTES, tmSFB, 0, ks * 16,
@@ -419,6 +456,14 @@ struct Roles {
         Segment seg;
         for (; walk.get(seg); ++iter) {
             const uint32_t acc = tmem + (iter & 1u) * Cfg::ACC_STRIDE;
+            uint32_t idesc = Cfg::IDESC, sfb_shift = 0;
+            if constexpr (Cfg::RAGGED) {
+                int tm, tn, b_base, n0, width;
+                tile_coords(int(seg.tile), g, tm, tn, b_base);
+                ragged_span(g, tn, n0, width);
+                idesc = (1u << 7) | (1u << 10) | (uint32_t(width >> 3) << 17) | (uint32_t(Cfg::TILE_M >> 4) << 24);
+                sfb_shift = uint32_t(n0 % 128) / 32u;           // the tile's first row inside its first scale atom
+            }
             unsigned long long* tr = nullptr;
             if (PROF && unit == 0 && lane == 0 && iter > 0 && iter <= TR_TILES)
                 tr = g.prof + size_t(units) * CG * PROF_WORDS + size_t(iter - 1) * 8;
@@ -452,7 +497,7 @@ struct Roles {
                     // K advances 32 bytes inside the 128-byte swizzled row per MMA.
                     const uint32_t sf = sf_tmem + j * Cfg::SF_COLS_PER_MMA;
                     mma_nvfp4<CG>(acc, lo + ((j * (MMA_K / 2)) >> 4), lo + ((Cfg::OFF_B + j * (MMA_K / 2)) >> 4),
-                                  OPERAND_HI, Cfg::IDESC, sf, sf + 4, j != 0 ? 1u : first);
+                                  OPERAND_HI, idesc, sf, sf + 4 + sfb_shift, j != 0 ? 1u : first);
                 };
                 const bool handover = ks == seg.k0 && iter > 0;
                 if (handover) {
@@ -615,7 +660,12 @@ struct Roles {
             int tm, tn, b_base;
             tile_coords(int(t), g, tm, tn, b_base);
             const int row0 = tm * Cfg::TILE_M + int(rank) * BLOCK_M + warp * 32;
-            const int col0 = tn * UN;
+            int col0 = tn * UN, chunks = UN / EPI_COLS;
+            if constexpr (Cfg::RAGGED) {
+                int width;
+                ragged_span(g, tn, col0, width);
+                chunks = width / EPI_COLS;
+            }
             // The whole warp leaves together: the Tensor Memory loads below are warp-collective.
             const long long w0 = now();
             const bool ready = wait(&ctrl->acc_full, iter & 1u, lane == 0 ? STATUS_TIMEOUT_EPILOGUE : 0u, 0x30000000u | iter);
@@ -635,10 +685,10 @@ struct Roles {
                 if (lane == 0) mbar_arrive_cluster(acc_free_leader);
             }
             #pragma unroll 1
-            for (int c = 0; c < UN / EPI_COLS; ++c) {
+            for (int c = 0; c < chunks; ++c) {
                 if (Cfg::EPI_WARPS == 8 && (c & 1) != half) continue;
                 // Columns shared with the other accumulator go first: top of buffer 0, bottom of buffer 1.
-                const int chunk = (iter & 1u) ? c : UN / EPI_COLS - 1 - c;
+                const int chunk = (iter & 1u) ? c : chunks - 1 - c;
                 uint32_t v[EPI_COLS];
                 tmem_ld_32x32(acc + chunk * EPI_COLS, v);
                 tmem_ld_32x32(acc + chunk * EPI_COLS + 32, v + 32);
@@ -729,7 +779,7 @@ struct Roles {
                     for (int r = 0; r < g.gather_world; ++r)
                         store_row_chunk(reinterpret_cast<uint16_t*>(__ldg(reinterpret_cast<const unsigned long long*>(g.gather_ptrs) + r)) + at,
                                         v, alpha, true);
-                } else if constexpr (EPI == EPI_DIRECT) {
+                } else if constexpr (EPI == EPI_DIRECT || EPI == EPI_DIRECT_RAGGED) {
                     store_row_chunk(static_cast<uint16_t*>(g.c) + size_t(row0 + lane) * g.ldc + col0 + chunk * EPI_COLS, v, alpha, true);
                 } else {
                     // EPI_TMA / EPI_GATHER_TMA: the chunk goes through one of the warp's two swizzled buffers
@@ -1016,6 +1066,22 @@ uint32_t* status_slot(int device, int slot) { return status_base(device) + size_
 
 std::atomic<unsigned> g_next_slot{0};
 
+// Ragged tiling of a one-tile-row plan over `tiles` single-CTA tiles (see GemmArgs::ragged_base); tiles = 0
+// switches it off. Returns whether the plan now uses it: M = 128, single-CTA 256-column variant, the widths
+// come out as 2/3 or 3/4 units of 64 columns, and it is more tiles than the uniform tiling has.
+bool set_ragged_tiles(gpu_kernels::Nvfp4Params& p, const uint8_t* B, int tiles) {
+    p.ragged_base = p.ragged_extra = p.ragged_units = 0;
+    if (tiles <= 0 || !B) return false;
+    if (p.M != 128 || p.cta_group != 1 || p.tile_n != 256 || p.N % 64) return false;
+    const int units = p.N / 64, base = units / tiles, extra = units % tiles;
+    if ((base != 2 && base != 3) || tiles <= p.N / 256) return false;
+    p.B64 = operand_map(B, p.N, p.K, 64);
+    p.ragged_base = base;
+    p.ragged_extra = extra;
+    p.ragged_units = tiles;
+    return true;
+}
+
 void prepare(gpu_kernels::Nvfp4Params& p, const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB,
              int M, int N, int K, cudaStream_t) {
     require_sm100();
@@ -1060,6 +1126,9 @@ void prepare(gpu_kernels::Nvfp4Params& p, const uint8_t* A, const uint8_t* B, co
     p.group_m = std::max(1, std::min(env_int("NVFP4_B200_GROUP_M", gm), M / (128 * p.cta_group)));
     // Measured: 128x28672x8192 30.2 -> 28.9 us, 8192^3 199.8 -> 199.0 us with the tiles' K walks de-phased.
     p.k_skew = env_int("NVFP4_B200_K_SKEW", 11);
+    // One tile row whose 256-column tiles would leave SMs idle: deal the columns, in units of 64, to as many
+    // tiles as there are SMs (128x28672x8192: 112 tiles of 256 columns become 4 of 256 and 144 of 192).
+    if (env_int("NVFP4_B200_RAGGED", 1)) set_ragged_tiles(p, B, fit_units(device, 1, 256));
     p.pdl = env_int("NVFP4_B200_PDL", 1);
     p.status_slot = 1 + int(g_next_slot.fetch_add(1, std::memory_order_relaxed) % unsigned(STATUS_SLOTS - 1));
     (void)status_base(device);
@@ -1183,6 +1252,15 @@ void launch_dense(const gpu_kernels::Nvfp4Params& p, const CUtensorMap& tmC, con
         // those far better than 32-byte register stores (8192^3 on two GPUs: 141 against 264 us per step).
         if constexpr (CG == 2) return launch_instance<CG, UN, EPI_GATHER_TMA>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream, pdl);
         launch_instance<CG, UN, EPI_GATHER_DIRECT>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream, pdl);
+    } else if (CG == 1 && UN == 256 && p.ragged_units > 0 && !g.prof) {
+        if constexpr (CG == 1 && UN == 256) {
+            GemmArgs r = g;
+            r.tiles_m = 1;
+            r.tiles_n = p.ragged_units;
+            r.ragged_base = p.ragged_base;
+            r.ragged_extra = p.ragged_extra;
+            launch_instance<1, 256, EPI_DIRECT_RAGGED>(dev, p.ragged_units, p.A, p.B64, p.SFA, p.SFB, tmC, r, stream, pdl);
+        }
     } else if (g.prof) {
         if constexpr (CG == 2) {
             if (staged) return launch_instance<CG, UN, EPI_TMA, true>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream, pdl);
@@ -1406,6 +1484,8 @@ void nvfp4_set_gather(Nvfp4Params& p, void* const* buffers, int world, int col0,
                       cudaStream_t stream) {
     nvfp4_b200::set_gather(p, buffers, world, col0, n_total, table, stream);
 }
+
+bool nvfp4_set_ragged_tiles(Nvfp4Params& p, const uint8_t* B, int tiles) { return nvfp4_b200::set_ragged_tiles(p, B, tiles); }
 
 bool nvfp4_set_l2_side_order(Nvfp4Params& p, int on, cudaStream_t stream) {
     p.route = p.sm_side = p.unit_side = nullptr;

@@ -59,7 +59,7 @@ class Nvfp4Gemm:
         buf = (ctypes.c_int * 16)()
         _lib.check(_lib.load().gpu_kernels_nvfp4_plan_info(self._plan, buf))
         keys = ("M", "N", "K", "units", "cta_group", "tile_n", "group_m", "stages", "split_k", "k_skew",
-                "direct_store", "out_bf16", "l2_side", "side0_units", "side1_units", "status_slot")
+                "direct_store", "out_bf16", "l2_side", "side0_units", "side1_units", "ragged_tiles")
         return dict(zip(keys, list(buf)))
 
     def placement_misses(self) -> int:

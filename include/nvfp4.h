@@ -59,6 +59,11 @@ struct Nvfp4Params {
     // write B or SFB (weights): their first tiles are fetched while it drains; 2 = it writes none of A, B, SFA,
     // SFB: this launch computes while it drains and only holds back its stores of C until it has finished.
     int static_operands;
+    // Ragged tiling of a one-tile-row plan (M = 128) whose 256-column tiles would leave SMs without a tile:
+    // ragged_units tiles (0 = off), the first ragged_extra of them ragged_base + 1 units of 64 columns wide, the
+    // others ragged_base; B64 is B's tensor map with 64-row boxes.
+    CUtensorMap B64;
+    int ragged_base, ragged_extra, ragged_units;
 };
 
 struct Nvfp4Implementation {
@@ -84,6 +89,11 @@ void nvfp4_set_alpha(Nvfp4Params&, float alpha);
 // Extension: synchronises the device and throws if a launch of THIS plan reported an error since the last
 // check of this plan; other plans' reports are left alone.
 void nvfp4_validate_plan(const Nvfp4Params&);
+
+// Extension: ragged tiling for plans with one tile row (M = 128) whose uniform 256-column tiles number fewer
+// than the SMs (prepare switches it on by itself for such shapes, with as many tiles as SMs). B: the pointer
+// the plan was prepared with. tiles = 0 returns to uniform tiles. Returns whether ragged tiles are in use.
+bool nvfp4_set_ragged_tiles(Nvfp4Params&, const uint8_t* B, int tiles);
 
 // Extension: L2-side-aware tile order, the counterpart of the reference's prepare_schedule
 // (kernels/gemm/matmul/sm100.cu:566-673). B200's L2 has two sides; an SM reaches the far one more slowly.

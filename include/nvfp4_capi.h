@@ -58,6 +58,9 @@ int gpu_kernels_nvfp4_dequantize(const void* packed, const void* scales, void* o
 int gpu_kernels_nvfp4_plan_set_alpha(void* plan, float alpha);
 /* Tuning knobs. key: "group_m" (tile rows per rasterisation band, >= 1); "c_evict_first" (0/1: L2 policy
  * of the C stores); "direct_store" (0/1: epilogue writes C from registers instead of staging it for TMA stores);
+ * "ragged_tiles" (T: deal the columns of a plan with M = 128, in units of 64, to T single-CTA tiles of two widths
+ * (2/3 or 3/4 units) instead of N/256 tiles of 256 columns; plan_create does this by itself, with T = the SM count,
+ * where N/256 tiles would leave SMs idle; 0 = uniform tiles);
  * "pdl" (0/1, default 1: launches carry the programmatic stream-serialisation attribute, so that this kernel's
  * set-up overlaps the tail of the kernel in front of it in the stream; 0 = ordinary launches);
  * "static_operands" (0/1/2, default 0: the caller's promise about the kernel that runs in front of each launch
@@ -88,7 +91,7 @@ int gpu_kernels_nvfp4_plan_set_option(void* plan, const char* key, int value);
  * off. Not inside stream capture (synchronises once). */
 int gpu_kernels_nvfp4_plan_set_gather(void* plan, void* const* buffers, int world, int col0, int n_total);
 /* Fills info[0..15] = {M, N, K, units, cta_group, tile_n, group_m, stages, split_k, k_skew, direct_store,
- * out_bf16, l2_side order in use, clusters on L2 side 0, on side 1, status slot}. */
+ * out_bf16, l2_side order in use, clusters on L2 side 0, on side 1, ragged tiles (0 = uniform tiling)}. */
 int gpu_kernels_nvfp4_plan_info(void* plan, int* info);
 
 /* With the "l2_side" order: how many clusters, summed over this plan's launches, found themselves on the

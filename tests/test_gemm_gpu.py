@@ -110,6 +110,46 @@ def test_k_multiple_of_64_against_oracle(g, m, n, k, variant):
     assert_gemm_close(out, ref, f"K tail {m}x{n}x{k}")
 
 
+@pytest.mark.parametrize("n,k,tiles", [(1280, 1024, 6), (1536, 512, 10), (2304, 2240, 10), (28672, 512, 148)])
+def test_ragged_tiles_of_a_single_tile_row(g, n, k, tiles):
+    # M = 128: the columns dealt, in units of 64, to `tiles` single-CTA tiles of two widths (256 + 192 or 192 + 128)
+    # instead of N / 256 tiles of 256 (N a multiple of 256 here: the plan must be of the 256-column kind). Tile starts that are not multiples of 128 read their scale atoms from a
+    # column offset. With every tile walking K from 0 the accumulation order per output is the uniform tiling's:
+    # bit-identical; with the default K walk: within the bound.
+    m = 128
+    pa, sa = g.quantize(random_operand(m, k, seed=400 + n))
+    pb, sb = g.quantize(random_operand(n, k, seed=401 + n, scale=0.02))
+    ref = g.dequantize(pa, sa) @ g.dequantize(pb, sb).T
+    plan = g.Nvfp4Gemm(pa, pb, sa, sb)
+    plan.set_option("ragged_tiles", 0)
+    plan.set_option("k_skew", 0)
+    uniform = plan.run(nan_output(m, n)).clone()
+    assert plan.info()["ragged_tiles"] == 0
+    try:
+        plan.set_option("ragged_tiles", tiles)
+    except RuntimeError:
+        if tiles > torch.cuda.get_device_properties(0).multi_processor_count:
+            pytest.skip("more tiles than this device has SMs")
+        raise
+    assert plan.info()["ragged_tiles"] == tiles
+    ragged = plan.run(nan_output(m, n))
+    plan.validate()
+    assert not torch.isnan(ragged).any()
+    assert torch.equal(ragged, uniform)
+    plan.set_option("k_skew", 11)
+    assert_gemm_close(plan.run(nan_output(m, n)), ref, f"ragged tiles 128x{n}x{k}")
+    for mode in (1, 2):                                     # overlapping launch chains through the ragged route
+        plan.set_option("static_operands", mode)
+        plan.set_option("k_skew", 0)
+        outs = [plan.run(nan_output(m, n)) for _ in range(4)]
+        torch.cuda.synchronize()
+        assert all(torch.equal(o, uniform) for o in outs)
+    plan.validate()
+    with pytest.raises(RuntimeError):
+        plan.set_option("ragged_tiles", 1)                  # one tile cannot take the whole row
+    plan.close()
+
+
 def test_bf16_output(g):
     # the reference writes FP16 only (include/nvfp4.h:21); "out_bf16" makes the same launch write bfloat16
     for m, n, k in ((256, 512, 1024), (128, 384, 512), (512, 256, 4096)):
