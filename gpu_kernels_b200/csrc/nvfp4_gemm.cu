@@ -1126,9 +1126,12 @@ void prepare(gpu_kernels::Nvfp4Params& p, const uint8_t* A, const uint8_t* B, co
     p.group_m = std::max(1, std::min(env_int("NVFP4_B200_GROUP_M", gm), M / (128 * p.cta_group)));
     // Measured: 128x28672x8192 30.2 -> 28.9 us, 8192^3 199.8 -> 199.0 us with the tiles' K walks de-phased.
     p.k_skew = env_int("NVFP4_B200_K_SKEW", 11);
-    // One tile row whose 256-column tiles would leave SMs idle: deal the columns, in units of 64, to as many
-    // tiles as there are SMs (128x28672x8192: 112 tiles of 256 columns become 4 of 256 and 144 of 192).
-    if (env_int("NVFP4_B200_RAGGED", 1)) set_ragged_tiles(p, B, fit_units(device, 1, 256));
+    // One tile row whose 256-column tiles would leave SMs idle can deal its columns, in units of 64, to as many
+    // tiles as there are SMs (128x28672x8192: 112 tiles of 256 columns become 4 of 256 and 144 of 192): plan
+    // option "ragged_tiles". Off unless asked for: measured 27.9 against 28.3 us for dependent launches, but a
+    // launch that fills every SM leaves no room for the next launch of a chain to start early (independent
+    // launches: 28.5 against 24.7-26.1 us).
+    if (env_int("NVFP4_B200_RAGGED", 0)) set_ragged_tiles(p, B, fit_units(device, 1, 256));
     p.pdl = env_int("NVFP4_B200_PDL", 1);
     p.status_slot = 1 + int(g_next_slot.fetch_add(1, std::memory_order_relaxed) % unsigned(STATUS_SLOTS - 1));
     (void)status_base(device);

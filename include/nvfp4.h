@@ -91,7 +91,7 @@ void nvfp4_set_alpha(Nvfp4Params&, float alpha);
 void nvfp4_validate_plan(const Nvfp4Params&);
 
 // Extension: ragged tiling for plans with one tile row (M = 128) whose uniform 256-column tiles number fewer
-// than the SMs (prepare switches it on by itself for such shapes, with as many tiles as SMs). B: the pointer
+// than the SMs (off unless asked for). B: the pointer
 // the plan was prepared with. tiles = 0 returns to uniform tiles. Returns whether ragged tiles are in use.
 bool nvfp4_set_ragged_tiles(Nvfp4Params&, const uint8_t* B, int tiles);
 

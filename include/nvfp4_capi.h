@@ -59,8 +59,8 @@ int gpu_kernels_nvfp4_plan_set_alpha(void* plan, float alpha);
 /* Tuning knobs. key: "group_m" (tile rows per rasterisation band, >= 1); "c_evict_first" (0/1: L2 policy
  * of the C stores); "direct_store" (0/1: epilogue writes C from registers instead of staging it for TMA stores);
  * "ragged_tiles" (T: deal the columns of a plan with M = 128, in units of 64, to T single-CTA tiles of two widths
- * (2/3 or 3/4 units) instead of N/256 tiles of 256 columns; plan_create does this by itself, with T = the SM count,
- * where N/256 tiles would leave SMs idle; 0 = uniform tiles);
+ * (2/3 or 3/4 units) instead of N/256 tiles of 256 columns, e.g. T = the SM count where N/256 tiles would leave SMs idle; 0 = uniform
+ * tiles, the default);
  * "pdl" (0/1, default 1: launches carry the programmatic stream-serialisation attribute, so that this kernel's
  * set-up overlaps the tail of the kernel in front of it in the stream; 0 = ordinary launches);
  * "static_operands" (0/1/2, default 0: the caller's promise about the kernel that runs in front of each launch
