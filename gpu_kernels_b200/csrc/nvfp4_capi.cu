@@ -134,10 +134,12 @@ struct HostGemm {
     uint8_t *A = nullptr, *B = nullptr, *SFA = nullptr, *SFB = nullptr;
     __half* C = nullptr;
     Plan plan;
-    // Row pieces of the product, so that the copy of one piece's result to the host overlaps the next
-    // piece's operand copy and kernel (the two directions of the host link run at the same time).
-    std::vector<gpu_kernels::Nvfp4Params> pieces;
-    int piece_rows = 0;
+    // The product in row pieces x column pieces. Copies in and kernels go on the caller's stream in the order
+    // A piece 0, B piece 0, block (0,0), B piece 1, block (0,1), ..., A piece 1, block (1,0), ...; every block's
+    // result leaves on a second stream as soon as it is computed. So the first bytes of C travel back after one
+    // piece of each operand has arrived, and from then on both directions of the host link are busy.
+    std::vector<gpu_kernels::Nvfp4Params> pieces;      // [row piece][column piece]
+    int piece_rows = 0, piece_cols = 0, row_pieces = 0, col_pieces = 0;
     cudaStream_t out_stream = nullptr;
     std::vector<cudaEvent_t> piece_done;
     void release() {
@@ -149,7 +151,7 @@ struct HostGemm {
         piece_done.clear();
         pieces.clear();
         out_stream = nullptr;
-        piece_rows = 0;
+        piece_rows = piece_cols = row_pieces = col_pieces = 0;
         A = B = SFA = SFB = nullptr;
         C = nullptr;
         M = N = K = 0;
@@ -384,42 +386,64 @@ int gpu_kernels_nvfp4_gemm_host(int M, int N, int K, const void* A, const void* 
             cuda_check(cudaMalloc(&h.C, c_bytes));
             h.plan.impl = gpu_kernels::nvfp4_sm100_implementation();
             h.plan.impl.prepare(h.plan.params, h.A, h.B, h.SFA, h.SFB, M, N, K, stream);
-            // large products go in 4 (or 2) row pieces of whole 256-row tiles
-            const int count = (M >= 2048 && M % 1024 == 0) ? 4 : (M >= 1024 && M % 512 == 0) ? 2 : 1;
-            if (count > 1) {
-                h.piece_rows = M / count;
-                h.pieces.resize(count);
-                h.piece_done.resize(count);
+            // large products go in 4 (or 2) row pieces and as many column pieces, all of whole 256-wide tiles
+            auto split = [](int extent) { return (extent >= 2048 && extent % 1024 == 0) ? 4 : (extent >= 1024 && extent % 512 == 0) ? 2 : 1; };
+            const int rows_n = split(M), cols_n = rows_n > 1 ? split(N) : 1;
+            if (rows_n > 1) {
+                h.row_pieces = rows_n;
+                h.col_pieces = cols_n;
+                h.piece_rows = M / rows_n;
+                h.piece_cols = N / cols_n;
+                h.pieces.resize(size_t(rows_n) * cols_n);
+                h.piece_done.resize(h.pieces.size());
                 cuda_check(cudaStreamCreateWithFlags(&h.out_stream, cudaStreamNonBlocking));
-                for (int i = 0; i < count; ++i) {
-                    const size_t row0 = size_t(i) * h.piece_rows;
-                    h.plan.impl.prepare(h.pieces[i], h.A + row0 * K / 2, h.B, h.SFA + row0 * K / 16, h.SFB, h.piece_rows, N, K, stream);
-                    cuda_check(cudaEventCreateWithFlags(&h.piece_done[i], cudaEventDisableTiming));
-                }
+                for (int r = 0; r < rows_n; ++r)
+                    for (int c = 0; c < cols_n; ++c) {
+                        const size_t row0 = size_t(r) * h.piece_rows, col0 = size_t(c) * h.piece_cols;
+                        const size_t i = size_t(r) * cols_n + c;
+                        h.plan.impl.prepare(h.pieces[i], h.A + row0 * K / 2, h.B + col0 * K / 2, h.SFA + row0 * K / 16,
+                                            h.SFB + col0 * K / 16, h.piece_rows, h.piece_cols, K, stream);
+                        cuda_check(cudaEventCreateWithFlags(&h.piece_done[i], cudaEventDisableTiming));
+                    }
             }
             h.M = M; h.N = N; h.K = K;
         }
-        cuda_check(cudaMemcpyAsync(h.B, B, b_bytes, cudaMemcpyHostToDevice, stream));
-        cuda_check(cudaMemcpyAsync(h.SFB, SFB, sfb_bytes, cudaMemcpyHostToDevice, stream));
-        cuda_check(cudaMemcpyAsync(h.SFA, SFA, sfa_bytes, cudaMemcpyHostToDevice, stream));
         if (h.pieces.empty()) {
             h.plan.params.alpha = alpha;
+            cuda_check(cudaMemcpyAsync(h.B, B, b_bytes, cudaMemcpyHostToDevice, stream));
+            cuda_check(cudaMemcpyAsync(h.SFB, SFB, sfb_bytes, cudaMemcpyHostToDevice, stream));
+            cuda_check(cudaMemcpyAsync(h.SFA, SFA, sfa_bytes, cudaMemcpyHostToDevice, stream));
             cuda_check(cudaMemcpyAsync(h.A, A, a_bytes, cudaMemcpyHostToDevice, stream));
             h.plan.impl.launch(h.plan.params, h.C, stream);
             cuda_check(cudaMemcpyAsync(C, h.C, c_bytes, cudaMemcpyDeviceToHost, stream));
             cuda_check(cudaStreamSynchronize(stream));
             return;
         }
-        const size_t a_piece = size_t(h.piece_rows) * K / 2, c_piece = size_t(h.piece_rows) * N;      // bytes, elements
-        for (size_t i = 0; i < h.pieces.size(); ++i) {
-            h.pieces[i].alpha = alpha;
-            cuda_check(cudaMemcpyAsync(h.A + i * a_piece, static_cast<const uint8_t*>(A) + i * a_piece, a_piece,
-                                       cudaMemcpyHostToDevice, stream));
-            h.plan.impl.launch(h.pieces[i], h.C + i * c_piece, stream);
-            cuda_check(cudaEventRecord(h.piece_done[i], stream));
-            cuda_check(cudaStreamWaitEvent(h.out_stream, h.piece_done[i], 0));
-            cuda_check(cudaMemcpyAsync(static_cast<__half*>(C) + i * c_piece, h.C + i * c_piece, c_piece * 2,
-                                       cudaMemcpyDeviceToHost, h.out_stream));
+        const size_t a_piece = size_t(h.piece_rows) * K / 2, sfa_piece = size_t(h.piece_rows) * K / 16;
+        const size_t b_piece = size_t(h.piece_cols) * K / 2, sfb_piece = size_t(h.piece_cols) * K / 16;
+        const size_t block_elems = size_t(h.piece_rows) * h.piece_cols;
+        auto in = [&](uint8_t* dst, const void* src, size_t offset, size_t bytes) {
+            cuda_check(cudaMemcpyAsync(dst + offset, static_cast<const uint8_t*>(src) + offset, bytes, cudaMemcpyHostToDevice, stream));
+        };
+        for (int r = 0; r < h.row_pieces; ++r) {
+            in(h.A, A, r * a_piece, a_piece);
+            in(h.SFA, SFA, r * sfa_piece, sfa_piece);
+            for (int c = 0; c < h.col_pieces; ++c) {
+                if (r == 0) {
+                    in(h.B, B, c * b_piece, b_piece);
+                    in(h.SFB, SFB, c * sfb_piece, sfb_piece);
+                }
+                const size_t i = size_t(r) * h.col_pieces + c;
+                h.pieces[i].alpha = alpha;
+                // every block has its own compact [piece_rows, piece_cols] area of the staging C
+                __half* block = h.C + i * block_elems;
+                h.plan.impl.launch(h.pieces[i], block, stream);
+                cuda_check(cudaEventRecord(h.piece_done[i], stream));
+                cuda_check(cudaStreamWaitEvent(h.out_stream, h.piece_done[i], 0));
+                __half* dst = static_cast<__half*>(C) + size_t(r) * h.piece_rows * N + size_t(c) * h.piece_cols;
+                cuda_check(cudaMemcpy2DAsync(dst, size_t(N) * 2, block, size_t(h.piece_cols) * 2, size_t(h.piece_cols) * 2,
+                                             size_t(h.piece_rows), cudaMemcpyDeviceToHost, h.out_stream));
+            }
         }
         cuda_check(cudaStreamSynchronize(h.out_stream));
         cuda_check(cudaStreamSynchronize(stream));

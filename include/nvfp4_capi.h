@@ -118,11 +118,12 @@ int gpu_kernels_nvfp4_plan_profile(void* plan, void* C, void* stream, unsigned l
 unsigned gpu_kernels_nvfp4_last_kernel_cycles(void);
 
 /* Whole GEMM from HOST buffers (pinned memory recommended): copies the four operands to the device, runs
- * the kernel and copies C back, then synchronises. From M = 1024 the product goes in 2 or 4 row pieces:
- * copies in and kernels on `stream`, copies out on a second stream of the library's, so that both directions
- * of the host link are busy at once. Device staging is cached per (M,N,K) inside the library. This is the
- * end-to-end call a host-side user of the reference path would make in place of its CPU dequantise + matmul
- * (benchmarks/nvfp4.py:41). */
+ * the kernel and copies C back, then synchronises. From M = 1024 the product goes in 2 or 4 row pieces and (from
+ * N = 1024) as many column pieces: copies in and kernels on `stream` in the order A piece, B piece, block, next B
+ * piece, block, ...; every block's result leaves on a second stream of the library's as soon as it is computed,
+ * so C starts to travel back after one piece of each operand has arrived and both directions of the host link
+ * stay busy. Device staging is cached per device and (M,N,K) inside the library. This is the end-to-end call a
+ * host-side user of the reference path would make in place of its CPU dequantise + matmul (benchmarks/nvfp4.py:41). */
 int gpu_kernels_nvfp4_gemm_host(int M, int N, int K, const void* A, const void* B, const void* SFA, const void* SFB,
                                 void* C, float alpha, void* stream);
 

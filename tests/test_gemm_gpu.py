@@ -357,9 +357,10 @@ def test_host_entry_point(g):
     assert_gemm_close(out, O.gemm_f32(to_np(pa), to_np(sa), to_np(pb), to_np(sb)), "host entry point")
 
 
-@pytest.mark.parametrize("m,n,k", [(2048, 512, 512), (1024, 384, 768), (4096, 256, 256)])
+@pytest.mark.parametrize("m,n,k", [(2048, 512, 512), (1024, 384, 768), (4096, 256, 256), (2048, 2048, 512), (1024, 1024, 256)])
 def test_host_entry_point_in_row_pieces(g, m, n, k):
-    # large M: the host entry point computes and copies back in 4 (or 2) row pieces on two streams; against
+    # large M: the host entry point computes and copies back in 4 (or 2) row pieces, and from N = 1024 as many
+    # column pieces, on two streams; against
     # one plan over the whole product (tiles start their K walk elsewhere, so single FP16 roundings may
     # differ) and the FP32 reference, also on a second call with other operands
     for seed in (71, 72):
