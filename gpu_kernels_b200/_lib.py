@@ -24,6 +24,7 @@ SIGNATURES = {
     "gpu_kernels_nvfp4_validate": ([P], I),
     "gpu_kernels_nvfp4_l2_bytes": ([], I),
     "gpu_kernels_nvfp4_quantize": ([P, I, P, P, I, I, P], I),
+    "gpu_kernels_nvfp4_quantize_scaled": ([P, I, F, P, P, I, I, P], I),
     "gpu_kernels_nvfp4_dequantize": ([P, P, P, I, I, P], I),
     "gpu_kernels_nvfp4_plan_set_alpha": ([P, F], I),
     "gpu_kernels_nvfp4_plan_set_option": ([P, ctypes.c_char_p, I], I),

@@ -275,6 +275,16 @@ int gpu_kernels_nvfp4_quantize(const void* x, int dtype, void* packed, void* sca
     });
 }
 
+int gpu_kernels_nvfp4_quantize_scaled(const void* x, int dtype, float inv_tensor_scale, void* packed, void* scales, int rows,
+                                      int K, void* stream) {
+    return guarded([&] {
+        nvfp4_b200::require_sm100();
+        nvfp4_b200::quantise_scaled(x, dtype, inv_tensor_scale, static_cast<uint8_t*>(packed), static_cast<uint8_t*>(scales),
+                                    rows, K, static_cast<cudaStream_t>(stream));
+        nvfp4_b200::g_launches.fetch_add(1, std::memory_order_relaxed);
+    });
+}
+
 int gpu_kernels_nvfp4_dequantize(const void* packed, const void* scales, void* out, int rows, int K, void* stream) {
     return guarded([&] {
         nvfp4_b200::require_sm100();

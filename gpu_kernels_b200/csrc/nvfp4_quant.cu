@@ -120,6 +120,50 @@ quantise_kernel(const T* __restrict__ x, uint8_t* __restrict__ packed, uint8_t* 
     }
 }
 
+// Two-level scaling: every value is first multiplied (in FP32) by the reciprocal of a per-tensor scale, then
+// quantised as above; the GEMM undoes the tensor scales through its alpha. One 16-value block per thread and pass,
+// through the FP32 block routine whatever the input type (the product is no longer a 16-bit value).
+template <typename T>
+__global__ void __launch_bounds__(Q_THREADS)
+quantise_scaled_kernel(const T* __restrict__ x, float inv_global, uint8_t* __restrict__ packed,
+                       uint8_t* __restrict__ scales, int rows, int K) {
+    __shared__ __align__(16) uint8_t sf_tile[4 * 512];
+    const int kb = threadIdx.x & 15, row_in_pass = threadIdx.x >> 4;
+    const int col0 = blockIdx.x * 256, row_base = blockIdx.y * Q_ROWS;
+    const int k = col0 + kb * 16;
+    if (k < K) {
+        #pragma unroll 2
+        for (int pass = 0; pass < 8; ++pass) {
+            const int r = pass * 16 + row_in_pass;
+            const T* p = x + size_t(row_base + r) * K + k;
+            float v[16];
+            if constexpr (sizeof(T) == 4) {
+                Loader<float>::load(reinterpret_cast<const float*>(p), v);
+            } else {
+                const uint4 a = __ldg(reinterpret_cast<const uint4*>(p)), b = __ldg(reinterpret_cast<const uint4*>(p) + 1);
+                const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+                #pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    v[2 * i] = PairFormat<T>::type::widen(w[i] & 0xFFFFu);
+                    v[2 * i + 1] = PairFormat<T>::type::widen(w[i] >> 16);
+                }
+            }
+            #pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = __fmul_rn(v[i], inv_global);
+            uint2 out;
+            const uint32_t sbyte = quantise_block<true>(v, out);
+            *reinterpret_cast<uint2*>(packed + size_t(row_base + r) * (K / 2) + k / 2) = out;
+            sf_tile[(kb >> 2) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (kb & 3)] = static_cast<uint8_t>(sbyte);
+        }
+    }
+    __syncthreads();
+    const int atoms = min(4, (K - col0) / 64);
+    if (int(threadIdx.x) < atoms * 32) {
+        const size_t first_atom = size_t(blockIdx.y) * (K / 64) + size_t(blockIdx.x) * 4;
+        reinterpret_cast<uint4*>(scales + first_atom * 512)[threadIdx.x] = reinterpret_cast<const uint4*>(sf_tile)[threadIdx.x];
+    }
+}
+
 // packed + scales -> FP32 [rows, K]; one thread per 16-value block
 // (reference/python/nvfp4.py:40-47).
 __global__ void __launch_bounds__(256)
@@ -187,6 +231,30 @@ void quantise(const void* x, int dtype, uint8_t* packed, uint8_t* scales, int ro
         case DTYPE_BF16: launch(__nv_bfloat16{}); break;
         case DTYPE_F16: launch(__half{}); break;
         case DTYPE_F32: launch(float{}); break;
+        default:
+            throw std::invalid_argument("nvfp4 quantise: dtype must be 0 (bf16), 1 (fp16) or 2 (fp32)");
+    }
+    cuda_check(cudaGetLastError());
+}
+
+void quantise_scaled(const void* x, int dtype, float inv_global, uint8_t* packed, uint8_t* scales, int rows, int K,
+                     cudaStream_t stream) {
+    check_quant_shape(rows, K);
+    if (!x || !packed || !scales) throw std::invalid_argument("nvfp4 quantise: null pointer");
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(packed) | reinterpret_cast<uintptr_t>(scales)) & 15)
+        throw std::invalid_argument("nvfp4 quantise: pointers must be 16-byte aligned");
+    if (!(inv_global > 0.0f) || !(inv_global < 3.0e38f)) throw std::invalid_argument("nvfp4 quantise: the tensor scale must be positive and finite");
+    const dim3 grid((K + 255) / 256, rows / Q_ROWS);
+    switch (dtype) {
+        case DTYPE_BF16:
+            quantise_scaled_kernel<<<grid, Q_THREADS, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), inv_global, packed, scales, rows, K);
+            break;
+        case DTYPE_F16:
+            quantise_scaled_kernel<<<grid, Q_THREADS, 0, stream>>>(static_cast<const __half*>(x), inv_global, packed, scales, rows, K);
+            break;
+        case DTYPE_F32:
+            quantise_scaled_kernel<<<grid, Q_THREADS, 0, stream>>>(static_cast<const float*>(x), inv_global, packed, scales, rows, K);
+            break;
         default:
             throw std::invalid_argument("nvfp4 quantise: dtype must be 0 (bf16), 1 (fp16) or 2 (fp32)");
     }

@@ -25,8 +25,11 @@ def _require_cuda(t: torch.Tensor, name: str) -> None:
         raise ValueError(f"{name} must be a CUDA tensor: this package has no CPU path")
 
 
-def quantize(values: torch.Tensor):
-    """[rows, K] -> (packed [rows, K/2] uint8, scales [rows*K/16] uint8 in the VEC16 layout)."""
+def quantize(values: torch.Tensor, tensor_scale: float | None = None):
+    """[rows, K] -> (packed [rows, K/2] uint8, scales [rows*K/16] uint8 in the VEC16 layout).
+
+    tensor_scale (two-level scaling, not in the reference): the values are first multiplied, in FP32, by
+    float32(1 / tensor_scale); the GEMM's alpha then carries the product of the operands' tensor scales."""
     _require_cuda(values, "values")
     if values.dim() != 2:
         raise ValueError("values must be 2-D [rows, K]")
@@ -37,9 +40,25 @@ def quantize(values: torch.Tensor):
     packed = torch.empty((rows, k // 2), dtype=torch.uint8, device=values.device)
     scales = torch.empty((rows * k // 16,), dtype=torch.uint8, device=values.device)
     with torch.cuda.device(values.device):
-        _lib.check(_lib.load().gpu_kernels_nvfp4_quantize(
-            values.data_ptr(), _DTYPES[values.dtype], packed.data_ptr(), scales.data_ptr(), rows, k, _stream()))
+        if tensor_scale is None:
+            _lib.check(_lib.load().gpu_kernels_nvfp4_quantize(
+                values.data_ptr(), _DTYPES[values.dtype], packed.data_ptr(), scales.data_ptr(), rows, k, _stream()))
+        else:
+            _lib.check(_lib.load().gpu_kernels_nvfp4_quantize_scaled(
+                values.data_ptr(), _DTYPES[values.dtype], inverse_tensor_scale(tensor_scale), packed.data_ptr(),
+                scales.data_ptr(), rows, k, _stream()))
     return packed, scales
+
+
+def inverse_tensor_scale(tensor_scale: float) -> float:
+    """float32(1 / tensor_scale) as a Python float: the multiplier the scaled quantiser applies."""
+    return float(torch.tensor(1.0, dtype=torch.float32) / torch.tensor(float(tensor_scale), dtype=torch.float32))
+
+
+def tensor_scale_for(values: torch.Tensor) -> float:
+    """The usual per-tensor scale of two-level NVFP4: amax / (6 * 448), so that the largest block scale is 448."""
+    amax = float(values.detach().abs().max().float())
+    return amax / (6.0 * 448.0) if amax > 0.0 else 1.0
 
 
 def dequantize(packed: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:

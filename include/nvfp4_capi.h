@@ -49,6 +49,13 @@ int gpu_kernels_nvfp4_l2_bytes(void);
  * x [rows,K] device, dtype 0 = bf16, 1 = fp16, 2 = fp32; packed [rows,K/2]; scales rows*K/16 bytes.
  * rows % 128 == 0, K % 64 == 0. Bit-exact with the reference on finite and non-finite input. */
 int gpu_kernels_nvfp4_quantize(const void* x, int dtype, void* packed, void* scales, int rows, int K, void* stream);
+/* Two-level scaling (no counterpart in the reference, whose quantiser has the block scales only): the same as
+ * gpu_kernels_nvfp4_quantize applied to fp32(x) * inv_tensor_scale (one FP32 product per value), i.e.
+ * reference `quantize(values.float() * inv_tensor_scale)`. With tensor scales gA, gB (typically amax / (6 * 448), so
+ * that the block scales use the whole E4M3 range) the product is recovered by alpha = gA * gB
+ * (gpu_kernels_nvfp4_plan_set_alpha). Bit-exact with that definition. */
+int gpu_kernels_nvfp4_quantize_scaled(const void* x, int dtype, float inv_tensor_scale, void* packed, void* scales, int rows,
+                                      int K, void* stream);
 /* replaces reference/python/nvfp4.py:40-47 `dequantize`: FP32 [rows,K] out. */
 int gpu_kernels_nvfp4_dequantize(const void* packed, const void* scales, void* out_f32, int rows, int K, void* stream);
 

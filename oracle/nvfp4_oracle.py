@@ -141,6 +141,12 @@ def quantize(values: np.ndarray):
     return np.ascontiguousarray(packed), pack_scales(sbyte)
 
 
+def quantize_scaled(values: np.ndarray, inv_tensor_scale: float):
+    """Two-level scaling (this repository's extension; the reference has block scales only): the reference's
+    `quantize` applied to float32(values) * float32(inv_tensor_scale), one FP32 product per value."""
+    return quantize(np.asarray(values, dtype=np.float32) * np.float32(inv_tensor_scale))
+
+
 def dequantize(packed: np.ndarray, scales_flat: np.ndarray) -> np.ndarray:
     """Stored bytes -> FP32 [rows, K] (reference/python/nvfp4.py:40-47)."""
     rows, half_k = packed.shape

@@ -188,3 +188,32 @@ def test_shape_errors(g):
         g.quantize(torch.zeros(100, 64, device="cuda"))
     with pytest.raises(Nvfp4Error):
         g.quantize(torch.zeros(128, 48, device="cuda"))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_two_level_scaling_is_bit_exact_and_recovers_the_product(g, dtype):
+    # tensor scale gA = amax / (6 * 448): values * float32(1 / gA) quantised by the block rule; bit-exact against the
+    # oracle's statement of exactly that, and the GEMM with alpha = gA * gB gives back the unscaled product
+    rows, k = 256, 512
+    a = (random_operand(rows, k, seed=5, scale=37.0, dtype=torch.float32)).to(dtype)
+    b = (random_operand(384, k, seed=6, scale=0.003, dtype=torch.float32)).to(dtype)
+    ga, gb = g.nvfp4.tensor_scale_for(a), g.nvfp4.tensor_scale_for(b)
+    pa, sa = g.quantize(a, tensor_scale=ga)
+    pb, sb = g.quantize(b, tensor_scale=gb)
+    for x, scale, p, s in ((a, ga, pa, sa), (b, gb, pb, sb)):
+        want_p, want_s = O.quantize_scaled(to_np(x.float()), g.nvfp4.inverse_tensor_scale(scale))
+        assert np.array_equal(to_np(s), want_s) and np.array_equal(to_np(p), want_p)
+        assert int(to_np(s).max()) >= 0x7E - 8          # the largest block scale sits at the top of the E4M3 range
+    plan = g.Nvfp4Gemm(pa, pb, sa, sb, alpha=ga * gb)
+    out = plan.run()
+    plan.validate()
+    ref = to_np(a.float()) @ to_np(b.float()).T
+    got = to_np(out.float())
+    rel = np.linalg.norm(got - ref) / np.linalg.norm(ref)
+    assert rel < 0.2, rel                                # FP4 quantisation noise of both operands, not a scaling error
+    deq = (O.dequantize(to_np(pa), to_np(sa)) @ O.dequantize(to_np(pb), to_np(sb)).T) * np.float32(ga * gb)
+    assert np.linalg.norm(got - deq) / np.linalg.norm(deq) < 2e-3
+    plan.close()
+    # without the tensor scale the small operand loses its block scales to the E4M3 subnormals
+    _, s_plain = g.quantize(b)
+    assert int(to_np(s_plain).max()) < int(to_np(sb).max())
