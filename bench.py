@@ -60,8 +60,10 @@ DTYPE = "nvfp4 (e2m1 x ue4m3), f32 accumulate, f16 out"
 
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of the workload's kernel, from one
 # ncu capture of that workload; None where no capture exists. A reported constant, not measured by this run.
-NCU_DRAM_BYTES_PER_LAUNCH = {"gemm8192": 218_190_336, "gemm16384": None, "skinny": 136_602_624,
-                             "quantise8192": 155_176_960}
+NCU_DRAM_BYTES_PER_LAUNCH = {"gemm8192": 222_000_000, "gemm16384": 1_747_000_000, "skinny": 138_900_000,
+                             "quantise8192": 156_000_000}
+# MXFP4 (the adjacent format of the same kernel; no counterpart in the reference): M, N, K, sigma of B
+MX_WORKLOADS = {"mxfp4_gemm8192": (8192, 8192, 8192, 0.02)}
 
 # GEMM acceptance against the FP32 dequantise-then-matmul path (the bound the tests use).
 REL_FROBENIUS = 1e-3
@@ -676,6 +678,64 @@ def run_quantise(args, ranks: Ranks, workload, sampler, main):
             "cpu_baseline": cpu, "parity": {"bit_exact_vs_cpu_oracle_on_sampled_slabs": ok, "pass_all_ranks": ok}}
 
 
+def run_mx(args, ranks: Ranks, workload, sampler, main):
+    """One step = one MXFP4 GEMM (E2M1 values, UE8M0 scale per 32) on one GPU, timed like the NVFP4 GEMMs; checked on
+    sampled rows and columns against the CPU oracle's dequantise-then-matmul of the stored bytes."""
+    import numpy as np
+    import torch
+    import gpu_kernels_b200 as g
+    from gpu_kernels_b200 import _lib
+    from oracle import nvfp4_oracle as O
+    dev = torch.device("cuda", ranks.local_rank)
+    m, n, k, sigma = MX_WORKLOADS[workload]
+    warmup_s, trials, sample_ms = timing_plan(args, main)
+    l2 = _lib.load().gpu_kernels_nvfp4_l2_bytes()
+    gen = torch.Generator(device=dev).manual_seed(7)
+
+    def operand(rows, sd):
+        x = torch.empty((rows, k), dtype=torch.bfloat16, device=dev)
+        for r0 in range(0, rows, 4096):
+            x[r0:r0 + 4096] = (torch.randn((min(4096, rows - r0), k), generator=gen, device=dev) * sd).bfloat16()
+        return g.quantize_mx(x)
+
+    pa, sa = operand(m, 1.0)
+    pb, sb = operand(n, sigma)
+    in_bytes = sum(t.numel() for t in (pa, sa, pb, sb))
+    rotations = min(64, max(2, -(-2 * l2 // in_bytes)))
+    sets = [(pa, sa, pb, sb)] + [tuple(t.clone() for t in (pa, sa, pb, sb)) for _ in range(rotations - 1)]
+    plans = [g.Nvfp4Gemm(x[0], x[2], x[1], x[3], mx=True) for x in sets]
+    for plan in plans:
+        plan.set_option("static_operands", 1)
+    out = torch.full((m, n), float("nan"), dtype=torch.float16, device=dev)
+    timed = time_replays(lambda i: plans[i % rotations].run(out), ranks, rotations, 10, warmup_s, trials, sample_ms, sampler)
+    ms = timed["median_ms"]
+    for plan in plans:
+        plan.validate()
+    flops = 2.0 * m * n * k
+    alg = m * k // 2 + n * k // 2 + (m + n) * k // 32 + m * n * 2
+    rows = sorted({0, 129, m // 2 + 5, m - 1})
+    cols = sorted({0, 200, n // 2 + 77, n - 1})
+    ra = O.dequantize_mx(pa.cpu().numpy(), sa.cpu().numpy())[rows]
+    rb = O.dequantize_mx(pb.cpu().numpy(), sb.cpu().numpy())
+    got = out.float().cpu().numpy()
+    rel_r, worst_r = gemm_errors(torch.from_numpy(got[rows]), torch.from_numpy(ra @ rb.T))
+    ra_all = O.dequantize_mx(pa.cpu().numpy(), sa.cpu().numpy())
+    rel_c, worst_c = gemm_errors(torch.from_numpy(np.ascontiguousarray(got[:, cols])), torch.from_numpy(ra_all @ rb[cols].T))
+    ok = bool(max(rel_r, rel_c) <= REL_FROBENIUS and max(worst_r, worst_c) <= MAX_ABS_OVER_RMS)
+    info = plans[0].info()
+    for plan in plans:
+        plan.close()
+    return {"workload": workload, "M": m, "N": n, "K": k, "metric": "mxfp4_gemm_tflops", "value": flops / (ms * 1e-3) / 1e12,
+            "unit": UNIT, "ms_per_step": ms, "n_gpus": 1, "timing": timing_note(timed, warmup_s, sample_ms),
+            "clocks": timed["clocks"], "gpu_launches": timed["timed_launches"],
+            "plan": {k_: info[k_] for k_ in ("units", "cta_group", "tile_n", "stages")},
+            "l2": f"operand rotation over {rotations} copies ({rotations * in_bytes >> 20} MiB > 2 x L2 {l2 >> 20} MiB)",
+            "roofline": tensor_roofline(flops, alg, ms, measured_peaks(), True, "nvfp4_gemm_kernel<2,256,direct,mx>", None),
+            "parity": {"checked": f"rows {rows} and columns {cols} of C against the CPU oracle (dequantize_mx, FP32 matmul); "
+                                  "parity unpinned: the reference has no MXFP4",
+                       "rel_frobenius": max(rel_r, rel_c), "max_abs_over_rms": max(worst_r, worst_c), "pass_all_ranks": ok}}
+
+
 # ---- routed-MoE expert layer -------------------------------------------------------------------------------------
 
 def expert_weights(e_global, dev):
@@ -880,6 +940,10 @@ def run_ours(args, rank, world, local_rank):
             if world > 1:
                 raise SystemExit("the quantiser workloads run on one GPU")
             head = run_quantise(args, ranks, wl, sampler, True)
+        elif wl in MX_WORKLOADS:
+            if world > 1:
+                raise SystemExit("the MXFP4 workload runs on one GPU")
+            head = run_mx(args, ranks, wl, sampler, True)
         else:
             moe = MoeBench(args, ranks)
             head = moe.run(wl, sampler, True)
@@ -888,7 +952,7 @@ def run_ours(args, rank, world, local_rank):
         if not args.only:
             order = [w for w in ("gemm16384", "skinny") if w != wl]
             if world == 1:
-                order += [w for w in ("quantise8192",) if w != wl]
+                order += [w for w in ("quantise8192", "mxfp4_gemm8192") if w != wl]
             order += [w for w in MOE_WORKLOADS if w != wl]
             for name in order:
                 t0 = time.perf_counter()
@@ -898,6 +962,8 @@ def run_ours(args, rank, world, local_rank):
                         r = run_gemm(args, ranks, name, sampler, False, gathers if world > 1 else ("none",))
                     elif name in QUANT_WORKLOADS:
                         r = run_quantise(args, ranks, name, sampler, False)
+                    elif name in MX_WORKLOADS:
+                        r = run_mx(args, ranks, name, sampler, False)
                     else:
                         if moe is None:
                             moe = MoeBench(args, ranks)
@@ -950,7 +1016,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5, help="warm-up steps before the burst leg")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="gemm8192",
-                    choices=sorted(GEMM_WORKLOADS) + sorted(MOE_WORKLOADS) + sorted(QUANT_WORKLOADS))
+                    choices=sorted(GEMM_WORKLOADS) + sorted(MOE_WORKLOADS) + sorted(QUANT_WORKLOADS) + sorted(MX_WORKLOADS))
     ap.add_argument("--only", action="store_true", help="measure the named workload only (no `configs`)")
     ap.add_argument("--gather", default="auto", choices=["auto", "none", "fused", "nccl"],
                     help="N>1, GEMM workloads: also time the step that leaves the full C on every rank: 'fused' = the GEMM's "

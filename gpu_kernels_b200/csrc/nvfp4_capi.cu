@@ -231,11 +231,30 @@ int gpu_kernels_nvfp4_plan_create(void** out, int M, int N, int K, const void* A
     });
 }
 
+int gpu_kernels_nvfp4_plan_create_mx(void** out, int M, int N, int K, const void* A, const void* B, const void* SFA,
+                                     const void* SFB, void* stream) {
+    return guarded([&] {
+        if (!out) throw std::invalid_argument("plan_create_mx: null result pointer");
+        auto plan = std::make_unique<Plan>();
+        plan->impl = gpu_kernels::nvfp4_sm100_implementation();
+        gpu_kernels::mxfp4_prepare(plan->params, static_cast<const uint8_t*>(A), static_cast<const uint8_t*>(B),
+                                   static_cast<const uint8_t*>(SFA), static_cast<const uint8_t*>(SFB), M, N, K,
+                                   static_cast<cudaStream_t>(stream));
+        plan->sfa = SFA;
+        plan->sfb = SFB;
+        plan->b = B;
+        plan->whole_tile_units = plan->params.clusters;
+        plan->whole_tile_direct_store = plan->params.direct_store;
+        *out = plan.release();
+    });
+}
+
 void gpu_kernels_nvfp4_plan_destroy(void* plan) { delete static_cast<Plan*>(plan); }
 
 int gpu_kernels_nvfp4_cublas(void* plan, void* C, const void* A, const void* B, void* stream) {
     return guarded([&] {
         Plan& p = as_plan(plan);
+        if (p.params.mx) throw std::invalid_argument("cublas: the comparison path is set up for NVFP4 plans only");
         if (!p.lt)
             p.lt = std::make_unique<LtMatmul>(p.params.M, p.params.N, p.params.K, p.sfa, p.sfb,
                                               p.workspace ? p.workspace_bytes : 0);
@@ -281,6 +300,24 @@ int gpu_kernels_nvfp4_quantize_scaled(const void* x, int dtype, float inv_tensor
         nvfp4_b200::require_sm100();
         nvfp4_b200::quantise_scaled(x, dtype, inv_tensor_scale, static_cast<uint8_t*>(packed), static_cast<uint8_t*>(scales),
                                     rows, K, static_cast<cudaStream_t>(stream));
+        nvfp4_b200::g_launches.fetch_add(1, std::memory_order_relaxed);
+    });
+}
+
+int gpu_kernels_nvfp4_quantize_mx(const void* x, int dtype, void* packed, void* scales, int rows, int K, void* stream) {
+    return guarded([&] {
+        nvfp4_b200::require_sm100();
+        nvfp4_b200::quantise_mx(x, dtype, static_cast<uint8_t*>(packed), static_cast<uint8_t*>(scales), rows, K,
+                                static_cast<cudaStream_t>(stream));
+        nvfp4_b200::g_launches.fetch_add(1, std::memory_order_relaxed);
+    });
+}
+
+int gpu_kernels_nvfp4_dequantize_mx(const void* packed, const void* scales, void* out, int rows, int K, void* stream) {
+    return guarded([&] {
+        nvfp4_b200::require_sm100();
+        nvfp4_b200::dequantise_mx(static_cast<const uint8_t*>(packed), static_cast<const uint8_t*>(scales),
+                                  static_cast<float*>(out), rows, K, static_cast<cudaStream_t>(stream));
         nvfp4_b200::g_launches.fetch_add(1, std::memory_order_relaxed);
     });
 }

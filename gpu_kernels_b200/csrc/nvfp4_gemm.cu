@@ -71,7 +71,9 @@ enum Epi : int {
     EPI_DIRECT_RAGGED = 8, // EPI_DIRECT on single-CTA tiles of unequal width (see GemmArgs::ragged_base)
 };
 
-template <int CG, int UN, int EPI>
+// MX: the MXFP4 flavour of the same instruction: one UE8M0 (power-of-two) scale per 32 values, so a 512-byte
+// scale atom (128 rows x 4 scales) covers K = 128 and each MMA (K = 64) uses two of its four scale bytes.
+template <int CG, int UN, int EPI, bool MX = false>
 struct Config {
     static_assert(CG == 1 || CG == 2, "cta group");
     static_assert(UN == 128 || UN == 256, "tile width");
@@ -79,9 +81,10 @@ struct Config {
     static constexpr int B_ROWS = UN / CG;                       // B rows staged by each CTA
     static constexpr int A_BYTES = BLOCK_M * ROW_BYTES;
     static constexpr int B_BYTES = B_ROWS * ROW_BYTES;
-    static constexpr int SFA_BYTES = (STAGE_K / MMA_K) * SF_ATOM_BYTES;
+    static constexpr int SF_SLOTS = MX ? STAGE_K / 128 : STAGE_K / MMA_K;      // scale atoms per 128 rows and ring stage
+    static constexpr int SFA_BYTES = SF_SLOTS * SF_ATOM_BYTES;
     static constexpr int SFB_BLOCKS = UN / 128;                  // 128-row scale blocks across the tile width
-    static constexpr int SFB_BLOCK_BYTES = (STAGE_K / MMA_K) * SF_ATOM_BYTES;
+    static constexpr int SFB_BLOCK_BYTES = SF_SLOTS * SF_ATOM_BYTES;
     static constexpr int SFB_BYTES = SFB_BLOCKS * SFB_BLOCK_BYTES;
     static constexpr int OFF_B = A_BYTES;
     static constexpr int OFF_SFA = OFF_B + B_BYTES;
@@ -113,8 +116,8 @@ struct Config {
     static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + CTRL_BYTES;
     // Tensor Memory columns: scale columns for the four MMAs of a stage at the top,
     // two accumulators below them (overlapping when they cannot both fit).
-    static constexpr int SF_COLS_PER_MMA = 4 + UN / 32;
-    static constexpr int SF_COLS = (STAGE_K / MMA_K) * SF_COLS_PER_MMA;
+    static constexpr int SF_COLS_PER_MMA = 4 + UN / 32;          // columns of one atom of SFA and the tile's atoms of SFB
+    static constexpr int SF_COLS = SF_SLOTS * SF_COLS_PER_MMA;
     static constexpr int SF_BASE = TMEM_COLS - SF_COLS;
     static constexpr int ACC_STRIDE = (2 * UN <= SF_BASE) ? UN : SF_BASE - UN;
     static constexpr int OVERLAP = UN - ACC_STRIDE;              // columns shared by the two accumulators
@@ -125,8 +128,9 @@ struct Config {
     // Instruction descriptor of kind::mxf4nvf4: A and B E2M1 (format 1) at bits 7 and 10,
     // both K-major, N >> 3 at bit 17, UE4M3 scales (bit 23 = 0), M >> 4 at bit 24,
     // scale-factor ids 0 (each MMA reads whole 32-bit scale columns).
+    // MX: scale format UE8M0 (bit 23); the scale-factor ids (bits 29-30 for A, 4-5 for B) are set per MMA.
     static constexpr uint32_t IDESC = (1u << 7) | (1u << 10) | (uint32_t(UN >> 3) << 17) |
-                                      (uint32_t(TILE_M >> 4) << 24);
+                                      (uint32_t(TILE_M >> 4) << 24) | (MX ? (1u << 23) : 0u);
 };
 
 struct Control {
@@ -289,9 +293,9 @@ __device__ __forceinline__ void tile_coords(int t, const GemmArgs& g, int& tm, i
     tn = (band & 1) ? g.tiles_n - 1 - c : c;
 }
 
-template <int CG, int UN, int EPI, bool PROF>
+template <int CG, int UN, int EPI, bool PROF, bool MX = false>
 struct Roles {
-    using Cfg = Config<CG, UN, EPI>;
+    using Cfg = Config<CG, UN, EPI, MX>;
 
     uint32_t smem;            // 1024-aligned shared-window address of stage 0
     Control* ctrl;
@@ -367,7 +371,7 @@ struct Roles {
                         mbar_arrive_expect_tx(own_full, stage_bytes);
                         if (!split_issue) {
                             tma_load_2d(base, tmA, ks * ROW_BYTES, a_row, own_full);
-                            tma_load_3d(base + Cfg::OFF_SFA, tmSFA, 0, ks * 16, sfa_block, own_full);
+                            tma_load_3d(base + Cfg::OFF_SFA, tmSFA, 0, ks * (Cfg::SF_SLOTS * 4), sfa_block, own_full);
                         }
                         if constexpr (Cfg::RAGGED) {
                             for (int u = 0; u < b_boxes; ++u)
@@ -377,7 +381,7 @@ struct Roles {
                         }
                         #pragma unroll
                         for (int b = 0; b < Cfg::SFB_BLOCKS; ++b)
-                            tma_load_3d(base + Cfg::OFF_SFB + b * Cfg::SFB_BLOCK_BYTES, tmSFB, 0, ks * 16,
+                            tma_load_3d(base + Cfg::OFF_SFB + b * Cfg::SFB_BLOCK_BYTES, tmSFB, 0, ks * (Cfg::SF_SLOTS * 4),
                                         sfb_block + b, own_full);
                     }
                 } else {
@@ -387,12 +391,12 @@ struct Roles {
                         if (rank == 0) mbar_arrive_expect_tx(own_full, 2 * Cfg::STAGE_BYTES);
                         if (!split_issue) {
                             tma_load_2d_pair(base, tmA, ks * ROW_BYTES, a_row, full);
-                            tma_load_3d_pair(base + Cfg::OFF_SFA, tmSFA, 0, ks * 16, sfa_block, full);
+                            tma_load_3d_pair(base + Cfg::OFF_SFA, tmSFA, 0, ks * (Cfg::SF_SLOTS * 4), sfa_block, full);
                         }
                         tma_load_2d_pair(base + Cfg::OFF_B, tmB, ks * ROW_BYTES, b_row, full);
                         #pragma unroll
                         for (int b = 0; b < Cfg::SFB_BLOCKS; ++b)
-                            tma_load_3d_pair(base + Cfg::OFF_SFB + b * Cfg::SFB_BLOCK_BYTES, tmSFB, 0, ks * 16,
+                            tma_load_3d_pair(base + Cfg::OFF_SFB + b * Cfg::SFB_BLOCK_BYTES, tmSFB, 0, ks * (Cfg::SF_SLOTS * 4),
                                              sfb_block + b, full);
                     }
                 }
@@ -420,11 +424,11 @@ struct Roles {
                 const uint32_t own_full = bar(&ctrl->full[i]);
                 if constexpr (CG == 1) {
                     tma_load_2d(base, tmA, held[i].ks * ROW_BYTES, held[i].a_row, own_full);
-                    tma_load_3d(base + Cfg::OFF_SFA, tmSFA, 0, held[i].ks * 16, held[i].sfa_block, own_full);
+                    tma_load_3d(base + Cfg::OFF_SFA, tmSFA, 0, held[i].ks * (Cfg::SF_SLOTS * 4), held[i].sfa_block, own_full);
                 } else {
                     const uint32_t full = map_to_cta(own_full, 0);
                     tma_load_2d_pair(base, tmA, held[i].ks * ROW_BYTES, held[i].a_row, full);
-                    tma_load_3d_pair(base + Cfg::OFF_SFA, tmSFA, 0, held[i].ks * 16, held[i].sfa_block, full);
+                    tma_load_3d_pair(base + Cfg::OFF_SFA, tmSFA, 0, held[i].ks * (Cfg::SF_SLOTS * 4), held[i].sfa_block, full);
                 }
             }
         }
@@ -484,20 +488,27 @@ struct Roles {
                 const uint32_t lo = ring_lo + uint32_t(stage) * (Cfg::STAGE_BYTES >> 4);
                 const uint32_t empty = bar(&ctrl->empty[stage]);
                 const uint32_t first = ks != seg.k0 ? 1u : 0u;   // 0: the first MMA of the segment overwrites the accumulator
+                // j: the MMA (K = 64) inside the stage. NVFP4: MMA j has its own scale atom j. MXFP4: MMAs 2a and 2a+1
+                // share atom a (copied before the first of them) and read its bytes 0-1 and 2-3.
                 auto copies = [&](int j) {
-                    const uint32_t sf = sf_tmem + j * Cfg::SF_COLS_PER_MMA;
-                    tmem_copy_scales<CG>(sf, (lo + ((Cfg::OFF_SFA + j * SF_ATOM_BYTES) >> 4)) | SCALE_LBO, SCALE_HI);
+                    if (MX && (j & 1)) return;
+                    const int slot = MX ? j / 2 : j;
+                    const uint32_t sf = sf_tmem + slot * Cfg::SF_COLS_PER_MMA;
+                    tmem_copy_scales<CG>(sf, (lo + ((Cfg::OFF_SFA + slot * SF_ATOM_BYTES) >> 4)) | SCALE_LBO, SCALE_HI);
                     #pragma unroll
                     for (int b = 0; b < Cfg::SFB_BLOCKS; ++b)
                         tmem_copy_scales<CG>(sf + 4 + 4 * b,
-                                             (lo + ((Cfg::OFF_SFB + b * Cfg::SFB_BLOCK_BYTES + j * SF_ATOM_BYTES) >> 4)) | SCALE_LBO,
+                                             (lo + ((Cfg::OFF_SFB + b * Cfg::SFB_BLOCK_BYTES + slot * SF_ATOM_BYTES) >> 4)) | SCALE_LBO,
                                              SCALE_HI);
                 };
                 auto mma = [&](int j) {
                     // K advances 32 bytes inside the 128-byte swizzled row per MMA.
-                    const uint32_t sf = sf_tmem + j * Cfg::SF_COLS_PER_MMA;
-                    mma_nvfp4<CG>(acc, lo + ((j * (MMA_K / 2)) >> 4), lo + ((Cfg::OFF_B + j * (MMA_K / 2)) >> 4),
-                                  OPERAND_HI, idesc, sf, sf + 4 + sfb_shift, j != 0 ? 1u : first);
+                    const int slot = MX ? j / 2 : j;
+                    const uint32_t sf = sf_tmem + slot * Cfg::SF_COLS_PER_MMA;
+                    const uint32_t sf_id = MX ? uint32_t(j & 1) * 2u : 0u;
+                    mma_block_scaled<CG, MX>(acc, lo + ((j * (MMA_K / 2)) >> 4), lo + ((Cfg::OFF_B + j * (MMA_K / 2)) >> 4),
+                                             OPERAND_HI, idesc | (sf_id << 29) | (sf_id << 4), sf, sf + 4 + sfb_shift,
+                                             j != 0 ? 1u : first);
                 };
                 const bool handover = ks == seg.k0 && iter > 0;
                 if (handover) {
@@ -834,12 +845,12 @@ struct Roles {
     }
 };
 
-template <int CG, int UN, int EPI, bool PROF>
+template <int CG, int UN, int EPI, bool PROF, bool MX = false>
 __global__ void __launch_bounds__(Config<CG, UN, EPI>::THREADS, 1)
 nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB,
                   const __grid_constant__ CUtensorMap tmC, const GemmArgs g) {
-    using Cfg = Config<CG, UN, EPI>;
+    using Cfg = Config<CG, UN, EPI, MX>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t smem = (raw + 1023u) & ~1023u;
@@ -889,7 +900,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     // caller has declared operands that the grid in front cannot be writing (then the roles wait where they must).
     if (g.static_operands == 0) grid_dependency_wait();
 
-    Roles<CG, UN, EPI, PROF> roles{smem, ctrl, rank, unit, gridDim.x / CG,
+    Roles<CG, UN, EPI, PROF, MX> roles{smem, ctrl, rank, unit, gridDim.x / CG,
                                    uint32_t(g.block_expert ? __ldg(g.num_blocks) : g.tiles_m) * uint32_t(g.tiles_n),
                                    CG == 2 ? map_to_cta(smem_u32(const_cast<uint32_t*>(&ctrl->wait.abort)), rank ^ 1u) : 0u, g};
 
@@ -961,11 +972,12 @@ CUtensorMap operand_map(const uint8_t* p, int rows, int K, int box_rows) {
 // The scale bytes of one 128-row block are K/64 atoms of 512 bytes = 4 * K/64 rows of 128 bytes; the map is
 // {128 bytes, those rows, row blocks}, and one 16-row box is the four atoms of a K = 256 step (zeros beyond
 // the block's last atom).
-CUtensorMap scale_map(const uint8_t* p, int rows, int K) {
-    const cuuint64_t per_block = cuuint64_t(K / 64) * 4;
+// atom_k: K values one scale atom covers (64 for NVFP4's scale per 16, 128 for MXFP4's scale per 32).
+CUtensorMap scale_map(const uint8_t* p, int rows, int K, int atom_k = 64) {
+    const cuuint64_t per_block = cuuint64_t(K / atom_k) * 4;
     const cuuint64_t shape[3] = {128, per_block, cuuint64_t(rows / 128)};
     const cuuint64_t strides[2] = {128, per_block * 128};
-    const cuuint32_t box[3] = {128, 16, 1};
+    const cuuint32_t box[3] = {128, cuuint32_t(STAGE_K / atom_k * 4), 1};
     return make_map(CU_TENSOR_MAP_DATA_TYPE_UINT8, p, 3, shape, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE,
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
 }
@@ -987,11 +999,11 @@ std::mutex g_host_state;            // guards the per-device caches below
 // One kernel instance: sets its shared-memory limit once per device, then launches.
 // pdl: launch with the programmatic stream-serialisation attribute, so that the prologue of this launch overlaps
 // the tail of the kernel in front of it in the stream (when that kernel allows it, as this kernel does).
-template <int CG, int UN, int EPI, bool PROF = false>
+template <int CG, int UN, int EPI, bool PROF = false, bool MX = false>
 void launch_instance(int device, int units, const CUtensorMap& A, const CUtensorMap& B, const CUtensorMap& SFA,
                      const CUtensorMap& SFB, const CUtensorMap& tmC, const GemmArgs& g, cudaStream_t stream, bool pdl) {
-    using Cfg = Config<CG, UN, EPI>;
-    auto kernel = nvfp4_gemm_kernel<CG, UN, EPI, PROF>;
+    using Cfg = Config<CG, UN, EPI, MX>;
+    auto kernel = nvfp4_gemm_kernel<CG, UN, EPI, PROF, MX>;
     {
         static bool ready[64] = {};
         std::lock_guard<std::mutex> hold(g_host_state);
@@ -1072,7 +1084,7 @@ std::atomic<unsigned> g_next_slot{0};
 bool set_ragged_tiles(gpu_kernels::Nvfp4Params& p, const uint8_t* B, int tiles) {
     p.ragged_base = p.ragged_extra = p.ragged_units = 0;
     if (tiles <= 0 || !B) return false;
-    if (p.M != 128 || p.cta_group != 1 || p.tile_n != 256 || p.N % 64) return false;
+    if (p.mx || p.M != 128 || p.cta_group != 1 || p.tile_n != 256 || p.N % 64) return false;
     const int units = p.N / 64, base = units / tiles, extra = units % tiles;
     if ((base != 2 && base != 3) || tiles <= p.N / 256) return false;
     p.B64 = operand_map(B, p.N, p.K, 64);
@@ -1082,12 +1094,13 @@ bool set_ragged_tiles(gpu_kernels::Nvfp4Params& p, const uint8_t* B, int tiles) 
     return true;
 }
 
-void prepare(gpu_kernels::Nvfp4Params& p, const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB,
-             int M, int N, int K, cudaStream_t) {
+void prepare_format(gpu_kernels::Nvfp4Params& p, const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB,
+                    int M, int N, int K, bool mx) {
     require_sm100();
     if (M <= 0 || N <= 0 || K <= 0) throw std::invalid_argument("nvfp4 gemm: M, N, K must be positive");
     if (M % 128 || N % 128) throw std::invalid_argument("nvfp4 gemm: M and N must be multiples of 128 (whole scale atoms)");
-    if (K % 64) throw std::invalid_argument("nvfp4 gemm: K must be a multiple of 64 (whole scale atoms)");
+    if (K % (mx ? 128 : 64)) throw std::invalid_argument(mx ? "mxfp4 gemm: K must be a multiple of 128 (whole scale atoms)"
+                                                              : "nvfp4 gemm: K must be a multiple of 64 (whole scale atoms)");
     if (!A || !B || !SFA || !SFB) throw std::invalid_argument("nvfp4 gemm: null operand pointer");
     if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(SFA) |
          reinterpret_cast<uintptr_t>(SFB)) & 15)
@@ -1096,6 +1109,7 @@ void prepare(gpu_kernels::Nvfp4Params& p, const uint8_t* A, const uint8_t* B, co
     cuda_check(cudaGetDevice(&device));
     p = gpu_kernels::Nvfp4Params{};
     p.M = M; p.N = N; p.K = K;
+    p.mx = mx ? 1 : 0;
     p.alpha = 1.0f;
     p.device = device;
     p.c_evict_first = env_int("NVFP4_B200_C_EVICT_FIRST", 1);
@@ -1113,8 +1127,8 @@ void prepare(gpu_kernels::Nvfp4Params& p, const uint8_t* A, const uint8_t* B, co
     const int box_b = p.tile_n / p.cta_group;
     p.A = operand_map(A, M, K, BLOCK_M);
     p.B = operand_map(B, N, K, box_b);
-    p.SFA = scale_map(SFA, M, K);
-    p.SFB = scale_map(SFB, N, K);
+    p.SFA = scale_map(SFA, M, K, mx ? 128 : 64);
+    p.SFB = scale_map(SFB, N, K, mx ? 128 : 64);
     const int tiles = (M / (128 * p.cta_group)) * (N / p.tile_n);
     p.clusters = std::min(fit_units(device, p.cta_group, p.tile_n), tiles);
     // About sqrt(units) tile rows per band keeps the A and B panels of the tiles in flight balanced.
@@ -1131,10 +1145,15 @@ void prepare(gpu_kernels::Nvfp4Params& p, const uint8_t* A, const uint8_t* B, co
     // option "ragged_tiles". Off unless asked for: measured 27.9 against 28.3 us for dependent launches, but a
     // launch that fills every SM leaves no room for the next launch of a chain to start early (independent
     // launches: 28.5 against 24.7-26.1 us).
-    if (env_int("NVFP4_B200_RAGGED", 0)) set_ragged_tiles(p, B, fit_units(device, 1, 256));
+    if (!mx && env_int("NVFP4_B200_RAGGED", 0)) set_ragged_tiles(p, B, fit_units(device, 1, 256));
     p.pdl = env_int("NVFP4_B200_PDL", 1);
     p.status_slot = 1 + int(g_next_slot.fetch_add(1, std::memory_order_relaxed) % unsigned(STATUS_SLOTS - 1));
     (void)status_base(device);
+}
+
+void prepare(gpu_kernels::Nvfp4Params& p, const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB,
+             int M, int N, int K, cudaStream_t) {
+    prepare_format(p, A, B, SFA, SFB, M, N, K, false);
 }
 
 // table: device memory of gather_table_bytes(world), filled here (on `stream`) with one tensor map and one
@@ -1176,7 +1195,7 @@ int split_k_factor(const gpu_kernels::Nvfp4Params& p) {
     const int fit = fit_units(p.device, p.cta_group, p.tile_n);
     const int ksteps = (p.K + STAGE_K - 1) / STAGE_K, chunks = p.tile_n / EPI_COLS;
     for (int s : {4})
-        if (p.K % STAGE_K == 0 && s <= chunks && tiles * s <= fit && ksteps % s == 0 && ksteps / s >= 4 &&
+        if (!p.mx && p.K % STAGE_K == 0 && s <= chunks && tiles * s <= fit && ksteps % s == 0 && ksteps / s >= 4 &&
             size_t(tiles) * s * p.cta_group * 4 * sizeof(uint32_t) <= SPLIT_K_FLAG_BYTES / 2)
             return s;
     return 0;
@@ -1248,7 +1267,11 @@ void launch_dense(const gpu_kernels::Nvfp4Params& p, const CUtensorMap& tmC, con
     const bool staged = CG == 2 && !p.direct_store;
     const bool pdl = p.pdl != 0 && !g.prof;
     const int dev = p.device, units = p.clusters;
-    if (p.split_k > 1) {
+    if (p.mx) {
+        // MXFP4 plans have the register-store route only
+        if (p.split_k > 1 || p.gather_world || g.prof) throw std::invalid_argument("mxfp4 gemm: plain launches only");
+        launch_instance<CG, UN, EPI_DIRECT, false, true>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream, pdl);
+    } else if (p.split_k > 1) {
         launch_instance<CG, UN, EPI_SPLIT_K>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream, pdl);
     } else if (p.gather_world) {
         // CTA pairs send the slab with TMA stores of staged 32 x 64 chunks (one per destination): NVLink carries
@@ -1472,6 +1495,11 @@ Nvfp4Implementation nvfp4_sm100_implementation() {
 }
 
 void nvfp4_set_alpha(Nvfp4Params& p, float alpha) { p.alpha = alpha; }
+
+void mxfp4_prepare(Nvfp4Params& p, const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int M, int N,
+                   int K, cudaStream_t) {
+    nvfp4_b200::prepare_format(p, A, B, SFA, SFB, M, N, K, true);
+}
 
 void nvfp4_validate_plan(const Nvfp4Params& p) { nvfp4_b200::validate_slot(p.device, p.status_slot); }
 

@@ -37,6 +37,8 @@ void check_quant_shape(int rows, int K);
 void quantise(const void* x, int dtype, uint8_t* packed, uint8_t* scales, int rows, int K, cudaStream_t stream);
 void quantise_scaled(const void* x, int dtype, float inv_global, uint8_t* packed, uint8_t* scales, int rows, int K,
                      cudaStream_t stream);
+void quantise_mx(const void* x, int dtype, uint8_t* packed, uint8_t* scales, int rows, int K, cudaStream_t stream);
+void dequantise_mx(const uint8_t* packed, const uint8_t* scales, float* out, int rows, int K, cudaStream_t stream);
 void dequantise(const uint8_t* packed, const uint8_t* scales, float* out, int rows, int K, cudaStream_t stream);
 
 // nvfp4_gemm.cu: grouped GEMM for routed-MoE experts. A is a pool of 128-row blocks

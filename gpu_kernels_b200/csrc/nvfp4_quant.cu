@@ -197,6 +197,93 @@ dequantise_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict_
     }
 }
 
+// ---- MXFP4 (OCP microscaling): E2M1 values, one UE8M0 power-of-two scale per 32 values ------------------------
+// Per block: e = floor(log2(amax)) - 2 (2 = the largest exponent of E2M1), clamped to [-127, 127]; scale byte
+// e + 127; q = x * 2^-e (exact but for underflow) encoded as E2M1 with the quantiser's rounding and sign rule.
+// An all-zero block takes e = -127; a block with a NaN or an infinity takes the NaN scale 0xFF and the codes of
+// the NVFP4 NaN block. One thread per block. The scale bytes go to cuBLASLt's VEC32 order: the VEC16 atoms with
+// K/32 blocks per row.
+template <typename T>
+__global__ void __launch_bounds__(256)
+quantise_mx_kernel(const T* __restrict__ x, uint8_t* __restrict__ packed, uint8_t* __restrict__ scales, int rows, int K) {
+    const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    const int blocks_per_row = K / 32;
+    if (idx >= size_t(rows) * blocks_per_row) return;
+    const int r = int(idx / blocks_per_row), b = int(idx % blocks_per_row);
+    const T* p = x + size_t(r) * K + size_t(b) * 32;
+    float v[32];
+    if constexpr (sizeof(T) == 4) {
+        #pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float4 f = __ldg(reinterpret_cast<const float4*>(p) + i);
+            v[4 * i] = f.x; v[4 * i + 1] = f.y; v[4 * i + 2] = f.z; v[4 * i + 3] = f.w;
+        }
+    } else {
+        #pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint4 a = __ldg(reinterpret_cast<const uint4*>(p) + i);
+            const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+            #pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                v[8 * i + 2 * j] = PairFormat<T>::type::widen(w[j] & 0xFFFFu);
+                v[8 * i + 2 * j + 1] = PairFormat<T>::type::widen(w[j] >> 16);
+            }
+        }
+    }
+    uint32_t mx = 0;
+    #pragma unroll
+    for (int i = 0; i < 32; ++i) mx = max(mx, __float_as_uint(v[i]) & 0x7FFFFFFFu);
+    uint4* out = reinterpret_cast<uint4*>(packed + size_t(r) * (K / 2) + size_t(b) * 16);
+    // the scale of (row, block of 32) sits where the VEC16 layout of a K/2-wide tensor puts (row, block of 16)
+    uint8_t* sbyte = scales + scale_byte_offset(r, b, K / 2);
+    if (mx >= 0x7F800000u) {
+        *out = make_uint4(0x77777777u, 0x77777777u, 0x77777777u, 0x77777777u);
+        *sbyte = 0xFFu;
+        return;
+    }
+    int e = mx ? ilogbf(__uint_as_float(mx)) - 2 : -127;
+    e = min(max(e, -127), 127);
+    const float inv = scalbnf(1.0f, -e);
+    uint32_t words[4];
+    #pragma unroll
+    for (int h = 0; h < 4; ++h) {
+        float q[8];
+        uint32_t signs = 0;
+        #pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float t = __fmul_rn(v[8 * h + i], inv);
+            q[i] = fabsf(t);
+            signs |= t < 0.0f ? (8u << (4 * i)) : 0u;
+        }
+        words[h] = e2m1x8_from_quotients(q) | signs;
+    }
+    *out = make_uint4(words[0], words[1], words[2], words[3]);
+    *sbyte = static_cast<uint8_t>(e + 127);
+}
+
+// MXFP4 bytes -> FP32 [rows, K]; one thread per block of 32 (the check path).
+__global__ void __launch_bounds__(256)
+dequantise_mx_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ scales, float* __restrict__ out,
+                     int rows, int K) {
+    const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    const int blocks_per_row = K / 32;
+    if (idx >= size_t(rows) * blocks_per_row) return;
+    const int r = int(idx / blocks_per_row), b = int(idx % blocks_per_row);
+    const uint32_t sb = scales[scale_byte_offset(r, b, K / 2)];
+    const float s = sb == 0xFFu ? __uint_as_float(0x7FC00000u) : scalbnf(1.0f, int(sb) - 127);
+    const uint4 p = __ldg(reinterpret_cast<const uint4*>(packed + size_t(r) * (K / 2) + size_t(b) * 16));
+    const uint32_t w[4] = {p.x, p.y, p.z, p.w};
+    float* dst = out + size_t(r) * K + size_t(b) * 32;
+    #pragma unroll
+    for (int h = 0; h < 4; ++h)
+        #pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t c = (w[h] >> (4 * i)) & 15u, m = c & 7u;
+            const float level = m < 2u ? 0.5f * m : __uint_as_float(((126u + (m >> 1)) << 23) | ((m & 1u) << 22));
+            dst[8 * h + i] = level * (1.0f - 2.0f * static_cast<float>(c >> 3)) * s;
+        }
+}
+
 }  // namespace
 
 void check_quant_shape(int rows, int K) {
@@ -258,6 +345,36 @@ void quantise_scaled(const void* x, int dtype, float inv_global, uint8_t* packed
         default:
             throw std::invalid_argument("nvfp4 quantise: dtype must be 0 (bf16), 1 (fp16) or 2 (fp32)");
     }
+    cuda_check(cudaGetLastError());
+}
+
+void check_mx_shape(int rows, int K) {
+    if (rows <= 0 || K <= 0) throw std::invalid_argument("mxfp4: rows and K must be positive");
+    if (rows % 128 != 0) throw std::invalid_argument("mxfp4: rows must be a multiple of 128");
+    if (K % 128 != 0) throw std::invalid_argument("mxfp4: K must be a multiple of 128 (one scale atom covers 4 blocks of 32)");
+}
+
+void quantise_mx(const void* x, int dtype, uint8_t* packed, uint8_t* scales, int rows, int K, cudaStream_t stream) {
+    check_mx_shape(rows, K);
+    if (!x || !packed || !scales) throw std::invalid_argument("mxfp4 quantise: null pointer");
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(packed) | reinterpret_cast<uintptr_t>(scales)) & 15)
+        throw std::invalid_argument("mxfp4 quantise: pointers must be 16-byte aligned");
+    const size_t blocks = size_t(rows) * (K / 32);
+    const unsigned grid = static_cast<unsigned>((blocks + 255) / 256);
+    switch (dtype) {
+        case DTYPE_BF16: quantise_mx_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), packed, scales, rows, K); break;
+        case DTYPE_F16: quantise_mx_kernel<<<grid, 256, 0, stream>>>(static_cast<const __half*>(x), packed, scales, rows, K); break;
+        case DTYPE_F32: quantise_mx_kernel<<<grid, 256, 0, stream>>>(static_cast<const float*>(x), packed, scales, rows, K); break;
+        default: throw std::invalid_argument("mxfp4 quantise: dtype must be 0 (bf16), 1 (fp16) or 2 (fp32)");
+    }
+    cuda_check(cudaGetLastError());
+}
+
+void dequantise_mx(const uint8_t* packed, const uint8_t* scales, float* out, int rows, int K, cudaStream_t stream) {
+    check_mx_shape(rows, K);
+    if (!packed || !scales || !out) throw std::invalid_argument("mxfp4 dequantise: null pointer");
+    const size_t blocks = size_t(rows) * (K / 32);
+    dequantise_mx_kernel<<<static_cast<unsigned>((blocks + 255) / 256), 256, 0, stream>>>(packed, scales, out, rows, K);
     cuda_check(cudaGetLastError());
 }
 

@@ -325,24 +325,26 @@ __device__ __forceinline__ void tmem_copy_scales(uint32_t taddr, uint32_t desc_l
                      "tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], d;\n\t}"
                      :: "r"(taddr), "r"(desc_lo), "r"(desc_hi) : "memory");
 }
-template <int CG>
-__device__ __forceinline__ void mma_nvfp4(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi,
-                                          uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
-    if constexpr (CG == 1)
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
-            "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\tsetp.ne.b32 p, %7, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], da, db, %4, [%5], [%6], p;\n\t}"
-            :: "r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
-            : "memory");
-    else
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
-            "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\tsetp.ne.b32 p, %7, 0;\n\t"
-            "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], da, db, %4, [%5], [%6], p;\n\t}"
-            :: "r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
-            : "memory");
+// D[tmem] (+)= (A * sfA) x (B * sfB)^T, E2M1 operands from shared memory, K = 64 per instruction; the 64-bit
+// descriptors are passed as halves (see above). MX = false: NVFP4, one UE4M3 scale per 16 values (scale_vec::4X);
+// MX = true: MXFP4, one UE8M0 scale per 32 values (scale_vec::2X; the instruction descriptor then carries the
+// UE8M0 flag and the scale-factor ids that pick two of the four scale bytes).
+#define NVFP4_B200_MMA(GROUP, VEC)                                                                                       \
+    asm volatile(                                                                                                        \
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"                                                                  \
+        "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\tsetp.ne.b32 p, %7, 0;\n\t"                                   \
+        "tcgen05.mma.cta_group::" GROUP ".kind::mxf4nvf4.block_scale.scale_vec::" VEC " [%0], da, db, %4, [%5], [%6], p;\n\t}" \
+        :: "r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)   \
+        : "memory")
+template <int CG, bool MX>
+__device__ __forceinline__ void mma_block_scaled(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi,
+                                                 uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+    if constexpr (CG == 1 && !MX) NVFP4_B200_MMA("1", "4X");
+    else if constexpr (CG == 2 && !MX) NVFP4_B200_MMA("2", "4X");
+    else if constexpr (CG == 1 && MX) NVFP4_B200_MMA("1", "2X");
+    else NVFP4_B200_MMA("2", "2X");
 }
+#undef NVFP4_B200_MMA
 
 // D[tmem] (+)= (A * sfA) x (B * sfB)^T, E2M1 operands from shared memory, one
 // UE4M3 scale per 16 values along K, K = 64 per instruction.

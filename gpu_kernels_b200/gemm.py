@@ -20,7 +20,9 @@ def _stream() -> int:
 
 
 class Nvfp4Gemm:
-    def __init__(self, a_packed, b_packed, sfa, sfb, alpha: float = 1.0, workspace: torch.Tensor | None = None):
+    def __init__(self, a_packed, b_packed, sfa, sfb, alpha: float = 1.0, workspace: torch.Tensor | None = None,
+                 mx: bool = False):
+        """mx = True: the operands are MXFP4 (one UE8M0 scale per 32 values, from `quantize_mx`)."""
         for name, t in (("a_packed", a_packed), ("b_packed", b_packed), ("sfa", sfa), ("sfb", sfb)):
             if not (t.is_cuda and t.dtype == torch.uint8 and t.is_contiguous()):
                 raise ValueError(f"{name} must be a contiguous CUDA uint8 tensor")
@@ -29,19 +31,26 @@ class Nvfp4Gemm:
         if half_k != half_kb:
             raise ValueError("A and B disagree on K")
         self.k = 2 * half_k
-        if sfa.numel() != self.m * self.k // 16 or sfb.numel() != self.n * self.k // 16:
-            raise ValueError("scale tensors must hold rows*K/16 bytes")
+        per = 32 if mx else 16
+        if sfa.numel() != self.m * self.k // per or sfb.numel() != self.n * self.k // per:
+            raise ValueError(f"scale tensors must hold rows*K/{per} bytes")
+        self.mx = mx
         self._keep = (a_packed, b_packed, sfa, sfb, workspace)
         self.device = a_packed.device
         self.out_dtype = torch.float16
         self._plan = ctypes.c_void_p()
         lib = _lib.load()
         with torch.cuda.device(self.device):
-            _lib.check(lib.gpu_kernels_nvfp4_plan_create(
-                ctypes.byref(self._plan), self.m, self.n, self.k, a_packed.data_ptr(), b_packed.data_ptr(),
-                sfa.data_ptr(), sfb.data_ptr(),
-                workspace.data_ptr() if workspace is not None else None,
-                workspace.numel() if workspace is not None else 0, _stream()))
+            if mx:
+                _lib.check(lib.gpu_kernels_nvfp4_plan_create_mx(
+                    ctypes.byref(self._plan), self.m, self.n, self.k, a_packed.data_ptr(), b_packed.data_ptr(),
+                    sfa.data_ptr(), sfb.data_ptr(), _stream()))
+            else:
+                _lib.check(lib.gpu_kernels_nvfp4_plan_create(
+                    ctypes.byref(self._plan), self.m, self.n, self.k, a_packed.data_ptr(), b_packed.data_ptr(),
+                    sfa.data_ptr(), sfb.data_ptr(),
+                    workspace.data_ptr() if workspace is not None else None,
+                    workspace.numel() if workspace is not None else 0, _stream()))
         if alpha != 1.0:
             self.set_alpha(alpha)
 

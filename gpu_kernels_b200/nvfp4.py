@@ -88,3 +88,36 @@ def unpack_scales(scales: torch.Tensor, rows: int, k: int) -> torch.Tensor:
     """VEC16 bytes -> [rows, K/16] bytes (reference/python/nvfp4.py:24-27, without the float cast)."""
     return (scales.reshape(rows // 128, k // 64, 32, 4, 4)
             .permute(0, 3, 2, 1, 4).contiguous().reshape(rows, k // 16))
+
+
+def quantize_mx(values: torch.Tensor):
+    """MXFP4: [rows, K] -> (packed [rows, K/2] uint8, scales [rows*K/32] uint8 UE8M0 in the VEC32 atom order).
+    No counterpart in the reference; see include/nvfp4_capi.h for the rule."""
+    _require_cuda(values, "values")
+    if values.dim() != 2:
+        raise ValueError("values must be 2-D [rows, K]")
+    if values.dtype not in _DTYPES:
+        values = values.float()
+    values = values.contiguous()
+    rows, k = values.shape
+    packed = torch.empty((rows, k // 2), dtype=torch.uint8, device=values.device)
+    scales = torch.empty((rows * k // 32,), dtype=torch.uint8, device=values.device)
+    with torch.cuda.device(values.device):
+        _lib.check(_lib.load().gpu_kernels_nvfp4_quantize_mx(
+            values.data_ptr(), _DTYPES[values.dtype], packed.data_ptr(), scales.data_ptr(), rows, k, _stream()))
+    return packed, scales
+
+
+def dequantize_mx(packed: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
+    """MXFP4 bytes -> FP32 [rows, K]."""
+    _require_cuda(packed, "packed")
+    _require_cuda(scales, "scales")
+    packed, scales = packed.contiguous(), scales.contiguous()
+    rows, half_k = packed.shape
+    if scales.numel() != rows * half_k // 16:
+        raise ValueError("scales must hold rows*K/32 bytes")
+    out = torch.empty((rows, 2 * half_k), dtype=torch.float32, device=packed.device)
+    with torch.cuda.device(packed.device):
+        _lib.check(_lib.load().gpu_kernels_nvfp4_dequantize_mx(
+            packed.data_ptr(), scales.data_ptr(), out.data_ptr(), rows, 2 * half_k, _stream()))
+    return out

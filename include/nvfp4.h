@@ -64,6 +64,7 @@ struct Nvfp4Params {
     // others ragged_base; B64 is B's tensor map with 64-row boxes.
     CUtensorMap B64;
     int ragged_base, ragged_extra, ragged_units;
+    int mx;                         // 1: MXFP4 operands (one UE8M0 scale per 32 values), see mxfp4_prepare
 };
 
 struct Nvfp4Implementation {
@@ -85,6 +86,14 @@ Nvfp4Implementation nvfp4_sm100_implementation();
 
 // Extension: set the FP32 global scale of a prepared plan (takes effect at the next launch).
 void nvfp4_set_alpha(Nvfp4Params&, float alpha);
+
+// Extension: the MXFP4 flavour of the same path (OCP microscaling: E2M1 values, one UE8M0 power-of-two scale per 32
+// values along K, stored in cuBLASLt's VEC32 order: the same 512-byte atoms of 128 rows x 4 scales, ordered
+// [row/128][k/128]). Same arguments and ownership as Nvfp4Implementation::prepare; K a multiple of 128; launch and
+// validate are the implementation's. The reference has no MXFP4 path (its kernel is scale_vec::4X only,
+// kernels/gemm/matmul/sm100.cu:341-342).
+void mxfp4_prepare(Nvfp4Params&, const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB, int M, int N,
+                   int K, cudaStream_t);
 
 // Extension: synchronises the device and throws if a launch of THIS plan reported an error since the last
 // check of this plan; other plans' reports are left alone.

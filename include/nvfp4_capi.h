@@ -59,6 +59,24 @@ int gpu_kernels_nvfp4_quantize_scaled(const void* x, int dtype, float inv_tensor
 /* replaces reference/python/nvfp4.py:40-47 `dequantize`: FP32 [rows,K] out. */
 int gpu_kernels_nvfp4_dequantize(const void* packed, const void* scales, void* out_f32, int rows, int K, void* stream);
 
+/* ---- MXFP4: the adjacent format of the same instruction (no counterpart in the reference, whose kernel is
+ *      scale_vec::4X only, kernels/gemm/matmul/sm100.cu:341-342). OCP microscaling: E2M1 values packed as above, one
+ *      UE8M0 power-of-two scale per 32 values along K, in cuBLASLt's VEC32 order: the same 512-byte atoms of 128 rows x
+ *      4 scales, ordered [row/128][k/128]. rows % 128 == 0, K % 128 == 0. ---- */
+
+/* Per block of 32: e = floor(log2(amax)) - 2 clamped to [-127, 127], scale byte e + 127, codes = E2M1 of x * 2^-e with
+ * the NVFP4 quantiser's rounding (nearest, ties to the even code, saturating at 6) and sign rule (bit 3 = q < 0); an
+ * all-zero block takes e = -127; a block holding a NaN or an infinity takes scale byte 0xFF and codes 0x7. */
+int gpu_kernels_nvfp4_quantize_mx(const void* x, int dtype, void* packed, void* scales, int rows, int K, void* stream);
+/* level * sign * 2^(byte - 127) -> FP32 [rows,K]; scale byte 0xFF gives NaN. */
+int gpu_kernels_nvfp4_dequantize_mx(const void* packed, const void* scales, void* out_f32, int rows, int K, void* stream);
+/* A plan like gpu_kernels_nvfp4_plan_create's for MXFP4 operands (tcgen05.mma ... block_scale.scale_vec::2X with
+ * UE8M0 scales); run it with gpu_kernels_nvfp4_custom, check it with gpu_kernels_nvfp4_validate, free it with
+ * gpu_kernels_nvfp4_plan_destroy. Options alpha, group_m, k_skew, out_bf16, pdl, static_operands, l2_side apply;
+ * split_k, the gather and the cuBLASLt comparison do not. */
+int gpu_kernels_nvfp4_plan_create_mx(void** plan, int M, int N, int K, const void* A, const void* B, const void* SFA,
+                                     const void* SFB, void* stream);
+
 /* ---- extensions of the plan ---- */
 
 /* FP32 global scale: C = fp16(alpha * accumulator). The reference fixes alpha = 1 (nvfp4_bridge.cu:101). */

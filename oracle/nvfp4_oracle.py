@@ -147,6 +147,46 @@ def quantize_scaled(values: np.ndarray, inv_tensor_scale: float):
     return quantize(np.asarray(values, dtype=np.float32) * np.float32(inv_tensor_scale))
 
 
+def quantize_mx(values: np.ndarray):
+    """MXFP4 (this repository's extension: PARITY UNPINNED, the reference has no MXFP4 and no fixture for it).
+
+    The OCP Microscaling v1.0 conversion, restated: per 32 values along K the shared exponent is
+    e = floor(log2(amax)) - 2 (2 = the exponent of E2M1's largest value, 6 = 1.5 * 2**2), clamped to [-127, 127]
+    and stored as the UE8M0 byte e + 127; each value becomes the E2M1 code of x * 2**-e under `encode_e2m1`'s
+    rule. An all-zero block takes e = -127; a block with a NaN or an infinity takes byte 0xFF (UE8M0's NaN) and
+    codes 0x7. Scales sit in 512-byte atoms of 128 rows x 4 blocks as in the VEC16 layout, [rows/128][K/128].
+    Returns (packed uint8 [rows, K/2], scales uint8 [rows*K/32]).
+    """
+    values = np.asarray(values, dtype=np.float32)
+    rows, k = values.shape
+    assert rows % 128 == 0 and k % 128 == 0
+    blocks = values.reshape(rows, k // 32, 32)
+    with np.errstate(invalid="ignore", over="ignore"):
+        amax = np.abs(blocks).max(axis=-1)
+        special = ~np.isfinite(amax)
+        safe = np.where(special | (amax == 0), np.float32(1.0), amax)
+        _, ex = np.frexp(safe)                                        # safe = m * 2**ex, m in [0.5, 1)
+        e = np.where(amax == 0, -127, np.clip(ex.astype(np.int64) - 3, -127, 127))
+        q = blocks * np.ldexp(np.float32(1.0), -e)[..., None].astype(np.float32)
+    codes = encode_e2m1(q)
+    codes = np.where(special[..., None], np.uint8(7), codes).reshape(rows, k)
+    sbyte = np.where(special, 0xFF, e + 127).astype(np.uint8)
+    packed = codes[:, 0::2] | (codes[:, 1::2] << 4)
+    return np.ascontiguousarray(packed), pack_scales(sbyte)
+
+
+def dequantize_mx(packed: np.ndarray, scales_flat: np.ndarray) -> np.ndarray:
+    """MXFP4 bytes -> FP32 [rows, K]: level * sign * 2**(byte - 127); byte 0xFF gives NaN."""
+    rows, half_k = packed.shape
+    k = 2 * half_k
+    codes = np.stack((packed & 15, packed >> 4), axis=-1).reshape(rows, k)
+    vals = E2M1_LEVELS[codes & 7] * (1.0 - 2.0 * (codes >> 3).astype(np.float32))
+    sb = unpack_scales_u8(scales_flat, rows, k // 2).astype(np.int64)  # blocks of 32: the K/2-wide VEC16 order
+    s = np.where(sb == 0xFF, np.float32(np.nan), np.ldexp(np.float32(1.0), np.minimum(sb, 254) - 127)).astype(np.float32)
+    with np.errstate(invalid="ignore"):
+        return (vals.reshape(rows, -1, 32) * s[..., None]).reshape(rows, k).astype(np.float32)
+
+
 def dequantize(packed: np.ndarray, scales_flat: np.ndarray) -> np.ndarray:
     """Stored bytes -> FP32 [rows, K] (reference/python/nvfp4.py:40-47)."""
     rows, half_k = packed.shape

@@ -119,3 +119,29 @@ def test_expert_streaming_oracle_matches_the_whole_layer_oracle():
     zero_weight[2, 1] = 0.0
     assert np.array_equal(MO.moe_forward_nvfp4_experts(x, dropped, wts, pick),
                           MO.moe_forward_nvfp4(x, ids, zero_weight, w1, w2))
+
+
+def test_mxfp4_oracle_round_trip_and_known_answers():
+    # no reference fixture exists for MXFP4 (the reference has none): known answers from the format's definition
+    x = np.zeros((128, 128), dtype=np.float32)
+    x[0, :8] = [6.0, -6.0, 3.0, 0.5, 0.25, 0.75, -0.2, 7.0]            # amax 7: e = floor(log2 7) - 2 = 0
+    x[1, :4] = [1.0, 0.1, -0.6, 0.3]                                    # amax 1: e = -2, steps of 0.125
+    x[2, 32:36] = [2.0 ** 20, 3 * 2.0 ** 18, 0, 0]                      # e = 18
+    x[3, 0] = np.inf
+    packed, scales = O.quantize_mx(x)
+    u = O.unpack_scales_u8(scales, 128, 64)
+    assert [u[0, 0], u[1, 0], u[2, 1], u[3, 0], u[4, 0]] == [127, 125, 145, 255, 0]
+    codes = np.stack((packed & 15, packed >> 4), axis=-1).reshape(128, 128)
+    assert codes[0, :8].tolist() == [7, 15, 5, 1, 0, 2, 8, 7]          # ties to the even code; -0.2 keeps its sign
+    assert codes[1, :4].tolist() == [6, 1, 12, 2]                       # 4.0, 0.4 -> 0.5, -2.4 -> -2, 1.2 -> 1.0
+    assert codes[2, 32:34].tolist() == [6, 5] and (codes[3, :32] == 7).all()
+    back = O.dequantize_mx(packed, scales)
+    assert back[0, :8].tolist() == [6.0, -6.0, 3.0, 0.5, 0.0, 1.0, -0.0, 6.0]
+    assert back[2, 32] == 2.0 ** 20 and back[2, 33] == 3 * 2.0 ** 18 and np.isnan(back[3, :32]).all()
+    # idempotence: what the format can hold survives a second pass bit for bit
+    rng = np.random.default_rng(3)
+    y = (rng.standard_normal((256, 384)) * np.exp2(rng.integers(-20, 20, (256, 1)))).astype(np.float32)
+    p1, s1 = O.quantize_mx(y)
+    p2, s2 = O.quantize_mx(O.dequantize_mx(p1, s1))
+    d1, d2 = O.dequantize_mx(p1, s1), O.dequantize_mx(p2, s2)
+    assert np.array_equal(d1, d2)
