@@ -69,6 +69,7 @@ enum Epi : int {
     EPI_GATHER_DIRECT = 6, // the same with register stores
     EPI_SPLIT_K = 7,       // FP32 partial sums + finish (to C or to every rank's full C)
     EPI_DIRECT_RAGGED = 8, // EPI_DIRECT on single-CTA tiles of unequal width (see GemmArgs::ragged_base)
+    EPI_DIRECT_EDGE = 9,   // EPI_DIRECT with rows >= M and columns >= N masked (M, N not multiples of the tile), 16-byte stores
 };
 
 // MX: the MXFP4 flavour of the same instruction: one UE8M0 (power-of-two) scale per 32 values, so a 512-byte
@@ -105,7 +106,7 @@ struct Config {
     // launch with one tile per CTA. The routes that stage in shared memory keep one warp per quarter (a second
     // set of staging buffers would cost a ring stage), as does split-K.
     static constexpr int EPI_WARPS = (EPI == EPI_DIRECT || EPI == EPI_ACT || EPI == EPI_SCATTER || EPI == EPI_GATHER_DIRECT ||
-                                      EPI == EPI_DIRECT_RAGGED) ? 8 : 4;
+                                      EPI == EPI_DIRECT_RAGGED || EPI == EPI_DIRECT_EDGE) ? 8 : 4;
     static constexpr bool RAGGED = EPI == EPI_DIRECT_RAGGED;
     static_assert(!RAGGED || (CG == 1 && UN == 256), "ragged tiles are single-CTA tiles of up to 256 columns");
     static constexpr int THREADS = (2 + EPI_WARPS) * 32;        // warps 0-3 epilogue, 4 MMA, 5 producer, 6-9 epilogue
@@ -575,6 +576,22 @@ struct Roles {
         }
     }
 
+    // The same for a tile that reaches beyond C: nothing leaves for a row >= M, and of the chunk's 64 columns only
+    // the first cols_left (a multiple of 8: N is) are written, in 16-byte stores (a row of C starts on a 16-byte
+    // boundary, not on a 32-byte one).
+    __device__ __forceinline__ void store_row_chunk_edge(uint16_t* dst, const uint32_t (&v)[EPI_COLS], float alpha, bool row_ok,
+                                                         int cols_left) const {
+        #pragma unroll
+        for (int q = 0; q < EPI_COLS / 8; ++q) {
+            uint32_t h[4];
+            #pragma unroll
+            for (int i = 0; i < 4; ++i) h[i] = pack_pair(v[q * 8 + 2 * i], v[q * 8 + 2 * i + 1], alpha);
+            if (row_ok && q * 8 < cols_left)
+                asm volatile("st.global.L1::no_allocate.v4.b32 [%0], {%1, %2, %3, %4};"
+                             :: "l"(dst + q * 8), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]) : "memory");
+        }
+    }
+
     // Destination of pool row `row` on the scatter routes: false = nothing to deliver (a padding row, or a
     // code outside the agreed buffers, which is reported through the status word).
     __device__ __forceinline__ bool scatter_target(int row, uint16_t*& base) const {
@@ -792,6 +809,9 @@ struct Roles {
                                         v, alpha, true);
                 } else if constexpr (EPI == EPI_DIRECT || EPI == EPI_DIRECT_RAGGED) {
                     store_row_chunk(static_cast<uint16_t*>(g.c) + size_t(row0 + lane) * g.ldc + col0 + chunk * EPI_COLS, v, alpha, true);
+                } else if constexpr (EPI == EPI_DIRECT_EDGE) {
+                    store_row_chunk_edge(static_cast<uint16_t*>(g.c) + size_t(row0 + lane) * g.ldc + col0 + chunk * EPI_COLS, v, alpha,
+                                         row0 + lane < g.M, g.N - (col0 + chunk * EPI_COLS));
                 } else {
                     // EPI_TMA / EPI_GATHER_TMA: the chunk goes through one of the warp's two swizzled buffers
                     const uint32_t buf = stage_base + (stores & 1u) * Cfg::EPI_WARP_BYTES;
@@ -975,7 +995,7 @@ CUtensorMap operand_map(const uint8_t* p, int rows, int K, int box_rows) {
 // atom_k: K values one scale atom covers (64 for NVFP4's scale per 16, 128 for MXFP4's scale per 32).
 CUtensorMap scale_map(const uint8_t* p, int rows, int K, int atom_k = 64) {
     const cuuint64_t per_block = cuuint64_t(K / atom_k) * 4;
-    const cuuint64_t shape[3] = {128, per_block, cuuint64_t(rows / 128)};
+    const cuuint64_t shape[3] = {128, per_block, cuuint64_t((rows + 127) / 128)};       // a last partial row block is a whole atom
     const cuuint64_t strides[2] = {128, per_block * 128};
     const cuuint32_t box[3] = {128, cuuint32_t(STAGE_K / atom_k * 4), 1};
     return make_map(CU_TENSOR_MAP_DATA_TYPE_UINT8, p, 3, shape, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE,
@@ -1084,7 +1104,7 @@ std::atomic<unsigned> g_next_slot{0};
 bool set_ragged_tiles(gpu_kernels::Nvfp4Params& p, const uint8_t* B, int tiles) {
     p.ragged_base = p.ragged_extra = p.ragged_units = 0;
     if (tiles <= 0 || !B) return false;
-    if (p.mx || p.M != 128 || p.cta_group != 1 || p.tile_n != 256 || p.N % 64) return false;
+    if (p.mx || p.M != 128 || p.cta_group != 1 || p.tile_n != 256 || p.N % 128) return false;
     const int units = p.N / 64, base = units / tiles, extra = units % tiles;
     if ((base != 2 && base != 3) || tiles <= p.N / 256) return false;
     p.B64 = operand_map(B, p.N, p.K, 64);
@@ -1098,7 +1118,7 @@ void prepare_format(gpu_kernels::Nvfp4Params& p, const uint8_t* A, const uint8_t
                     int M, int N, int K, bool mx) {
     require_sm100();
     if (M <= 0 || N <= 0 || K <= 0) throw std::invalid_argument("nvfp4 gemm: M, N, K must be positive");
-    if (M % 128 || N % 128) throw std::invalid_argument("nvfp4 gemm: M and N must be multiples of 128 (whole scale atoms)");
+    if (N % 8) throw std::invalid_argument("nvfp4 gemm: N must be a multiple of 8 (rows of C start on 16-byte boundaries)");
     if (K % (mx ? 128 : 64)) throw std::invalid_argument(mx ? "mxfp4 gemm: K must be a multiple of 128 (whole scale atoms)"
                                                               : "nvfp4 gemm: K must be a multiple of 64 (whole scale atoms)");
     if (!A || !B || !SFA || !SFB) throw std::invalid_argument("nvfp4 gemm: null operand pointer");
@@ -1115,10 +1135,14 @@ void prepare_format(gpu_kernels::Nvfp4Params& p, const uint8_t* A, const uint8_t
     p.c_evict_first = env_int("NVFP4_B200_C_EVICT_FIRST", 1);
 
     const int force = env_int("NVFP4_B200_VARIANT", 0);        // 0 auto, 2256 / 1256 / 1128 for experiments
-    if ((force == 0 && M % 256 == 0 && N % 256 == 0) || force == 2256) { p.cta_group = 2; p.tile_n = 256; }
-    else if ((force == 0 && N % 256 == 0) || force == 1256) { p.cta_group = 1; p.tile_n = 256; }
+    // M and N need not be whole tiles: the scale arrays end in whole 128-row atoms whatever the row count (rows
+    // the tensor does not have read as zeros through the tensor maps), and the variant is chosen for the sizes
+    // rounded up to 128.
+    const int Mp = (M + 127) / 128 * 128, Np = (N + 127) / 128 * 128;
+    if ((force == 0 && Mp % 256 == 0 && Np % 256 == 0) || force == 2256) { p.cta_group = 2; p.tile_n = 256; }
+    else if ((force == 0 && Np % 256 == 0) || force == 1256) { p.cta_group = 1; p.tile_n = 256; }
     else { p.cta_group = 1; p.tile_n = 128; }
-    if (M % (128 * p.cta_group) || N % p.tile_n) throw std::invalid_argument("nvfp4 gemm: forced variant does not divide the shape");
+    if (Mp % (128 * p.cta_group) || Np % p.tile_n) throw std::invalid_argument("nvfp4 gemm: forced variant does not divide the shape");
     // Epilogue route. C leaves from registers (32-byte stores, two epilogue warps per Tensor Memory lane
     // quarter) unless the caller asks for the staged route (rows through swizzled shared memory, TMA stores):
     // measured by graph replay under sustained load, registers / staged: 8192^3 222.0 / 227.2 us, 16384^3
@@ -1129,15 +1153,15 @@ void prepare_format(gpu_kernels::Nvfp4Params& p, const uint8_t* A, const uint8_t
     p.B = operand_map(B, N, K, box_b);
     p.SFA = scale_map(SFA, M, K, mx ? 128 : 64);
     p.SFB = scale_map(SFB, N, K, mx ? 128 : 64);
-    const int tiles = (M / (128 * p.cta_group)) * (N / p.tile_n);
+    const int tiles = (Mp / (128 * p.cta_group)) * (Np / p.tile_n);
     p.clusters = std::min(fit_units(device, p.cta_group, p.tile_n), tiles);
     // About sqrt(units) tile rows per band keeps the A and B panels of the tiles in flight balanced.
     int gm = 1;
     while ((gm + 1) * (gm + 1) <= p.clusters) ++gm;
     // Measured at 16384^3 (64 x 64 tiles, operands beyond L2): bands of 16 beat 8 by 1.3 %, 32 and 4 lose 10 %;
     // at 8192^3 (everything L2-resident) the band height does not matter.
-    if (M / (128 * p.cta_group) >= 48) gm = std::max(gm, 16);
-    p.group_m = std::max(1, std::min(env_int("NVFP4_B200_GROUP_M", gm), M / (128 * p.cta_group)));
+    if (Mp / (128 * p.cta_group) >= 48) gm = std::max(gm, 16);
+    p.group_m = std::max(1, std::min(env_int("NVFP4_B200_GROUP_M", gm), Mp / (128 * p.cta_group)));
     // Measured: 128x28672x8192 30.2 -> 28.9 us, 8192^3 199.8 -> 199.0 us with the tiles' K walks de-phased.
     p.k_skew = env_int("NVFP4_B200_K_SKEW", 11);
     // One tile row whose 256-column tiles would leave SMs idle can deal its columns, in units of 64, to as many
@@ -1164,6 +1188,7 @@ void set_gather(gpu_kernels::Nvfp4Params& p, void* const* buffers, int world, in
                 cudaStream_t stream) {
     if (world == 0) { p.gather_world = 0; p.gather_maps = nullptr; p.gather_ptrs = nullptr; return; }
     if (!buffers || !table || world < 1 || world > 64) throw std::invalid_argument("nvfp4 gemm gather: 1..64 destination buffers and a table");
+    if (p.M % 128 || p.N % 128) throw std::invalid_argument("nvfp4 gemm gather: M and the slab width must be multiples of 128");
     if (col0 < 0 || col0 % 64 || n_total % 8 || col0 + p.N > n_total)
         throw std::invalid_argument("nvfp4 gemm gather: the slab [col0, col0 + N) must lie inside the full C, col0 a multiple of 64");
     if (reinterpret_cast<uintptr_t>(table) & 127) throw std::invalid_argument("nvfp4 gemm gather: table must be 128-byte aligned");
@@ -1191,6 +1216,7 @@ void set_gather(gpu_kernels::Nvfp4Params& p, void* const* buffers, int world, in
 // 1024x2048x4096 18.1 / 12.9): publishing, waiting for the slowest slice and re-reading the partial sums cost
 // about 17k cycles, which is what a quarter of a 32-step K loop saves.
 int split_k_factor(const gpu_kernels::Nvfp4Params& p) {
+    if (p.M % 128 || p.N % 128) return 0;
     const int tiles = (p.M / (128 * p.cta_group)) * (p.N / p.tile_n);
     const int fit = fit_units(p.device, p.cta_group, p.tile_n);
     const int ksteps = (p.K + STAGE_K - 1) / STAGE_K, chunks = p.tile_n / EPI_COLS;
@@ -1228,8 +1254,8 @@ GemmArgs dense_args(const gpu_kernels::Nvfp4Params& p, void* c, unsigned long lo
     GemmArgs g{};
     g.M = p.M; g.N = p.N; g.K = p.K;
     g.ksteps = (p.K + STAGE_K - 1) / STAGE_K;
-    g.tiles_m = p.M / tile_m;
-    g.tiles_n = p.N / p.tile_n;
+    g.tiles_m = (p.M + tile_m - 1) / tile_m;
+    g.tiles_n = (p.N + p.tile_n - 1) / p.tile_n;
     g.group_m = std::max(1, p.group_m);
     g.alpha = p.alpha;
     g.status = status_slot(p.device, p.status_slot);
@@ -1268,9 +1294,12 @@ void launch_dense(const gpu_kernels::Nvfp4Params& p, const CUtensorMap& tmC, con
     const bool pdl = p.pdl != 0 && !g.prof;
     const int dev = p.device, units = p.clusters;
     if (p.mx) {
-        // MXFP4 plans have the register-store route only
+        // MXFP4 plans have the masked register-store route only
         if (p.split_k > 1 || p.gather_world || g.prof) throw std::invalid_argument("mxfp4 gemm: plain launches only");
-        launch_instance<CG, UN, EPI_DIRECT, false, true>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream, pdl);
+        launch_instance<CG, UN, EPI_DIRECT_EDGE, false, true>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream, pdl);
+    } else if (p.M % 128 || p.N % 128) {
+        if (p.split_k > 1 || p.gather_world || g.prof) throw std::invalid_argument("nvfp4 gemm: M or N is no multiple of 128: plain launches only");
+        launch_instance<CG, UN, EPI_DIRECT_EDGE>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream, pdl);
     } else if (p.split_k > 1) {
         launch_instance<CG, UN, EPI_SPLIT_K>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream, pdl);
     } else if (p.gather_world) {
@@ -1523,7 +1552,8 @@ bool nvfp4_set_l2_side_order(Nvfp4Params& p, int on, cudaStream_t stream) {
     p.side_units[0] = p.side_units[1] = 0;
     if (!on || p.split_k > 1) return false;
     nvfp4_b200::TileRoute r{};
-    const int tiles_m = p.M / (128 * p.cta_group), tiles_n = p.N / p.tile_n;
+    const int tile_m = 128 * p.cta_group;
+    const int tiles_m = (p.M + tile_m - 1) / tile_m, tiles_n = (p.N + p.tile_n - 1) / p.tile_n;
     if (!nvfp4_b200::l2_side_route(p.device, p.cta_group, p.clusters, tiles_m, tiles_n, p.group_m,
                                    nvfp4_b200::gemm_smem_bytes(p.cta_group, p.tile_n), stream, r))
         return false;

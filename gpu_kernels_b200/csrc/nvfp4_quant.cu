@@ -56,10 +56,13 @@ __device__ __forceinline__ uint32_t quantise_from(const T* p, uint2& out) {
 // 4 CTAs 34.9 us, 5 CTAs, which leaves no registers for the loads ahead, 39.1 us).
 // COLS: K values per CTA tile (256 = four scale atoms, or 128 = two). The narrower tile gives twice the CTAs,
 // which evens out the last wave of a grid that is only a few waves long.
-template <typename T, int COLS>
+// TAIL: the instance for a last row tile that the tensor fills only in part (rows % 128 != 0), launched for that
+// tile alone (row_tile0 = its index): rows the tensor does not have are read as zeros, which gives them the scale
+// byte of a zero block (0x01) in the atom and no packed bytes.
+template <typename T, int COLS, bool TAIL = false>
 __global__ void __launch_bounds__(Q_THREADS, 4)
 quantise_kernel(const T* __restrict__ x, uint8_t* __restrict__ packed, uint8_t* __restrict__ scales,
-                int rows, int K) {
+                int rows, int K, int row_tile0) {
     constexpr int BLOCKS = COLS / 16;                           // 16-value blocks across the tile
     constexpr int ROWS_PER_PASS = Q_THREADS / BLOCKS;
     constexpr int PASSES = Q_ROWS / ROWS_PER_PASS;
@@ -68,11 +71,13 @@ quantise_kernel(const T* __restrict__ x, uint8_t* __restrict__ packed, uint8_t* 
     const int kb = threadIdx.x % BLOCKS;                        // 16-value block inside the tile
     const int row_in_pass = threadIdx.x / BLOCKS;
     const int col0 = blockIdx.x * COLS;
-    const int row_base = blockIdx.y * Q_ROWS;
+    const int row_tile = blockIdx.y + row_tile0;
+    const int row_base = row_tile * Q_ROWS;
     const int k = col0 + kb * 16;
     const bool live = k < K;                                    // K is a multiple of 64, the tile of COLS
     auto emit = [&](int r, uint32_t sbyte, const uint2& out) {
-        *reinterpret_cast<uint2*>(packed + size_t(row_base + r) * (K / 2) + k / 2) = out;
+        if (!TAIL || row_base + r < rows)
+            *reinterpret_cast<uint2*>(packed + size_t(row_base + r) * (K / 2) + k / 2) = out;
         sf_tile[(kb >> 2) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (kb & 3)] = static_cast<uint8_t>(sbyte);
     };
     if constexpr (sizeof(T) == 2) {
@@ -83,6 +88,7 @@ quantise_kernel(const T* __restrict__ x, uint8_t* __restrict__ packed, uint8_t* 
         auto fetch = [&](int pass, uint4& a, uint4& b) {
             const int r = pass * ROWS_PER_PASS + row_in_pass;
             const uint4* p = reinterpret_cast<const uint4*>(x + size_t(row_base + r) * K + k);
+            if (TAIL && row_base + r >= rows) { a = b = make_uint4(0u, 0u, 0u, 0u); return; }
             a = __ldg(p);
             b = __ldg(p + 1);
         };
@@ -105,7 +111,9 @@ quantise_kernel(const T* __restrict__ x, uint8_t* __restrict__ packed, uint8_t* 
             const int r = pass * ROWS_PER_PASS + row_in_pass;
             if (live) {
                 uint2 out;
-                const uint32_t sbyte = quantise_from(x + size_t(row_base + r) * K + k, out);
+                uint32_t sbyte = 0x01u;
+                if (TAIL && row_base + r >= rows) out = make_uint2(0u, 0u);
+                else sbyte = quantise_from(x + size_t(row_base + r) * K + k, out);
                 emit(r, sbyte, out);
             }
         }
@@ -114,7 +122,7 @@ quantise_kernel(const T* __restrict__ x, uint8_t* __restrict__ packed, uint8_t* 
     // The tile's atoms are consecutive in the VEC16 layout: one 16-byte store per thread.
     const int atoms = min(ATOMS, (K - col0) / 64);
     if (int(threadIdx.x) < atoms * 32) {
-        const size_t first_atom = size_t(blockIdx.y) * (K / 64) + size_t(blockIdx.x) * ATOMS;
+        const size_t first_atom = size_t(row_tile) * (K / 64) + size_t(blockIdx.x) * ATOMS;
         reinterpret_cast<uint4*>(scales + first_atom * 512)[threadIdx.x] =
             reinterpret_cast<const uint4*>(sf_tile)[threadIdx.x];
     }
@@ -136,6 +144,10 @@ quantise_scaled_kernel(const T* __restrict__ x, float inv_global, uint8_t* __res
         for (int pass = 0; pass < 8; ++pass) {
             const int r = pass * 16 + row_in_pass;
             const T* p = x + size_t(row_base + r) * K + k;
+            if (row_base + r >= rows) {                         // a row the tensor does not have: a zero block's scale
+                sf_tile[(kb >> 2) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (kb & 3)] = 0x01u;
+                continue;
+            }
             float v[16];
             if constexpr (sizeof(T) == 4) {
                 Loader<float>::load(reinterpret_cast<const float*>(p), v);
@@ -208,8 +220,12 @@ __global__ void __launch_bounds__(256)
 quantise_mx_kernel(const T* __restrict__ x, uint8_t* __restrict__ packed, uint8_t* __restrict__ scales, int rows, int K) {
     const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
     const int blocks_per_row = K / 32;
-    if (idx >= size_t(rows) * blocks_per_row) return;
+    if (idx >= size_t((rows + 127) / 128 * 128) * blocks_per_row) return;
     const int r = int(idx / blocks_per_row), b = int(idx % blocks_per_row);
+    if (r >= rows) {                                            // a row the tensor does not have: a zero block's scale
+        scales[scale_byte_offset(r, b, K / 2)] = 0u;
+        return;
+    }
     const T* p = x + size_t(r) * K + size_t(b) * 32;
     float v[32];
     if constexpr (sizeof(T) == 4) {
@@ -288,7 +304,6 @@ dequantise_mx_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restri
 
 void check_quant_shape(int rows, int K) {
     if (rows <= 0 || K <= 0) throw std::invalid_argument("nvfp4 quantise: rows and K must be positive");
-    if (rows % 128 != 0) throw std::invalid_argument("nvfp4 quantise: rows must be a multiple of 128");
     if (K % 64 != 0) throw std::invalid_argument("nvfp4 quantise: K must be a multiple of 64");
 }
 
@@ -306,12 +321,13 @@ void quantise(const void* x, int dtype, uint8_t* packed, uint8_t* scales, int ro
     const bool narrow = K % 128 == 0 && wide_ctas < 2LL * 4 * sms;
     auto launch = [&](auto tag) {
         using T = decltype(tag);
+        const int full = rows / Q_ROWS;                         // whole row tiles; a last partial one goes to the TAIL instance
         if (narrow) {
-            const dim3 grid(K / 128, rows / Q_ROWS);
-            quantise_kernel<T, 128><<<grid, Q_THREADS, 0, stream>>>(static_cast<const T*>(x), packed, scales, rows, K);
+            if (full) quantise_kernel<T, 128><<<dim3(K / 128, full), Q_THREADS, 0, stream>>>(static_cast<const T*>(x), packed, scales, rows, K, 0);
+            if (rows % Q_ROWS) quantise_kernel<T, 128, true><<<dim3(K / 128, 1), Q_THREADS, 0, stream>>>(static_cast<const T*>(x), packed, scales, rows, K, full);
         } else {
-            const dim3 grid((K + 255) / 256, rows / Q_ROWS);
-            quantise_kernel<T, 256><<<grid, Q_THREADS, 0, stream>>>(static_cast<const T*>(x), packed, scales, rows, K);
+            if (full) quantise_kernel<T, 256><<<dim3((K + 255) / 256, full), Q_THREADS, 0, stream>>>(static_cast<const T*>(x), packed, scales, rows, K, 0);
+            if (rows % Q_ROWS) quantise_kernel<T, 256, true><<<dim3((K + 255) / 256, 1), Q_THREADS, 0, stream>>>(static_cast<const T*>(x), packed, scales, rows, K, full);
         }
     };
     switch (dtype) {
@@ -331,7 +347,7 @@ void quantise_scaled(const void* x, int dtype, float inv_global, uint8_t* packed
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(packed) | reinterpret_cast<uintptr_t>(scales)) & 15)
         throw std::invalid_argument("nvfp4 quantise: pointers must be 16-byte aligned");
     if (!(inv_global > 0.0f) || !(inv_global < 3.0e38f)) throw std::invalid_argument("nvfp4 quantise: the tensor scale must be positive and finite");
-    const dim3 grid((K + 255) / 256, rows / Q_ROWS);
+    const dim3 grid((K + 255) / 256, (rows + Q_ROWS - 1) / Q_ROWS);
     switch (dtype) {
         case DTYPE_BF16:
             quantise_scaled_kernel<<<grid, Q_THREADS, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), inv_global, packed, scales, rows, K);
@@ -350,7 +366,6 @@ void quantise_scaled(const void* x, int dtype, float inv_global, uint8_t* packed
 
 void check_mx_shape(int rows, int K) {
     if (rows <= 0 || K <= 0) throw std::invalid_argument("mxfp4: rows and K must be positive");
-    if (rows % 128 != 0) throw std::invalid_argument("mxfp4: rows must be a multiple of 128");
     if (K % 128 != 0) throw std::invalid_argument("mxfp4: K must be a multiple of 128 (one scale atom covers 4 blocks of 32)");
 }
 
@@ -359,7 +374,7 @@ void quantise_mx(const void* x, int dtype, uint8_t* packed, uint8_t* scales, int
     if (!x || !packed || !scales) throw std::invalid_argument("mxfp4 quantise: null pointer");
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(packed) | reinterpret_cast<uintptr_t>(scales)) & 15)
         throw std::invalid_argument("mxfp4 quantise: pointers must be 16-byte aligned");
-    const size_t blocks = size_t(rows) * (K / 32);
+    const size_t blocks = size_t((rows + 127) / 128 * 128) * (K / 32);    // the rows of the last atom the tensor lacks get their scale byte
     const unsigned grid = static_cast<unsigned>((blocks + 255) / 256);
     switch (dtype) {
         case DTYPE_BF16: quantise_mx_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), packed, scales, rows, K); break;

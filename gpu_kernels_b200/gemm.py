@@ -32,8 +32,9 @@ class Nvfp4Gemm:
             raise ValueError("A and B disagree on K")
         self.k = 2 * half_k
         per = 32 if mx else 16
-        if sfa.numel() != self.m * self.k // per or sfb.numel() != self.n * self.k // per:
-            raise ValueError(f"scale tensors must hold rows*K/{per} bytes")
+        from .nvfp4 import scale_rows
+        if sfa.numel() != scale_rows(self.m) * self.k // per or sfb.numel() != scale_rows(self.n) * self.k // per:
+            raise ValueError(f"scale tensors must hold ceil(rows/128)*128*K/{per} bytes")
         self.mx = mx
         self._keep = (a_packed, b_packed, sfa, sfb, workspace)
         self.device = a_packed.device

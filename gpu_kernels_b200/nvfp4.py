@@ -20,13 +20,21 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+def scale_rows(rows: int) -> int:
+    """Rows the scale array of a `rows`-row tensor covers: whole 128-row atoms. The reference's layout has no
+    partial atoms (reference/python/nvfp4.py:20 asserts rows % 128 == 0); a tensor with another row count is
+    quantised as if zero rows filled its last atom (their scale bytes are those of zero blocks), and its packed
+    array keeps the true row count."""
+    return -(-rows // 128) * 128
+
+
 def _require_cuda(t: torch.Tensor, name: str) -> None:
     if not t.is_cuda:
         raise ValueError(f"{name} must be a CUDA tensor: this package has no CPU path")
 
 
 def quantize(values: torch.Tensor, tensor_scale: float | None = None):
-    """[rows, K] -> (packed [rows, K/2] uint8, scales [rows*K/16] uint8 in the VEC16 layout).
+    """[rows, K] -> (packed [rows, K/2] uint8, scales [scale_rows(rows)*K/16] uint8 in the VEC16 layout).
 
     tensor_scale (two-level scaling, not in the reference): the values are first multiplied, in FP32, by
     float32(1 / tensor_scale); the GEMM's alpha then carries the product of the operands' tensor scales."""
@@ -38,7 +46,7 @@ def quantize(values: torch.Tensor, tensor_scale: float | None = None):
     values = values.contiguous()
     rows, k = values.shape
     packed = torch.empty((rows, k // 2), dtype=torch.uint8, device=values.device)
-    scales = torch.empty((rows * k // 16,), dtype=torch.uint8, device=values.device)
+    scales = torch.empty((scale_rows(rows) * k // 16,), dtype=torch.uint8, device=values.device)
     with torch.cuda.device(values.device):
         if tensor_scale is None:
             _lib.check(_lib.load().gpu_kernels_nvfp4_quantize(
@@ -67,8 +75,8 @@ def dequantize(packed: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
     _require_cuda(scales, "scales")
     packed, scales = packed.contiguous(), scales.contiguous()
     rows, half_k = packed.shape
-    if scales.numel() != rows * half_k // 8:
-        raise ValueError("scales must hold rows*K/16 bytes")
+    if scales.numel() != scale_rows(rows) * half_k // 8:
+        raise ValueError("scales must hold ceil(rows/128)*128*K/16 bytes")
     out = torch.empty((rows, 2 * half_k), dtype=torch.float32, device=packed.device)
     with torch.cuda.device(packed.device):
         _lib.check(_lib.load().gpu_kernels_nvfp4_dequantize(
@@ -101,7 +109,7 @@ def quantize_mx(values: torch.Tensor):
     values = values.contiguous()
     rows, k = values.shape
     packed = torch.empty((rows, k // 2), dtype=torch.uint8, device=values.device)
-    scales = torch.empty((rows * k // 32,), dtype=torch.uint8, device=values.device)
+    scales = torch.empty((scale_rows(rows) * k // 32,), dtype=torch.uint8, device=values.device)
     with torch.cuda.device(values.device):
         _lib.check(_lib.load().gpu_kernels_nvfp4_quantize_mx(
             values.data_ptr(), _DTYPES[values.dtype], packed.data_ptr(), scales.data_ptr(), rows, k, _stream()))
@@ -114,8 +122,8 @@ def dequantize_mx(packed: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
     _require_cuda(scales, "scales")
     packed, scales = packed.contiguous(), scales.contiguous()
     rows, half_k = packed.shape
-    if scales.numel() != rows * half_k // 16:
-        raise ValueError("scales must hold rows*K/32 bytes")
+    if scales.numel() != scale_rows(rows) * half_k // 16:
+        raise ValueError("scales must hold ceil(rows/128)*128*K/32 bytes")
     out = torch.empty((rows, 2 * half_k), dtype=torch.float32, device=packed.device)
     with torch.cuda.device(packed.device):
         _lib.check(_lib.load().gpu_kernels_nvfp4_dequantize_mx(

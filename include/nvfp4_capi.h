@@ -25,7 +25,11 @@ extern "C" {
 const char* gpu_kernels_nvfp4_last_error(void);
 /* replaces nvfp4_bridge.cu:45-92. A [M,K/2], B [N,K/2] packed E2M1; SFA/SFB VEC16 UE4M3 scales;
  * workspace is only used by the cuBLASLt comparison path. Device pointers are baked into the
- * plan and must outlive it. Not capture-safe. */
+ * plan and must outlive it. Not capture-safe.
+ * Shapes: K % 64 == 0, N % 8 == 0, any M >= 1 (the reference wants multiples of 256 in all three,
+ * include/nvfp4.h:11). The scale arrays always end in whole atoms: ceil(rows/128)*128 * K/16 bytes; what the
+ * bytes of the rows beyond M (or N) hold does not matter. A plan whose M or N is no multiple of 128 has plain
+ * launches only (no split_k, gather, profile). */
 int gpu_kernels_nvfp4_plan_create(void** plan, int M, int N, int K, const void* A, const void* B,
                                   const void* SFA, const void* SFB, void* workspace, size_t workspace_bytes,
                                   void* stream);
@@ -46,8 +50,11 @@ int gpu_kernels_nvfp4_l2_bytes(void);
 /* ---- entry points the reference only has in Python (reference/python/nvfp4.py) ---- */
 
 /* replaces reference/python/nvfp4.py:30-37 `quantize` (+ :17-21 `pack_scales`, :6-14 `encode_e2m1`).
- * x [rows,K] device, dtype 0 = bf16, 1 = fp16, 2 = fp32; packed [rows,K/2]; scales rows*K/16 bytes.
- * rows % 128 == 0, K % 64 == 0. Bit-exact with the reference on finite and non-finite input. */
+ * x [rows,K] device, dtype 0 = bf16, 1 = fp16, 2 = fp32; packed [rows,K/2]; scales ceil(rows/128)*128 * K/16 bytes.
+ * K % 64 == 0. Bit-exact with the reference on finite and non-finite input. The reference wants rows % 128 == 0
+ * (reference/python/nvfp4.py:20); for another row count the result is the reference's for the tensor with zero
+ * rows appended up to the next multiple of 128 (their scale bytes are 0x01, a zero block's), with the packed array
+ * cut back to `rows` rows. */
 int gpu_kernels_nvfp4_quantize(const void* x, int dtype, void* packed, void* scales, int rows, int K, void* stream);
 /* Two-level scaling (no counterpart in the reference, whose quantiser has the block scales only): the same as
  * gpu_kernels_nvfp4_quantize applied to fp32(x) * inv_tensor_scale (one FP32 product per value), i.e.
@@ -62,7 +69,7 @@ int gpu_kernels_nvfp4_dequantize(const void* packed, const void* scales, void* o
 /* ---- MXFP4: the adjacent format of the same instruction (no counterpart in the reference, whose kernel is
  *      scale_vec::4X only, kernels/gemm/matmul/sm100.cu:341-342). OCP microscaling: E2M1 values packed as above, one
  *      UE8M0 power-of-two scale per 32 values along K, in cuBLASLt's VEC32 order: the same 512-byte atoms of 128 rows x
- *      4 scales, ordered [row/128][k/128]. rows % 128 == 0, K % 128 == 0. ---- */
+ *      4 scales, ordered [row/128][k/128]. K % 128 == 0; scale arrays of ceil(rows/128)*128 * K/32 bytes. ---- */
 
 /* Per block of 32: e = floor(log2(amax)) - 2 clamped to [-127, 127], scale byte e + 127, codes = E2M1 of x * 2^-e with
  * the NVFP4 quantiser's rounding (nearest, ties to the even code, saturating at 6) and sign rule (bit 3 = q < 0); an

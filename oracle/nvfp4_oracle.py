@@ -141,6 +141,25 @@ def quantize(values: np.ndarray):
     return np.ascontiguousarray(packed), pack_scales(sbyte)
 
 
+def quantize_padded(values: np.ndarray, fn=None):
+    """Any row count: the reference's `quantize` (which wants rows % 128 == 0, reference/python/nvfp4.py:20)
+    applied to the tensor with zero rows appended up to the next multiple of 128; the packed array is cut back
+    to the true rows, the scale array keeps its whole atoms. fn: `quantize` (default) or `quantize_mx`."""
+    values = np.asarray(values, dtype=np.float32)
+    rows = values.shape[0]
+    pad = -rows % 128
+    packed, scales = (fn or quantize)(np.concatenate([values, np.zeros((pad, values.shape[1]), np.float32)]) if pad else values)
+    return np.ascontiguousarray(packed[:rows]), scales
+
+
+def dequantize_padded(packed: np.ndarray, scales_flat: np.ndarray, fn=None) -> np.ndarray:
+    """Inverse companion of quantize_padded: FP32 [rows, K] from a packed array with any row count."""
+    rows = packed.shape[0]
+    pad = -rows % 128
+    full = np.concatenate([packed, np.zeros((pad, packed.shape[1]), np.uint8)]) if pad else packed
+    return (fn or dequantize)(full, scales_flat)[:rows]
+
+
 def quantize_scaled(values: np.ndarray, inv_tensor_scale: float):
     """Two-level scaling (this repository's extension; the reference has block scales only): the reference's
     `quantize` applied to float32(values) * float32(inv_tensor_scale), one FP32 product per value."""

@@ -380,10 +380,68 @@ def test_argument_errors(g):
     z = lambda *s: torch.zeros(*s, dtype=torch.uint8, device="cuda")
     with pytest.raises(Nvfp4Error):          # K not a multiple of 64
         g.Nvfp4Gemm(z(128, 48), z(128, 48), z(128 * 6), z(128 * 6))
-    with pytest.raises(Nvfp4Error):          # M not a multiple of 128
+    with pytest.raises(Nvfp4Error):          # N not a multiple of 8
+        g.Nvfp4Gemm(z(128, 128), z(12, 128), z(128 * 16), z(128 * 16))
+    with pytest.raises(ValueError):          # scale arrays end in whole atoms
         g.Nvfp4Gemm(z(64, 128), z(128, 128), z(64 * 16), z(128 * 16))
     with pytest.raises(ValueError):
         g.Nvfp4Gemm(z(128, 128), z(128, 256), z(128 * 16), z(128 * 32))
+
+
+# M any, N any multiple of 8: tiles that reach beyond C (rows >= M, columns >= N are masked in the epilogue; operand
+# rows the tensors do not have read as zeros through the tensor maps)
+EDGE_SHAPES = [
+    (1, 256, 256, 1256), (1, 8, 64, 1128), (7, 136, 128, 1256), (100, 200, 512, 1256), (129, 8, 64, 1128),
+    (200, 136, 320, 2256), (300, 1000, 1024, 1256), (500, 1000, 512, 2256), (250, 248, 2240, 2256),
+    (128, 4104, 512, 1128), (4097, 264, 256, 1128), (33, 28664, 1024, 1256),
+]
+
+
+@pytest.mark.parametrize("m,n,k,variant", EDGE_SHAPES)
+def test_m_and_n_that_are_not_whole_tiles(g, m, n, k, variant):
+    a = random_operand(m, k, seed=m + 3 * k)
+    b = random_operand(n, k, seed=n + 5 * k, scale=0.05)
+    pa, sa = g.quantize(a)
+    pb, sb = g.quantize(b)
+    # what the scale bytes of the rows beyond M and N hold must not matter: NaN scales there
+    sa = sa.clone(); sb = sb.clone()
+    ua = g.unpack_scales(sa, -(-m // 128) * 128, k); ua[m:] = 0x7F
+    ub = g.unpack_scales(sb, -(-n // 128) * 128, k); ub[n:] = 0x7F
+    sa2, sb2 = g.pack_scales(ua), g.pack_scales(ub)
+    plan = g.Nvfp4Gemm(pa, pb, sa2, sb2)
+    info = plan.info()
+    assert info["cta_group"] * 1000 + info["tile_n"] == variant, info
+    whole = torch.full((m + 3, n), float("nan"), dtype=torch.float16, device="cuda")
+    whole[m:] = 77.0
+    out = whole[:m]
+    plan.run(out)
+    plan.validate()
+    ref = O.dequantize_padded(to_np(pa), to_np(sa)) @ O.dequantize_padded(to_np(pb), to_np(sb)).T
+    assert_gemm_close(out, ref, f"edge {m}x{n}x{k}")
+    assert bool((whole[m:] == 77.0).all()), "rows beyond M were written"
+    plan.set_option("out_bf16", 1)
+    got = plan.run().float().cpu().numpy()
+    assert np.linalg.norm(got - ref) / np.linalg.norm(ref) < 8e-3
+    plan.set_option("out_bf16", 0)
+    for key in ("split_k",):
+        with pytest.raises(Exception):
+            plan.set_option(key, 1)
+    plan.close()
+
+
+def test_mxfp4_edge_shapes(g):
+    for m, n, k in [(1, 264, 256), (100, 200, 512), (500, 1000, 384)]:
+        a = random_operand(m, k, seed=m + k)
+        b = random_operand(n, k, seed=n + k, scale=0.05)
+        pa, sa = g.quantize_mx(a)
+        pb, sb = g.quantize_mx(b)
+        plan = g.Nvfp4Gemm(pa, pb, sa, sb, mx=True)
+        out = plan.run(torch.full((m, n), float("nan"), dtype=torch.float16, device="cuda"))
+        plan.validate()
+        ref = (O.dequantize_padded(to_np(pa), to_np(sa), O.dequantize_mx) @
+               O.dequantize_padded(to_np(pb), to_np(sb), O.dequantize_mx).T)
+        assert_gemm_close(out, ref, f"mxfp4 edge {m}x{n}x{k}")
+        plan.close()
 
 
 def fp32_reference_on_gpu(g, pa, sa, pb, sb):

@@ -185,9 +185,43 @@ def test_full_size_slabs_match_oracle(g):
 def test_shape_errors(g):
     from gpu_kernels_b200._lib import Nvfp4Error
     with pytest.raises(Nvfp4Error):
-        g.quantize(torch.zeros(100, 64, device="cuda"))
-    with pytest.raises(Nvfp4Error):
         g.quantize(torch.zeros(128, 48, device="cuda"))
+    with pytest.raises(Nvfp4Error):
+        g.quantize(torch.zeros(0, 64, device="cuda"))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("rows,k", [(1, 64), (100, 192), (129, 256), (300, 1024), (1000, 320)])
+def test_any_row_count(g, dtype, rows, k):
+    # the reference's quantiser applied to the tensor with zero rows appended up to whole atoms, bit for bit:
+    # packed bytes of the true rows, and every byte of the scale atoms (0x01 for the rows that do not exist)
+    x = random_operand(rows, k, seed=rows + k, scale=2.0, dtype=dtype)
+    packed, scales = g.quantize(x)
+    assert packed.shape == (rows, k // 2) and scales.numel() == -(-rows // 128) * 128 * k // 16
+    want_p, want_s = O.quantize_padded(to_np(x.float()))
+    assert np.array_equal(to_np(packed), want_p) and np.array_equal(to_np(scales), want_s)
+    assert np.array_equal(to_np(g.dequantize(packed, scales)), O.dequantize_padded(want_p, want_s))
+    # the scaled and the MXFP4 quantisers follow the same rule
+    ps, ss = g.quantize(x, tensor_scale=0.37)
+    wp, ws = O.quantize_padded(to_np(x.float()) * np.float32(g.nvfp4.inverse_tensor_scale(0.37)))
+    assert np.array_equal(to_np(ps), wp) and np.array_equal(to_np(ss), ws)
+    if k % 128 == 0:
+        pm, sm = g.quantize_mx(x)
+        wp, ws = O.quantize_padded(to_np(x.float()), O.quantize_mx)
+        assert np.array_equal(to_np(pm), wp) and np.array_equal(to_np(sm), ws)
+        assert np.array_equal(to_np(g.dequantize_mx(pm, sm)), O.dequantize_padded(wp, ws, O.dequantize_mx))
+
+
+def test_a_partial_last_tile_writes_nothing_beyond_its_rows(g):
+    rows, k = 130, 256
+    x = random_operand(rows, k, seed=3)
+    whole = torch.full((rows + 64, k // 2), 0xEE, dtype=torch.uint8, device="cuda")
+    scales = torch.empty(256 * k // 16, dtype=torch.uint8, device="cuda")
+    from gpu_kernels_b200 import _lib
+    _lib.check(_lib.load().gpu_kernels_nvfp4_quantize(x.data_ptr(), 0, whole.data_ptr(), scales.data_ptr(), rows, k,
+                                                     torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert bool((whole[rows:] == 0xEE).all())
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
