@@ -26,6 +26,7 @@ SIGNATURES = {
     "gpu_kernels_nvfp4_quantize": ([P, I, P, P, I, I, P], I),
     "gpu_kernels_nvfp4_quantize_scaled": ([P, I, F, P, P, I, I, P], I),
     "gpu_kernels_nvfp4_dequantize": ([P, P, P, I, I, P], I),
+    "gpu_kernels_nvfp4_linear": ([P, P, I, P, P], I),
     "gpu_kernels_nvfp4_quantize_mx": ([P, I, P, P, I, I, P], I),
     "gpu_kernels_nvfp4_dequantize_mx": ([P, P, P, I, I, P], I),
     "gpu_kernels_nvfp4_plan_create_mx": ([ctypes.POINTER(P), I, I, I, P, P, P, P, P], I),

@@ -106,6 +106,7 @@ struct Plan {
     const void* sfa = nullptr;
     const void* sfb = nullptr;
     const void* b = nullptr;
+    const void* a = nullptr;
     void* workspace = nullptr;
     size_t workspace_bytes = 0;
     std::unique_ptr<LtMatmul> lt;
@@ -215,6 +216,7 @@ int gpu_kernels_nvfp4_plan_create(void** out, int M, int N, int K, const void* A
         plan->sfa = SFA;
         plan->sfb = SFB;
         plan->b = B;
+        plan->a = A;
         plan->workspace = workspace;
         plan->workspace_bytes = workspace_bytes;
         plan->whole_tile_units = plan->params.clusters;
@@ -243,6 +245,7 @@ int gpu_kernels_nvfp4_plan_create_mx(void** out, int M, int N, int K, const void
         plan->sfa = SFA;
         plan->sfb = SFB;
         plan->b = B;
+        plan->a = A;
         plan->whole_tile_units = plan->params.clusters;
         plan->whole_tile_direct_store = plan->params.direct_store;
         *out = plan.release();
@@ -266,6 +269,24 @@ int gpu_kernels_nvfp4_custom(void* plan, void* C, void* stream) {
     return guarded([&] {
         Plan& p = as_plan(plan);
         p.impl.launch(p.params, static_cast<__half*>(C), static_cast<cudaStream_t>(stream));
+    });
+}
+
+int gpu_kernels_nvfp4_linear(void* plan, const void* x, int dtype, void* C, void* stream) {
+    return guarded([&] {
+        Plan& p = as_plan(plan);
+        if (p.params.mx) throw std::invalid_argument("linear: NVFP4 plans only");
+        auto s = static_cast<cudaStream_t>(stream);
+        // x -> the plan's own A and SFA buffers, then the GEMM. The quantiser lets its dependents start at once
+        // and the GEMM is told that the kernel in front of it leaves B alone, so under programmatic dependent
+        // launch it sets itself up and requests its first tiles of B while the quantiser runs, and waits for the
+        // quantiser's bytes only before its first load of A.
+        nvfp4_b200::quantise(x, dtype, static_cast<uint8_t*>(const_cast<void*>(p.a)),
+                             static_cast<uint8_t*>(const_cast<void*>(p.sfa)), p.params.M, p.params.K, s);
+        gpu_kernels::Nvfp4Params q = p.params;
+        if (q.static_operands != 1) q.static_operands = 1;      // 2 would let the GEMM read A before it is written
+        p.impl.launch(q, static_cast<__half*>(C), s);
+        nvfp4_b200::g_launches.fetch_add(1, std::memory_order_relaxed);
     });
 }
 

@@ -63,6 +63,9 @@ template <typename T, int COLS, bool TAIL = false>
 __global__ void __launch_bounds__(Q_THREADS, 4)
 quantise_kernel(const T* __restrict__ x, uint8_t* __restrict__ packed, uint8_t* __restrict__ scales,
                 int rows, int K, int row_tile0) {
+    // A kernel behind this one on the stream that was launched with the programmatic stream-serialisation
+    // attribute may set itself up now; it still waits for this grid to finish before it reads what is written here.
+    asm volatile("griddepcontrol.launch_dependents;");
     constexpr int BLOCKS = COLS / 16;                           // 16-value blocks across the tile
     constexpr int ROWS_PER_PASS = Q_THREADS / BLOCKS;
     constexpr int PASSES = Q_ROWS / ROWS_PER_PASS;
@@ -71,7 +74,7 @@ quantise_kernel(const T* __restrict__ x, uint8_t* __restrict__ packed, uint8_t* 
     const int kb = threadIdx.x % BLOCKS;                        // 16-value block inside the tile
     const int row_in_pass = threadIdx.x / BLOCKS;
     const int col0 = blockIdx.x * COLS;
-    const int row_tile = blockIdx.y + row_tile0;
+    const int row_tile = TAIL ? row_tile0 : int(blockIdx.y);
     const int row_base = row_tile * Q_ROWS;
     const int k = col0 + kb * 16;
     const bool live = k < K;                                    // K is a multiple of 64, the tile of COLS

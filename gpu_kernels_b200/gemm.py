@@ -88,6 +88,20 @@ class Nvfp4Gemm:
             _lib.check(_lib.load().gpu_kernels_nvfp4_custom(self._plan, out.data_ptr(), _stream()))
         return out
 
+    def linear(self, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """x [M, K] in bf16 / fp16 / fp32 -> C = alpha * quantize(x) @ B.T: the quantiser writes the plan's own
+        A and SFA tensors (the ones given to the constructor), the GEMM starts while it runs."""
+        from .nvfp4 import _DTYPES
+        if not x.is_cuda or x.dtype not in _DTYPES or x.shape != (self.m, self.k) or not x.is_contiguous():
+            raise ValueError("x must be a contiguous CUDA tensor [M, K] of bf16, fp16 or fp32")
+        if self.mx:
+            raise ValueError("linear: NVFP4 plans only")
+        if out is None:
+            out = torch.empty((self.m, self.n), dtype=self.out_dtype, device=self.device)
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.load().gpu_kernels_nvfp4_linear(self._plan, x.data_ptr(), _DTYPES[x.dtype], out.data_ptr(), _stream()))
+        return out
+
     def profile(self, out: torch.Tensor):
         """One launch with the kernel's per-role wait counters on. Returns a list of dicts, one per CTA."""
         n = 4096 * 16

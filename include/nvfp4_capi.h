@@ -84,6 +84,14 @@ int gpu_kernels_nvfp4_dequantize_mx(const void* packed, const void* scales, void
 int gpu_kernels_nvfp4_plan_create_mx(void** plan, int M, int N, int K, const void* A, const void* B, const void* SFA,
                                      const void* SFB, void* stream);
 
+/* Activations that arrive in bf16 / fp16 / fp32 (no counterpart in the reference, which quantises in PyTorch before
+ * it builds a plan): quantises x [M,K] (dtype as gpu_kernels_nvfp4_quantize) into the plan's own A and SFA buffers
+ * (the pointers given to plan_create, which the caller therefore leaves to the plan) and runs the GEMM behind it on
+ * the same stream. B and SFB are taken to be weights nothing on the stream writes: the GEMM starts under
+ * programmatic dependent launch while the quantiser runs, requests its first tiles of B and waits for the
+ * quantiser only before it reads A. Asynchronous, capture-safe. */
+int gpu_kernels_nvfp4_linear(void* plan, const void* x, int dtype, void* C, void* stream);
+
 /* ---- extensions of the plan ---- */
 
 /* FP32 global scale: C = fp16(alpha * accumulator). The reference fixes alpha = 1 (nvfp4_bridge.cu:101). */

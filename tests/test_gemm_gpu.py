@@ -546,3 +546,47 @@ def test_split_k_is_left_off_where_it_cannot_gain(g):
         with pytest.raises(RuntimeError):
             plan.set_option("split_k", 1)
         plan.close()
+
+
+@pytest.mark.parametrize("m,n,k,dtype", [(128, 1024, 512, torch.bfloat16), (256, 512, 1024, torch.float16),
+                                         (100, 264, 256, torch.float32), (128, 7168, 2048, torch.bfloat16)])
+def test_linear_quantises_into_the_plan_and_multiplies(g, m, n, k, dtype):
+    # quantise + GEMM chained on the stream (the GEMM starts while the quantiser runs): the plan's A and SFA hold
+    # exactly what `quantize` gives, C is bit-equal to the two-call sequence, also when replayed from a graph
+    # with other activations each time
+    b = random_operand(n, k, seed=9, scale=0.05)
+    pb, sb = g.quantize(b)
+    pa = torch.zeros((m, k // 2), dtype=torch.uint8, device="cuda")
+    sa = torch.zeros(g.nvfp4.scale_rows(m) * k // 16, dtype=torch.uint8, device="cuda")
+    plan = g.Nvfp4Gemm(pa, pb, sa, sb)
+    xs = [random_operand(m, k, seed=40 + i, dtype=torch.float32).to(dtype) for i in range(3)]
+    want = []
+    for x in xs:
+        qa, qs = g.quantize(x)
+        ref_plan = g.Nvfp4Gemm(qa, pb, qs, sb)
+        want.append((qa, qs, ref_plan.run().clone()))
+        ref_plan.validate()
+        ref_plan.close()
+    for x, (qa, qs, c) in zip(xs, want):
+        out = plan.linear(x)
+        plan.validate()
+        assert torch.equal(pa, qa) and torch.equal(sa, qs)
+        assert torch.equal(out, c)
+    x_in = xs[0].clone()
+    out = torch.empty((m, n), dtype=torch.float16, device="cuda")
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            plan.linear(x_in, out)
+            plan.linear(x_in, out)
+    torch.cuda.current_stream().wait_stream(side)
+    for x, (_, _, c) in zip(xs, want):
+        x_in.copy_(x)
+        out.fill_(float("nan"))
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, c)
+    plan.validate()
+    plan.close()
