@@ -301,19 +301,10 @@ __device__ __forceinline__ void tmem_ld_wait() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// Shared memory -> Tensor Memory copy of one 32-row x 16-byte scale atom,
-// replicated into the four 32-lane quarters.
-template <int CG>
-__device__ __forceinline__ void tmem_copy_scales(uint32_t taddr, uint64_t smem_desc) {
-    if constexpr (CG == 1)
-        asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" :: "r"(taddr), "l"(smem_desc) : "memory");
-    else
-        asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" :: "r"(taddr), "l"(smem_desc) : "memory");
-}
-
-// The same two instructions with each 64-bit shared-memory descriptor passed as its two 32-bit
-// halves: the halves are warp-uniform values computed outside the one-lane issue block, and
-// only the cheap pack into a 64-bit register happens beside the instruction.
+// Shared memory -> Tensor Memory copy of one 32-row x 16-byte scale atom, replicated into the four
+// 32-lane quarters. The 64-bit shared-memory descriptor is passed as its two 32-bit halves: the halves are
+// warp-uniform values computed outside the one-lane issue block, and only the cheap pack into a 64-bit
+// register happens beside the instruction.
 template <int CG>
 __device__ __forceinline__ void tmem_copy_scales(uint32_t taddr, uint32_t desc_lo, uint32_t desc_hi) {
     if constexpr (CG == 1)
@@ -326,7 +317,7 @@ __device__ __forceinline__ void tmem_copy_scales(uint32_t taddr, uint32_t desc_l
                      :: "r"(taddr), "r"(desc_lo), "r"(desc_hi) : "memory");
 }
 // D[tmem] (+)= (A * sfA) x (B * sfB)^T, E2M1 operands from shared memory, K = 64 per instruction; the 64-bit
-// descriptors are passed as halves (see above). MX = false: NVFP4, one UE4M3 scale per 16 values (scale_vec::4X);
+// descriptors are passed as halves (as for the scale copies). MX = false: NVFP4, one UE4M3 scale per 16 values (scale_vec::4X);
 // MX = true: MXFP4, one UE8M0 scale per 32 values (scale_vec::2X; the instruction descriptor then carries the
 // UE8M0 flag and the scale-factor ids that pick two of the four scale bytes).
 #define NVFP4_B200_MMA(GROUP, VEC)                                                                                       \
@@ -345,25 +336,6 @@ __device__ __forceinline__ void mma_block_scaled(uint32_t d_tmem, uint32_t a_lo,
     else NVFP4_B200_MMA("2", "2X");
 }
 #undef NVFP4_B200_MMA
-
-// D[tmem] (+)= (A * sfA) x (B * sfB)^T, E2M1 operands from shared memory, one
-// UE4M3 scale per 16 values along K, K = 64 per instruction.
-template <int CG>
-__device__ __forceinline__ void mma_nvfp4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                          uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
-    if constexpr (CG == 1)
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %6, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
-            :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
-            : "memory");
-    else
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %6, 0;\n\t"
-            "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
-            :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
-            : "memory");
-}
 
 // Arrive on `bar` once all tcgen05 operations issued so far by this thread have
 // completed. For a pair the arrival is delivered to the same barrier offset in
