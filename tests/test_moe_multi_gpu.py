@@ -47,18 +47,22 @@ def _worker(rank, world, port, out_dir):
         for exchange, fused_dispatch in (("peer", True), ("peer", False), ("nccl", False)):
             layer = g.Nvfp4MoE(w1[rank * local:(rank + 1) * local], w2[rank * local:(rank + 1) * local], experts, topk,
                                max_tokens=128, exchange=exchange, fused_dispatch=fused_dispatch)
-            for call, tokens in enumerate((50 + 30 * rank, 7, 128)):               # ragged token counts; the last call uses 256-row blocks
+            for call, tokens in enumerate((50 + 11 * rank, 7, 128)):               # ragged token counts (at most 127); the last call uses 256-row blocks
                 gen_r = torch.Generator(device="cuda").manual_seed(1000 * call + rank)
                 x = torch.randn((tokens, hidden), generator=gen_r, device="cuda").bfloat16()
                 ids, wts = g.route(torch.randn((tokens, experts), generator=gen_r, device="cuda"), topk)
                 layer.block_rows = 256 if call == 2 else None
-                y = layer(x, ids, wts)
-                torch.cuda.synchronize()
-                ref = MO.moe_forward_nvfp4(x.float().cpu().numpy(), ids.cpu().numpy(), wts.cpu().numpy(),
-                                           w1.float().cpu().numpy(), w2.float().cpu().numpy(), 10.0)
-                got = y.float().cpu().numpy()
-                rel = np.linalg.norm(got - ref) / np.linalg.norm(ref)
-                _agree(not np.isnan(got).any() and rel <= 2e-2, f"{exchange} call {call}: rel {rel:.3e}", rank)
+                try:                                                               # an exception here is a verdict too
+                    y = layer(x, ids, wts)
+                    torch.cuda.synchronize()
+                    ref = MO.moe_forward_nvfp4(x.float().cpu().numpy(), ids.cpu().numpy(), wts.cpu().numpy(),
+                                               w1.float().cpu().numpy(), w2.float().cpu().numpy(), 10.0)
+                    got = y.float().cpu().numpy()
+                    rel = np.linalg.norm(got - ref) / np.linalg.norm(ref)
+                    ok, what = bool(not np.isnan(got).any() and rel <= 2e-2), f"rel {rel:.3e}"
+                except Exception as exc:                                           # noqa: BLE001
+                    got, ok, what = np.zeros((tokens, hidden), np.float32), False, f"{type(exc).__name__}: {exc}"
+                _agree(ok, f"{exchange} call {call}: {what}", rank)
                 # both exchanges deliver the same rows and the reduce adds them in the same order: identical bits
                 _agree(np.array_equal(outputs.setdefault(call, got), got),
                        f"call {call}: {exchange} fused_dispatch={fused_dispatch} differs from the first exchange", rank)
