@@ -50,9 +50,10 @@ SIGNATURES = {
     "gpu_kernels_nvfp4_grouped_run_scatter": ([P, P, P, P, I, I, I, P], I),
     "gpu_kernels_nvfp4_moe_payload_bytes": ([I], I),
     "gpu_kernels_nvfp4_moe_route_count": ([P, I, I, P, P], I),
-    "gpu_kernels_nvfp4_moe_route_plan": ([P, I, P, I, I, I, P, P, P, P, P, P, P, P], I),
+    "gpu_kernels_nvfp4_moe_route_plan": ([P, I, P, I, I, I, P, P, P, P, P, P, P, P, P], I),
     "gpu_kernels_nvfp4_moe_clear_live": ([P, I, I, I, P, P, P, P], I),
-    "gpu_kernels_nvfp4_moe_plan": ([P, I, I, I, I, I, P, P, P, P, P, P, P, I, P, P], I),
+    "gpu_kernels_nvfp4_moe_plan": ([P, I, I, I, I, I, P, P, P, P, P, P, P, I, P, P, P], I),
+    "gpu_kernels_nvfp4_grouped_set_valid_rows": ([P, P], I),
     "gpu_kernels_nvfp4_moe_unpack_meta": ([P, I, P, I, I, I, P, P, P, P, P, P], I),
     "gpu_kernels_nvfp4_moe_count_exchange": ([P, I, I, P, P, I, I, I, P, P], I),
     "gpu_kernels_nvfp4_moe_pack": ([P, P, P, P, I, I, I, I, P, P, P, P, P], I),

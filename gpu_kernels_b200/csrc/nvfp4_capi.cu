@@ -552,6 +552,13 @@ int gpu_kernels_nvfp4_grouped_plan_create(void** out, int pool_rows, int n, int 
 
 void gpu_kernels_nvfp4_grouped_plan_destroy(void* plan) { delete static_cast<nvfp4_b200::GroupedGemm*>(plan); }
 
+int gpu_kernels_nvfp4_grouped_set_valid_rows(void* plan, const void* block_valid) {
+    return guarded([&] {
+        if (!plan) throw std::invalid_argument("grouped set_valid_rows: null plan");
+        static_cast<nvfp4_b200::GroupedGemm*>(plan)->block_valid = static_cast<const int*>(block_valid);
+    });
+}
+
 int gpu_kernels_nvfp4_grouped_run(void* plan, void* C, int out_bf16, void* stream) {
     return guarded([&] {
         if (!plan) throw std::invalid_argument("null plan");
@@ -596,10 +603,11 @@ int gpu_kernels_nvfp4_moe_route_count(const void* ids, int routes, int experts, 
 
 int gpu_kernels_nvfp4_moe_plan(const void* counts_matrix, int world, int rank, int experts, int capacity_rows,
                                int block_rows, void* send_offset, void* seg_src_offset, void* seg_pool_offset, void* block_expert,
-                               void* num_blocks, void* totals, void* peer_offset, int peer_to_pool, void* cursor, void* stream) {
+                               void* num_blocks, void* totals, void* peer_offset, int peer_to_pool, void* cursor, void* block_valid,
+                               void* stream) {
     return guarded([&] {
         nvfp4_b200::require_sm100();
-        nvfp4_b200::moe_plan(const_cast<int*>(static_cast<const int*>(counts_matrix)), world, rank, experts, capacity_rows,
+        nvfp4_b200::moe_plan(static_cast<int*>(block_valid), const_cast<int*>(static_cast<const int*>(counts_matrix)), world, rank, experts, capacity_rows,
                              block_rows, static_cast<int*>(send_offset), static_cast<int*>(seg_src_offset),
                              static_cast<int*>(seg_pool_offset), static_cast<int*>(block_expert),
                              static_cast<int*>(num_blocks), static_cast<int*>(totals), static_cast<int*>(peer_offset),
@@ -610,11 +618,11 @@ int gpu_kernels_nvfp4_moe_plan(const void* counts_matrix, int world, int rank, i
 
 int gpu_kernels_nvfp4_moe_route_plan(const void* ids, int routes, void* counts, int experts, int capacity_rows, int block_rows,
                                      void* send_offset, void* seg_src_offset, void* seg_pool_offset, void* block_expert,
-                                     void* num_blocks, void* totals, void* cursor, void* stream) {
+                                     void* num_blocks, void* totals, void* cursor, void* block_valid, void* stream) {
     return guarded([&] {
         nvfp4_b200::require_sm100();
         if (!ids || !counts || !cursor) throw std::invalid_argument("moe route_plan: null pointer");
-        nvfp4_b200::moe_plan(static_cast<int*>(counts), 1, 0, experts, capacity_rows, block_rows,
+        nvfp4_b200::moe_plan(static_cast<int*>(block_valid), static_cast<int*>(counts), 1, 0, experts, capacity_rows, block_rows,
                              static_cast<int*>(send_offset), static_cast<int*>(seg_src_offset),
                              static_cast<int*>(seg_pool_offset), static_cast<int*>(block_expert),
                              static_cast<int*>(num_blocks), static_cast<int*>(totals), nullptr,

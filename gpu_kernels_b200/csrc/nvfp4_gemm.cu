@@ -158,6 +158,10 @@ struct GemmArgs {
     const int* block_expert;
     const int* num_blocks;
     int b_rows_per_expert;
+    // Grouped mode, EPI_DIRECT_EDGE: block i holds block_valid[i] real rows followed by padding, and only the real
+    // rows of C are written (a pool of 128-row blocks with a few routes per expert is mostly padding: at 1024
+    // tokens, 256 experts, top-6 the second expert GEMM wrote 248 MB where 50 MB are rows anyone reads).
+    const int* block_valid;
     void* c;                        // C base and leading dimension (elements), used by the register-store routes
     int ldc;
     // EPI_ACT (grouped mode only): the weight rows arrive interleaved as 16 gate rows, 16 up rows, ..., so a
@@ -689,6 +693,10 @@ struct Roles {
             tile_coords(int(t), g, tm, tn, b_base);
             const int row0 = tm * Cfg::TILE_M + int(rank) * BLOCK_M + warp * 32;
             int col0 = tn * UN, chunks = UN / EPI_COLS;
+            int row_limit = g.M;                                 // EPI_DIRECT_EDGE: first row that is not written
+            if constexpr (EPI == EPI_DIRECT_EDGE || EPI == EPI_ACT) {
+                if (g.block_valid) row_limit = tm * Cfg::TILE_M + __ldg(g.block_valid + tm);
+            }
             if constexpr (Cfg::RAGGED) {
                 int width;
                 ragged_span(g, tn, col0, width);
@@ -769,10 +777,12 @@ struct Roles {
                             sb[b] = quantise_block_pairs<Bf16Pairs>(act, codes[b]);
                         }
                     }
-                    *reinterpret_cast<uint4*>(g.act_packed + size_t(row) * (inter / 2) + act_col / 2) =
-                        make_uint4(codes[0].x, codes[0].y, codes[1].x, codes[1].y);
-                    *reinterpret_cast<uint16_t*>(g.act_scales + scale_byte_offset(row, act_col / 16, inter)) =
-                        static_cast<uint16_t>(sb[0] | (sb[1] << 8));
+                    if (row < row_limit) {                        // the padding behind a block's real rows is not written: nobody reads it
+                        *reinterpret_cast<uint4*>(g.act_packed + size_t(row) * (inter / 2) + act_col / 2) =
+                            make_uint4(codes[0].x, codes[0].y, codes[1].x, codes[1].y);
+                        *reinterpret_cast<uint16_t*>(g.act_scales + scale_byte_offset(row, act_col / 16, inter)) =
+                            static_cast<uint16_t>(sb[0] | (sb[1] << 8));
+                    }
                 } else if constexpr (EPI == EPI_SCATTER_ROWS) {
                     // Scatter through shared memory: every lane stages its own row of the tile, chunk by chunk,
                     // and after the last chunk sends the UN columns (512 bytes) with ONE bulk copy to the row's
@@ -811,7 +821,7 @@ struct Roles {
                     store_row_chunk(static_cast<uint16_t*>(g.c) + size_t(row0 + lane) * g.ldc + col0 + chunk * EPI_COLS, v, alpha, true);
                 } else if constexpr (EPI == EPI_DIRECT_EDGE) {
                     store_row_chunk_edge(static_cast<uint16_t*>(g.c) + size_t(row0 + lane) * g.ldc + col0 + chunk * EPI_COLS, v, alpha,
-                                         row0 + lane < g.M, g.N - (col0 + chunk * EPI_COLS));
+                                         row0 + lane < row_limit, g.N - (col0 + chunk * EPI_COLS));
                 } else {
                     // EPI_TMA / EPI_GATHER_TMA: the chunk goes through one of the warp's two swizzled buffers
                     const uint32_t buf = stage_base + (stores & 1u) * Cfg::EPI_WARP_BYTES;
@@ -1429,6 +1439,7 @@ unsigned last_kernel_cycles() {
 void grouped_prepare(GroupedGemm& p, const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB,
                      int pool_rows, int n, int k, int experts, int block_rows, const int* block_expert,
                      const int* num_blocks) {
+    p.block_valid = nullptr;
     require_sm100();
     if (block_rows != 128 && block_rows != 256) throw std::invalid_argument("grouped gemm: block rows must be 128 or 256");
     if (pool_rows <= 0 || pool_rows % block_rows) throw std::invalid_argument("grouped gemm: pool rows must be a positive multiple of the block rows");
@@ -1481,6 +1492,7 @@ void grouped_launch_fused(const GroupedGemm& p, void* C, int out_bf16, uint8_t* 
     g.out_bf16 = out_bf16;
     g.block_expert = p.block_expert;
     g.num_blocks = p.num_blocks;
+    g.block_valid = p.block_valid;
     g.b_rows_per_expert = p.n;
     g.c = C;
     g.ldc = p.n;
@@ -1497,10 +1509,12 @@ void grouped_launch_fused(const GroupedGemm& p, void* C, int out_bf16, uint8_t* 
     if (p.block_rows == 256) {
         if (fused) launch_instance<2, 256, EPI_ACT>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream, pdl);
         else if (row_dst) launch_instance<2, 256, EPI_SCATTER_ROWS>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream, pdl);
+        else if (p.block_valid) launch_instance<2, 256, EPI_DIRECT_EDGE>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream, pdl);
         else launch_instance<2, 256, EPI_DIRECT>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream, pdl);
     } else {
         if (fused) launch_instance<1, 256, EPI_ACT>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream, pdl);
         else if (row_dst) launch_instance<1, 256, EPI_SCATTER>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream, pdl);
+        else if (p.block_valid) launch_instance<1, 256, EPI_DIRECT_EDGE>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream, pdl);
         else launch_instance<1, 256, EPI_DIRECT>(dev, units, p.A, p.B, p.SFA, p.SFB, tmC, g, stream, pdl);
     }
 }

@@ -50,6 +50,7 @@ struct GroupedGemm {
     int pool_rows, n, k, experts, units, tile_n, device, block_rows;
     const int* block_expert;
     const int* num_blocks;
+    const int* block_valid;     // real rows per block (device, from the plan kernel); null = every row of C is written
 };
 void grouped_prepare(GroupedGemm& p, const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB,
                      int pool_rows, int n, int k, int experts, int block_rows, const int* block_expert,
@@ -70,7 +71,8 @@ struct MoeShape {
     float clamp;
 };
 void moe_route_count(const long long* ids, int routes, int experts, int* counts, cudaStream_t stream);
-void moe_plan(int* counts_matrix, int world, int rank, int experts, int pool_capacity_rows, int block_rows,
+// block_valid (may be null): [pool_capacity_rows / block_rows], the real rows of every live block.
+void moe_plan(int* block_valid, int* counts_matrix, int world, int rank, int experts, int pool_capacity_rows, int block_rows,
               int* send_offset, int* seg_src_offset, int* seg_pool_offset, int* block_expert, int* num_blocks,
               int* totals, int* peer_offset, const long long* ids, int routes, int* cursor, int peer_to_pool,
               cudaStream_t stream);

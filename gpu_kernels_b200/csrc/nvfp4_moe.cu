@@ -94,7 +94,7 @@ __device__ void block_exclusive_scan(int* data, int n, int* chunk_sums) {
 }
 
 // counts[r * experts + ge]: routes rank r sends to global expert ge. One CTA of 256 threads; experts <= 4096.
-__global__ void plan_kernel(int* counts, int world, int rank, int experts, int capacity_rows,
+__global__ void plan_kernel(int* __restrict__ block_valid, int* counts, int world, int rank, int experts, int capacity_rows,
                             int block_rows,
                             int* __restrict__ send_offset, int* __restrict__ seg_src_offset,
                             int* __restrict__ seg_pool_offset, int* __restrict__ block_expert,
@@ -172,6 +172,9 @@ __global__ void plan_kernel(int* counts, int world, int rank, int experts, int c
             seg_pool_offset[r * local_experts + e] = acc;
             acc += counts[r * experts + rank * local_experts + e];
         }
+        if (block_valid && !overflow)                           // acc: one past the expert's last real row
+            for (int blk = scan[e] / block_rows; blk < end / block_rows; ++blk)
+                block_valid[blk] = min(block_rows, max(0, acc - blk * block_rows));
     }
     if (threadIdx.x == 0) {
         *num_blocks = overflow ? 0 : pool_rows / block_rows;     // an overflowing plan computes nothing; the host reports it
@@ -655,7 +658,7 @@ void moe_route_count(const long long* ids, int routes, int experts, int* counts,
     launch_chained(route_count_kernel, dim3(blocks), dim3(256), size_t(experts * sizeof(int)), stream, ids, routes, experts, counts);
 }
 
-void moe_plan(int* counts_matrix, int world, int rank, int experts, int pool_capacity_rows, int block_rows,
+void moe_plan(int* block_valid, int* counts_matrix, int world, int rank, int experts, int pool_capacity_rows, int block_rows,
               int* send_offset, int* seg_src_offset, int* seg_pool_offset, int* block_expert, int* num_blocks,
               int* totals, int* peer_offset, const long long* ids, int routes, int* cursor, int peer_to_pool,
               cudaStream_t stream) {
@@ -665,7 +668,7 @@ void moe_plan(int* counts_matrix, int world, int rank, int experts, int pool_cap
     if (block_rows != 128 && block_rows != 256) throw std::invalid_argument("moe plan: block rows must be 128 or 256");
     if (pool_capacity_rows <= 0 || pool_capacity_rows % block_rows) throw std::invalid_argument("moe plan: pool capacity must be a multiple of the block rows");
     const int local = experts / world;
-    launch_chained(plan_kernel, dim3(1), dim3(256), size_t((experts + local + 257) * sizeof(int)), stream, counts_matrix, world, rank, experts, pool_capacity_rows, block_rows,
+    launch_chained(plan_kernel, dim3(1), dim3(256), size_t((experts + local + 257) * sizeof(int)), stream, block_valid, counts_matrix, world, rank, experts, pool_capacity_rows, block_rows,
                                                                    send_offset, seg_src_offset, seg_pool_offset,
                                                                    block_expert, num_blocks, totals, peer_offset, ids, routes, cursor, peer_to_pool);
 }

@@ -107,6 +107,7 @@ class Nvfp4MoE:
         self.seg_src = torch.zeros(self.world * self.local_experts + 1, dtype=i32, device=d)
         self.seg_pool = torch.zeros(self.world * self.local_experts, dtype=i32, device=d)
         self.block_expert = torch.zeros(self.pool_rows // 128, dtype=i32, device=d)        # sized for the smaller block
+        self.block_valid = torch.zeros(self.pool_rows // 128, dtype=i32, device=d)         # real rows per block (the rest is padding)
         self.num_blocks = torch.zeros(1, dtype=i32, device=d)
         self.totals = torch.zeros(4, dtype=i32, device=d)
         self.cursor = torch.zeros(num_experts, dtype=i32, device=d)
@@ -152,6 +153,9 @@ class Nvfp4MoE:
                     ctypes.byref(fc2), self.pool_rows, self.hidden, self.inter, self.local_experts, rows,
                     self.act_packed.data_ptr(), self.w2q.data_ptr(), self.act_scales.data_ptr(), self.w2s.data_ptr(),
                     self.block_expert.data_ptr(), self.num_blocks.data_ptr()))
+                # the plain and SwiGLU routes write only the real rows of their output pools (nobody reads the rest)
+                _lib.check(lib.gpu_kernels_nvfp4_grouped_set_valid_rows(fc1, self.block_valid.data_ptr()))
+                _lib.check(lib.gpu_kernels_nvfp4_grouped_set_valid_rows(fc2, self.block_valid.data_ptr()))
                 self._plans[rows] = (fc1, fc2)
 
     def __getattr__(self, name):
@@ -225,7 +229,7 @@ class Nvfp4MoE:
                 ids.data_ptr(), routes, self.counts_matrix.data_ptr(), self.experts, self.pool_rows, block_rows,
                 self.send_offset.data_ptr(), self.seg_src.data_ptr(), self.seg_pool.data_ptr(),
                 self.block_expert.data_ptr(), self.num_blocks.data_ptr(), self.totals.data_ptr(),
-                self.cursor.data_ptr(), s))
+                self.cursor.data_ptr(), self.block_valid.data_ptr(), s))
         else:
             if self._peer is not None and routes <= 4096:
                 # small batch: histogram, peer stores of the counts and the barrier in one kernel
@@ -247,7 +251,7 @@ class Nvfp4MoE:
                 self.send_offset.data_ptr(), self.seg_src.data_ptr(), self.seg_pool.data_ptr(),
                 self.block_expert.data_ptr(), self.num_blocks.data_ptr(), self.totals.data_ptr(),
                 self.peer_offset.data_ptr() if self._peer is not None else None, 1 if self.to_pool else 0,
-                self.cursor.data_ptr(), s))
+                self.cursor.data_ptr(), self.block_valid.data_ptr(), s))
         # padding rows of the live blocks must contribute nothing: clear their scale bytes, weights and codes
         _lib.check(lib.gpu_kernels_nvfp4_moe_clear_live(
             self.num_blocks.data_ptr(), block_rows, self.pool_rows, self.hidden, self.pool_scales.data_ptr(),

@@ -182,6 +182,10 @@ int gpu_kernels_nvfp4_grouped_plan_create(void** plan, int pool_rows, int n, int
                                           const void* A, const void* B, const void* SFA, const void* SFB,
                                           const void* block_expert, const void* num_blocks);
 void gpu_kernels_nvfp4_grouped_plan_destroy(void* plan);
+/* block_valid: device array from the plan kernel (real rows per block), or NULL. With it gpu_kernels_nvfp4_grouped_run
+ * writes only the real rows of C: the padding rows of a pool of 128- or 256-row blocks (most of the pool when an
+ * expert sees a few rows) stay out of HBM, and the caller must not read them. */
+int gpu_kernels_nvfp4_grouped_set_valid_rows(void* plan, const void* block_valid);
 int gpu_kernels_nvfp4_grouped_run(void* plan, void* C, int out_bf16, void* stream);
 
 /* The first expert GEMM with the activation fused into its epilogue (FC1 + kernels/moe/swiglu.cu:12-26 + the
@@ -214,16 +218,18 @@ int gpu_kernels_nvfp4_moe_route_count(const void* ids, int routes, int experts, 
  * buffer of the rank that owns it, for gpu_kernels_nvfp4_moe_pack_peer; with peer_to_pool != 0 instead the row of
  * that rank's POOL where they start (every rank can do the owner's layout arithmetic from the gathered counts), for
  * the dispatch that writes packed rows straight into the pools. cursor [experts] (may be null): the arrival
- * counters of the dispatch kernels, zeroed here. */
+ * counters of the dispatch kernels, zeroed here. block_valid [capacity_rows/block_rows] (may be null): the number
+ * of real rows at the head of every live block, for gpu_kernels_nvfp4_grouped_set_valid_rows. */
 int gpu_kernels_nvfp4_moe_plan(const void* counts_matrix, int world, int rank, int experts, int capacity_rows,
                                int block_rows, void* send_offset, void* seg_src_offset, void* seg_pool_offset, void* block_expert,
-                               void* num_blocks, void* totals, void* peer_offset, int peer_to_pool, void* cursor, void* stream);
+                               void* num_blocks, void* totals, void* peer_offset, int peer_to_pool, void* cursor, void* block_valid,
+                               void* stream);
 /* One rank (nothing to exchange): histogram of the routes (ids int64 [routes] -> counts int32 [experts], written
  * here) and the plan above in ONE launch, which also zeroes cursor [experts], the arrival counters of the
  * dispatch kernels. Replaces a memset, route_count, a copy, plan and another memset. */
 int gpu_kernels_nvfp4_moe_route_plan(const void* ids, int routes, void* counts, int experts, int capacity_rows, int block_rows,
                                      void* send_offset, void* seg_src_offset, void* seg_pool_offset, void* block_expert,
-                                     void* num_blocks, void* totals, void* cursor, void* stream);
+                                     void* num_blocks, void* totals, void* cursor, void* block_valid, void* stream);
 /* Clears scale bytes, route weights and (if not null) destination codes of the pool rows of the live blocks
  * (num_blocks [1] on the device, from the plan), so that padding rows contribute nothing; rows beyond the live
  * blocks are not touched. pool_rows: allocated rows (multiple of 128). Run between the plan and the dispatch. */

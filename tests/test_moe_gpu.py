@@ -93,7 +93,10 @@ def test_fused_and_unfused_first_gemm_agree(g):
                      O.unpack_scales_u8(to_np(layer.act_scales), layer.pool_rows, inter)[:rows].copy(),
                      to_np(layer.pool_weight[:rows]).copy()))
         layer.close()
+    # the padding rows behind an expert's real rows (route weight 0) are written by neither route
+    acts = [tuple(a[w != 0] for a in (p, sc, w)) for p, sc, w in acts]
     (pf, sf, wf), (pu, su, wu) = acts
+    assert len(wf) == tokens * topk
     # rows land in an arbitrary order inside an expert's group: match them through the route weight
     order_f, order_u = np.argsort(wf, kind="stable"), np.argsort(wu, kind="stable")
     assert np.array_equal(wf[order_f], wu[order_u])
@@ -218,12 +221,23 @@ def test_plan_agrees_across_ranks_on_pool_rows(g, world, experts, block_rows):
         i32 = lambda n: torch.zeros(n, dtype=torch.int32, device="cuda")
         send_offset, seg_src, seg_pool = i32(experts + 1), i32(experts + 1), i32(experts)
         block_expert, num_blocks, totals, peer_offset, cursor = i32(capacity // 128), i32(1), i32(4), i32(experts), i32(experts)
+        block_valid = i32(capacity // 128)
         _lib.check(lib.gpu_kernels_nvfp4_moe_plan(
             matrix.data_ptr(), world, rank, experts, capacity, block_rows, send_offset.data_ptr(), seg_src.data_ptr(),
             seg_pool.data_ptr(), block_expert.data_ptr(), num_blocks.data_ptr(), totals.data_ptr(), peer_offset.data_ptr(),
-            1, cursor.data_ptr(), stream))
+            1, cursor.data_ptr(), block_valid.data_ptr(), stream))
         torch.cuda.synchronize()
         assert int(totals[2].item()) == 0
+        # real rows per live block: an expert's rows fill its blocks from the front
+        live = int(num_blocks.item())
+        owned = to_np(matrix).reshape(world, experts)[:, rank * local:(rank + 1) * local].sum(axis=0)
+        want_valid = []
+        for e in range(local):
+            left = int(owned[e])
+            for _ in range(-(-left // block_rows)):
+                want_valid.append(min(block_rows, left))
+                left -= block_rows
+        assert to_np(block_valid)[:live].tolist() == want_valid
         peer_offsets.append(to_np(peer_offset))
         seg_pools.append(to_np(seg_pool).reshape(world, local))            # [source rank, local expert] on this owner
     for src in range(world):
@@ -324,4 +338,36 @@ def test_pool_overflow_is_reported(g):
     layer = g.Nvfp4MoE(w1, w2, 4, 2, max_tokens=64, pool_rows=256)
     with pytest.raises(RuntimeError, match="overflow"):
         layer(x, ids, wts)
+    layer.close()
+
+
+@pytest.mark.parametrize("block_rows", [128, 256])
+def test_plain_second_gemm_writes_only_the_real_rows(g, block_rows):
+    # with the plan's rows-per-block table the output pool gets its real rows, bit-equal to the launch that writes
+    # every row, and the padding behind them keeps what was there
+    import ctypes
+    from gpu_kernels_b200 import _lib
+    lib = _lib.load()
+    tokens, hidden, inter, experts, topk = 150, 512, 256, 8, 2
+    x, logits, w1, w2 = make_layer(9, tokens, hidden, inter, experts, topk, skew=True)
+    ids, wts = g.route(logits, topk)
+    layer = g.Nvfp4MoE(w1, w2, experts, topk, max_tokens=256, block_rows=block_rows)
+    layer(x, ids, wts)
+    torch.cuda.synchronize()
+    rows = int(layer.totals[1].item())
+    real = layer.pool_weight[:rows] != 0
+    assert int(real.sum()) == tokens * topk and rows > tokens * topk
+    fc2 = layer._plans[block_rows][1]
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    outs = []
+    for table in (None, layer.block_valid.data_ptr()):
+        _lib.check(lib.gpu_kernels_nvfp4_grouped_set_valid_rows(fc2, table))
+        layer.out_pool.fill_(-3.0)
+        _lib.check(lib.gpu_kernels_nvfp4_grouped_run(fc2, layer.out_pool.data_ptr(), 1, stream))
+        torch.cuda.synchronize()
+        outs.append(layer.out_pool[:rows].clone())
+    everything, masked = outs
+    assert torch.equal(masked[real], everything[real])
+    assert bool((masked[~real] == -3.0).all()) and not bool((everything[~real] == -3.0).all())
+    assert lib.gpu_kernels_nvfp4_validate(None) == 0
     layer.close()
