@@ -371,3 +371,29 @@ def test_plain_second_gemm_writes_only_the_real_rows(g, block_rows):
     assert bool((masked[~real] == -3.0).all()) and not bool((everything[~real] == -3.0).all())
     assert lib.gpu_kernels_nvfp4_validate(None) == 0
     layer.close()
+
+
+@pytest.mark.parametrize("fused,block_rows", [(True, 128), (False, 128), (True, 256), (False, 256)])
+def test_nothing_the_layer_reads_is_left_over_from_before(g, fused, block_rows):
+    # every data buffer of the layer is filled with NaN patterns before each call (padding rows are not written any
+    # more, so whatever they hold must never reach a real row), a large batch first, then a small one whose padding
+    # lies where the large one had real rows
+    hidden, inter, experts, topk = 512, 256, 8, 2
+    x, logits, w1, w2 = make_layer(31, 300, hidden, inter, experts, topk)
+    layer = g.Nvfp4MoE(w1, w2, experts, topk, clamp=10.0, max_tokens=300, fused=fused, block_rows=block_rows)
+
+    def poison():
+        for name in ("pool_packed", "pool_scales", "act_packed", "act_scales"):
+            getattr(layer, name).fill_(0xFF)
+        for name in ("pool_weight", "gate_up", "out_pool", "y"):
+            getattr(layer, name).fill_(float("nan"))
+        layer.send_pos.fill_(2 ** 30)
+
+    for tokens in (300, 37, 1, 170):
+        ids, wts = g.route(logits[:tokens], topk)
+        poison()
+        y = layer(x[:tokens], ids, wts).clone()
+        torch.cuda.synchronize()
+        layer.check()
+        assert_layer_close(y, oracle_layer(x[:tokens], ids, wts, w1, w2, 10.0), f"poisoned buffers, T={tokens}")
+    layer.close()
