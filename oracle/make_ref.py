@@ -25,7 +25,8 @@ import sys
 from pathlib import Path
 
 ROOT = Path(__file__).resolve().parents[1]
-DEFAULT_REFERENCE = Path(os.environ.get("GPU_KERNELS_REFERENCE", "/root/reference"))
+# a checkout named `reference` beside this repository, unless GPU_KERNELS_REFERENCE names another place
+DEFAULT_REFERENCE = Path(os.environ.get("GPU_KERNELS_REFERENCE", str(ROOT.parent / "reference")))
 
 PYTHON_FILES = ("reference/python/__init__.py", "reference/python/nvfp4.py", "reference/python/moe.py")
 HARNESS_FILES = ("benchmarks/run.py", "benchmarks/common.py", "benchmarks/nvfp4.py")
