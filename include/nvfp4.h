@@ -70,9 +70,10 @@ struct Nvfp4Params {
 struct Nvfp4Implementation {
     // Builds descriptors for the given device buffers, which must outlive the
     // plan. May query the device; never call it during stream capture.
-    // Throws std::invalid_argument on a shape or pointer it cannot serve:
-    // M, N multiples of 128 (whole scale atoms), K a multiple of 64 (the quantiser's own rule; the
-    // reference kernel needs multiples of 256 in all three), pointers 16-byte aligned.
+    // Throws std::invalid_argument on a shape or pointer it cannot serve: M >= 1, N a multiple of 8 (rows of C start
+    // on 16-byte boundaries), K a multiple of 64 (the quantiser's own rule; the reference kernel needs multiples of
+    // 256 in all three), pointers 16-byte aligned. SFA and SFB always hold whole 128-row atoms: ceil(rows / 128) *
+    // 128 * K / 16 bytes; the bytes of the rows beyond M and N may hold anything.
     void (*prepare)(Nvfp4Params&, const uint8_t* A, const uint8_t* B, const uint8_t* SFA, const uint8_t* SFB,
                     int M, int N, int K, cudaStream_t);
     // One asynchronous kernel launch on `stream`; safe inside stream capture.
